@@ -1,0 +1,82 @@
+/* ns_attn.h: the attention entry points of libnextsycl-llm.so on CUDA (sm_100a).
+ *
+ * Two groups:
+ *  1. The reference's own symbols, with identical signatures, so the per-model engines' dlsym tables
+ *     (llm/qwen35/src/ffi.rs:155-160,204-208; llm/glm5next/src/ffi.rs:33-54; llm/deepseek2/src/ffi.rs:37-39) bind
+ *     unchanged: float32 queries and outputs, fp16 caches, every size an int64_t, work queued on the ns_gpu's compute
+ *     stream, 0 or -1 (+ ns_last_error).
+ *  2. Native ns_b200_* entry points: fp16 / bf16 queries and outputs, a batch dimension, lengths read from device
+ *     memory (so a decode step can be replayed as a CUDA graph), and the multi-GPU split-KV combine.
+ *
+ * Cache layouts are the reference's: GQA keys and values in separate fp16 buffers [Hkv][cap][D], element
+ * (h*cap + pos)*D + d (kernels/llm/qwen35/q35.cpp:580-584); the deepseek2 latent cache one fp16 row
+ * [512 latent | 64 rotated] per token (kernels/llm/deepseek2/ds2.cpp:99-107).
+ */
+#ifndef NS_ATTN_H
+#define NS_ATTN_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ns_gpu ns_gpu;
+
+/* ================= 1. reference-compatible symbols ================= */
+
+/* kernels/llm/qwen35/q35.h:55-57 - fp32 rows k [T][Hkv*D] (ks floats apart) and v (vs apart) into the fp16 caches at
+ * positions p0 .. p0+T-1. -1 when p0+T > cap. */
+int ns_q35_kv_store(ns_gpu* g, const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hkv, int64_t D, int64_t cap, int64_t p0,
+                    void* kc, void* vc);
+
+/* kernels/llm/qwen35/q35.h:62-66 - causal attention of rows q [T][Hq*D] (qs floats apart) at positions p0.. against the
+ * caches; out [T][Hq*D]; scratch of ns_q35_attn_scratch floats (0: none needed, may be null). The reference covers
+ * D 256 with 2/4/6/8 query heads a key head and D 128 with one; this library covers D 128 and 256 with any whole
+ * number of query heads a key head up to 16. */
+int64_t ns_q35_attn_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0);
+int ns_q35_attn(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t cap,
+                int64_t p0, float* out, float* scratch);
+
+/* kernels/llm/qwen35/silo/silo.h:43-59 - decode rows (1..8), each at its own position p0+t; a row's result is the same
+ * whatever rows share its pass. `_supported` is widened from the reference's (D 256, 6 heads a key head) to D 128 / 256
+ * with 1..16 query heads a key head. kt: cache form, 0 = fp16 (the only one this build takes). */
+int ns_q35_attn_decode_supported(int64_t T, int64_t Hq, int64_t Hkv, int64_t D);
+int64_t ns_q35_attn_decode_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0);
+int ns_q35_attn_decode(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                       int64_t cap, int64_t p0, float* out, float* scratch);
+int ns_q35_attn_decode_kv(ns_gpu* g, int kt, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv,
+                          int64_t D, int64_t cap, int64_t p0, float* out, float* scratch);
+
+/* kernels/llm/nemotronh/nh.h:39-44 and silo/nhs.h:63-69 - the same kernels under the nemotronh engine's names (D 128) */
+int64_t ns_nh_attn_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0);
+int ns_nh_attn(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t cap,
+               int64_t p0, float* out, float* scratch);
+int ns_nhs_attn_decode_supported(int64_t T, int64_t Hq, int64_t Hkv, int64_t D);
+int64_t ns_nhs_attn_decode_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0);
+int ns_nhs_attn_decode(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                       int64_t cap, int64_t p0, float* out, float* scratch);
+
+/* ================= 2. native entry points ================= */
+
+/* One sequence of a decode batch, resident in device memory: its caches ([Hkv][cap][D] fp16 each), their capacity in
+ * tokens and the position of the pass's first row (row t sees keys 0 .. p0+t). */
+typedef struct ns_b200_seq {
+    const void* kc;
+    const void* vc;
+    int64_t cap;
+    int64_t p0;
+} ns_b200_seq;
+
+/* Split-KV GQA decode of a batch (replaces one ns_q35_attn_decode call per sequence, llm/qwen35/src/engine.rs:1535,
+ * 1596-1600). q [B][T][Hq*D] fp16 (qs elements between rows, q_seq between sequences), seqs a DEVICE array [B],
+ * out [B][T][Hq*D] fp16 dense. max_kv bounds every p0+T (it sizes the grid and the scratch; the lengths themselves
+ * are read on the device). T 1..8, D 128 or 256, Hq/Hkv 1..16. scratch: ns_b200_gqa_decode_scratch floats. */
+int64_t ns_b200_gqa_decode_scratch(int64_t B, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t max_kv);
+int ns_b200_gqa_decode(ns_gpu* g, const void* q, int64_t qs, int64_t q_seq, const ns_b200_seq* seqs, int64_t B, int64_t T, int64_t Hq, int64_t Hkv,
+                       int64_t D, int64_t max_kv, void* out, float* scratch);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

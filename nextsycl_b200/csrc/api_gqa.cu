@@ -1,0 +1,161 @@
+// api_gqa.cu: the C-ABI entry points of GQA attention (include/ns_attn.h): argument checks, then the launchers.
+#include "kernels.cuh"
+
+#include <algorithm>
+
+namespace {
+
+bool shape_ok(int64_t Hq, int64_t Hkv, int64_t D) {
+    return (D == 128 || D == 256) && Hkv > 0 && Hq > 0 && Hq % Hkv == 0 && Hq / Hkv <= 16;
+}
+
+int64_t decode_ns_max(int64_t T, int64_t Hkv, int64_t p0) {
+    int64_t ns = 1;
+    for (int64_t r = 0; r < T; ++r) ns = std::max(ns, ns_dec_splits(p0 + r + 1, Hkv));
+    return ns;
+}
+
+// rows 1..8 at p0.., fp32 in and out, one sequence: what ns_q35_attn_decode and its namesakes share
+int decode_f32(ns_gpu* g, const char* name, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv,
+               int64_t D, int64_t cap, int64_t p0, float* out, float* scratch) {
+    if (ns_enter(g, name)) return -1;
+    if (T < 1 || T > 8 || !shape_ok(Hq, Hkv, D)) return ns_fail(std::string(name) + ": 1..8 rows, heads of 128 or 256, 1..16 query heads a key head");
+    if (p0 < 0 || p0 + T > cap) return ns_fail(std::string(name) + ": past the cache's capacity");
+    if (p0 + T >= ((int64_t) 1 << 31)) return ns_fail(std::string(name) + ": positions below 2^31");
+    if (qs % 4 != 0 || ((uintptr_t) q & 15) != 0) return ns_fail(std::string(name) + ": query rows 16-byte aligned");
+    if (!q || !kc || !vc || !out) return ns_fail(std::string(name) + ": a null buffer");
+    const int64_t ns = decode_ns_max(T, Hkv, p0);
+    if (ns > 1 && !scratch) return ns_fail(std::string(name) + ": no scratch");
+    GqaDecodeArgs a{};
+    a.q = q;
+    a.qs = qs;
+    a.q_seq = 0;
+    a.seqs = nullptr;
+    a.one = ns_b200_seq{kc, vc, cap, p0};
+    a.out = out;
+    a.part = scratch;
+    a.B = 1, a.T = T, a.Hq = Hq, a.Hkv = Hkv, a.D = D;
+    a.ns_max = ns;
+    a.q_f32 = 1, a.out_f32 = 1;
+    return ns_launch_gqa_decode(g, a, name);
+}
+
+int64_t decode_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0) {
+    if (T < 1 || Hkv < 1) return 0;
+    const int64_t ns = decode_ns_max(T, Hkv, p0);
+    return ns > 1 ? T * Hq * ns * (D + 2) : 0;
+}
+
+// any number of rows through the decode kernel, 8 at a time (each block of rows its own positions)
+int64_t rows_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0) {
+    int64_t s = 0;
+    for (int64_t r0 = 0; r0 < T; r0 += 8) s = std::max(s, decode_scratch(std::min<int64_t>(8, T - r0), Hq, Hkv, D, p0 + r0));
+    return s;
+}
+int rows_f32(ns_gpu* g, const char* name, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+             int64_t cap, int64_t p0, float* out, float* scratch) {
+    if (T <= 0) return 0;
+    if (p0 + T > cap) return ns_fail(std::string(name) + ": past the cache's capacity");
+    for (int64_t r0 = 0; r0 < T; r0 += 8) {
+        const int64_t tr = std::min<int64_t>(8, T - r0);
+        if (decode_f32(g, name, q + r0 * qs, qs, kc, vc, tr, Hq, Hkv, D, cap, p0 + r0, out + r0 * Hq * D, scratch)) return -1;
+    }
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ns_q35_kv_store(ns_gpu* g, const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hkv, int64_t D, int64_t cap, int64_t p0,
+                    void* kc, void* vc) {
+    NS_TRY
+    if (ns_enter(g, "ns_q35_kv_store")) return -1;
+    if (T <= 0) return 0;
+    if (p0 < 0 || p0 + T > cap) return ns_fail("ns_q35_kv_store: past the cache's capacity");
+    if (D % 8 != 0 || ks % 4 != 0 || vs % 4 != 0) return ns_fail("ns_q35_kv_store: head width a multiple of 8, rows 16-byte aligned");
+    return ns_launch_kv_store(g, k, ks, v, vs, T, Hkv, D, cap, p0, kc, vc);
+    NS_CATCH("ns_q35_kv_store")
+}
+
+int64_t ns_q35_attn_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0) { return rows_scratch(T, Hq, Hkv, D, p0); }
+
+int ns_q35_attn(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t cap,
+                int64_t p0, float* out, float* scratch) {
+    NS_TRY
+    return rows_f32(g, "ns_q35_attn", q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out, scratch);
+    NS_CATCH("ns_q35_attn")
+}
+
+int ns_q35_attn_decode_supported(int64_t T, int64_t Hq, int64_t Hkv, int64_t D) { return T >= 1 && T <= 8 && shape_ok(Hq, Hkv, D); }
+
+int64_t ns_q35_attn_decode_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0) { return decode_scratch(T, Hq, Hkv, D, p0); }
+
+int ns_q35_attn_decode(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                       int64_t cap, int64_t p0, float* out, float* scratch) {
+    NS_TRY
+    return decode_f32(g, "ns_q35_attn_decode", q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out, scratch);
+    NS_CATCH("ns_q35_attn_decode")
+}
+
+int ns_q35_attn_decode_kv(ns_gpu* g, int kt, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv,
+                          int64_t D, int64_t cap, int64_t p0, float* out, float* scratch) {
+    NS_TRY
+    if (kt != 0) return ns_fail("ns_q35_attn_decode_kv: a cache form 0 (half); q8_0 and q4_0 caches are not built in this library");
+    return decode_f32(g, "ns_q35_attn_decode_kv", q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out, scratch);
+    NS_CATCH("ns_q35_attn_decode_kv")
+}
+
+int64_t ns_nh_attn_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0) { return rows_scratch(T, Hq, Hkv, D, p0); }
+
+int ns_nh_attn(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t cap,
+               int64_t p0, float* out, float* scratch) {
+    NS_TRY
+    return rows_f32(g, "ns_nh_attn", q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out, scratch);
+    NS_CATCH("ns_nh_attn")
+}
+
+int ns_nhs_attn_decode_supported(int64_t T, int64_t Hq, int64_t Hkv, int64_t D) { return T >= 1 && T <= 8 && D == 128 && shape_ok(Hq, Hkv, D); }
+
+int64_t ns_nhs_attn_decode_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0) { return decode_scratch(T, Hq, Hkv, D, p0); }
+
+int ns_nhs_attn_decode(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                       int64_t cap, int64_t p0, float* out, float* scratch) {
+    NS_TRY
+    return decode_f32(g, "ns_nhs_attn_decode", q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out, scratch);
+    NS_CATCH("ns_nhs_attn_decode")
+}
+
+int64_t ns_b200_gqa_decode_scratch(int64_t B, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t max_kv) {
+    if (B < 1 || T < 1 || Hkv < 1 || max_kv < 1) return 0;
+    const int64_t ns = ns_dec_splits(max_kv, Hkv);
+    return ns > 1 ? B * T * Hq * ns * (D + 2) : 0;
+}
+
+int ns_b200_gqa_decode(ns_gpu* g, const void* q, int64_t qs, int64_t q_seq, const ns_b200_seq* seqs, int64_t B, int64_t T, int64_t Hq, int64_t Hkv,
+                       int64_t D, int64_t max_kv, void* out, float* scratch) {
+    NS_TRY
+    const char* name = "ns_b200_gqa_decode";
+    if (ns_enter(g, name)) return -1;
+    if (B < 1) return 0;
+    if (T < 1 || T > 8 || !shape_ok(Hq, Hkv, D)) return ns_fail(std::string(name) + ": 1..8 rows, heads of 128 or 256, 1..16 query heads a key head");
+    if (max_kv < T || max_kv >= ((int64_t) 1 << 31)) return ns_fail(std::string(name) + ": max_kv between T and 2^31");
+    if (qs % 8 != 0 || q_seq % 8 != 0 || ((uintptr_t) q & 15) != 0) return ns_fail(std::string(name) + ": query rows 16-byte aligned");
+    if (!q || !seqs || !out) return ns_fail(std::string(name) + ": a null buffer");
+    const int64_t ns = ns_dec_splits(max_kv, Hkv);
+    if (ns > 1 && !scratch) return ns_fail(std::string(name) + ": no scratch");
+    GqaDecodeArgs a{};
+    a.q = q;
+    a.qs = qs;
+    a.q_seq = q_seq;
+    a.seqs = seqs;
+    a.out = out;
+    a.part = scratch;
+    a.B = B, a.T = T, a.Hq = Hq, a.Hkv = Hkv, a.D = D;
+    a.ns_max = ns;
+    a.q_f32 = 0, a.out_f32 = 0;
+    return ns_launch_gqa_decode(g, a, name);
+    NS_CATCH("ns_b200_gqa_decode")
+}
+
+}  // extern "C"

@@ -1,0 +1,411 @@
+// gqa_decode.cu: split-KV GQA decode for sm_100a - the bandwidth-bound kernel of the path.
+//
+// What it computes is the SPLIT form of the reference's flash kernel (kernels/llm/qwen35/silo/attn.cpp:105-313 with
+// the decode driver :321-370): for 1..8 rows at positions p0+t, out = softmax(q k^T / sqrt(D)) v over the fp16 caches,
+// the query scaled by 1/sqrt(D) log2(e) and rounded to fp16, weights exp2 and rounded to fp16 before they meet V,
+// fp32 sums, partials (O, m in log2 units, l) per key split merged by attn.cpp:352-368's formula.
+//
+// How: a CTA takes one (key split, key head, group of <= 32 query rows = rows x the key head's query heads). Its 4
+// warps each stream every 4th 16-key tile of the split through a private cp.async pipeline (16-byte, fully coalesced
+// loads; 256 B a key row, XOR-swizzled in shared memory), compute S = Q K^T and O += P V on mma.sync m16n8k16 (the
+// rows are too few for a tcgen05 tile; the kernel is HBM-bound), keep their own online softmax (quad shuffles for
+// the row max and sum) and merge once at the end through shared memory. No block-wide barrier in the key loop.
+#include "kernels.cuh"
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int THREADS = WARPS * 32;
+constexpr int KT = 16;   // keys a warp tile
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t) __cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;   // 0: the 16 bytes are zero-filled, nothing is read
+    asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+// D (fp32 16x8) += A (fp16 16x16, row) x B (fp16 16x8, col)
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+struct Params {
+    const void* q;
+    int64_t qs, q_seq;
+    const ns_b200_seq* seqs;
+    ns_b200_seq one;
+    void* out;
+    float* part;
+    int T, Hq, Hkv, G, ns_max, groups;
+    int q_f32, out_f32;
+    float qscale;
+};
+
+// byte offset of 16-byte chunk c of row r in a tile whose rows are ROWB bytes: chunks XOR-swizzled by the row
+template <int ROWB>
+__device__ __forceinline__ uint32_t swz(int r, int c) {
+    return (uint32_t) (r * ROWB + ((c ^ (r & 7)) << 4));
+}
+
+template <int D, int MT, int NSTAGE>
+__global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
+    constexpr int RG = 16 * MT;          // query rows a CTA
+    constexpr int ROWB = D * 2;          // bytes a key row
+    constexpr int CPR = ROWB / 16;       // 16-byte chunks a row
+    constexpr int TILE = KT * ROWB;      // bytes a K (or V) tile
+    constexpr int NT = D / 8;            // output n-tiles
+    constexpr int KS = D / 16;           // k-steps of S = Q K^T
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* q_s = smem;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint8_t* w_s = smem + RG * ROWB + warp * (NSTAGE * 2 * TILE);
+
+    const int split = blockIdx.x, hk = blockIdx.y;
+    const int b = blockIdx.z / p.groups, rg = blockIdx.z % p.groups;
+    const ns_b200_seq seq = p.seqs ? p.seqs[b] : p.one;
+    const int T = p.T, G = p.G, R = T * G, row0 = rg * RG;
+    const int64_t p0 = seq.p0;
+    const int t_lo = row0 / G, t_hi = min(T - 1, (row0 + RG - 1) / G);
+
+    // ---- the group's queries, scaled and rounded to fp16, swizzled like the key tiles (rows past R: zeros)
+    for (int i = tid; i < RG * CPR; i += THREADS) {
+        const int r = i / CPR, c = i % CPR, rho = row0 + r;
+        uint4 w = make_uint4(0, 0, 0, 0);
+        if (rho < R) {
+            const int t = rho / G, gq = rho % G;
+            const int64_t at = (int64_t) b * p.q_seq + (int64_t) t * p.qs + (int64_t) (hk * G + gq) * D + c * 8;
+            float f[8];
+            if (p.q_f32) {
+                const float4 a = *reinterpret_cast<const float4*>((const float*) p.q + at);
+                const float4 bb = *reinterpret_cast<const float4*>((const float*) p.q + at + 4);
+                f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = bb.x, f[5] = bb.y, f[6] = bb.z, f[7] = bb.w;
+            } else {
+                const uint4 a = *reinterpret_cast<const uint4*>((const __half*) p.q + at);
+                const __half2* h = reinterpret_cast<const __half2*>(&a);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 x = __half22float2(h[e]);
+                    f[2 * e] = x.x, f[2 * e + 1] = x.y;
+                }
+            }
+            w.x = pack_h2(f[0] * p.qscale, f[1] * p.qscale);
+            w.y = pack_h2(f[2] * p.qscale, f[3] * p.qscale);
+            w.z = pack_h2(f[4] * p.qscale, f[5] * p.qscale);
+            w.w = pack_h2(f[6] * p.qscale, f[7] * p.qscale);
+        }
+        *reinterpret_cast<uint4*>(q_s + swz<ROWB>(r, c)) = w;
+    }
+    __syncthreads();
+
+    // rows of one pass share a split size; where the rows' own sizes differ (a row's context crosses a step of the
+    // split function) the rows go one at a time, each with its own - the same arithmetic either way
+    bool same = true;
+    for (int t = t_lo; t <= t_hi; ++t) same = same && ns_dec_split(p0 + t + 1, p.Hkv) == ns_dec_split(p0 + t_lo + 1, p.Hkv);
+    const int npass = same ? 1 : t_hi - t_lo + 1;
+
+    const uint8_t* kbase = (const uint8_t*) seq.kc + (int64_t) hk * seq.cap * ROWB;
+    const uint8_t* vbase = (const uint8_t*) seq.vc + (int64_t) hk * seq.cap * ROWB;
+
+    for (int pass = 0; pass < npass; ++pass) {
+        const int t_a = same ? t_lo : t_lo + pass, t_b = same ? t_hi : t_a;
+        const int64_t kb = ns_dec_split(p0 + t_a + 1, p.Hkv);
+        const int64_t kv_end = p0 + t_b + 1;
+        const int64_t jbeg = (int64_t) split * kb, jend = min(kv_end, (int64_t) (split + 1) * kb);
+        if (jbeg >= jend) continue;   // the whole CTA
+        const int ntiles = (int) ((jend - jbeg + KT - 1) / KT);
+
+        // this thread's rows: (mt, lane/4) and 8 below; a row outside the pass sees no key
+        int64_t lim[MT][2];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int rho = row0 + mt * 16 + hh * 8 + (lane >> 2), t = rho / G;
+                lim[mt][hh] = (rho < R && t >= t_a && t <= t_b) ? p0 + t : -1;
+            }
+
+        float o[MT][NT][4];
+        float m[MT][2], l[MT][2];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o[mt][nt][e] = 0.f;
+            m[mt][0] = m[mt][1] = -INFINITY;
+            l[mt][0] = l[mt][1] = 0.f;
+        }
+
+        // a tile's loads: 16 keys x ROWB bytes of K and of V, 16 bytes a lane a step (two whole rows a warp step)
+        auto issue = [&](int tile, int stage) {
+            if (tile < ntiles) {
+                const int64_t j0 = jbeg + (int64_t) tile * KT;
+                uint8_t* ks = w_s + stage * (2 * TILE);
+                uint8_t* vs = ks + TILE;
+#pragma unroll
+                for (int i = 0; i < KT * CPR / 32; ++i) {
+                    const int idx = i * 32 + lane, r = idx / CPR, c = idx % CPR;
+                    const bool ok = j0 + r < jend;
+                    const int64_t off = ok ? (j0 + r) * ROWB + c * 16 : 0;
+                    cp_async16(smem_u32(ks + swz<ROWB>(r, c)), kbase + off, ok);
+                    cp_async16(smem_u32(vs + swz<ROWB>(r, c)), vbase + off, ok);
+                }
+            }
+            cp_async_commit();
+        };
+
+#pragma unroll
+        for (int s = 0; s < NSTAGE - 1; ++s) issue(warp + s * WARPS, s);
+
+        int stage = 0;
+        for (int tile = warp; tile < ntiles; tile += WARPS) {
+            {
+                int ps = stage + NSTAGE - 1;
+                if (ps >= NSTAGE) ps -= NSTAGE;
+                issue(tile + (NSTAGE - 1) * WARPS, ps);
+            }
+            cp_async_wait<NSTAGE - 1>();
+            __syncwarp();
+            const uint8_t* ks = w_s + stage * (2 * TILE);
+            const uint8_t* vs = ks + TILE;
+            const int64_t j0 = jbeg + (int64_t) tile * KT;
+
+            // ---- S = Q K^T: MT x (16 rows x 16 keys)
+            float s[MT][2][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[mt][nt][e] = 0.f;
+#pragma unroll
+            for (int k = 0; k < KS; ++k) {
+                uint32_t kf[4];
+                ldsm_x4(smem_u32(ks + swz<ROWB>((lane & 7) + (lane >> 4) * 8, 2 * k + ((lane >> 3) & 1))), kf);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    uint32_t qf[4];
+                    ldsm_x4(smem_u32(q_s + swz<ROWB>(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * k + (lane >> 4))), qf);
+                    mma16816(s[mt][0], qf, kf[0], kf[1]);
+                    mma16816(s[mt][1], qf, kf[2], kf[3]);
+                }
+            }
+            // ---- mask, online softmax (a row's 16 scores sit in its quad: 4 a lane)
+            uint32_t pf[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int64_t last = min(lim[mt][hh], jend - 1);
+                    float x[4];
+                    float mx = -INFINITY;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int nt = e >> 1;
+                        const int64_t key = j0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+                        x[e] = key <= last ? s[mt][nt][hh * 2 + (e & 1)] : -INFINITY;
+                        mx = fmaxf(mx, x[e]);
+                    }
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                    const float mo = m[mt][hh], mn = fmaxf(mo, mx);
+                    const float c = mn == -INFINITY ? 1.0f : exp2f(mo - mn);
+                    float pv[4], sum = 0.f;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        pv[e] = x[e] == -INFINITY ? 0.f : exp2f(x[e] - mn);
+                        sum += pv[e];
+                    }
+                    l[mt][hh] = l[mt][hh] * c + sum;   // this lane's share; the quad's shares are added at the end
+                    m[mt][hh] = mn;
+                    pf[mt][hh] = pack_h2(pv[0], pv[1]);       // keys 0..7 of the tile -> A fragment k 0..7
+                    pf[mt][2 + hh] = pack_h2(pv[2], pv[3]);   // keys 8..15 -> k 8..15
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        o[mt][nt][hh * 2] *= c;
+                        o[mt][nt][hh * 2 + 1] *= c;
+                    }
+                }
+            }
+            // ---- O += P V
+#pragma unroll
+            for (int jj = 0; jj < NT / 2; ++jj) {
+                uint32_t vf[4];
+                ldsm_x4_t(smem_u32(vs + swz<ROWB>((lane & 7) + ((lane >> 3) & 1) * 8, 2 * jj + (lane >> 4))), vf);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    mma16816(o[mt][2 * jj], pf[mt], vf[0], vf[1]);
+                    mma16816(o[mt][2 * jj + 1], pf[mt], vf[2], vf[3]);
+                }
+            }
+            __syncwarp();
+            if (++stage == NSTAGE) stage = 0;
+        }
+        cp_async_wait<0>();
+        __syncthreads();   // every warp's tiles are consumed: the stage memory becomes the merge buffer
+
+        // ---- the 4 warps' (m, l, O) merged: [WARPS][RG] m, l and [WARPS][RG][D] O over the stage memory
+        float* ms = reinterpret_cast<float*>(smem + RG * ROWB);
+        float* ls = ms + WARPS * RG;
+        float* os = ls + WARPS * RG;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                float lt = l[mt][hh];
+                lt += __shfl_xor_sync(0xffffffffu, lt, 1);
+                lt += __shfl_xor_sync(0xffffffffu, lt, 2);
+                const int r = mt * 16 + hh * 8 + (lane >> 2);
+                if ((lane & 3) == 0) {
+                    ms[warp * RG + r] = m[mt][hh];
+                    ls[warp * RG + r] = lt;
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                    *reinterpret_cast<float2*>(os + ((size_t) (warp * RG + r)) * D + nt * 8 + 2 * (lane & 3)) =
+                        make_float2(o[mt][nt][hh * 2], o[mt][nt][hh * 2 + 1]);
+            }
+        __syncthreads();
+        for (int i = tid; i < RG * D; i += THREADS) {
+            const int r = i / D, d = i % D, rho = row0 + r;
+            if (rho >= R) break;   // i ascends with r
+            const int t = rho / G, gq = rho % G;
+            if (t < t_a || t > t_b) continue;
+            const int64_t kv = p0 + t + 1;
+            if (jbeg >= kv) continue;   // this split holds none of the row's keys: not one of its splits
+            float mx = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, ms[w * RG + r]);
+            float L = 0.f, A = 0.f;
+            if (mx != -INFINITY) {
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) {
+                    const float mw = ms[w * RG + r];
+                    const float e = mw == -INFINITY ? 0.f : exp2f(mw - mx);
+                    L += ls[w * RG + r] * e;
+                    A += os[((size_t) (w * RG + r)) * D + d] * e;
+                }
+            }
+            const int hq = hk * G + gq;
+            const int64_t row = ((int64_t) b * T + t) * p.Hq + hq;
+            if (ns_dec_splits(kv, p.Hkv) == 1) {
+                const float v = L > 0.f ? A / L : 0.f;
+                if (p.out_f32) ((float*) p.out)[row * D + d] = v;
+                else ((__half*) p.out)[row * D + d] = __float2half_rn(v);
+            } else {
+                float* pr = p.part + (row * p.ns_max + split) * (D + 2);
+                pr[d] = A;
+                if (d == 0) {
+                    pr[D] = mx;
+                    pr[D + 1] = L;
+                }
+            }
+        }
+        __syncthreads();   // the merge buffer is stage memory again for the next pass
+    }
+}
+
+// the splits of each (sequence, row, head) merged: attn.cpp:352-368's formula; rows with one split were written by
+// the first kernel
+template <int D>
+__global__ void __launch_bounds__(D) gqa_merge_kernel(const Params p) {
+    const int64_t rh = blockIdx.x;   // (b, t, hq)
+    const int d = threadIdx.x;
+    const int hq = (int) (rh % p.Hq), t = (int) ((rh / p.Hq) % p.T), b = (int) (rh / ((int64_t) p.Hq * p.T));
+    (void) hq;
+    const int64_t p0 = p.seqs ? p.seqs[b].p0 : p.one.p0;
+    const int nsr = (int) ns_dec_splits(p0 + t + 1, p.Hkv);
+    if (nsr == 1) return;
+    const float* pp = p.part + rh * p.ns_max * (D + 2);
+    float mx = -INFINITY;
+    for (int k = 0; k < nsr; ++k) mx = fmaxf(mx, pp[k * (D + 2) + D]);
+    float L = 0.f, A = 0.f;
+    if (mx != -INFINITY) {
+        for (int k = 0; k < nsr; ++k) {
+            const float mk = pp[k * (D + 2) + D];
+            const float e = mk == -INFINITY ? 0.f : exp2f(mk - mx);
+            L += pp[k * (D + 2) + D + 1] * e;
+            A += pp[k * (D + 2) + d] * e;
+        }
+    }
+    const float v = L > 0.f ? A / L : 0.f;
+    if (p.out_f32) ((float*) p.out)[rh * D + d] = v;
+    else ((__half*) p.out)[rh * D + d] = __float2half_rn(v);
+}
+
+template <int D, int MT, int NSTAGE>
+int launch(ns_gpu* g, const Params& p, int64_t B, const char* where) {
+    constexpr int RG = 16 * MT;
+    constexpr size_t smem = (size_t) RG * D * 2 + (size_t) WARPS * NSTAGE * 2 * KT * D * 2;
+    static_assert(smem >= (size_t) RG * D * 2 + (size_t) WARPS * RG * (D + 2) * 4, "the merge buffer fits the stage memory");
+    auto kern = gqa_decode_kernel<D, MT, NSTAGE>;
+    static bool set[64] = {};
+    if (!set[g->dev & 63]) {
+        NS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem), where);
+        set[g->dev & 63] = true;
+    }
+    dim3 grid((unsigned) p.ns_max, (unsigned) p.Hkv, (unsigned) (B * p.groups));
+    kern<<<grid, THREADS, smem, g->compute>>>(p);
+    if (ns_launched(where)) return -1;
+    if (p.ns_max > 1) {
+        gqa_merge_kernel<D><<<(unsigned) (B * p.T * p.Hq), D, 0, g->compute>>>(p);
+        if (ns_launched(where)) return -1;
+    }
+    return 0;
+}
+
+}  // namespace
+
+int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where) {
+    Params p;
+    p.q = a.q;
+    p.qs = a.qs;
+    p.q_seq = a.q_seq;
+    p.seqs = a.seqs;
+    p.one = a.one;
+    p.out = a.out;
+    p.part = a.part;
+    p.T = (int) a.T;
+    p.Hq = (int) a.Hq;
+    p.Hkv = (int) a.Hkv;
+    p.G = (int) (a.Hq / a.Hkv);
+    p.ns_max = (int) a.ns_max;
+    p.q_f32 = a.q_f32;
+    p.out_f32 = a.out_f32;
+    p.qscale = 1.0f / sqrtf((float) a.D) * 1.4426950408889634f;
+    const int R = p.T * p.G;
+    if (a.B * (int64_t) ((R + 15) / 16) > 65535) return ns_fail(std::string(where) + ": too many sequences for one launch");
+    if (a.D == 128) {
+        if (R <= 16) {
+            p.groups = 1;
+            return launch<128, 1, 3>(g, p, a.B, where);
+        }
+        p.groups = (R + 31) / 32;
+        return launch<128, 2, 3>(g, p, a.B, where);
+    }
+    if (a.D == 256) {
+        p.groups = (R + 15) / 16;
+        return launch<256, 1, 3>(g, p, a.B, where);
+    }
+    return ns_fail(std::string(where) + ": heads of 128 or 256");
+}

@@ -1,0 +1,38 @@
+// kernels.cuh: launchers of the attention kernels, as the C-ABI wrappers (api_*.cu) call them. Each queues work on the
+// given stream and returns 0, or -1 through ns_fail.
+#pragma once
+#include "ns_internal.cuh"
+#include "ns_attn.h"
+
+// ---- GQA decode (gqa_decode.cu) -------------------------------------------------------------------------------------
+// Keys a split for a row that sees `kv` keys: enough splits that key heads x splits fill two CTAs per SM, in
+// multiples of 64 keys. A function of the row's own length only, so a row's arithmetic does not depend on what else
+// shares its launch (the property of kernels/llm/qwen35/silo/attn.cpp:100-104).
+constexpr int NS_DEC_TARGET_CTAS = 296;
+__host__ __device__ inline int64_t ns_dec_split(int64_t kv, int64_t Hkv) {
+    const int64_t want = (kv * Hkv + NS_DEC_TARGET_CTAS - 1) / NS_DEC_TARGET_CTAS;
+    const int64_t kb = (want + 63) / 64 * 64;
+    return kb < 64 ? 64 : kb;
+}
+__host__ __device__ inline int64_t ns_dec_splits(int64_t kv, int64_t Hkv) {
+    const int64_t kb = ns_dec_split(kv, Hkv);
+    return (kv + kb - 1) / kb;
+}
+
+struct GqaDecodeArgs {
+    const void* q;             // [B][T] rows of Hq*D, fp32 or fp16
+    int64_t qs;                // elements between rows
+    int64_t q_seq;             // elements between sequences
+    const ns_b200_seq* seqs;   // device array [B], or null: `one`
+    ns_b200_seq one;
+    void* out;                 // [B][T][Hq*D], fp32 or fp16
+    float* part;               // [B][T][Hq][ns_max][D+2]
+    int64_t B, T, Hq, Hkv, D;
+    int64_t ns_max;            // splits the partial buffer is laid out for
+    int q_f32, out_f32;
+};
+int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where);
+
+// ---- cache writers (kv_store.cu) ------------------------------------------------------------------------------------
+int ns_launch_kv_store(ns_gpu* g, const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hkv, int64_t D, int64_t cap, int64_t p0,
+                       void* kc, void* vc);

@@ -1,0 +1,648 @@
+// attn_oracle.cpp: CPU restatement of the numerics of nextsycl's attention kernels.
+//
+// TEST INFRASTRUCTURE ONLY. Nothing in the shipped library calls into this file; it is the checker the GPU parity
+// tests, the smoke test and the benchmark's CPU-baseline leg compare against.
+//
+// PARITY UNPINNED: the reference tree holds no golden vector, known-answer test or fixture for any attention kernel,
+// and its SYCL kernels cannot be compiled without a oneAPI toolchain. Every function below restates the arithmetic
+// of the reference file and lines it cites (where values are rounded, in which order chunks are visited, which
+// exponential is used); the summation order inside one matrix tile is hardware-defined in the reference and is a
+// plain sequential fp32 sum here.
+//
+// Storage: fp16 / bf16 values travel as raw uint16_t bit patterns. All functions are pure (no global state) and
+// parallelise over (row, head) with OpenMP only, so a result does not depend on the thread count.
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace {
+
+typedef _Float16 h16;
+
+inline float h2f(uint16_t b) {
+    h16 h;
+    std::memcpy(&h, &b, 2);
+    return (float) h;
+}
+inline uint16_t f2h(float f) {
+    h16 h = (h16) f;   // round to nearest even
+    uint16_t b;
+    std::memcpy(&b, &h, 2);
+    return b;
+}
+inline float round_h(float f) { return (float) (h16) f; }
+inline float bf2f(uint16_t b) {
+    uint32_t w = (uint32_t) b << 16;
+    float f;
+    std::memcpy(&f, &w, 4);
+    return f;
+}
+inline uint16_t f2bf(float f) {
+    uint32_t w;
+    std::memcpy(&w, &f, 4);
+    if ((w & 0x7fffffffu) > 0x7f800000u) return (uint16_t) ((w >> 16) | 0x40);
+    w += 0x7fffu + ((w >> 16) & 1u);
+    return (uint16_t) (w >> 16);
+}
+inline float round_bf(float f) { return bf2f(f2bf(f)); }
+
+const float LOG2E = 1.4426950408889634f;
+const float NEG_INF = -INFINITY;
+
+// ---- split sizes -------------------------------------------------------------------------------------------------
+// kernels/llm/qwen35/silo/attn.cpp:325-331 (XMX decode: multiples of 64 keys, ~512 work-groups)
+int64_t flash_split(int64_t kv, int64_t Hkv) {
+    const int64_t want = (kv * Hkv + 511) / 512;
+    return std::max<int64_t>(64, (want + 63) / 64 * 64);
+}
+int64_t flash_splits(int64_t kv, int64_t Hkv) {
+    const int64_t kb = flash_split(kv, Hkv);
+    return (kv + kb - 1) / kb;
+}
+// kernels/llm/qwen35/q35.cpp:34-42 and kernels/llm/nemotronh/nh.cpp:22-30 (vector-unit kernel: only a single row
+// is split, in multiples of 32 keys)
+int64_t plain_split(int64_t S, int64_t kv, int64_t groups) {
+    if (S != 1) return kv;
+    const int64_t want = (kv * groups + 511) / 512;
+    return std::max<int64_t>(32, (want + 31) / 32 * 32);
+}
+int64_t plain_splits(int64_t S, int64_t kv, int64_t groups) {
+    const int64_t kb = plain_split(S, kv, groups);
+    return kv > kb ? (kv + kb - 1) / kb : 1;
+}
+
+// ---- GQA, "flash numerics": kernels/llm/qwen35/silo/attn.cpp:105-313 ---------------------------------------------
+// One (row, head) over keys [jbeg, jend), visited in ascending chunks of 16 (attn.cpp:163); keys past `lim` (the
+// row's own position, attn.cpp:206,213) are masked. qh is the query already scaled and rounded to fp16
+// (attn.cpp:112,147). State (m in log2 units, l, O[D]) is updated in place.
+void flash_range(const float* qh, const uint16_t* K, const uint16_t* V, int D, int64_t jbeg, int64_t jend, int64_t lim, float& m, float& l,
+                 float* O) {
+    const int half_d = D / 2;
+    for (int64_t j0 = jbeg; j0 < jend; j0 += 16) {
+        float s[16];
+        float mx = NEG_INF;
+        for (int n = 0; n < 16; ++n) {
+            const int64_t j = j0 + n;
+            if (j <= lim && j < jend) {
+                const uint16_t* kr = K + j * D;
+                float lo = 0.f, hi = 0.f;   // two sub-groups, each half of the features, summed after (attn.cpp:213)
+                for (int d = 0; d < half_d; ++d) lo += qh[d] * h2f(kr[d]);
+                for (int d = half_d; d < D; ++d) hi += qh[d] * h2f(kr[d]);
+                s[n] = lo + hi;
+            } else {
+                s[n] = NEG_INF;
+            }
+            mx = std::fmax(mx, s[n]);
+        }
+        const float mn = std::fmax(m, mx);
+        const float c = mn == NEG_INF ? 1.0f : std::exp2(m - mn);   // attn.cpp:219-220
+        float sum = 0.f;
+        float p16[16];
+        for (int n = 0; n < 16; ++n) {
+            const float pv = s[n] == NEG_INF ? 0.f : std::exp2(s[n] - mn);
+            sum += pv;               // the denominator takes the unrounded weight (attn.cpp:225-233)
+            p16[n] = round_h(pv);    // the numerator the fp16 one (attn.cpp:227)
+        }
+        l = l * c + sum;
+        for (int d = 0; d < D; ++d) O[d] *= c;   // attn.cpp:244
+        for (int n = 0; n < 16; ++n) {
+            if (p16[n] == 0.f) continue;
+            const uint16_t* vr = V + (j0 + n) * D;
+            for (int d = 0; d < D; ++d) O[d] += p16[n] * h2f(vr[d]);
+        }
+        m = mn;
+    }
+}
+
+void scale_query_h(const float* q, int D, float qscale, float* qh) {
+    for (int d = 0; d < D; ++d) qh[d] = round_h(q[d] * qscale);
+}
+
+}  // namespace
+
+extern "C" {
+
+int orc_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+int64_t orc_flash_split(int64_t kv, int64_t Hkv) { return flash_split(kv, Hkv); }
+int64_t orc_flash_splits(int64_t kv, int64_t Hkv) { return flash_splits(kv, Hkv); }
+int64_t orc_plain_split(int64_t S, int64_t kv, int64_t groups) { return plain_split(S, kv, groups); }
+int64_t orc_plain_splits(int64_t S, int64_t kv, int64_t groups) { return plain_splits(S, kv, groups); }
+
+// Causal GQA attention in flash numerics, one split a row (the prompt kernel, attn.cpp:379-400, and a decode row with
+// one split). q [T][qs] fp32 (row t's head h at h*D), caches fp16 [Hkv][cap][D], out fp32 [T][Hq*D].
+void orc_gqa_flash_prefill(const float* q, int64_t qs, const uint16_t* kc, const uint16_t* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                           int64_t cap, int64_t p0, float* out) {
+    const int64_t G = Hq / Hkv;
+    const float qscale = 1.0f / std::sqrt((float) D) * LOG2E;
+#pragma omp parallel for collapse(2) schedule(dynamic, 4)
+    for (int64_t t = 0; t < T; ++t) {
+        for (int64_t h = 0; h < Hq; ++h) {
+            std::vector<float> qh(D), O(D, 0.f);
+            scale_query_h(q + t * qs + h * D, (int) D, qscale, qh.data());
+            float m = NEG_INF, l = 0.f;
+            const int64_t hk = h / G;
+            flash_range(qh.data(), kc + hk * cap * D, vc + hk * cap * D, (int) D, 0, p0 + t + 1, p0 + t, m, l, O.data());
+            float* o = out + (t * Hq + h) * D;
+            for (int64_t d = 0; d < D; ++d) o[d] = l > 0.f ? O[d] / l : 0.f;   // attn.cpp:300
+        }
+    }
+}
+
+// Decode rows (T <= 8) in flash numerics with the reference's own key splits and merge: split size from each row's
+// own position (attn.cpp:325-350), partial (O, m in log2 units, l), merge attn.cpp:352-368. part (nullable) receives
+// [T][Hq][ns][D+2] as the reference's scratch would, ns = the largest split count of the rows.
+void orc_gqa_flash_decode(const float* q, int64_t qs, const uint16_t* kc, const uint16_t* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                          int64_t cap, int64_t p0, float* out, float* part) {
+    const int64_t G = Hq / Hkv;
+    const float qscale = 1.0f / std::sqrt((float) D) * LOG2E;
+    int64_t ns = 1;
+    for (int64_t r = 0; r < T; ++r) ns = std::max(ns, flash_splits(p0 + r + 1, Hkv));
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+    for (int64_t t = 0; t < T; ++t) {
+        for (int64_t h = 0; h < Hq; ++h) {
+            const int64_t kv = p0 + t + 1, kb = flash_split(kv, Hkv), nsr = flash_splits(kv, Hkv), hk = h / G;
+            std::vector<float> qh(D), P((size_t) nsr * (D + 2));
+            scale_query_h(q + t * qs + h * D, (int) D, qscale, qh.data());
+            for (int64_t s = 0; s < nsr; ++s) {
+                float* O = P.data() + s * (D + 2);
+                std::fill(O, O + D, 0.f);
+                float m = NEG_INF, l = 0.f;
+                flash_range(qh.data(), kc + hk * cap * D, vc + hk * cap * D, (int) D, s * kb, std::min(kv, (s + 1) * kb), kv - 1, m, l, O);
+                O[D] = m;
+                O[D + 1] = l;
+            }
+            float* o = out + (t * Hq + h) * D;
+            if (nsr == 1) {
+                for (int64_t d = 0; d < D; ++d) o[d] = P[D + 1] > 0.f ? P[d] / P[D + 1] : 0.f;   // attn.cpp:276-277
+            } else {
+                float mx = NEG_INF;
+                for (int64_t s = 0; s < nsr; ++s) mx = std::fmax(mx, P[s * (D + 2) + D]);
+                for (int64_t d = 0; d < D; ++d) {
+                    float Ls = 0.f, A = 0.f;
+                    if (mx != NEG_INF) {
+                        for (int64_t s = 0; s < nsr; ++s) {
+                            const float e = std::exp2(P[s * (D + 2) + D] - mx);
+                            Ls += P[s * (D + 2) + D + 1] * e;
+                            A += P[s * (D + 2) + d] * e;
+                        }
+                    }
+                    o[d] = Ls > 0.f ? A / Ls : 0.f;
+                }
+                if (part) std::memcpy(part + ((t * Hq + h) * ns) * (D + 2), P.data(), sizeof(float) * nsr * (D + 2));
+            }
+        }
+    }
+}
+
+// Causal GQA attention in "plain" numerics, the vector-unit kernel attn<DL,G> (kernels/llm/qwen35/q35.cpp:44-148;
+// D=128 instance kernels/llm/nemotronh/nh.cpp:32-37): fp32 q * 1/sqrt(D), natural exp, fp32 weights; 4 sub-groups
+// each take every 4th key of the split (q35.cpp:76), each lane D/16 features (the score a 16-lane reduction); merged
+// with q35.cpp:104-128; a single row (S == 1) is split over keys and merged by q35.cpp:131-147. `groups` is what the
+// split size is computed from: Hkv for q35.cpp, Hq/8 for nh.cpp.
+void orc_gqa_plain(const float* q, int64_t qs, const uint16_t* kc, const uint16_t* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t cap,
+                   int64_t p0, int64_t groups, float* out) {
+    const int64_t G = Hq / Hkv;
+    const int DL = (int) (D / 16);
+    const float scale = 1.0f / std::sqrt((float) D);
+    const int64_t ns = plain_splits(T, p0 + T, groups), KB = plain_split(T, p0 + T, groups);
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+    for (int64_t t = 0; t < T; ++t) {
+        for (int64_t h = 0; h < Hq; ++h) {
+            const int64_t hk = h / G, kv_end = p0 + t + 1;
+            const uint16_t* K = kc + hk * cap * D;
+            const uint16_t* V = vc + hk * cap * D;
+            std::vector<float> qv(D), P((size_t) ns * (D + 2)), sub((size_t) 4 * (D + 2));
+            for (int64_t d = 0; d < D; ++d) qv[d] = q[t * qs + h * D + d] * scale;
+            for (int64_t sp = 0; sp < ns; ++sp) {
+                const int64_t j0 = sp * (ns > 1 ? KB : kv_end), j1 = std::min(kv_end, ns > 1 ? (sp + 1) * KB : kv_end);
+                for (int sg = 0; sg < 4; ++sg) {
+                    float* acc = sub.data() + sg * (D + 2);
+                    std::fill(acc, acc + D, 0.f);
+                    float m = NEG_INF, l = 0.f;
+                    for (int64_t j = j0 + sg; j < j1; j += 4) {
+                        float sc = 0.f;
+                        for (int lane = 0; lane < 16; ++lane) {   // a lane's DL features, then the lanes
+                            float d = 0.f;
+                            for (int i = 0; i < DL; ++i) d += qv[lane * DL + i] * h2f(K[j * D + lane * DL + i]);
+                            sc += d;
+                        }
+                        const float mn = std::fmax(m, sc);
+                        const float c = std::exp(m - mn), e = std::exp(sc - mn);
+                        for (int64_t d = 0; d < D; ++d) acc[d] = acc[d] * c + e * h2f(V[j * D + d]);
+                        l = l * c + e;
+                        m = mn;
+                    }
+                    acc[D] = m;
+                    acc[D + 1] = l;
+                }
+                float mx = NEG_INF;
+                for (int k = 0; k < 4; ++k) mx = std::fmax(mx, sub[k * (D + 2) + D]);
+                float* o = P.data() + sp * (D + 2);
+                float L = 0.f;
+                for (int64_t d = 0; d < D; ++d) {
+                    float A = 0.f;
+                    L = 0.f;
+                    if (mx != NEG_INF) {
+                        for (int k = 0; k < 4; ++k) {
+                            const float e = std::exp(sub[k * (D + 2) + D] - mx);
+                            L += sub[k * (D + 2) + D + 1] * e;
+                            A += sub[k * (D + 2) + d] * e;
+                        }
+                    }
+                    o[d] = A;
+                }
+                o[D] = mx;
+                o[D + 1] = L;
+            }
+            float* o = out + (t * Hq + h) * D;
+            if (ns == 1) {
+                for (int64_t d = 0; d < D; ++d) o[d] = P[D + 1] > 0.f ? P[d] / P[D + 1] : 0.f;
+            } else {
+                float mx = NEG_INF;
+                for (int64_t k = 0; k < ns; ++k) mx = std::fmax(mx, P[k * (D + 2) + D]);
+                for (int64_t d = 0; d < D; ++d) {
+                    float L = 0.f, A = 0.f;
+                    if (mx != NEG_INF) {
+                        for (int64_t k = 0; k < ns; ++k) {
+                            const float e = std::exp(P[k * (D + 2) + D] - mx);
+                            L += P[k * (D + 2) + D + 1] * e;
+                            A += P[k * (D + 2) + d] * e;
+                        }
+                    }
+                    o[d] = L > 0.f ? A / L : 0.f;
+                }
+            }
+        }
+    }
+}
+
+// Exact causal attention in fp64 over already-rounded inputs: the yardstick both numerics modes are measured
+// against. q fp32 [T][qs]; K [Hkv][cap][Dqk], V [Hkv][cap][Dv] as fp16 (kind 0) or bf16 (kind 1) bit patterns;
+// out fp64 [T][Hq*Dv]. Row t sees keys 0 .. p0+t.
+void orc_attn_exact(const float* q, int64_t qs, const uint16_t* kc, const uint16_t* vc, int kind, int64_t T, int64_t Hq, int64_t Hkv, int64_t Dqk,
+                    int64_t Dv, int64_t cap, int64_t p0, double scale, double* out) {
+    const int64_t G = Hq / Hkv;
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+    for (int64_t t = 0; t < T; ++t) {
+        for (int64_t h = 0; h < Hq; ++h) {
+            const int64_t hk = h / G, n = p0 + t + 1;
+            const uint16_t* K = kc + hk * cap * Dqk;
+            const uint16_t* V = vc + hk * cap * Dv;
+            std::vector<double> s((size_t) n), acc((size_t) Dv, 0.0);
+            double mx = -INFINITY;
+            for (int64_t j = 0; j < n; ++j) {
+                double d = 0.0;
+                for (int64_t i = 0; i < Dqk; ++i) d += (double) q[t * qs + h * Dqk + i] * (double) (kind ? bf2f(K[j * Dqk + i]) : h2f(K[j * Dqk + i]));
+                s[j] = d * scale;
+                mx = std::max(mx, s[j]);
+            }
+            double sum = 0.0;
+            for (int64_t j = 0; j < n; ++j) {
+                const double p = std::exp(s[j] - mx);
+                sum += p;
+                for (int64_t i = 0; i < Dv; ++i) acc[i] += p * (double) (kind ? bf2f(V[j * Dv + i]) : h2f(V[j * Dv + i]));
+            }
+            for (int64_t i = 0; i < Dv; ++i) out[(t * Hq + h) * Dv + i] = acc[i] / sum;
+        }
+    }
+}
+
+// Generic causal multi-head attention in "tensor-core numerics" for shapes the reference has no kernel for (bf16 MLA
+// prefill with 192-wide keys and 128-wide values): the flash restatement above with the storage type a parameter
+// (kind 0 fp16, 1 bf16): q rounded to the type after scaling by scale*log2e, weights rounded to the type before
+// they meet V, fp32 sums. K [Hkv][cap][Dqk], V [Hkv][cap][Dv].
+void orc_attn_tc(const float* q, int64_t qs, const uint16_t* kc, const uint16_t* vc, int kind, int64_t T, int64_t Hq, int64_t Hkv, int64_t Dqk,
+                 int64_t Dv, int64_t cap, int64_t p0, float scale, float* out) {
+    const int64_t G = Hq / Hkv;
+    const float qscale = scale * LOG2E;
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+    for (int64_t t = 0; t < T; ++t) {
+        for (int64_t h = 0; h < Hq; ++h) {
+            const int64_t hk = h / G, n = p0 + t + 1;
+            const uint16_t* K = kc + hk * cap * Dqk;
+            const uint16_t* V = vc + hk * cap * Dv;
+            std::vector<float> qh((size_t) Dqk), O((size_t) Dv, 0.f);
+            for (int64_t i = 0; i < Dqk; ++i) {
+                const float x = q[t * qs + h * Dqk + i] * qscale;
+                qh[i] = kind ? round_bf(x) : round_h(x);
+            }
+            float m = NEG_INF, l = 0.f;
+            for (int64_t j0 = 0; j0 < n; j0 += 16) {
+                float s[16], mx = NEG_INF;
+                for (int c = 0; c < 16; ++c) {
+                    const int64_t j = j0 + c;
+                    s[c] = NEG_INF;
+                    if (j < n) {
+                        float d = 0.f;
+                        for (int64_t i = 0; i < Dqk; ++i) d += qh[i] * (kind ? bf2f(K[j * Dqk + i]) : h2f(K[j * Dqk + i]));
+                        s[c] = d;
+                    }
+                    mx = std::fmax(mx, s[c]);
+                }
+                const float mn = std::fmax(m, mx), cf = mn == NEG_INF ? 1.f : std::exp2(m - mn);
+                float sum = 0.f;
+                for (int64_t i = 0; i < Dv; ++i) O[i] *= cf;
+                for (int c = 0; c < 16; ++c) {
+                    if (s[c] == NEG_INF) continue;
+                    const float pv = std::exp2(s[c] - mn);
+                    sum += pv;
+                    const float pr = kind ? round_bf(pv) : round_h(pv);
+                    for (int64_t i = 0; i < Dv; ++i) O[i] += pr * (kind ? bf2f(V[(j0 + c) * Dv + i]) : h2f(V[(j0 + c) * Dv + i]));
+                }
+                l = l * cf + sum;
+                m = mn;
+            }
+            for (int64_t i = 0; i < Dv; ++i) out[(t * Hq + h) * Dv + i] = l > 0.f ? O[i] / l : 0.f;
+        }
+    }
+}
+
+// ---- absorbed MLA ------------------------------------------------------------------------------------------------
+
+// The middle stage of the fused decode kernel mla_decode_t (kernels/llm/deepseek2/ds2.cpp:186-235): q [T][H][L+R]
+// fp32 (the absorbed query, then the rotated part), cache fp16 [n][L+R], row t sees cells 0 .. pos0+t;
+// u [T][H][L]. 16 sub-groups stride the cells by 16, each with its own online (m, sum, acc) using natural exp
+// (ds2.cpp:193-216); a lane owns L/16 latent and R/16 rope features and the score is the 16 lanes' sum times scale
+// (ds2.cpp:198-209); final merge ds2.cpp:218-235.
+void orc_mla_fused(const float* q, const uint16_t* cache, int64_t T, int64_t H, int64_t L, int64_t R, int64_t pos0, float scale, float* u) {
+    const int64_t CR = L + R;
+    const int DL = (int) (L / 16), DR = (int) (R / 16);
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+    for (int64_t t = 0; t < T; ++t) {
+        for (int64_t h = 0; h < H; ++h) {
+            const float* qr = q + (t * H + h) * CR;
+            const int64_t n = pos0 + t + 1;
+            std::vector<float> acc((size_t) 16 * L, 0.f), x((size_t) L);
+            float m[16], sum[16];
+            for (int sg = 0; sg < 16; ++sg) {
+                m[sg] = NEG_INF;
+                sum[sg] = 0.f;
+                float* a = acc.data() + sg * L;
+                for (int64_t i = sg; i < n; i += 16) {
+                    const uint16_t* row = cache + i * CR;
+                    float d = 0.f;
+                    for (int lane = 0; lane < 16; ++lane) {
+                        float dl = 0.f;
+                        for (int f = 0; f < DL; ++f) {
+                            x[lane * DL + f] = h2f(row[lane * DL + f]);
+                            dl += qr[lane * DL + f] * x[lane * DL + f];
+                        }
+                        for (int f = 0; f < DR; ++f) dl += qr[L + lane * DR + f] * h2f(row[L + lane * DR + f]);
+                        d += dl;
+                    }
+                    d *= scale;
+                    const float mn = std::fmax(m[sg], d);
+                    const float ca = std::exp(m[sg] - mn), cb = std::exp(d - mn);
+                    sum[sg] = sum[sg] * ca + cb;
+                    for (int64_t f = 0; f < L; ++f) a[f] = a[f] * ca + cb * x[f];
+                    m[sg] = mn;
+                }
+            }
+            float mx = NEG_INF;
+            for (int k = 0; k < 16; ++k) mx = std::fmax(mx, m[k]);
+            float tot = 0.f;
+            for (int k = 0; k < 16; ++k) tot += m[k] == NEG_INF ? 0.f : sum[k] * std::exp(m[k] - mx);
+            float* o = u + (t * H + h) * L;
+            for (int64_t f = 0; f < L; ++f) {
+                float v = 0.f;
+                for (int k = 0; k < 16; ++k) v += acc[k * L + f] * (m[k] == NEG_INF ? 0.f : std::exp(m[k] - mx));
+                o[f] = v / tot;
+            }
+        }
+    }
+}
+
+// The GEMM form the deepseek2 engine uses past NS_DS2_MLA_FUSED_MAX cells and for prompt rows
+// (llm/deepseek2/src/engine.rs:1204-1224 with ns_softmax_masked, kernels/llm/glm5next/glm.cpp:1042-1060):
+// qh = fp16(q); S = qh . cache^T in fp32; P = exp(S*scale - max) / sum over the row's first pos0+t+1 cells, fp32;
+// P16 = fp16(P); u = P16 . cache[:, :L] in fp32.
+void orc_mla_gemm(const float* q, const uint16_t* cache, int64_t T, int64_t H, int64_t L, int64_t R, int64_t pos0, float scale, float* u) {
+    const int64_t CR = L + R;
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+    for (int64_t t = 0; t < T; ++t) {
+        for (int64_t h = 0; h < H; ++h) {
+            const int64_t n = pos0 + t + 1;
+            std::vector<float> qh((size_t) CR), s((size_t) n), acc((size_t) L, 0.f);
+            for (int64_t f = 0; f < CR; ++f) qh[f] = round_h(q[(t * H + h) * CR + f]);
+            float mx = NEG_INF;
+            for (int64_t i = 0; i < n; ++i) {
+                const uint16_t* row = cache + i * CR;
+                float d = 0.f;
+                for (int64_t f = 0; f < CR; ++f) d += qh[f] * h2f(row[f]);
+                s[i] = d;
+                mx = std::fmax(mx, d * scale);
+            }
+            float sum = 0.f;
+            for (int64_t i = 0; i < n; ++i) sum += std::exp(s[i] * scale - mx);
+            for (int64_t i = 0; i < n; ++i) {
+                const float p = round_h(std::exp(s[i] * scale - mx) / sum);
+                if (p == 0.f) continue;
+                const uint16_t* row = cache + i * CR;
+                for (int64_t f = 0; f < L; ++f) acc[f] += p * h2f(row[f]);
+            }
+            std::memcpy(u + (t * H + h) * L, acc.data(), sizeof(float) * L);
+        }
+    }
+}
+
+// fp64 yardstick for absorbed MLA over the fp16 cache (q fp32 as given).
+void orc_mla_exact(const float* q, const uint16_t* cache, int64_t T, int64_t H, int64_t L, int64_t R, int64_t pos0, double scale, double* u) {
+    const int64_t CR = L + R;
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+    for (int64_t t = 0; t < T; ++t) {
+        for (int64_t h = 0; h < H; ++h) {
+            const int64_t n = pos0 + t + 1;
+            std::vector<double> s((size_t) n), acc((size_t) L, 0.0);
+            double mx = -INFINITY;
+            for (int64_t i = 0; i < n; ++i) {
+                double d = 0.0;
+                for (int64_t f = 0; f < CR; ++f) d += (double) q[(t * H + h) * CR + f] * (double) h2f(cache[i * CR + f]);
+                s[i] = d * scale;
+                mx = std::max(mx, s[i]);
+            }
+            double sum = 0.0;
+            for (int64_t i = 0; i < n; ++i) {
+                const double p = std::exp(s[i] - mx);
+                sum += p;
+                for (int64_t f = 0; f < L; ++f) acc[f] += p * (double) h2f(cache[i * CR + f]);
+            }
+            for (int64_t f = 0; f < L; ++f) u[(t * H + h) * L + f] = acc[f] / sum;
+        }
+    }
+}
+
+// ns_mla_attend (kernels/llm/glm5next/glm.cpp:782-812): dense causal absorbed MLA over fp32 latents, exact two-pass
+// softmax with natural exp; the dot product is 256 work-items' strided partial sums (glm.cpp:795) added together.
+void orc_mla_attend_f32(const float* qa, const float* c, float* u, int64_t T, int64_t H, int64_t L, int64_t pos0, float scale) {
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+    for (int64_t t = 0; t < T; ++t) {
+        for (int64_t h = 0; h < H; ++h) {
+            const float* qr = qa + (t * H + h) * L;
+            const int64_t n = pos0 + t + 1;
+            std::vector<float> s((size_t) n), acc((size_t) L, 0.f);
+            float mx = NEG_INF;
+            for (int64_t i = 0; i < n; ++i) {
+                float part[256];
+                for (int w = 0; w < 256; ++w) {
+                    float d = 0.f;
+                    for (int64_t r = w; r < L; r += 256) d += qr[r] * c[i * L + r];
+                    part[w] = d;
+                }
+                float d = 0.f;
+                for (int w = 0; w < 256; ++w) d += part[w];
+                s[i] = d * scale;
+                mx = std::fmax(mx, s[i]);
+            }
+            float sum = 0.f;
+            for (int64_t i = 0; i < n; ++i) {
+                const float p = std::exp(s[i] - mx);
+                sum += p;
+                for (int64_t f = 0; f < L; ++f) acc[f] += p * c[i * L + f];
+            }
+            for (int64_t f = 0; f < L; ++f) u[(t * H + h) * L + f] = acc[f] / sum;
+        }
+    }
+}
+
+// q8 latent rows (kernels/llm/glm5next/glm.cpp:1282-1299): a row of 512 = 16 fp16 scales then 512 int8; block scale
+// fp16(amax/127), values round(x / scale) clamped to +-127. y holds n rows of 544 bytes.
+void orc_to_q8row(const float* x, uint8_t* y, int64_t n) {
+    for (int64_t r = 0; r < n; ++r) {
+        uint8_t* row = y + r * 544;
+        for (int b = 0; b < 16; ++b) {
+            const float* xr = x + r * 512 + b * 32;
+            float amax = 0.f;
+            for (int e = 0; e < 32; ++e) amax = std::fmax(amax, std::fabs(xr[e]));
+            const uint16_t dh = f2h(amax / 127.f);
+            const float d = h2f(dh), inv = d > 0.f ? 1.f / d : 0.f;
+            std::memcpy(row + 2 * b, &dh, 2);
+            int8_t* qs = reinterpret_cast<int8_t*>(row + 32 + b * 32);
+            for (int e = 0; e < 32; ++e) qs[e] = (int8_t) std::min(127.f, std::max(-127.f, std::round(xr[e] * inv)));
+        }
+    }
+}
+
+// mla_dec<512,Q8> (kernels/llm/glm5next/glm.cpp:1079-1186): decode rows over the row's cells - every earlier token
+// when sel_cnt is null or negative, else 4 tokens of each selected pool then the incomplete pool (glm.cpp:1094-1102).
+// Pass 1 scores (a lane's 32 features, 16 lanes, times scale) and the max; pass 2 natural exp, each of 16 sub-groups
+// sums every 16th cell, then the sub-groups are added in order (glm.cpp:1173-1183). c is fp16 [n][512] (q8 == 0) or
+// q8 rows of 544 bytes (q8 == 1).
+void orc_mla_dec512(const float* qa, const void* cv, float* u, int64_t T, int64_t H, int64_t pos0, float scale, const int32_t* sel,
+                    const int32_t* sel_cnt, int64_t K, int q8) {
+    const int64_t L = 512;
+    const uint16_t* c16 = static_cast<const uint16_t*>(cv);
+    const uint8_t* c8 = static_cast<const uint8_t*>(cv);
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+    for (int64_t t = 0; t < T; ++t) {
+        for (int64_t h = 0; h < H; ++h) {
+            const int64_t p = pos0 + t;
+            const int32_t ns = sel_cnt ? sel_cnt[t] : -1;
+            const int64_t tail0 = 4 * ((p + 1) / 4);
+            const int64_t n = ns < 0 ? p + 1 : 4 * (int64_t) ns + (p + 1 - tail0);
+            auto cell = [&](int64_t i) -> int64_t {
+                if (ns < 0) return i;
+                if (i < 4 * (int64_t) ns) return 4 * (int64_t) sel[t * K + i / 4] + i % 4;
+                return tail0 + (i - 4 * (int64_t) ns);
+            };
+            auto load = [&](int64_t i, float* x) {
+                if (q8) {
+                    const uint8_t* row = c8 + cell(i) * 544;
+                    for (int b = 0; b < 16; ++b) {
+                        uint16_t dh;
+                        std::memcpy(&dh, row + 2 * b, 2);
+                        const float d = h2f(dh);
+                        const int8_t* qs = reinterpret_cast<const int8_t*>(row + 32 + b * 32);
+                        for (int e = 0; e < 32; ++e) x[b * 32 + e] = d * (float) qs[e];
+                    }
+                } else {
+                    const uint16_t* row = c16 + cell(i) * L;
+                    for (int64_t f = 0; f < L; ++f) x[f] = h2f(row[f]);
+                }
+            };
+            const float* qr = qa + (t * H + h) * L;
+            std::vector<float> sc((size_t) n), x((size_t) L), acc((size_t) 16 * L, 0.f);
+            float mx = NEG_INF;
+            for (int64_t i = 0; i < n; ++i) {
+                load(i, x.data());
+                float d = 0.f;
+                for (int lane = 0; lane < 16; ++lane) {
+                    float dl = 0.f;
+                    for (int f = 0; f < 32; ++f) dl += qr[lane * 32 + f] * x[lane * 32 + f];
+                    d += dl;
+                }
+                sc[i] = d * scale;
+                mx = std::fmax(mx, sc[i]);
+            }
+            float sk[16] = {};
+            for (int64_t i = 0; i < n; ++i) {
+                const int sg = (int) (i % 16);
+                const float w = std::exp(sc[i] - mx);
+                sk[sg] += w;
+                load(i, x.data());
+                float* a = acc.data() + sg * L;
+                for (int64_t f = 0; f < L; ++f) a[f] += w * x[f];
+            }
+            float sum = 0.f;
+            for (int k = 0; k < 16; ++k) sum += sk[k];
+            for (int64_t f = 0; f < L; ++f) {
+                float v = 0.f;
+                for (int k = 0; k < 16; ++k) v += acc[k * L + f];
+                u[(t * H + h) * L + f] = v / sum;
+            }
+        }
+    }
+}
+
+// ---- cache writers -----------------------------------------------------------------------------------------------
+
+// ns_q35_kv_store (kernels/llm/qwen35/q35.cpp:573-588): fp32 rows k [T][ks], v [T][vs] -> fp16 caches [Hkv][cap][D]
+// at positions p0 ..
+void orc_kv_store(const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hkv, int64_t D, int64_t cap, int64_t p0, uint16_t* kc,
+                  uint16_t* vc) {
+    for (int64_t t = 0; t < T; ++t)
+        for (int64_t h = 0; h < Hkv; ++h)
+            for (int64_t d = 0; d < D; ++d) {
+                const int64_t at = (h * cap + p0 + t) * D + d;
+                kc[at] = f2h(k[t * ks + h * D + d]);
+                vc[at] = f2h(v[t * vs + h * D + d]);
+            }
+}
+
+// Merge of per-split partials (O unnormalised, m in log2 units, l), optionally with a per-head sink that joins the
+// denominator only (kernels/llm/qwen35/silo/attn.cpp:352-368; sink form kernels/llm/deepseek41/silo/attn.cpp:266-285).
+// part [rows][ns][PS] with O at 0..D-1, m at D, l at D+1; sinks (nullable) [rows] in natural-log units.
+void orc_merge(const float* part, int64_t rows, int64_t ns, int64_t D, int64_t PS, const float* sinks, float* out) {
+    for (int64_t r = 0; r < rows; ++r) {
+        const float* pp = part + r * ns * PS;
+        float mx = NEG_INF;
+        for (int64_t k = 0; k < ns; ++k) mx = std::fmax(mx, pp[k * PS + D]);
+        if (sinks) mx = std::fmax(mx, sinks[r] * LOG2E);
+        for (int64_t d = 0; d < D; ++d) {
+            float Ls = 0.f, A = 0.f;
+            if (mx != NEG_INF) {
+                for (int64_t k = 0; k < ns; ++k) {
+                    const float e = std::exp2(pp[k * PS + D] - mx);
+                    Ls += pp[k * PS + D + 1] * e;
+                    A += pp[k * PS + d] * e;
+                }
+                if (sinks) Ls += std::exp2(sinks[r] * LOG2E - mx);
+            }
+            out[r * D + d] = Ls > 0.f ? A / Ls : 0.f;
+        }
+    }
+}
+
+}  // extern "C"

@@ -1,0 +1,171 @@
+"""ctypes front of the CPU oracle (oracle/attn_oracle.cpp -> oracle/liboracle.so).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke test and by the benchmark's CPU-baseline leg, never by the
+library. Parity unpinned: the reference holds no golden vectors for attention (see attn_oracle.cpp's header).
+
+Arrays are numpy: fp32 as float32, fp16 / bf16 storage as uint16 bit patterns (`np.float16.view(np.uint16)` for fp16;
+`to_bf16_bits` below for bf16).
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "liboracle.so")
+_lib = None
+
+i64 = C.c_int64
+_pf = C.POINTER(C.c_float)
+_pd = C.POINTER(C.c_double)
+_ph = C.POINTER(C.c_uint16)
+_pi = C.POINTER(C.c_int32)
+
+
+def build(force=False):
+    """Compiles the oracle with its Makefile (g++, OpenMP)."""
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(os.path.join(_HERE, "attn_oracle.cpp")):
+        subprocess.check_call(["make", "-C", _HERE, "-B", "liboracle.so"], stdout=subprocess.DEVNULL)
+    return _SO
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_SO):
+            build()
+        _lib = C.CDLL(_SO)
+        _lib.orc_threads.restype = C.c_int
+        for n in ("orc_flash_split", "orc_flash_splits"):
+            getattr(_lib, n).restype = i64
+            getattr(_lib, n).argtypes = [i64, i64]
+        for n in ("orc_plain_split", "orc_plain_splits"):
+            getattr(_lib, n).restype = i64
+            getattr(_lib, n).argtypes = [i64, i64, i64]
+    return _lib
+
+
+def threads():
+    return int(lib().orc_threads())
+
+
+def _f(a):
+    assert a.dtype == np.float32 and a.flags.c_contiguous
+    return a.ctypes.data_as(_pf)
+
+
+def _h(a):
+    assert a.dtype == np.uint16 and a.flags.c_contiguous
+    return a.ctypes.data_as(_ph)
+
+
+def to_f16_bits(x):
+    return np.ascontiguousarray(x, dtype=np.float32).astype(np.float16).view(np.uint16)
+
+
+def to_bf16_bits(x):
+    """fp32 -> bf16 bit patterns, round to nearest even."""
+    w = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    w = w + 0x7FFF + ((w >> 16) & 1)
+    return (w >> 16).astype(np.uint16)
+
+
+def from_bf16_bits(b):
+    return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def flash_split(kv, hkv):
+    return int(lib().orc_flash_split(kv, hkv))
+
+
+def flash_splits(kv, hkv):
+    return int(lib().orc_flash_splits(kv, hkv))
+
+
+def gqa_flash_prefill(q, kc, vc, T, Hq, Hkv, D, cap, p0):
+    """q fp32 [T, Hq*D]; kc, vc uint16 [Hkv, cap, D] -> fp32 [T, Hq*D] (flash numerics, one split a row)."""
+    out = np.empty((T, Hq * D), np.float32)
+    lib().orc_gqa_flash_prefill(_f(q), i64(q.shape[1]), _h(kc), _h(vc), i64(T), i64(Hq), i64(Hkv), i64(D), i64(cap), i64(p0), _f(out))
+    return out
+
+
+def gqa_flash_decode(q, kc, vc, T, Hq, Hkv, D, cap, p0):
+    """Decode rows (T <= 8) with the reference's own key splits and merge."""
+    out = np.empty((T, Hq * D), np.float32)
+    lib().orc_gqa_flash_decode(_f(q), i64(q.shape[1]), _h(kc), _h(vc), i64(T), i64(Hq), i64(Hkv), i64(D), i64(cap), i64(p0), _f(out), None)
+    return out
+
+
+def gqa_plain(q, kc, vc, T, Hq, Hkv, D, cap, p0, groups=None):
+    out = np.empty((T, Hq * D), np.float32)
+    lib().orc_gqa_plain(_f(q), i64(q.shape[1]), _h(kc), _h(vc), i64(T), i64(Hq), i64(Hkv), i64(D), i64(cap), i64(p0),
+                        i64(Hkv if groups is None else groups), _f(out))
+    return out
+
+
+def attn_exact(q, kc, vc, T, Hq, Hkv, Dqk, Dv, cap, p0, scale, kind=0):
+    """fp64 yardstick. kind 0: fp16 caches, 1: bf16. -> float64 [T, Hq*Dv]."""
+    out = np.empty((T, Hq * Dv), np.float64)
+    lib().orc_attn_exact(_f(q), i64(q.shape[1]), _h(kc), _h(vc), C.c_int(kind), i64(T), i64(Hq), i64(Hkv), i64(Dqk), i64(Dv), i64(cap), i64(p0),
+                         C.c_double(scale), out.ctypes.data_as(_pd))
+    return out
+
+
+def attn_tc(q, kc, vc, T, Hq, Hkv, Dqk, Dv, cap, p0, scale, kind=0):
+    """Tensor-core numerics with the storage type a parameter (0 fp16, 1 bf16) -> fp32 [T, Hq*Dv]."""
+    out = np.empty((T, Hq * Dv), np.float32)
+    lib().orc_attn_tc(_f(q), i64(q.shape[1]), _h(kc), _h(vc), C.c_int(kind), i64(T), i64(Hq), i64(Hkv), i64(Dqk), i64(Dv), i64(cap), i64(p0),
+                      C.c_float(scale), _f(out))
+    return out
+
+
+def mla_fused(q, cache, T, H, L, R, pos0, scale):
+    """q fp32 [T, H, L+R]; cache uint16 [n, L+R] -> fp32 [T, H, L] (deepseek2's fused decode kernel, middle stage)."""
+    u = np.empty((T, H, L), np.float32)
+    lib().orc_mla_fused(_f(q), _h(cache), i64(T), i64(H), i64(L), i64(R), i64(pos0), C.c_float(scale), _f(u))
+    return u
+
+
+def mla_gemm(q, cache, T, H, L, R, pos0, scale):
+    u = np.empty((T, H, L), np.float32)
+    lib().orc_mla_gemm(_f(q), _h(cache), i64(T), i64(H), i64(L), i64(R), i64(pos0), C.c_float(scale), _f(u))
+    return u
+
+
+def mla_exact(q, cache, T, H, L, R, pos0, scale):
+    u = np.empty((T, H, L), np.float64)
+    lib().orc_mla_exact(_f(q), _h(cache), i64(T), i64(H), i64(L), i64(R), i64(pos0), C.c_double(scale), u.ctypes.data_as(_pd))
+    return u
+
+
+def mla_attend_f32(qa, c, T, H, L, pos0, scale):
+    u = np.empty((T, H, L), np.float32)
+    lib().orc_mla_attend_f32(_f(qa), _f(c), _f(u), i64(T), i64(H), i64(L), i64(pos0), C.c_float(scale))
+    return u
+
+
+def to_q8row(x):
+    """fp32 [n, 512] -> uint8 [n, 544] (16 fp16 scales then 512 int8)."""
+    n = x.shape[0]
+    y = np.empty((n, 544), np.uint8)
+    lib().orc_to_q8row(_f(x), y.ctypes.data_as(C.POINTER(C.c_uint8)), i64(n))
+    return y
+
+
+def mla_dec512(qa, c, T, H, pos0, scale, sel=None, sel_cnt=None, K=0, q8=False):
+    u = np.empty((T, H, 512), np.float32)
+    lib().orc_mla_dec512(_f(qa), c.ctypes.data_as(C.c_void_p), _f(u), i64(T), i64(H), i64(pos0), C.c_float(scale),
+                         None if sel is None else sel.ctypes.data_as(_pi), None if sel_cnt is None else sel_cnt.ctypes.data_as(_pi), i64(K),
+                         C.c_int(1 if q8 else 0))
+    return u
+
+
+def kv_store(k, v, T, Hkv, D, cap, p0, kc, vc):
+    lib().orc_kv_store(_f(k), i64(k.shape[1]), _f(v), i64(v.shape[1]), i64(T), i64(Hkv), i64(D), i64(cap), i64(p0), _h(kc), _h(vc))
+
+
+def merge(part, rows, ns, D, PS, sinks=None):
+    out = np.empty((rows, D), np.float32)
+    lib().orc_merge(_f(part), i64(rows), i64(ns), i64(D), i64(PS), None if sinks is None else _f(sinks), _f(out))
+    return out

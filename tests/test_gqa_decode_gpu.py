@@ -1,0 +1,172 @@
+"""GQA split-KV decode on the GPU against the CPU oracle, through the C ABI.
+
+Tolerance: BASELINE's bar for this path, max-abs 2e-3 / max-rel 1e-2 against the reference numerics (the oracle's
+flash mode restates kernels/llm/qwen35/silo/attn.cpp), checked as |got - want| <= 2e-3 + 1e-2 |want|; the fp64 exact
+result is reported beside it with the same bar."""
+import numpy as np
+import pytest
+
+from nextsycl_b200 import DevBuf
+from nextsycl_b200 import workloads as W
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+ABS, REL = 2e-3, 1e-2
+
+
+def assert_close(got, want, what):
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    d = np.abs(got - want)
+    bad = d > ABS + REL * np.abs(want)
+    assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} outside tolerance, max abs {d.max():.3e}"
+
+
+def run_compat(gpu, ops, q, k, v, T, Hq, Hkv, D, cap, p0, name="ns_q35_attn_decode", qs=None):
+    qs = qs or Hq * D
+    qf = np.zeros((T, qs), np.float32)
+    qf[:, :Hq * D] = q.astype(np.float32)
+    dq, dk, dv = DevBuf.of(gpu, qf), DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+    out = DevBuf(gpu, T * Hq * D * 4)
+    out.fill(0xFF)
+    n = int(gpu.api.need(name + "_scratch")(T, Hq, Hkv, D, p0))
+    sc = DevBuf(gpu, n * 4) if n else None
+    if sc is not None:
+        sc.fill(0xFF)   # the arena hands out whatever was there before (NaN patterns here)
+    if name.endswith("decode"):
+        ops.attn_decode(dq, qs, dk, dv, T, Hq, Hkv, D, cap, p0, out, sc, name=name)
+    else:
+        ops.attn(dq, qs, dk, dv, T, Hq, Hkv, D, cap, p0, out, sc, name=name)
+    return out.read(np.float32).reshape(T, Hq * D)
+
+
+CASES = [
+    # T, Hq, Hkv, D, kv
+    (1, 8, 2, 128, 1),          # a single key
+    (1, 8, 2, 128, 15),         # less than one tile
+    (1, 64, 8, 128, 100),       # ragged, two splits
+    (4, 32, 4, 128, 1000),      # the verify shape, 32 rows a key head
+    (8, 16, 4, 128, 333),       # 8 rows x 4 heads
+    (3, 16, 1, 128, 2049),      # 16 heads a key head, 48 rows: two row groups
+    (1, 4, 4, 128, 4097),       # one query head a key head
+    (2, 24, 4, 256, 700),       # the qwen35 shape (D 256, 6 heads a key head)
+    (8, 24, 4, 256, 65),        # 48 rows of 256: three row groups
+    (1, 64, 8, 128, 5000),
+]
+
+
+@pytest.mark.parametrize("T,Hq,Hkv,D,kv", CASES)
+def test_decode_matches_oracle(gpu, ops, T, Hq, Hkv, D, kv):
+    cap = kv + 3
+    q, k, v, p0 = W.gqa_case(920, T, Hq, Hkv, D, kv, cap=cap)
+    got = run_compat(gpu, ops, q, k, v, T, Hq, Hkv, D, cap, p0)
+    qf, kb, vb = q.astype(np.float32), k.view(np.uint16), v.view(np.uint16)
+    assert_close(got, O.gqa_flash_decode(qf, kb, vb, T, Hq, Hkv, D, cap, p0), "vs flash numerics")
+    assert_close(got, O.attn_exact(qf, kb, vb, T, Hq, Hkv, D, D, cap, p0, 1 / np.sqrt(D)), "vs fp64")
+
+
+def test_query_row_stride_and_other_names(gpu, ops):
+    T, Hq, Hkv, D, kv = 2, 16, 2, 128, 300
+    q, k, v, p0 = W.gqa_case(921, T, Hq, Hkv, D, kv)
+    want = O.gqa_flash_decode(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, kv, p0)
+    assert_close(run_compat(gpu, ops, q, k, v, T, Hq, Hkv, D, kv, p0, qs=Hq * D + 64), want, "strided q")
+    assert_close(run_compat(gpu, ops, q, k, v, T, Hq, Hkv, D, kv, p0, name="ns_nhs_attn_decode"), want, "nhs name")
+    assert_close(run_compat(gpu, ops, q, k, v, T, Hq, Hkv, D, kv, p0, name="ns_nh_attn"), want, "nh name")
+
+
+def test_a_row_does_not_depend_on_its_pass(gpu, ops):
+    """Verify rows equal one-row passes bit for bit, also where the rows' split sizes differ
+    (the invariant of kernels/llm/qwen35/silo/attn.cpp:100-104 that `spec-check` tests, cli/nextsycl/src/main.rs:967-989)."""
+    Hq, Hkv, D = 32, 4, 128
+    for kv in (900, 4739):   # 4739: rows 4736 | 4737.. sit either side of a step of the split size (4 key heads)
+        T = 4
+        q, k, v, p0 = W.gqa_case(922, T, Hq, Hkv, D, kv)
+        rows = run_compat(gpu, ops, q, k, v, T, Hq, Hkv, D, kv, p0)
+        for t in range(T):
+            one = run_compat(gpu, ops, q[t:t + 1], k, v, 1, Hq, Hkv, D, kv, p0 + t)
+            assert np.array_equal(one[0], rows[t]), (kv, t)
+
+
+def test_rows_path_any_T(gpu, ops):
+    """ns_q35_attn with more than 8 rows."""
+    T, Hq, Hkv, D, kv = 19, 8, 2, 128, 140
+    q, k, v, p0 = W.gqa_case(923, T, Hq, Hkv, D, kv)
+    got = run_compat(gpu, ops, q, k, v, T, Hq, Hkv, D, kv, p0, name="ns_q35_attn")
+    assert_close(got, O.gqa_flash_prefill(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, kv, p0), "rows")
+
+
+def test_kv_store_then_decode(gpu, ops):
+    T, Hkv, D, cap, p0 = 3, 4, 128, 64, 40
+    k = W.rng(924, 0).standard_normal((T, Hkv * D), dtype=np.float32)
+    v = W.rng(924, 1).standard_normal((T, Hkv * D), dtype=np.float32)
+    kc, vc = DevBuf(gpu, Hkv * cap * D * 2), DevBuf(gpu, Hkv * cap * D * 2)
+    kc.fill(0), vc.fill(0)
+    ops.kv_store(DevBuf.of(gpu, k), Hkv * D, DevBuf.of(gpu, v), Hkv * D, T, Hkv, D, cap, p0, kc, vc)
+    hk, hv = np.zeros((Hkv, cap, D), np.uint16), np.zeros((Hkv, cap, D), np.uint16)
+    O.kv_store(k, v, T, Hkv, D, cap, p0, hk, hv)
+    assert np.array_equal(kc.read(np.uint16).reshape(Hkv, cap, D), hk)      # bit-exact: one rounding to fp16
+    assert np.array_equal(vc.read(np.uint16).reshape(Hkv, cap, D), hv)
+    from nextsycl_b200 import Error
+    with pytest.raises(Error, match="capacity"):
+        ops.kv_store(DevBuf.of(gpu, k), Hkv * D, DevBuf.of(gpu, v), Hkv * D, T, Hkv, D, cap, cap - 1, kc, vc)
+
+
+def test_argument_errors(gpu, ops):
+    api = gpu.api
+    d = DevBuf(gpu, 1 << 20)
+    assert api.ns_q35_attn_decode(gpu.raw, d.ptr, 1024, d.ptr, d.ptr, 9, 8, 2, 128, 100, 0, d.ptr, None) == -1
+    assert "1..8 rows" in api.last_error()
+    assert api.ns_q35_attn_decode(gpu.raw, d.ptr, 1024, d.ptr, d.ptr, 1, 8, 2, 128, 100, 100, d.ptr, None) == -1
+    assert "capacity" in api.last_error()
+    assert api.ns_q35_attn_decode(gpu.raw, d.ptr, 8 * 128, d.ptr, d.ptr, 1, 8, 2, 128, 100000, 50000, d.ptr, None) == -1
+    assert "scratch" in api.last_error()
+    assert api.ns_q35_attn_decode_kv(gpu.raw, 1, d.ptr, 1024, d.ptr, d.ptr, 1, 8, 2, 128, 100, 0, d.ptr, None) == -1
+    gpu.sync()
+
+
+def test_native_batch_fp16(gpu, ops):
+    """ns_b200_gqa_decode: 3 sequences of different lengths in one launch equal their own one-sequence results."""
+    B, T, Hq, Hkv, D = 3, 2, 16, 2, 128
+    kvs = [50, 1500, 777]
+    cap = 1600
+    qs, seqs, want = [], [], []
+    keep = []
+    for b, kv in enumerate(kvs):
+        q, k, v, p0 = W.gqa_case(925, T, Hq, Hkv, D, kv, cap=cap, seq=b)
+        qs.append(q)
+        dk, dv = DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+        keep += [dk, dv]
+        seqs.append((dk, dv, cap, p0))
+        want.append(O.gqa_flash_decode(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, cap, p0))
+    dq = DevBuf.of(gpu, np.stack(qs))
+    table = ops.seq_table(seqs)
+    out = DevBuf(gpu, B * T * Hq * D * 2)
+    n = ops.gqa_decode_scratch(B, T, Hq, Hkv, D, max(kvs))
+    sc = DevBuf(gpu, n * 4)
+    sc.fill(0xFF)
+    ops.gqa_decode(dq, Hq * D, T * Hq * D, table, B, T, Hq, Hkv, D, max(kvs), out, sc)
+    got = out.read(np.float16).reshape(B, T, Hq * D).astype(np.float32)
+    for b in range(B):
+        # fp16 output: half an ulp of fp16 on top of the kernel's own error
+        assert_close(got[b], want[b], f"sequence {b}")
+
+
+@pytest.mark.parametrize("B", [1, 2])
+def test_full_size_config_2(gpu, ops, B):
+    """BASELINE config 2 at full size: 64 query heads, 8 key heads, 32,768 cached tokens, batch of sequences."""
+    T, Hq, Hkv, D, kv = 1, 64, 8, 128, 32768
+    seqs, want, qs, keep = [], [], [], []
+    for b in range(B):
+        q, k, v, p0 = W.gqa_case(2, T, Hq, Hkv, D, kv, seq=b)
+        qs.append(q)
+        dk, dv = DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+        keep += [dk, dv]
+        seqs.append((dk, dv, kv, p0))
+        want.append(O.gqa_flash_decode(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, kv, p0))
+    dq = DevBuf.of(gpu, np.stack(qs))
+    out = DevBuf(gpu, B * T * Hq * D * 2)
+    sc = DevBuf(gpu, 4 * ops.gqa_decode_scratch(B, T, Hq, Hkv, D, kv))
+    ops.gqa_decode(dq, Hq * D, T * Hq * D, ops.seq_table(seqs), B, T, Hq, Hkv, D, kv, out, sc)
+    got = out.read(np.float16).reshape(B, T, Hq * D).astype(np.float32)
+    for b in range(B):
+        assert_close(got[b], want[b], f"sequence {b}")

@@ -1,0 +1,168 @@
+"""The CPU oracle checked on the CPU: against an independent numpy statement of causal softmax attention (the form
+the reference's own Python models use, reference/ricursive-65b/ripple_ref.py:279-294), against its fp64 mode, and
+against the committed known-answer file. Parity with the reference itself is unpinned (no golden vectors exist for
+attention in the reference tree); these tests pin the oracle to the mathematics and to itself."""
+import os
+
+import numpy as np
+import pytest
+
+from nextsycl_b200 import workloads as W
+from oracle import oracle as O
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "oracle_kat.npz")
+# BASELINE tolerance for fp16 tensor-core numerics against exact arithmetic
+ABS, REL = 2e-3, 1e-2
+
+
+def numpy_attention(q, k, v, T, Hq, Hkv, D, p0):
+    G = Hq // Hkv
+    out = np.zeros((T, Hq, D))
+    for t in range(T):
+        n = p0 + t + 1
+        for h in range(Hq):
+            s = (k[h // G, :n].astype(np.float64) @ q[t, h * D:(h + 1) * D].astype(np.float64)) / np.sqrt(D)
+            p = np.exp(s - s.max())
+            p /= p.sum()
+            out[t, h] = p @ v[h // G, :n].astype(np.float64)
+    return out.reshape(T, Hq * D)
+
+
+def close(a, b, abs_tol=ABS, rel_tol=REL):
+    d = np.abs(np.asarray(a, np.float64) - np.asarray(b, np.float64))
+    return bool(np.all(d <= abs_tol + rel_tol * np.abs(b)))
+
+
+@pytest.mark.parametrize("T,Hq,Hkv,D,kv", [(1, 8, 2, 128, 1), (5, 8, 2, 128, 37), (3, 12, 2, 256, 100), (9, 16, 4, 128, 64), (2, 64, 8, 128, 500)])
+def test_gqa_modes_agree_with_numpy(T, Hq, Hkv, D, kv):
+    q, k, v, p0 = W.gqa_case(910, T, Hq, Hkv, D, kv)
+    qf, kb, vb = q.astype(np.float32), k.view(np.uint16), v.view(np.uint16)
+    ref = numpy_attention(qf, k, v, T, Hq, Hkv, D, p0)
+    ex = O.attn_exact(qf, kb, vb, T, Hq, Hkv, D, D, kv, p0, 1 / np.sqrt(D))
+    assert np.abs(ex - ref).max() < 1e-12
+    assert np.abs(O.gqa_plain(qf, kb, vb, T, Hq, Hkv, D, kv, p0) - ex).max() < 5e-6
+    assert close(O.gqa_flash_prefill(qf, kb, vb, T, Hq, Hkv, D, kv, p0), ex)
+    assert close(O.attn_tc(qf, kb, vb, T, Hq, Hkv, D, D, kv, p0, 1 / np.sqrt(D), 0), ex)
+    if T <= 8:
+        assert close(O.gqa_flash_decode(qf, kb, vb, T, Hq, Hkv, D, kv, p0), ex)
+
+
+def test_flash_decode_splits_match_the_reference_formula():
+    # kernels/llm/qwen35/silo/attn.cpp:325-331: ~512 work-groups, multiples of 64 keys
+    assert O.flash_split(32768, 8) == 512 and O.flash_splits(32768, 8) == 64
+    assert O.flash_split(262144, 4) == 2048 and O.flash_splits(262144, 4) == 128
+    assert O.flash_split(100, 8) == 64 and O.flash_splits(100, 8) == 2
+    assert O.flash_splits(64, 8) == 1
+
+
+def test_flash_decode_row_does_not_depend_on_its_pass():
+    """A verify row equals the one-row pass at its position, bit for bit (kernels/llm/qwen35/silo/attn.cpp:100-104)."""
+    T, Hq, Hkv, D, kv = 4, 8, 2, 128, 700
+    q, k, v, p0 = W.gqa_case(911, T, Hq, Hkv, D, kv)
+    qf, kb, vb = q.astype(np.float32), k.view(np.uint16), v.view(np.uint16)
+    all_rows = O.gqa_flash_decode(qf, kb, vb, T, Hq, Hkv, D, kv, p0)
+    for t in range(T):
+        one = O.gqa_flash_decode(qf[t:t + 1].copy(), kb, vb, 1, Hq, Hkv, D, kv, p0 + t)
+        assert np.array_equal(one[0], all_rows[t])
+
+
+def test_empty_and_single_key():
+    # one key: the output is that key's value row
+    q, k, v, p0 = W.gqa_case(912, 1, 4, 1, 128, 1)
+    out = O.gqa_flash_prefill(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), 1, 4, 1, 128, 1, 0)
+    assert np.allclose(out.reshape(4, 128), np.broadcast_to(v[0, 0].astype(np.float32), (4, 128)), atol=1e-3)
+
+
+def test_bf16_generic_attention_192_128():
+    """The shape the reference has no kernel for (bf16, 192-wide keys, 128-wide values): tensor-core numerics against fp64."""
+    T, H, kv = 6, 4, 90
+    q = O.from_bf16_bits(W.normal_bf16_bits(913, 0, (T, H * 192)))
+    kb = W.normal_bf16_bits(913, 1, (H, kv, 192))
+    vb = W.normal_bf16_bits(913, 2, (H, kv, 128))
+    sc = 1 / np.sqrt(192.0)
+    ex = O.attn_exact(q, kb, vb, T, H, H, 192, 128, kv, kv - T, sc, kind=1)
+    tc = O.attn_tc(q, kb, vb, T, H, H, 192, 128, kv, kv - T, np.float32(sc), kind=1)
+    # bf16 weights carry 8 mantissa bits: the band is wider than fp16's
+    assert np.abs(tc - ex).max() < 2e-2
+
+
+@pytest.mark.parametrize("T,H,n", [(1, 4, 1), (1, 16, 130), (3, 8, 777)])
+def test_mla_modes(T, H, n):
+    q = W.rng(914, 0).standard_normal((T, H, 576), dtype=np.float32)
+    c = W.normal_f16(914, 1, (n, 576), 0.5).view(np.uint16)
+    sc = 1 / np.sqrt(192.0)
+    ex = O.mla_exact(q, c, T, H, 512, 64, n - T, sc)
+    assert np.abs(O.mla_fused(q, c, T, H, 512, 64, n - T, np.float32(sc)) - ex).max() < 5e-6
+    assert close(O.mla_gemm(q, c, T, H, 512, 64, n - T, np.float32(sc)), ex)
+
+
+def test_mla_glm_kernels():
+    T, H, n = 2, 4, 300
+    qa = W.rng(915, 0).standard_normal((T, H, 512), dtype=np.float32)
+    c32 = (0.5 * W.rng(915, 1).standard_normal((n, 512), dtype=np.float32)).astype(np.float16)
+    sc = np.float32(1 / 16.0)
+    dense = O.mla_attend_f32(qa, c32.astype(np.float32), T, H, 512, n - T, sc)
+    dec = O.mla_dec512(qa, c32.view(np.uint16), T, H, n - T, sc)
+    assert np.abs(dense - dec).max() < 5e-6
+    # q8 rows: 544 bytes, values within half a quantisation step of the fp32 source
+    x = c32.astype(np.float32)
+    rows = O.to_q8row(x)
+    assert rows.shape == (n, 544)
+    scales = rows[:, :32].copy().view(np.float16).astype(np.float32)          # [n, 16]
+    vals = rows[:, 32:].copy().view(np.int8).astype(np.float32).reshape(n, 16, 32)
+    deq = (vals * scales[:, :, None]).reshape(n, 512)
+    assert np.all(np.abs(deq - x) <= 0.5 * np.repeat(scales, 32, axis=1) + 1e-6)
+    dq8 = O.mla_dec512(qa, rows, T, H, n - T, sc, q8=True)
+    assert np.abs(dq8 - dec).max() < 2e-2
+    # a selection: pools 0 and 5 (4 tokens each) plus the incomplete pool
+    sel = np.array([[0, 5], [0, 5]], np.int32)
+    cnt = np.array([2, 2], np.int32)
+    s = O.mla_dec512(qa, c32.view(np.uint16), T, H, n - T, sc, sel=sel, sel_cnt=cnt, K=2)
+    assert np.isfinite(s).all() and np.abs(s - dec).max() > 0
+
+
+def test_merge_with_and_without_sink():
+    rng = np.random.default_rng(3)
+    rows, ns, D = 5, 3, 16
+    part = rng.standard_normal((rows, ns, D + 2)).astype(np.float32)
+    part[:, :, D + 1] = np.abs(part[:, :, D + 1]) + 0.1
+    out = O.merge(part, rows, ns, D, D + 2)
+    m, l, o = part[:, :, D].astype(np.float64), part[:, :, D + 1].astype(np.float64), part[:, :, :D].astype(np.float64)
+    w = np.exp2(m - m.max(1, keepdims=True))
+    ref = (o * w[:, :, None]).sum(1) / (l * w).sum(1)[:, None]
+    assert np.allclose(out, ref, rtol=1e-5, atol=1e-6)
+    sinks = rng.standard_normal(rows).astype(np.float32)
+    outs = O.merge(part, rows, ns, D, D + 2, sinks)
+    mx = np.maximum(m.max(1), sinks * np.log2(np.e))
+    w = np.exp2(m - mx[:, None])
+    ref = (o * w[:, :, None]).sum(1) / ((l * w).sum(1) + np.exp2(sinks * np.log2(np.e) - mx))[:, None]
+    assert np.allclose(outs, ref, rtol=1e-5, atol=1e-6)
+
+
+def test_kv_store_layout():
+    T, Hkv, D, cap, p0 = 3, 2, 128, 10, 4
+    k = W.rng(916, 0).standard_normal((T, Hkv * D), dtype=np.float32)
+    v = W.rng(916, 1).standard_normal((T, Hkv * D), dtype=np.float32)
+    kc = np.zeros((Hkv, cap, D), np.uint16)
+    vc = np.zeros((Hkv, cap, D), np.uint16)
+    O.kv_store(k, v, T, Hkv, D, cap, p0, kc, vc)
+    assert np.array_equal(kc[:, p0:p0 + T].view(np.float16), k.reshape(T, Hkv, D).transpose(1, 0, 2).astype(np.float16))
+    assert not kc[:, :p0].any() and not vc[:, p0 + T:].any()
+
+
+def test_known_answers():
+    g = np.load(GOLD)
+    for name in ("gqa_a", "gqa_b", "gqa_c", "gqa_d"):
+        T, Hq, Hkv, D, cap, p0 = [int(x) for x in g[name + "_meta"]]
+        qf = g[name + "_q"].astype(np.float32)
+        kb, vb = g[name + "_k"].view(np.uint16), g[name + "_v"].view(np.uint16)
+        assert np.allclose(O.gqa_flash_prefill(qf, kb, vb, T, Hq, Hkv, D, cap, p0), g[name + "_flash"], rtol=0, atol=1e-6)
+        assert np.allclose(O.gqa_plain(qf, kb, vb, T, Hq, Hkv, D, cap, p0), g[name + "_plain"], rtol=0, atol=1e-6)
+        if T <= 8:
+            assert np.allclose(O.gqa_flash_decode(qf, kb, vb, T, Hq, Hkv, D, cap, p0), g[name + "_flash_decode"], rtol=0, atol=1e-6)
+    for name in ("mla_a", "mla_b"):
+        T, H, pos0 = [int(x) for x in g[name + "_meta"]]
+        sc = np.float32(1.0 / np.sqrt(192.0))
+        c = g[name + "_c"].view(np.uint16)
+        assert np.allclose(O.mla_fused(g[name + "_q"], c, T, H, 512, 64, pos0, sc), g[name + "_fused"], rtol=0, atol=1e-6)
+        assert np.allclose(O.mla_gemm(g[name + "_q"], c, T, H, 512, 64, pos0, sc), g[name + "_gemm"], rtol=0, atol=1e-6)
