@@ -224,6 +224,15 @@ def run_ours(args):
     bytes_step = B * c2_bytes_per_seq(w)
     value = world * bytes_step / (ms_step * 1e-3) / 1e9
 
+    if args.kernel_only:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "ms_per_step": ms_step,
+                              "kernel_only": True, "clocks": clocks}))
+        if dist:
+            dist.destroy_process_group()
+        gpu.close()
+        return
+
     # ---- end to end through the reference's calls, host buffers in, host buffer out
     hq = HostBuf(gpu, B * Hq * D * 4)
     hk = HostBuf(gpu, B * Hkv * D * 4)
@@ -307,6 +316,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=6.0)
+    ap.add_argument("--kernel-only", action="store_true", help="device-timed leg only (no end-to-end or CPU leg): for profiler runs")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
