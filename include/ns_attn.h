@@ -76,6 +76,20 @@ int64_t ns_b200_gqa_decode_scratch(int64_t B, int64_t T, int64_t Hq, int64_t Hkv
 int ns_b200_gqa_decode(ns_gpu* g, const void* q, int64_t qs, int64_t q_seq, const ns_b200_seq* seqs, int64_t B, int64_t T, int64_t Hq, int64_t Hkv,
                        int64_t D, int64_t max_kv, void* out, float* scratch);
 
+/* No counterpart in the reference. ns_b200_gqa_decode for callers that can neither pass scratch nor tolerate an
+ * allocation: an engine whose device memory was planned to the last byte at load time, or a serving loop that must
+ * not hit the device-wide synchronisation a cudaMalloc brings. The split partials go to an array built into the
+ * library (NS_B200_STATIC_SCRATCH_FLOATS floats = 16 MiB, resident on every GPU the library is used on until the
+ * process exits). The call allocates nothing, on the device or through any library. Arguments as ns_b200_gqa_decode;
+ * -1 with a message when B*T*Hq*splits(max_kv)*(D+2) floats exceed the array.
+ * The first call on each device looks up the array's device address and queues a one-thread set-up kernel: make that
+ * first call before starting any stream capture. All calls share the one array, which keeps whatever the last call
+ * left in it (nothing in it needs to start at zero: each call writes every partial before reading it); two calls
+ * whose kernels overlap on the GPU - different streams or different ns_gpu handles of one device - race on it. */
+#define NS_B200_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024)
+int ns_b200_gqa_decode_static(ns_gpu* g, const void* q, int64_t qs, int64_t q_seq, const ns_b200_seq* seqs, int64_t B, int64_t T, int64_t Hq,
+                              int64_t Hkv, int64_t D, int64_t max_kv, void* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -70,6 +70,7 @@ ATTN = {
     "ns_nhs_attn_decode": (C.c_int, _ATTN_ARGS + [vp]),
     "ns_b200_gqa_decode_scratch": (i64, [i64, i64, i64, i64, i64, i64]),
     "ns_b200_gqa_decode": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, i64, vp, vp]),
+    "ns_b200_gqa_decode_static": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, i64, vp]),
 }
 
 

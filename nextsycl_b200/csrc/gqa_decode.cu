@@ -409,3 +409,67 @@ int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where) {
     }
     return ns_fail(std::string(where) + ": heads of 128 or 256");
 }
+
+// ---- decode without caller scratch -----------------------------------------------------------------------------------
+// Some callers cannot hand the library a scratch buffer and must not cause an allocation either: an engine whose
+// memory plan is fixed when the model is loaded (every byte of the GPU already assigned to weights and caches, so a
+// later cudaMalloc may fail, and in any case synchronises the device in the middle of serving), or a decode loop that
+// runs with its arena frozen. For them the split partials live in this fixed array instead. It costs
+// NS_B200_STATIC_SCRATCH_FLOATS * 4 bytes on every GPU the library is used on, for the life of the process.
+namespace {
+static __device__ __align__(256) float g_static_scratch[NS_B200_STATIC_SCRATCH_FLOATS];
+
+// touches the array from device code once a device (also keeps the symbol alive in the device image)
+__global__ void static_scratch_setup() { g_static_scratch[0] = 0.f; }
+
+std::mutex g_static_mu;
+float* g_static_ptr[64] = {};   // per device ordinal: the array's DEVICE address (the host-side name is only a handle)
+
+// the device address of g_static_scratch on g's device, looked up once per device with that device current
+int static_scratch(ns_gpu* g, float** out, const char* where) {
+    if (g->dev < 0 || g->dev >= 64) return ns_fail(std::string(where) + ": device ordinal out of range");
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_ptr[g->dev]) {
+        float* p = nullptr;
+        NS_CUDA(cudaGetSymbolAddress((void**) &p, g_static_scratch), where);
+        if (!p) return ns_fail(std::string(where) + ": the static scratch has no device address");
+        static_scratch_setup<<<1, 1, 0, g->compute>>>();
+        if (ns_launched(where)) return -1;
+        g_static_ptr[g->dev] = p;
+    }
+    *out = g_static_ptr[g->dev];
+    return 0;
+}
+}  // namespace
+
+extern "C" int ns_b200_gqa_decode_static(ns_gpu* g, const void* q, int64_t qs, int64_t q_seq, const ns_b200_seq* seqs, int64_t B, int64_t T,
+                                         int64_t Hq, int64_t Hkv, int64_t D, int64_t max_kv, void* out) {
+    NS_TRY
+    const char* name = "ns_b200_gqa_decode_static";
+    if (ns_enter(g, name)) return -1;
+    if (B < 1) return 0;
+    if (T < 1 || T > 8 || (D != 128 && D != 256) || Hkv < 1 || Hq < 1 || Hq % Hkv != 0 || Hq / Hkv > 16)
+        return ns_fail(std::string(name) + ": 1..8 rows, heads of 128 or 256, 1..16 query heads a key head");
+    if (max_kv < T || max_kv >= ((int64_t) 1 << 31)) return ns_fail(std::string(name) + ": max_kv between T and 2^31");
+    if (qs % 8 != 0 || q_seq % 8 != 0 || ((uintptr_t) q & 15) != 0) return ns_fail(std::string(name) + ": query rows 16-byte aligned");
+    if (!q || !seqs || !out) return ns_fail(std::string(name) + ": a null buffer");
+    const int64_t ns = ns_dec_splits(max_kv, Hkv);
+    const int64_t need = ns > 1 ? B * T * Hq * ns * (D + 2) : 0;
+    if (need > (int64_t) NS_B200_STATIC_SCRATCH_FLOATS)
+        return ns_fail(std::string(name) + ": this batch needs " + std::to_string(need) + " floats of split partials, the built-in scratch holds " +
+                       std::to_string((int64_t) NS_B200_STATIC_SCRATCH_FLOATS) + "; use ns_b200_gqa_decode with caller scratch");
+    float* part = nullptr;
+    if (static_scratch(g, &part, name)) return -1;
+    GqaDecodeArgs a{};
+    a.q = q;
+    a.qs = qs;
+    a.q_seq = q_seq;
+    a.seqs = seqs;
+    a.out = out;
+    a.part = part;
+    a.B = B, a.T = T, a.Hq = Hq, a.Hkv = Hkv, a.D = D;
+    a.ns_max = ns;
+    a.q_f32 = 0, a.out_f32 = 0;
+    return ns_launch_gqa_decode(g, a, name);
+    NS_CATCH("ns_b200_gqa_decode_static")
+}
