@@ -38,7 +38,16 @@ int64_t ns_q35_attn_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64
 int ns_q35_attn(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t cap,
                 int64_t p0, float* out, float* scratch);
 
-/* kernels/llm/qwen35/silo/silo.h:43-59 - decode rows (1..8), each at its own position p0+t; a row's result is the same
+/* kernels/llm/qwen35/silo/silo.h:43-48 - prompt rows (more than 8) on the tensor cores: out [T][Hq*D] = causal
+ * softmax(q k^T / sqrt(D)) v for rows at positions p0.. against the fp16 caches. `_supported` is widened from the
+ * reference's (D 256, 6 query heads a key head) to D 128 and 256 with any whole number of query heads a key head. */
+int ns_q35_attn_prompt_supported(int64_t T, int64_t Hq, int64_t Hkv, int64_t D);
+int ns_q35_attn_prompt(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                       int64_t cap, int64_t p0, float* out);
+int ns_q35_attn_prompt_kv(ns_gpu* g, int kt, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv,
+                          int64_t D, int64_t cap, int64_t p0, float* out);
+
+/* kernels/llm/qwen35/silo/silo.h:49-59 - decode rows (1..8), each at its own position p0+t; a row's result is the same
  * whatever rows share its pass. `_supported` is widened from the reference's (D 256, 6 heads a key head) to D 128 / 256
  * with 1..16 query heads a key head. kt: cache form, 0 = fp16 (the only one this build takes). */
 int ns_q35_attn_decode_supported(int64_t T, int64_t Hq, int64_t Hkv, int64_t D);
@@ -52,6 +61,9 @@ int ns_q35_attn_decode_kv(ns_gpu* g, int kt, const float* q, int64_t qs, const v
 int64_t ns_nh_attn_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0);
 int ns_nh_attn(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t cap,
                int64_t p0, float* out, float* scratch);
+int ns_nhs_attn_prompt_supported(int64_t T, int64_t Hq, int64_t Hkv, int64_t D);
+int ns_nhs_attn_prompt(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                       int64_t cap, int64_t p0, float* out);
 int ns_nhs_attn_decode_supported(int64_t T, int64_t Hq, int64_t Hkv, int64_t D);
 int64_t ns_nhs_attn_decode_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0);
 int ns_nhs_attn_decode(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
@@ -75,6 +87,19 @@ typedef struct ns_b200_seq {
 int64_t ns_b200_gqa_decode_scratch(int64_t B, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t max_kv);
 int ns_b200_gqa_decode(ns_gpu* g, const void* q, int64_t qs, int64_t q_seq, const ns_b200_seq* seqs, int64_t B, int64_t T, int64_t Hq, int64_t Hkv,
                        int64_t D, int64_t max_kv, void* out, float* scratch);
+
+/* Causal GQA prefill with 16-bit rows in and out (replaces ns_q35_attn_prompt_kv plus the fp32 staging around it,
+ * llm/qwen35/src/engine.rs:1586-1593). dtype 0 fp16, 1 bf16: q [T][Hq*D] (qs elements between rows), caches
+ * [Hkv][cap][D] and out [T][Hq*D] all of that type; D 128 (both types) or 256 (fp16); row t sees keys 0 .. p0+t. */
+int ns_b200_gqa_prefill(ns_gpu* g, int dtype, const void* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                        int64_t cap, int64_t p0, void* out);
+
+/* Non-absorbed MLA prefill in bf16 (no counterpart in the reference, which always runs the absorbed form): q
+ * [T][H][192] (128 nope + 64 rope, rotation applied), k [p0+T][H][192], v [p0+T][H][128], out [T][H][128] dense; the
+ * token strides q_tok, k_tok, v_tok in elements let a rank pass its slice of heads of a larger tensor. Causal over
+ * the p0 cached tokens plus the chunk; `scale` is the softmax scale (1/sqrt(192)). */
+int ns_b200_mla_prefill(ns_gpu* g, const void* q, int64_t q_tok, const void* k, int64_t k_tok, const void* v, int64_t v_tok, int64_t T, int64_t H,
+                        int64_t p0, float scale, void* out);
 
 /* No counterpart in the reference. ns_b200_gqa_decode for callers that can neither pass scratch nor tolerate an
  * allocation: an engine whose device memory was planned to the last byte at load time, or a serving loop that must

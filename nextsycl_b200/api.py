@@ -68,6 +68,13 @@ ATTN = {
     "ns_nhs_attn_decode_supported": (C.c_int, [i64, i64, i64, i64]),
     "ns_nhs_attn_decode_scratch": (i64, _SCRATCH_ARGS),
     "ns_nhs_attn_decode": (C.c_int, _ATTN_ARGS + [vp]),
+    "ns_q35_attn_prompt_supported": (C.c_int, [i64, i64, i64, i64]),
+    "ns_q35_attn_prompt": (C.c_int, _ATTN_ARGS),
+    "ns_q35_attn_prompt_kv": (C.c_int, [vp, C.c_int] + _ATTN_ARGS[1:]),
+    "ns_nhs_attn_prompt_supported": (C.c_int, [i64, i64, i64, i64]),
+    "ns_nhs_attn_prompt": (C.c_int, _ATTN_ARGS),
+    "ns_b200_gqa_prefill": (C.c_int, [vp, C.c_int, vp, i64, vp, vp, i64, i64, i64, i64, i64, i64, vp]),
+    "ns_b200_mla_prefill": (C.c_int, [vp, vp, i64, vp, i64, vp, i64, i64, i64, i64, C.c_float, vp]),
     "ns_b200_gqa_decode_scratch": (i64, [i64, i64, i64, i64, i64, i64]),
     "ns_b200_gqa_decode": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, i64, vp, vp]),
     "ns_b200_gqa_decode_static": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, i64, vp]),

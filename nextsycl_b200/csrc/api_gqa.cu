@@ -3,6 +3,9 @@
 
 #include <algorithm>
 
+int ns_prefill_f32(ns_gpu* g, const char* name, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv,
+                   int64_t D, int64_t cap, int64_t p0, float* out);
+
 namespace {
 
 bool shape_ok(int64_t Hq, int64_t Hkv, int64_t D) {
@@ -46,21 +49,16 @@ int64_t decode_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0
     return ns > 1 ? T * Hq * ns * (D + 2) : 0;
 }
 
-// any number of rows through the decode kernel, 8 at a time (each block of rows its own positions)
+// any number of rows: up to 8 through the decode kernel, more through the tensor-core prompt kernel (api_prefill.cu)
 int64_t rows_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0) {
-    int64_t s = 0;
-    for (int64_t r0 = 0; r0 < T; r0 += 8) s = std::max(s, decode_scratch(std::min<int64_t>(8, T - r0), Hq, Hkv, D, p0 + r0));
-    return s;
+    return T <= 8 ? decode_scratch(T, Hq, Hkv, D, p0) : 0;
 }
 int rows_f32(ns_gpu* g, const char* name, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
              int64_t cap, int64_t p0, float* out, float* scratch) {
     if (T <= 0) return 0;
     if (p0 + T > cap) return ns_fail(std::string(name) + ": past the cache's capacity");
-    for (int64_t r0 = 0; r0 < T; r0 += 8) {
-        const int64_t tr = std::min<int64_t>(8, T - r0);
-        if (decode_f32(g, name, q + r0 * qs, qs, kc, vc, tr, Hq, Hkv, D, cap, p0 + r0, out + r0 * Hq * D, scratch)) return -1;
-    }
-    return 0;
+    if (T <= 8) return decode_f32(g, name, q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out, scratch);
+    return ns_prefill_f32(g, name, q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out);
 }
 
 }  // namespace

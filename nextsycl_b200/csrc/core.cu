@@ -112,6 +112,11 @@ int ns_gpu_open(int index, ns_gpu** out) {
     cudaError_t e = cudaStreamCreateWithFlags(&g->compute, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&g->lane[0], cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&g->lane[1], cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaHostAlloc((void**) &g->status_host, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable);
+    if (e == cudaSuccess) {
+        *g->status_host = 0;
+        e = cudaHostGetDevicePointer((void**) &g->status_dev, g->status_host, 0);
+    }
     if (e != cudaSuccess) {
         delete g;
         return ns_cuda(e, "ns_gpu_open");
@@ -131,6 +136,7 @@ void ns_gpu_close(ns_gpu* g) {
     for (cudaEvent_t e : g->ring)
         if (e) cudaEventDestroy(e);
     if (g->kept) cudaFree(g->kept);
+    if (g->status_host) cudaFreeHost(g->status_host);
     cudaStreamDestroy(g->compute);
     cudaStreamDestroy(g->lane[0]);
     cudaStreamDestroy(g->lane[1]);
@@ -284,6 +290,11 @@ int ns_sync(ns_gpu* g) {
     if (ns_enter(g, "ns_sync")) return -1;
     NS_CUDA(cudaStreamSynchronize(g->compute), "ns_sync");
     NS_CUDA(cudaGetLastError(), "ns_sync");
+    if (g->status_host && *(volatile int*) g->status_host != 0) {
+        const int code = *(volatile int*) g->status_host;
+        *(volatile int*) g->status_host = 0;
+        return ns_fail("ns_sync: a kernel gave up a bounded wait (code " + std::to_string(code) + "); its output is not valid");
+    }
     return 0;
 }
 

@@ -1,0 +1,396 @@
+// flash_prefill.cu: causal flash-attention prefill on the Blackwell tensor path (tcgen05.mma, accumulators in tensor
+// memory, K/V tiles staged by TMA).
+//
+// What it computes is the reference's prompt kernel attn_flash (kernels/llm/qwen35/silo/attn.cpp:105-313; D=128 form
+// kernels/llm/nemotronh/silo/attn.cpp): out[t,h,:] = softmax_{j <= p0+t}(q k_j * scale) v_j with 16-bit operands, exp2,
+// weights rounded to the operand type before they meet V, fp32 sums. Also instantiated for the shape the reference has
+// no kernel for: bf16 with 192-wide keys and 128-wide values (non-absorbed MLA prefill).
+//
+// How: a CTA takes 128 query rows of one head. Warp 4 issues TMA loads (Q once; K and V tiles of BN keys through a
+// ring of stages, 128-byte swizzle). Warp 5 issues the MMAs: S = Q K^T into one of two S buffers in tensor memory, then
+// O += P V with P read from tensor memory (it overlays the S buffer it came from) and V as an MN-major shared-memory
+// operand. Warps 0-3 are the softmax: thread r owns row r (= tensor-memory lane r), so row max and sum need no
+// shuffles; it reads its S row, writes P back as packed 16-bit pairs, and rescales its O row only when the running
+// maximum grew by more than 2^8 (the final 1/l uses the same reference maximum, so the result is unchanged).
+// Every mbarrier wait is bounded; on a timeout the CTA records a status code and runs to its teardown.
+#include "kernels.cuh"
+#include "tc05.cuh"
+
+#include <cuda.h>
+
+namespace {
+using namespace tc05;
+
+constexpr int BM = 128;           // query rows a CTA
+constexpr int SOFTMAX_THREADS = 128;
+constexpr int THREADS = 192;      // 4 softmax warps, 1 TMA warp, 1 MMA warp
+constexpr float RESCALE_LOG2 = 8.0f;
+
+struct Params {
+    void* out;             // [T][Hq*DV] fp32, fp16 or bf16
+    int* status;           // a wait that gave up records its code here
+    int T, Hq, G;
+    int out_kind;          // 0 fp32, 1 same 16-bit type as the operands
+    int64_t p0, kv_len;    // row t sees keys 0 .. p0+t; kv_len = p0 + T
+    float scale_log2;      // multiplies S before exp2 (1 when the queries are pre-scaled)
+};
+
+template <int DQK, int DV, int BN, int NSTAGE>
+struct Smem {
+    static constexpr int Q_BYTES = BM * DQK * 2;
+    static constexpr int K_BYTES = BN * DQK * 2;
+    static constexpr int V_BYTES = BN * DV * 2;
+    static constexpr int STAGE = K_BYTES + V_BYTES;
+    static constexpr int BARS = 1024;   // mbarriers, the tensor-memory base slot, the abort flag
+    static constexpr int TOTAL = 1024 /* alignment slack */ + Q_BYTES + NSTAGE * STAGE + BARS;
+};
+
+template <int DQK, int DV, int BN, int NSTAGE, int BF16>
+__global__ void __launch_bounds__(THREADS, 1)
+flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                     const Params p) {
+    using L = Smem<DQK, DV, BN, NSTAGE>;
+    constexpr int S_COLS = BN;                   // fp32 columns of one S buffer
+    constexpr int O_COL = 2 * S_COLS;            // O after the two S buffers
+    constexpr int TMEM_COLS = (O_COL + DV) <= 256 ? 256 : 512;
+    static_assert(O_COL + DV <= 512, "tensor memory holds 512 columns");
+    static_assert(DQK % 64 == 0 && DV % 64 == 0 && BN % 32 == 0, "tiles in 64-element swizzle chunks");
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);   // 128-byte swizzle wants 1024-byte tile bases
+    uint8_t* q_s = smem;
+    uint8_t* kv_s = smem + L::Q_BYTES;
+    uint64_t* bars = (uint64_t*) (kv_s + NSTAGE * L::STAGE);
+    // barrier map
+    uint64_t* q_full = bars + 0;
+    uint64_t* k_full = bars + 1;                 // [NSTAGE]
+    uint64_t* v_full = k_full + NSTAGE;          // [NSTAGE]
+    uint64_t* k_empty = v_full + NSTAGE;         // [NSTAGE]
+    uint64_t* v_empty = k_empty + NSTAGE;        // [NSTAGE]
+    uint64_t* s_full = v_empty + NSTAGE;         // [2]
+    uint64_t* p_full = s_full + 2;               // [2]
+    uint64_t* pv_done = p_full + 2;              // [1]
+    uint32_t* tmem_slot = (uint32_t*) (pv_done + 1);
+    volatile int* abort_flag = (volatile int*) (tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // the heaviest row blocks (most keys) first
+    const int mblk = (int) gridDim.x - 1 - (int) blockIdx.x;
+    const int h = blockIdx.y, hk = h / p.G;
+    const int r0 = mblk * BM;
+    // keys this row block sees: up to the position of its last row
+    const int64_t last_pos = p.p0 + min((int64_t) r0 + BM, (int64_t) p.T) - 1;
+    const int ntiles = (int) (last_pos / BN) + 1;
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        mbar_init(smem_u32(q_full), 1);
+        for (int s = 0; s < NSTAGE; ++s) {
+            mbar_init(smem_u32(k_full + s), 1);
+            mbar_init(smem_u32(v_full + s), 1);
+            mbar_init(smem_u32(k_empty + s), 1);
+            mbar_init(smem_u32(v_empty + s), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(s_full + s), 1);
+            mbar_init(smem_u32(p_full + s), SOFTMAX_THREADS);
+        }
+        mbar_init(smem_u32(pv_done), 1);
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 4) {
+        // ================= TMA producer =================
+        if (elect_one()) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k);
+            tma_prefetch_desc(&tm_v);
+            mbar_expect_tx(smem_u32(q_full), L::Q_BYTES);
+            for (int c = 0; c < DQK / 64; ++c) tma_load_3d(smem_u32(q_s + c * (BM * 128)), &tm_q, c * 64, h, r0, smem_u32(q_full));
+            bool ok = true;
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int s = j % NSTAGE;
+                const uint32_t ph = (uint32_t) (j / NSTAGE) & 1;
+                uint8_t* ks = kv_s + s * L::STAGE;
+                uint8_t* vs = ks + L::K_BYTES;
+                if (j >= NSTAGE) ok = mbar_wait(smem_u32(k_empty + s), ph ^ 1, abort_flag, p.status, 101);
+                if (!ok) break;
+                mbar_expect_tx(smem_u32(k_full + s), L::K_BYTES);
+                for (int c = 0; c < DQK / 64; ++c) tma_load_3d(smem_u32(ks + c * (BN * 128)), &tm_k, c * 64, j * BN, hk, smem_u32(k_full + s));
+                if (j >= NSTAGE) ok = mbar_wait(smem_u32(v_empty + s), ph ^ 1, abort_flag, p.status, 102);
+                if (!ok) break;
+                mbar_expect_tx(smem_u32(v_full + s), L::V_BYTES);
+                for (int c = 0; c < DV / 64; ++c) tma_load_3d(smem_u32(vs + c * (BN * 128)), &tm_v, c * 64, j * BN, hk, smem_u32(v_full + s));
+            }
+        }
+    } else if (warp == 5) {
+        // ================= MMA issuer =================
+        if (elect_one()) {
+            constexpr uint32_t idesc_qk = idesc_f16(BM, BN, BF16, 0, 0);
+            constexpr uint32_t idesc_pv = idesc_f16(BM, DV, BF16, 0, 1);
+            bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, p.status, 201);
+            auto issue_qk = [&](int j) {
+                const int s = j % NSTAGE;
+                const uint32_t kb = smem_u32(kv_s + s * L::STAGE), qb = smem_u32(q_s);
+                const uint32_t d = tmem + (uint32_t) ((j & 1) * S_COLS);
+#pragma unroll
+                for (int k = 0; k < DQK / 16; ++k) {
+                    const uint64_t ad = smem_desc_sw128(qb + (k / 4) * (BM * 128) + (k % 4) * 32, 16, 1024);
+                    const uint64_t bd = smem_desc_sw128(kb + (k / 4) * (BN * 128) + (k % 4) * 32, 16, 1024);
+                    mma_ss(d, ad, bd, idesc_qk, k > 0);
+                }
+                mma_commit(smem_u32(k_empty + s));       // the K stage is free once these MMAs have read it
+                mma_commit(smem_u32(s_full + (j & 1)));  // and S is ready for the softmax
+            };
+            if (ok) ok = mbar_wait(smem_u32(k_full + 0), 0, abort_flag, p.status, 202);
+            if (ok) {
+                fence_after_sync();
+                issue_qk(0);
+            }
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int s = j % NSTAGE;
+                const uint32_t ph = (uint32_t) (j / NSTAGE) & 1;
+                if (j + 1 < ntiles) {
+                    // S(j+1) goes into the buffer P(j-1) lived in: the tensor pipe runs this thread's MMAs in order,
+                    // so it starts after P(j-1) V(j-1); the softmax's reads of S(j-1) ended before it published P(j-1)
+                    ok = mbar_wait(smem_u32(k_full + (j + 1) % NSTAGE), (uint32_t) ((j + 1) / NSTAGE) & 1, abort_flag, p.status, 203);
+                    if (!ok) break;
+                    fence_after_sync();
+                    issue_qk(j + 1);
+                }
+                ok = mbar_wait(smem_u32(v_full + s), ph, abort_flag, p.status, 204);
+                if (ok) ok = mbar_wait(smem_u32(p_full + (j & 1)), (uint32_t) (j >> 1) & 1, abort_flag, p.status, 205);
+                if (!ok) break;
+                fence_after_sync();
+                const uint32_t vb = smem_u32(kv_s + s * L::STAGE + L::K_BYTES);
+                const uint32_t pa = tmem + (uint32_t) ((j & 1) * S_COLS);
+                const uint32_t od = tmem + (uint32_t) O_COL;
+#pragma unroll
+                for (int k = 0; k < BN / 16; ++k) {
+                    // V tile: DV/64 chunks of [BN keys][64] 128 bytes a key; 16 keys a step
+                    const uint64_t bd = smem_desc_sw128(vb + k * (16 * 128), BN * 128, 1024);
+                    mma_ts(od, pa + (uint32_t) (k * 8), bd, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                }
+                mma_commit(smem_u32(v_empty + s));
+                mma_commit(smem_u32(pv_done));
+            }
+        }
+    } else {
+        // ================= softmax: thread r owns query row r0 + r =================
+        const int r = tid;                                  // 0..127 = tensor-memory lane
+        const uint32_t lane_base = (uint32_t) (warp * 32) << 16;
+        const int64_t row_pos = p.p0 + r0 + r;              // last key this row sees
+        const bool row_live = r0 + r < p.T;
+        float m_ref = -INFINITY, l = 0.f;                   // m_ref in units of S * scale_log2
+        bool ok = true;
+        for (int j = 0; j < ntiles; ++j) {
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(s_full + (j & 1)), (uint32_t) (j >> 1) & 1, abort_flag, p.status, 301));
+            if (!ok) break;
+            fence_after_sync();
+            const uint32_t s_addr = tmem + lane_base + (uint32_t) ((j & 1) * S_COLS);
+            float s[BN];
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(s_addr + c * 32, v);
+                tmem_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(v[e]);
+            }
+            const int64_t k0 = (int64_t) j * BN;
+            // mask: keys past the row's position (the causal edge; it also covers keys past kv_len)
+            if (k0 + BN - 1 > row_pos) {
+#pragma unroll
+                for (int e = 0; e < BN; ++e)
+                    if (k0 + e > row_pos) s[e] = -INFINITY;
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < BN; ++e) mx = fmaxf(mx, s[e]);
+            mx *= p.scale_log2;
+            // lazy rescale: move the reference maximum only when it would grow by more than 2^8
+            float corr = 1.0f;
+            bool need = false;
+            if (j == 0) {
+                m_ref = mx;
+            } else if (mx > m_ref + RESCALE_LOG2) {
+                corr = ex2(m_ref - mx);
+                m_ref = mx;
+                need = true;
+            }
+            if (__any_sync(0xffffffffu, need)) {
+                // O must be at rest: P(j-1) V(j-1) done
+                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(pv_done), (uint32_t) (j - 1) & 1, abort_flag, p.status, 302));
+                if (!ok) break;
+                fence_after_sync();
+                const uint32_t o_addr = tmem + lane_base + (uint32_t) O_COL;
+#pragma unroll
+                for (int c = 0; c < DV / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(o_addr + c * 32, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * corr);
+                    tmem_st32(o_addr + c * 32, v);
+                }
+                tmem_wait_st();
+                l *= corr;
+            }
+            // P = exp2(S * scale - m_ref), the sum from the unrounded weights, P rounded to the operand type
+            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+            float sum = 0.f;
+            const uint32_t p_addr = s_addr;   // P overlays the first BN/2 columns of its S buffer
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t w[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const float a = ex2(fmaf(s[c * 32 + 2 * e], p.scale_log2, neg_m));
+                    const float b = ex2(fmaf(s[c * 32 + 2 * e + 1], p.scale_log2, neg_m));
+                    sum += a + b;
+                    if (BF16) {
+                        __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+                        w[e] = *reinterpret_cast<uint32_t*>(&t);
+                    } else {
+                        __half2 t = __floats2half2_rn(a, b);
+                        w[e] = *reinterpret_cast<uint32_t*>(&t);
+                    }
+                }
+                tmem_st16(p_addr + c * 16, w);
+            }
+            l += sum;
+            tmem_wait_st();
+            fence_before_sync();
+            mbar_arrive(smem_u32(p_full + (j & 1)));
+        }
+        // ---- epilogue: O / l to global memory
+        if (ok) ok = mbar_wait(smem_u32(pv_done), (uint32_t) (ntiles - 1) & 1, abort_flag, p.status, 303);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            fence_after_sync();
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const uint32_t o_addr = tmem + lane_base + (uint32_t) O_COL;
+            const int64_t row = (int64_t) (r0 + r) * p.Hq + h;
+#pragma unroll
+            for (int c = 0; c < DV / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(o_addr + c * 32, v);
+                tmem_wait_ld();
+                if (row_live) {
+                    if (p.out_kind == 0) {
+                        float4* dst = reinterpret_cast<float4*>((float*) p.out + row * DV + c * 32);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            dst[e] = make_float4(__uint_as_float(v[4 * e]) * inv, __uint_as_float(v[4 * e + 1]) * inv, __uint_as_float(v[4 * e + 2]) * inv,
+                                                 __uint_as_float(v[4 * e + 3]) * inv);
+                    } else {
+                        uint32_t w[16];
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) {
+                            const float a = __uint_as_float(v[2 * e]) * inv, b = __uint_as_float(v[2 * e + 1]) * inv;
+                            if (BF16) {
+                                __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+                                w[e] = *reinterpret_cast<uint32_t*>(&t);
+                            } else {
+                                __half2 t = __floats2half2_rn(a, b);
+                                w[e] = *reinterpret_cast<uint32_t*>(&t);
+                            }
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>((uint16_t*) p.out + row * DV + c * 32);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) dst[e] = make_uint4(w[4 * e], w[4 * e + 1], w[4 * e + 2], w[4 * e + 3]);
+                    }
+                }
+            }
+        }
+    }
+    // ---- teardown: every role is out of its loops (all waits are bounded); tensor memory goes back
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 5) {
+        fence_after_sync();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+// ---- host side: tensor maps and launch --------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled) p;
+    }
+    return fn;
+}
+
+// rank-3 map over 16-bit elements: dims (inner, mid, outer) with byte strides for mid and outer; box (64, box_mid, box_outer)
+int make_map(CUtensorMap* m, const void* base, int bf16, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes,
+             uint32_t box1, uint32_t box2, const char* where) {
+    EncodeTiled fn = encode_fn();
+    if (!fn) return ns_fail(std::string(where) + ": cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+    cuuint32_t box[3] = {64, box1, box2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ns_fail(std::string(where) + ": tensor map rejected (code " + std::to_string((int) r) + ")");
+    return 0;
+}
+
+template <int DQK, int DV, int BN, int NSTAGE, int BF16>
+int launch(ns_gpu* g, const FlashPrefillArgs& a, const char* where) {
+    using L = Smem<DQK, DV, BN, NSTAGE>;
+    static_assert(L::TOTAL <= 232448, "shared memory of one CTA");
+    CUtensorMap tq, tk, tv;
+    // Q [T][Hq][DQK]: a box = 128 rows of one head, 64 features
+    if (make_map(&tq, a.q, BF16, DQK, (uint64_t) a.Hq, (uint64_t) a.T, (uint64_t) DQK * 2, (uint64_t) a.q_row * 2, 1, BM, where)) return -1;
+    // K, V: (feature, key, head); keys past kv_len read as zeros (whatever the buffer holds there is never loaded)
+    if (make_map(&tk, a.k, BF16, DQK, (uint64_t) a.kv_len, (uint64_t) a.Hkv, (uint64_t) a.k_key * 2, (uint64_t) a.k_head * 2, BN, 1, where)) return -1;
+    if (make_map(&tv, a.v, BF16, DV, (uint64_t) a.kv_len, (uint64_t) a.Hkv, (uint64_t) a.v_key * 2, (uint64_t) a.v_head * 2, BN, 1, where)) return -1;
+    Params p;
+    p.out = a.out;
+    p.status = a.status;
+    p.T = (int) a.T;
+    p.Hq = (int) a.Hq;
+    p.G = (int) (a.Hq / a.Hkv);
+    p.out_kind = a.out_f32 ? 0 : 1;
+    p.p0 = a.p0;
+    p.kv_len = a.kv_len;
+    p.scale_log2 = a.scale_log2;
+    auto kern = flash_prefill_kernel<DQK, DV, BN, NSTAGE, BF16>;
+    static bool set[64] = {};
+    if (!set[g->dev & 63]) {
+        NS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL), where);
+        set[g->dev & 63] = true;
+    }
+    dim3 grid((unsigned) ((a.T + BM - 1) / BM), (unsigned) a.Hq, 1);
+    kern<<<grid, THREADS, L::TOTAL, g->compute>>>(tq, tk, tv, p);
+    return ns_launched(where);
+}
+
+}  // namespace
+
+int ns_launch_flash_prefill(ns_gpu* g, const FlashPrefillArgs& a, const char* where) {
+    if (a.T <= 0) return 0;
+    if (a.Dqk == 128 && a.Dv == 128 && !a.bf16) return launch<128, 128, 128, 2, 0>(g, a, where);
+    if (a.Dqk == 128 && a.Dv == 128 && a.bf16) return launch<128, 128, 128, 2, 1>(g, a, where);
+    if (a.Dqk == 192 && a.Dv == 128 && a.bf16) return launch<192, 128, 128, 2, 1>(g, a, where);
+    if (a.Dqk == 192 && a.Dv == 128 && !a.bf16) return launch<192, 128, 128, 2, 0>(g, a, where);
+    if (a.Dqk == 256 && a.Dv == 256 && !a.bf16) return launch<256, 256, 64, 2, 0>(g, a, where);
+    return ns_fail(std::string(where) + ": head widths 128/128, 192/128 or 256/256");
+}

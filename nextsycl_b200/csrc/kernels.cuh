@@ -36,3 +36,23 @@ int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where);
 // ---- cache writers (kv_store.cu) ------------------------------------------------------------------------------------
 int ns_launch_kv_store(ns_gpu* g, const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hkv, int64_t D, int64_t cap, int64_t p0,
                        void* kc, void* vc);
+
+// fp32 rows -> 16-bit rows scaled by `scale` (one rounding, as the reference stages its queries: silo/attn.cpp:147)
+int ns_launch_scale_to_f16(ns_gpu* g, const float* src, int64_t src_row, void* dst, int64_t dst_row, int64_t rows, int64_t cols, float scale);
+
+// ---- flash prefill on tcgen05 (flash_prefill.cu) -------------------------------------------------------------------------
+struct FlashPrefillArgs {
+    const void* q;          // [T] rows of Hq*Dqk 16-bit elements, q_row elements apart
+    int64_t q_row;
+    const void* k;          // element (key, head, d) at key*k_key + head*k_head + d
+    int64_t k_key, k_head;
+    const void* v;
+    int64_t v_key, v_head;
+    void* out;              // [T][Hq*Dv] dense; fp32 when out_f32, else the operands' type
+    int* status;            // device-visible status word
+    int64_t T, Hq, Hkv, Dqk, Dv;
+    int64_t p0, kv_len;     // kv_len = p0 + T keys exist
+    float scale_log2;       // softmax scale times log2(e); 1 when q is pre-scaled
+    int bf16, out_f32;
+};
+int ns_launch_flash_prefill(ns_gpu* g, const FlashPrefillArgs& a, const char* where);

@@ -31,3 +31,25 @@ int ns_launch_kv_store(ns_gpu* g, const float* k, int64_t ks, const float* v, in
     kv_store_kernel<<<(unsigned) (blocks > 4096 ? 4096 : blocks), threads, 0, g->compute>>>(k, ks, v, vs, T, Hkv, D, cap, p0, (__half*) kc, (__half*) vc);
     return ns_launched("ns_q35_kv_store");
 }
+
+namespace {
+__global__ void scale_to_f16_kernel(const float* __restrict__ src, int64_t src_row, __half* __restrict__ dst, int64_t dst_row, int64_t rows, int64_t cols,
+                                    float scale) {
+    const int64_t n8 = rows * (cols / 8);
+    for (int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t) gridDim.x * blockDim.x) {
+        const int64_t r = i / (cols / 8), c = (i % (cols / 8)) * 8;
+        const float4 a = *reinterpret_cast<const float4*>(src + r * src_row + c);
+        const float4 b = *reinterpret_cast<const float4*>(src + r * src_row + c + 4);
+        __half2 o[4] = {__floats2half2_rn(a.x * scale, a.y * scale), __floats2half2_rn(a.z * scale, a.w * scale),
+                        __floats2half2_rn(b.x * scale, b.y * scale), __floats2half2_rn(b.z * scale, b.w * scale)};
+        *reinterpret_cast<uint4*>(dst + r * dst_row + c) = *reinterpret_cast<uint4*>(o);
+    }
+}
+}  // namespace
+
+int ns_launch_scale_to_f16(ns_gpu* g, const float* src, int64_t src_row, void* dst, int64_t dst_row, int64_t rows, int64_t cols, float scale) {
+    const int64_t n8 = rows * (cols / 8);
+    const int64_t blocks = (n8 + 255) / 256;
+    scale_to_f16_kernel<<<(unsigned) (blocks > 8192 ? 8192 : blocks), 256, 0, g->compute>>>(src, src_row, (__half*) dst, dst_row, rows, cols, scale);
+    return ns_launched("scale_to_f16");
+}

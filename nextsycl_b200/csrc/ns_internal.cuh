@@ -24,6 +24,8 @@ struct ns_gpu {
     int64_t next_ticket = 0;
     void* kept = nullptr;                // grow-only staging buffer (compat entry points: fp32 -> fp16 queries)
     size_t kept_bytes = 0;
+    int* status_host = nullptr;          // one word of mapped pinned memory: a kernel whose bounded wait gave up writes its code
+    int* status_dev = nullptr;           // the same word as the device sees it; ns_sync reports and clears it
 };
 
 static constexpr int64_t NS_RING = 1 << 16;

@@ -83,3 +83,34 @@ class Ops:
             _need(scratch, sc * 4, "gqa_decode scratch")
         check(self.api, self.api.need("ns_b200_gqa_decode")(self.gpu.raw, q.ptr, qs, q_seq, table.ptr, B, T, Hq, Hkv, D, max_kv, out.ptr,
                                                             scratch.ptr if scratch is not None else None), "ns_b200_gqa_decode")
+
+    # ---- prompt attention -------------------------------------------------------------------------------------------
+    def attn_prompt_supported(self, T, Hq, Hkv, D):
+        return bool(self.api.need("ns_q35_attn_prompt_supported")(T, Hq, Hkv, D))
+
+    def attn_prompt(self, q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out, name="ns_q35_attn_prompt"):
+        """fp32 rows in and out against the fp16 caches (ns_q35_attn_prompt / ns_nhs_attn_prompt)."""
+        _need(q, ((T - 1) * qs + Hq * D) * 4, "attn_prompt q")
+        _need(kc, Hkv * cap * D * 2, "attn_prompt key cache")
+        _need(vc, Hkv * cap * D * 2, "attn_prompt value cache")
+        _need(out, T * Hq * D * 4, "attn_prompt out")
+        check(self.api, self.api.need(name)(self.gpu.raw, q.ptr, qs, kc.ptr, vc.ptr, T, Hq, Hkv, D, cap, p0, out.ptr), name)
+
+    def gqa_prefill(self, dtype, q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out):
+        """16-bit rows in and out (dtype 0 fp16, 1 bf16)."""
+        _need(q, ((T - 1) * qs + Hq * D) * 2, "gqa_prefill q")
+        _need(kc, Hkv * cap * D * 2, "gqa_prefill key cache")
+        _need(vc, Hkv * cap * D * 2, "gqa_prefill value cache")
+        _need(out, T * Hq * D * 2, "gqa_prefill out")
+        check(self.api, self.api.need("ns_b200_gqa_prefill")(self.gpu.raw, dtype, q.ptr, qs, kc.ptr, vc.ptr, T, Hq, Hkv, D, cap, p0, out.ptr),
+              "ns_b200_gqa_prefill")
+
+    def mla_prefill(self, q, q_tok, k, k_tok, v, v_tok, T, H, p0, scale, out):
+        """bf16 q [T][H][192], k [p0+T][H][192], v [p0+T][H][128] -> out [T][H][128]."""
+        n = p0 + T
+        _need(q, ((T - 1) * q_tok + H * 192) * 2, "mla_prefill q")
+        _need(k, ((n - 1) * k_tok + H * 192) * 2, "mla_prefill k")
+        _need(v, ((n - 1) * v_tok + H * 128) * 2, "mla_prefill v")
+        _need(out, T * H * 128 * 2, "mla_prefill out")
+        check(self.api, self.api.need("ns_b200_mla_prefill")(self.gpu.raw, q.ptr, q_tok, k.ptr, k_tok, v.ptr, v_tok, T, H, p0, scale, out.ptr),
+              "ns_b200_mla_prefill")

@@ -1,0 +1,157 @@
+"""Causal flash prefill on the tensor path (tcgen05 / tensor memory / TMA) against the CPU oracle, through the C ABI.
+
+Tolerance: BASELINE's bar, |got - want| <= 2e-3 + 1e-2 |want| against the reference numerics (the oracle's flash mode
+restates kernels/llm/qwen35/silo/attn.cpp) and against fp64. bf16 cases (no reference kernel exists for them) are
+held to the same bar against the oracle's bf16 tensor-core numerics and to 2e-2 absolute against fp64."""
+import numpy as np
+import pytest
+
+from nextsycl_b200 import DevBuf
+from nextsycl_b200 import workloads as W
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+ABS, REL = 2e-3, 1e-2
+
+
+def assert_close(got, want, what, abs_tol=ABS, rel_tol=REL):
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    assert np.isfinite(got).all(), f"{what}: non-finite output"
+    d = np.abs(got - want)
+    bad = d > abs_tol + rel_tol * np.abs(want)
+    assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} outside tolerance, max abs {d.max():.3e}"
+
+
+def prefill_case(seed, T, Hq, Hkv, D, p0, cap=None):
+    kv = p0 + T
+    cap = cap or kv
+    q = W.normal_f16(seed, 0, (T, Hq * D))
+    k = np.zeros((Hkv, cap, D), np.float16)
+    v = np.zeros((Hkv, cap, D), np.float16)
+    k[:, :kv] = W.normal_f16(seed, 1, (Hkv, kv, D))
+    v[:, :kv] = W.normal_f16(seed, 2, (Hkv, kv, D))
+    # what lies past the written part of a cache is arbitrary: it must never reach the output
+    k[:, kv:] = np.float16(np.nan)
+    v[:, kv:] = np.float16(np.nan)
+    return q, k, v, cap
+
+
+SMALL = [
+    # T, Hq, Hkv, D, p0
+    (128, 1, 1, 128, 0),      # one tile, one head
+    (16, 2, 1, 128, 0),       # fewer rows than a tile
+    (256, 4, 2, 128, 0),      # two row blocks, a diagonal tile each
+    (200, 4, 1, 128, 77),     # ragged rows, an offset that is no multiple of anything
+    (9, 8, 2, 128, 1000),     # a short chunk far into the cache
+    (384, 16, 4, 128, 0),     # config 1's head geometry
+]
+
+
+@pytest.mark.parametrize("T,Hq,Hkv,D,p0", SMALL)
+def test_prompt_fp32_entry_matches_oracle(gpu, ops, T, Hq, Hkv, D, p0):
+    q, k, v, cap = prefill_case(930, T, Hq, Hkv, D, p0, cap=p0 + T + 5)
+    qf = q.astype(np.float32)
+    dq, dk, dv = DevBuf.of(gpu, qf), DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+    out = DevBuf(gpu, T * Hq * D * 4)
+    out.fill(0xFF)
+    assert ops.attn_prompt_supported(T, Hq, Hkv, D)
+    ops.attn_prompt(dq, Hq * D, dk, dv, T, Hq, Hkv, D, cap, p0, out)
+    gpu.sync()
+    got = out.read(np.float32).reshape(T, Hq * D)
+    kz, vz = np.nan_to_num(k).view(np.uint16), np.nan_to_num(v).view(np.uint16)
+    assert_close(got, O.gqa_flash_prefill(qf, kz, vz, T, Hq, Hkv, D, cap, p0), "vs flash numerics")
+    assert_close(got, O.attn_exact(qf, kz, vz, T, Hq, Hkv, D, D, cap, p0, 1 / np.sqrt(D)), "vs fp64")
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+def test_native_16bit_entry(gpu, ops, dtype):
+    T, Hq, Hkv, D, p0 = 300, 8, 2, 128, 60
+    kv = p0 + T
+    if dtype == 0:
+        q, k, v, cap = prefill_case(931, T, Hq, Hkv, D, p0)
+        qf = q.astype(np.float32)
+        qb, kb, vb = q.view(np.uint16), np.nan_to_num(k).view(np.uint16), np.nan_to_num(v).view(np.uint16)
+    else:
+        qb = W.normal_bf16_bits(931, 0, (T, Hq * D))
+        kb = W.normal_bf16_bits(931, 1, (Hkv, kv, D))
+        vb = W.normal_bf16_bits(931, 2, (Hkv, kv, D))
+        qf = O.from_bf16_bits(qb)
+        cap = kv
+    dq, dk, dv = DevBuf.of(gpu, qb), DevBuf.of(gpu, kb), DevBuf.of(gpu, vb)
+    out = DevBuf(gpu, T * Hq * D * 2)
+    ops.gqa_prefill(dtype, dq, Hq * D, dk, dv, T, Hq, Hkv, D, cap, p0, out)
+    gpu.sync()
+    raw = out.read(np.uint16).reshape(T, Hq * D)
+    got = raw.view(np.float16).astype(np.float32) if dtype == 0 else O.from_bf16_bits(raw)
+    sc = 1 / np.sqrt(D)
+    ex = O.attn_exact(qf, kb, vb, T, Hq, Hkv, D, D, cap, p0, sc, kind=dtype)
+    tc = O.attn_tc(qf, kb, vb, T, Hq, Hkv, D, D, cap, p0, np.float32(sc), kind=dtype)
+    if dtype == 0:
+        assert_close(got, tc, "vs fp16 tensor-core numerics")
+        assert_close(got, ex, "vs fp64")
+    else:
+        # the bf16 output itself carries 2^-9 relative rounding
+        assert_close(got, tc, "vs bf16 tensor-core numerics", abs_tol=4e-3)
+        assert_close(got, ex, "vs fp64", abs_tol=2e-2)
+
+
+def test_rows_entry_routes_long_passes_to_the_prompt_kernel(gpu, ops):
+    T, Hq, Hkv, D, p0 = 40, 8, 2, 128, 10
+    q, k, v, cap = prefill_case(932, T, Hq, Hkv, D, p0)
+    qf = q.astype(np.float32)
+    dq, dk, dv = DevBuf.of(gpu, qf), DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+    out = DevBuf(gpu, T * Hq * D * 4)
+    assert gpu.api.ns_q35_attn_scratch(T, Hq, Hkv, D, p0) == 0
+    ops.attn(dq, Hq * D, dk, dv, T, Hq, Hkv, D, cap, p0, out, None)
+    gpu.sync()
+    got = out.read(np.float32).reshape(T, Hq * D)
+    assert_close(got, O.gqa_flash_prefill(qf, k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, cap, p0), "rows")
+
+
+def test_head_256(gpu, ops):
+    """The qwen35 geometry: heads of 256, 6 query heads a key head."""
+    T, Hq, Hkv, D, p0 = 150, 12, 2, 256, 33
+    q, k, v, cap = prefill_case(933, T, Hq, Hkv, D, p0)
+    qf = q.astype(np.float32)
+    dq, dk, dv = DevBuf.of(gpu, qf), DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+    out = DevBuf(gpu, T * Hq * D * 4)
+    ops.attn_prompt(dq, Hq * D, dk, dv, T, Hq, Hkv, D, cap, p0, out)
+    gpu.sync()
+    got = out.read(np.float32).reshape(T, Hq * D)
+    assert_close(got, O.gqa_flash_prefill(qf, k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, cap, p0), "D 256")
+
+
+def test_mla_prefill_bf16_192_128(gpu, ops):
+    """BASELINE config 4's geometry at a small size: 192-wide keys (128 nope + 64 rope), 128-wide values, bf16,
+    token-major tensors, a chunk appended to cached tokens."""
+    T, H, p0 = 130, 3, 100
+    n = p0 + T
+    qb = W.normal_bf16_bits(934, 0, (T, H * 192))
+    kb = W.normal_bf16_bits(934, 1, (n, H, 192))
+    vb = W.normal_bf16_bits(934, 2, (n, H, 128))
+    dq, dk, dv = DevBuf.of(gpu, qb), DevBuf.of(gpu, kb), DevBuf.of(gpu, vb)
+    out = DevBuf(gpu, T * H * 128 * 2)
+    sc = 1 / np.sqrt(192.0)
+    ops.mla_prefill(dq, H * 192, dk, H * 192, dv, H * 128, T, H, p0, sc, out)
+    gpu.sync()
+    got = O.from_bf16_bits(out.read(np.uint16).reshape(T, H * 128))
+    # the oracle takes head-major caches
+    kh = np.ascontiguousarray(kb.transpose(1, 0, 2))
+    vh = np.ascontiguousarray(vb.transpose(1, 0, 2))
+    qf = O.from_bf16_bits(qb)
+    assert_close(got, O.attn_tc(qf, kh, vh, T, H, H, 192, 128, n, p0, np.float32(sc), kind=1), "vs bf16 tensor-core numerics", abs_tol=4e-3)
+    assert_close(got, O.attn_exact(qf, kh, vh, T, H, H, 192, 128, n, p0, sc, kind=1), "vs fp64", abs_tol=2e-2)
+
+
+def test_config_1_full_size(gpu, ops):
+    """BASELINE config 1: 2,048 rows, 16 query / 4 key heads of 128, fp16, from position 0."""
+    T, Hq, Hkv, D, p0 = 2048, 16, 4, 128, 0
+    q, k, v, p0 = W.gqa_case(1, T, Hq, Hkv, D, T)
+    dq, dk, dv = DevBuf.of(gpu, q), DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+    out = DevBuf(gpu, T * Hq * D * 2)
+    ops.gqa_prefill(0, dq, Hq * D, dk, dv, T, Hq, Hkv, D, T, 0, out)
+    gpu.sync()
+    got = out.read(np.float16).reshape(T, Hq * D).astype(np.float32)
+    qf = q.astype(np.float32)
+    assert_close(got, O.attn_tc(qf, k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, D, T, 0, np.float32(1 / np.sqrt(D)), kind=0), "config 1")
