@@ -101,6 +101,21 @@ int ns_b200_gqa_prefill(ns_gpu* g, int dtype, const void* q, int64_t qs, const v
 int ns_b200_mla_prefill(ns_gpu* g, const void* q, int64_t q_tok, const void* k, int64_t k_tok, const void* v, int64_t v_tok, int64_t T, int64_t H,
                         int64_t p0, float scale, void* out);
 
+/* kernels/llm/deepseek2/ds2.h:33-37 - MLA at decode widths: q [T][H][128 nope + 64 rope] fp32 (the rope part rotated),
+ * k_b [H][512][128] and v_b [H][128][512] fp16, the latent cache [n][512 + 64] fp16 (row t sees cells 0 .. pos0+t)
+ * -> out [T][H][128]: q~ = k_b q_nope, softmax((q~ . c + q_pe . k_pe) * scale) over the cells, u = sum p c[:512],
+ * out = v_b u. Here the middle stage runs on the tensor cores for any context length (the reference switches to a GEMM
+ * form past NS_DS2_MLA_FUSED_MAX cells, llm/deepseek2/src/engine.rs:1150-1224); q~ and p are rounded to fp16 as in
+ * that GEMM form. Intermediate buffers are the library's own. */
+int ns_ds2_mla_decode(ns_gpu* g, const float* q, const uint16_t* kb, const uint16_t* vb, const uint16_t* cache, float* out, int64_t T, int64_t H,
+                      int64_t pos0, float scale);
+
+/* The middle stage alone (BASELINE's absorbed-MLA decode): q [T][H][576] fp16 = absorbed query (512) then rotated
+ * part (64); cache [n][576] fp16; out u [T][H][512] fp32. scratch: ns_b200_mla_decode_scratch floats (it depends on
+ * the GPU's SM count, hence the handle), 0 when the row is not split. */
+int64_t ns_b200_mla_decode_scratch(ns_gpu* g, int64_t T, int64_t H, int64_t pos0);
+int ns_b200_mla_decode(ns_gpu* g, const void* q, const void* cache, int64_t T, int64_t H, int64_t pos0, float scale, float* out, float* scratch);
+
 /* No counterpart in the reference. ns_b200_gqa_decode for callers that can neither pass scratch nor tolerate an
  * allocation: an engine whose device memory was planned to the last byte at load time, or a serving loop that must
  * not hit the device-wide synchronisation a cudaMalloc brings. The split partials go to an array built into the

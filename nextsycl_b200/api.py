@@ -75,6 +75,9 @@ ATTN = {
     "ns_nhs_attn_prompt": (C.c_int, _ATTN_ARGS),
     "ns_b200_gqa_prefill": (C.c_int, [vp, C.c_int, vp, i64, vp, vp, i64, i64, i64, i64, i64, i64, vp]),
     "ns_b200_mla_prefill": (C.c_int, [vp, vp, i64, vp, i64, vp, i64, i64, i64, i64, C.c_float, vp]),
+    "ns_ds2_mla_decode": (C.c_int, [vp, vp, vp, vp, vp, vp, i64, i64, i64, C.c_float]),
+    "ns_b200_mla_decode_scratch": (i64, [vp, i64, i64, i64]),
+    "ns_b200_mla_decode": (C.c_int, [vp, vp, vp, i64, i64, i64, C.c_float, vp, vp]),
     "ns_b200_gqa_decode_scratch": (i64, [i64, i64, i64, i64, i64, i64]),
     "ns_b200_gqa_decode": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, i64, vp, vp]),
     "ns_b200_gqa_decode_static": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, i64, vp]),

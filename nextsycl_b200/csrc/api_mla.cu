@@ -1,0 +1,114 @@
+// api_mla.cu: the C-ABI entry points of absorbed MLA attention: deepseek2's fused decode under its own name
+// (kernels/llm/deepseek2/ds2.h:33-37) and the native middle stage.
+#include "kernels.cuh"
+
+namespace {
+
+constexpr int L = 512, R = 64, NOPE = 128, V = 128, KL = NOPE + R, CR = L + R;
+
+// q~[t,h,:512] = k_b[h] . q_nope[t,h] (k_b [H][512][128] fp16, fp32 sums: ds2.cpp:176-183), the rotated 64 copied
+// behind it; written as fp16 [T][H][576], the operand of the tensor-core stage. One warp a (t, h, 4 output rows).
+__global__ void __launch_bounds__(256) mla_absorb_kernel(const float* __restrict__ q, const __half* __restrict__ kb, __half* __restrict__ qa, int T, int H) {
+    __shared__ float qn[NOPE];
+    const int th = blockIdx.x, h = th % H;
+    const float* qr = q + (int64_t) th * KL;
+    if (threadIdx.x < NOPE) qn[threadIdx.x] = qr[threadIdx.x];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __half* dst = qa + (int64_t) th * CR;
+    for (int r = warp; r < L; r += 8) {
+        const uint2 w = reinterpret_cast<const uint2*>(kb + ((int64_t) h * L + r) * NOPE)[lane];   // 4 halves a lane
+        const __half2* hh = reinterpret_cast<const __half2*>(&w);
+        const float2 a = __half22float2(hh[0]), b = __half22float2(hh[1]);
+        float acc = a.x * qn[lane * 4] + a.y * qn[lane * 4 + 1] + b.x * qn[lane * 4 + 2] + b.y * qn[lane * 4 + 3];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) dst[r] = __float2half_rn(acc);
+    }
+    if (threadIdx.x < R) dst[L + threadIdx.x] = __float2half_rn(qr[NOPE + threadIdx.x]);
+}
+
+// out[t,h,:128] = v_b[h] . u[t,h] (v_b [H][128][512] fp16, fp32 sums: ds2.cpp:237-255). One warp an output value.
+__global__ void __launch_bounds__(256) mla_unabsorb_kernel(const float* __restrict__ u, const __half* __restrict__ vb, float* __restrict__ out, int T, int H) {
+    __shared__ float us[L];
+    const int th = blockIdx.x, h = th % H;
+    for (int i = threadIdx.x; i < L; i += blockDim.x) us[i] = u[(int64_t) th * L + i];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = warp; r < V; r += 8) {
+        const uint4* vr = reinterpret_cast<const uint4*>(vb + ((int64_t) h * V + r) * L);
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const uint4 w = vr[k * 32 + lane];
+            const __half2* hh = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 x = __half22float2(hh[e]);
+                acc += x.x * us[(k * 32 + lane) * 8 + 2 * e] + x.y * us[(k * 32 + lane) * 8 + 2 * e + 1];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) out[(int64_t) th * V + r] = acc;
+    }
+}
+
+int check_rows(const char* name, int64_t T, int64_t H, int64_t pos0) {
+    if (T < 1 || T > 64) return ns_fail(std::string(name) + ": 1..64 rows");
+    if (H < 1 || H > 1024) return ns_fail(std::string(name) + ": 1..1024 heads");
+    if (pos0 < 0 || pos0 + T >= ((int64_t) 1 << 31)) return ns_fail(std::string(name) + ": positions below 2^31");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t ns_b200_mla_decode_scratch(ns_gpu* g, int64_t T, int64_t H, int64_t pos0) {
+    if (!g || T < 1 || H < 1 || pos0 < 0) return 0;
+    return ns_mla_partial_floats(pos0 + T, T, H, g->sms);
+}
+
+int ns_b200_mla_decode(ns_gpu* g, const void* q, const void* cache, int64_t T, int64_t H, int64_t pos0, float scale, float* out, float* scratch) {
+    NS_TRY
+    const char* name = "ns_b200_mla_decode";
+    if (ns_enter(g, name)) return -1;
+    if (check_rows(name, T, H, pos0)) return -1;
+    if (!q || !cache || !out) return ns_fail(std::string(name) + ": a null buffer");
+    if (((uintptr_t) q & 15) != 0 || ((uintptr_t) cache & 15) != 0 || ((uintptr_t) out & 15) != 0 || ((uintptr_t) scratch & 15) != 0)
+        return ns_fail(std::string(name) + ": buffers 16-byte aligned");
+    if (ns_mla_partial_floats(pos0 + T, T, H, g->sms) > 0 && !scratch) return ns_fail(std::string(name) + ": no scratch");
+    MlaDecodeArgs a{q, cache, out, scratch, T, H, pos0, scale};
+    return ns_launch_mla_decode(g, a, name);
+    NS_CATCH("ns_b200_mla_decode")
+}
+
+// kernels/llm/deepseek2/ds2.h:33-37: q [T][H][192] fp32 (rope part rotated), k_b [H][512][128], v_b [H][128][512] and the
+// cache fp16 -> out [T][H][128]. Three stages on the compute stream: absorb (q~ = k_b q_nope), the tensor-core latent
+// attention, un-absorb (out = v_b u); q~, u and the split partials live in the GPU's kept buffer.
+int ns_ds2_mla_decode(ns_gpu* g, const float* q, const uint16_t* kb, const uint16_t* vb, const uint16_t* cache, float* out, int64_t T, int64_t H,
+                      int64_t pos0, float scale) {
+    NS_TRY
+    const char* name = "ns_ds2_mla_decode";
+    if (ns_enter(g, name)) return -1;
+    if (check_rows(name, T, H, pos0)) return -1;
+    if (!q || !kb || !vb || !cache || !out) return ns_fail(std::string(name) + ": a null buffer");
+    if (((uintptr_t) kb & 15) != 0 || ((uintptr_t) vb & 15) != 0 || ((uintptr_t) cache & 15) != 0) return ns_fail(std::string(name) + ": buffers 16-byte aligned");
+    const int64_t qa_bytes = (T * H * CR * 2 + 255) / 256 * 256, u_bytes = (T * H * L * 4 + 255) / 256 * 256;
+    const int64_t part_floats = ns_mla_partial_floats(pos0 + T, T, H, g->sms);
+    void* kept = nullptr;
+    if (ns_kept(g, (size_t) (qa_bytes + u_bytes + part_floats * 4), &kept)) return -1;
+    __half* qa = (__half*) kept;
+    float* u = (float*) ((uint8_t*) kept + qa_bytes);
+    float* part = part_floats ? (float*) ((uint8_t*) kept + qa_bytes + u_bytes) : nullptr;
+    mla_absorb_kernel<<<(unsigned) (T * H), 256, 0, g->compute>>>(q, (const __half*) kb, qa, (int) T, (int) H);
+    if (ns_launched(name)) return -1;
+    MlaDecodeArgs a{qa, cache, u, part, T, H, pos0, scale};
+    if (ns_launch_mla_decode(g, a, name)) return -1;
+    mla_unabsorb_kernel<<<(unsigned) (T * H), 256, 0, g->compute>>>(u, (const __half*) vb, out, (int) T, (int) H);
+    return ns_launched(name);
+    NS_CATCH("ns_ds2_mla_decode")
+}
+
+}  // extern "C"

@@ -70,7 +70,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     uint64_t* s_full = v_empty + NSTAGE;         // [2]
     uint64_t* p_full = s_full + 2;               // [2]
     uint64_t* pv_done = p_full + 2;              // [1]
-    uint32_t* tmem_slot = (uint32_t*) (pv_done + 1);
+    uint64_t* o_final = pv_done + 1;              // [1] the last P V done
+    uint32_t* tmem_slot = (uint32_t*) (o_final + 1);
     volatile int* abort_flag = (volatile int*) (tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -96,6 +97,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             mbar_init(smem_u32(p_full + s), SOFTMAX_THREADS);
         }
         mbar_init(smem_u32(pv_done), 1);
+        mbar_init(smem_u32(o_final), 1);
         mbar_fence_init();
     }
     if (warp == 5) {
@@ -181,6 +183,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 }
                 mma_commit(smem_u32(v_empty + s));
                 mma_commit(smem_u32(pv_done));
+                if (j == ntiles - 1) mma_commit(smem_u32(o_final));
             }
         }
     } else {
@@ -272,7 +275,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             mbar_arrive(smem_u32(p_full + (j & 1)));
         }
         // ---- epilogue: O / l to global memory
-        if (ok) ok = mbar_wait(smem_u32(pv_done), (uint32_t) (ntiles - 1) & 1, abort_flag, p.status, 303);
+        // (pv_done cannot serve here: a parity wait only tells the current phase from the one before it, and this thread
+        // has not followed its phases; o_final completes exactly once, after the last product)
+        if (ok) ok = mbar_wait(smem_u32(o_final), 0, abort_flag, p.status, 303);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             fence_after_sync();

@@ -56,3 +56,17 @@ struct FlashPrefillArgs {
     int bf16, out_f32;
 };
 int ns_launch_flash_prefill(ns_gpu* g, const FlashPrefillArgs& a, const char* where);
+
+// ---- absorbed MLA decode on tcgen05 (mla_decode.cu) --------------------------------------------------------------------
+struct MlaDecodeArgs {
+    const void* q;        // [T][H][576] fp16: the absorbed query (512) then the rotated part (64)
+    const void* cache;    // [n][576] fp16, n >= pos0 + T
+    float* out;           // [T][H][512] fp32
+    float* part;          // ns_mla_partial_floats floats (may be null when that is 0)
+    int64_t T, H, pos0;
+    float scale;
+};
+// cells a key split / floats of partials for rows that see up to n cells, on a GPU of `sms` SMs
+int64_t ns_mla_split(int64_t n, int64_t T, int64_t H, int sms);
+int64_t ns_mla_partial_floats(int64_t n, int64_t T, int64_t H, int sms);
+int ns_launch_mla_decode(ns_gpu* g, const MlaDecodeArgs& a, const char* where);

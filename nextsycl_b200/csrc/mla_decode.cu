@@ -1,0 +1,391 @@
+// mla_decode.cu: absorbed MLA latent attention at decode widths on the Blackwell tensor path.
+//
+// What it computes is the middle stage of the reference's fused kernel mla_decode_t (kernels/llm/deepseek2/ds2.cpp:
+// 186-235) in the numerics of its GEMM form (llm/deepseek2/src/engine.rs:1204-1224): per (row t, head h) over the
+// latent cache [n][576] fp16 (512 latent + 64 rotated), score = (q . c) * scale with q rounded to fp16, softmax over the
+// row's cells 0 .. pos0+t, u = sum_p p * c[:512] with p rounded to fp16, fp32 sums.
+//
+// How: the 128 heads of a row are the M = 128 rows of a tcgen05 tile, so every cell is read once for all heads. The
+// output tile [128 x 512] fp32 alone would fill tensor memory (512 columns), so a CTA owns one half of the 512 latent
+// output columns: grid = (2 x key splits, head tiles, rows). Tensor memory per CTA: O half (256 columns), two S
+// buffers of 64 columns (P overlays its S), and the first 256 features of Q as a tensor-memory A operand (128
+// columns); the other 320 features of Q sit in shared memory (80 KB) beside a two-stage ring of 64-cell tiles
+// (72 KB each). One TMA-staged cell tile serves both products: K-major for S = Q C^T (all 576 features) and MN-major
+// for O += P C[:, half] (its 256 columns). Splits are merged by a second kernel (log-sum-exp combine).
+// Every mbarrier wait is bounded; a wait that gives up records a status code and the CTA runs to its teardown.
+#include "kernels.cuh"
+#include "tc05.cuh"
+
+#include <cuda.h>
+
+namespace {
+using namespace tc05;
+
+constexpr int L = 512, R = 64, CR = L + R;     // latent, rotated, row width
+constexpr int BM = 128;                        // heads a tile
+constexpr int BN = 64;                         // cells a tile
+constexpr int NSTAGE = 2;
+constexpr int QT = 256;                        // features of Q kept in tensor memory
+constexpr int QS = CR - QT;                    // features of Q kept in shared memory (320)
+constexpr int DVH = 256;                       // output columns a CTA
+constexpr int THREADS = 192;
+constexpr int PS = 516;                        // floats a partial row: O[512], m, l, 2 pad
+constexpr float RESCALE_LOG2 = 8.0f;
+
+constexpr int O_COL = 0, Q_COL = 256, S_COL = 384;   // tensor-memory columns; S buffers at 384 and 448
+constexpr int TILE_BYTES = BN * CR * 2;              // 73,728
+constexpr int QS_BYTES = BM * QS * 2;                // 81,920
+constexpr int SMEM_TOTAL = 1024 + QS_BYTES + NSTAGE * TILE_BYTES + 512;
+
+struct Params {
+    const __half* q;       // [T][H][576] fp16
+    float* out;            // [T][H][512]
+    float* part;           // [T][H][ns][PS]
+    int* status;
+    int T, H, ns;
+    int64_t pos0, kb;      // cells a split
+    float scale_log2;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_c, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
+    uint8_t* q_s = smem;                       // 5 chunks of [128 heads][64 features]
+    uint8_t* c_s = smem + QS_BYTES;            // stages of 9 chunks of [64 cells][64 features]
+    uint64_t* bars = (uint64_t*) (c_s + NSTAGE * TILE_BYTES);
+    uint64_t* q_full = bars + 0;               // Q's shared-memory part landed
+    uint64_t* qt_full = bars + 1;              // Q's tensor-memory part written (128 arrivals)
+    uint64_t* c_full = bars + 2;               // [NSTAGE]
+    uint64_t* c_empty = c_full + NSTAGE;       // [NSTAGE] (both products of the tile done)
+    uint64_t* s_full = c_empty + NSTAGE;       // [2]
+    uint64_t* p_full = s_full + 2;             // [2]
+    uint64_t* pv_done = p_full + 2;            // [1]
+    uint64_t* o_final = pv_done + 1;              // [1] the last P V done
+    uint32_t* tmem_slot = (uint32_t*) (o_final + 1);
+    volatile int* abort_flag = (volatile int*) (tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int hv = blockIdx.x & 1, split = blockIdx.x >> 1;
+    const int h0 = blockIdx.y * BM, t = blockIdx.z;
+    const int64_t n = p.pos0 + t + 1;                       // cells this row sees
+    const int64_t jbeg = (int64_t) split * p.kb, jend = min(n, (int64_t) (split + 1) * p.kb);
+    const int ntiles = jbeg < jend ? (int) ((jend - jbeg + BN - 1) / BN) : 0;
+    if (ntiles == 0) return;                                // the whole CTA: this split holds none of the row's cells
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        mbar_init(smem_u32(q_full), 1);
+        mbar_init(smem_u32(qt_full), 128);
+        for (int s = 0; s < NSTAGE; ++s) {
+            mbar_init(smem_u32(c_full + s), 1);
+            mbar_init(smem_u32(c_empty + s), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(s_full + s), 1);
+            mbar_init(smem_u32(p_full + s), 128);
+        }
+        mbar_init(smem_u32(pv_done), 1);
+        mbar_init(smem_u32(o_final), 1);
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 4) {
+        // ================= TMA producer =================
+        if (elect_one()) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_c);
+            mbar_expect_tx(smem_u32(q_full), QS_BYTES);
+            for (int c = 0; c < QS / 64; ++c) tma_load_3d(smem_u32(q_s + c * (BM * 128)), &tm_q, QT + c * 64, h0, t, smem_u32(q_full));
+            bool ok = true;
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int s = j % NSTAGE;
+                if (j >= NSTAGE) ok = mbar_wait(smem_u32(c_empty + s), ((uint32_t) (j / NSTAGE) & 1) ^ 1, abort_flag, p.status, 401);
+                if (!ok) break;
+                mbar_expect_tx(smem_u32(c_full + s), TILE_BYTES);
+                uint8_t* dst = c_s + s * TILE_BYTES;
+                for (int c = 0; c < CR / 64; ++c) tma_load_3d(smem_u32(dst + c * (BN * 128)), &tm_c, c * 64, (int) (jbeg + (int64_t) j * BN), 0, smem_u32(c_full + s));
+            }
+        }
+    } else if (warp == 5) {
+        // ================= MMA issuer =================
+        if (elect_one()) {
+            constexpr uint32_t idesc_qk = idesc_f16(BM, BN, 0, 0, 0);
+            constexpr uint32_t idesc_pv = idesc_f16(BM, DVH, 0, 0, 1);
+            bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, p.status, 501);
+            if (ok) ok = mbar_wait(smem_u32(qt_full), 0, abort_flag, p.status, 502);
+            auto issue_qk = [&](int j) {
+                const uint32_t cb = smem_u32(c_s + (j % NSTAGE) * TILE_BYTES), qb = smem_u32(q_s);
+                const uint32_t d = tmem + (uint32_t) (S_COL + (j & 1) * BN);
+#pragma unroll
+                for (int k = 0; k < CR / 16; ++k) {
+                    const uint64_t bd = smem_desc_sw128(cb + (k / 4) * (BN * 128) + (k % 4) * 32, 16, 1024);
+                    if (k < QT / 16) {
+                        mma_ts(d, tmem + (uint32_t) (Q_COL + k * 8), bd, idesc_qk, k > 0);
+                    } else {
+                        const int ks = k - QT / 16;
+                        const uint64_t ad = smem_desc_sw128(qb + (ks / 4) * (BM * 128) + (ks % 4) * 32, 16, 1024);
+                        mma_ss(d, ad, bd, idesc_qk, 1);
+                    }
+                }
+                mma_commit(smem_u32(s_full + (j & 1)));
+            };
+            if (ok) ok = mbar_wait(smem_u32(c_full + 0), 0, abort_flag, p.status, 503);
+            if (ok) {
+                fence_after_sync();
+                issue_qk(0);
+            }
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int s = j % NSTAGE;
+                if (j + 1 < ntiles) {
+                    ok = mbar_wait(smem_u32(c_full + (j + 1) % NSTAGE), (uint32_t) ((j + 1) / NSTAGE) & 1, abort_flag, p.status, 504);
+                    if (!ok) break;
+                    fence_after_sync();
+                    issue_qk(j + 1);
+                }
+                ok = mbar_wait(smem_u32(p_full + (j & 1)), (uint32_t) (j >> 1) & 1, abort_flag, p.status, 505);
+                if (!ok) break;
+                fence_after_sync();
+                // the value operand: this CTA's 4 chunks of the same tile, MN-major; 16 cells a step
+                const uint32_t vb = smem_u32(c_s + s * TILE_BYTES) + (uint32_t) (hv * (DVH / 64) * (BN * 128));
+                const uint32_t pa = tmem + (uint32_t) (S_COL + (j & 1) * BN);
+#pragma unroll
+                for (int k = 0; k < BN / 16; ++k) {
+                    const uint64_t bd = smem_desc_sw128(vb + k * (16 * 128), BN * 128, 1024);
+                    mma_ts(tmem + (uint32_t) O_COL, pa + (uint32_t) (k * 8), bd, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                }
+                mma_commit(smem_u32(c_empty + s));
+                mma_commit(smem_u32(pv_done));
+                if (j == ntiles - 1) mma_commit(smem_u32(o_final));
+            }
+        }
+    } else {
+        // ================= softmax: thread r owns head h0 + r =================
+        const int r = tid;
+        const uint32_t lane_base = (uint32_t) (warp * 32) << 16;
+        const bool head_live = h0 + r < p.H;
+        // ---- the first 256 features of this head's query into tensor memory: column i = features (2i, 2i+1)
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((int64_t) t * p.H + (head_live ? h0 + r : 0)) * CR);
+#pragma unroll
+            for (int c = 0; c < QT / 64; ++c) {
+                uint32_t w[32];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const uint4 x = head_live ? src[c * 8 + e] : make_uint4(0, 0, 0, 0);
+                    w[4 * e] = x.x, w[4 * e + 1] = x.y, w[4 * e + 2] = x.z, w[4 * e + 3] = x.w;
+                }
+                tmem_st32(tmem + lane_base + (uint32_t) (Q_COL + c * 32), w);
+            }
+            tmem_wait_st();
+            fence_before_sync();
+            mbar_arrive(smem_u32(qt_full));
+        }
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < ntiles; ++j) {
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(s_full + (j & 1)), (uint32_t) (j >> 1) & 1, abort_flag, p.status, 601));
+            if (!ok) break;
+            fence_after_sync();
+            const uint32_t s_addr = tmem + lane_base + (uint32_t) (S_COL + (j & 1) * BN);
+            float s[BN];
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(s_addr + c * 32, v);
+                tmem_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(v[e]);
+            }
+            const int64_t c0 = jbeg + (int64_t) j * BN;
+            if (c0 + BN > jend) {
+#pragma unroll
+                for (int e = 0; e < BN; ++e)
+                    if (c0 + e >= jend) s[e] = -INFINITY;
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < BN; ++e) mx = fmaxf(mx, s[e]);
+            mx *= p.scale_log2;
+            float corr = 1.0f;
+            bool need = false;
+            if (j == 0) {
+                m_ref = mx;
+            } else if (mx > m_ref + RESCALE_LOG2) {
+                corr = ex2(m_ref - mx);
+                m_ref = mx;
+                need = true;
+            }
+            if (__any_sync(0xffffffffu, need)) {
+                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(pv_done), (uint32_t) (j - 1) & 1, abort_flag, p.status, 602));
+                if (!ok) break;
+                fence_after_sync();
+#pragma unroll
+                for (int c = 0; c < DVH / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem + lane_base + (uint32_t) (O_COL + c * 32), v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * corr);
+                    tmem_st32(tmem + lane_base + (uint32_t) (O_COL + c * 32), v);
+                }
+                tmem_wait_st();
+                l *= corr;
+            }
+            const float neg_m = -m_ref;   // finite: the first cell of the first tile is always inside the split
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t w[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const float a = ex2(fmaf(s[c * 32 + 2 * e], p.scale_log2, neg_m));
+                    const float b = ex2(fmaf(s[c * 32 + 2 * e + 1], p.scale_log2, neg_m));
+                    sum += a + b;
+                    __half2 hh = __floats2half2_rn(a, b);
+                    w[e] = *reinterpret_cast<uint32_t*>(&hh);
+                }
+                tmem_st16(s_addr + c * 16, w);
+            }
+            l += sum;
+            tmem_wait_st();
+            fence_before_sync();
+            mbar_arrive(smem_u32(p_full + (j & 1)));
+        }
+        // ---- epilogue: this half of O, and (from the half-0 CTA) the row's m and l
+        // (pv_done cannot serve here: a parity wait only tells the current phase from the one before it, and this thread
+        // has not followed its phases; o_final completes exactly once, after the last product)
+        if (ok) ok = mbar_wait(smem_u32(o_final), 0, abort_flag, p.status, 603);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            fence_after_sync();
+            const int64_t row = (int64_t) t * p.H + h0 + r;
+            const bool direct = p.ns == 1;
+            const float inv = direct ? (l > 0.f ? 1.0f / l : 0.f) : 1.0f;
+            float* dst = direct ? p.out + row * L + hv * DVH : p.part + (row * p.ns + split) * PS + hv * DVH;
+#pragma unroll
+            for (int c = 0; c < DVH / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem + lane_base + (uint32_t) (O_COL + c * 32), v);
+                tmem_wait_ld();
+                if (head_live) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        reinterpret_cast<float4*>(dst + c * 32)[e] =
+                            make_float4(__uint_as_float(v[4 * e]) * inv, __uint_as_float(v[4 * e + 1]) * inv, __uint_as_float(v[4 * e + 2]) * inv,
+                                        __uint_as_float(v[4 * e + 3]) * inv);
+                }
+            }
+            if (head_live && !direct && hv == 0) {
+                float* st = p.part + (row * p.ns + split) * PS + L;
+                st[0] = m_ref;
+                st[1] = l;
+            }
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 5) {
+        fence_after_sync();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// the splits of each (row, head) merged; a split past the row's cells wrote nothing and is skipped
+__global__ void __launch_bounds__(256) mla_merge_kernel(const Params p) {
+    const int64_t row = blockIdx.x;   // (t, h)
+    const int t = (int) (row / p.H);
+    const int64_t n = p.pos0 + t + 1;
+    const int nsr = (int) ((n + p.kb - 1) / p.kb);
+    const float* pp = p.part + row * p.ns * PS;
+    float mx = -INFINITY;
+    for (int k = 0; k < nsr; ++k) mx = fmaxf(mx, pp[k * PS + L]);
+    float den = 0.f;
+    for (int k = 0; k < nsr; ++k) den += pp[k * PS + L + 1] * exp2f(pp[k * PS + L] - mx);
+    const float inv = den > 0.f ? 1.0f / den : 0.f;
+    for (int d = threadIdx.x; d < L; d += blockDim.x) {
+        float a = 0.f;
+        for (int k = 0; k < nsr; ++k) a += pp[k * PS + d] * exp2f(pp[k * PS + L] - mx);
+        p.out[row * L + d] = a * inv;
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_map(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1, uint64_t s2, uint32_t box1, const char* where) {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled) ptr;
+    }
+    if (!fn) return ns_fail(std::string(where) + ": cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {s1, s2};
+    cuuint32_t box[3] = {64, box1, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ns_fail(std::string(where) + ": tensor map rejected (code " + std::to_string((int) r) + ")");
+    return 0;
+}
+
+}  // namespace
+
+int64_t ns_mla_split(int64_t n, int64_t T, int64_t H, int sms) {
+    const int64_t tiles = (H + BM - 1) / BM * T;
+    int64_t want = sms / (2 * tiles);           // splits that fill the SMs once
+    if (want < 1) want = 1;
+    int64_t kb = (n + want - 1) / want;
+    kb = (kb + BN - 1) / BN * BN;
+    if (kb < 2 * BN) kb = 2 * BN;               // at least two tiles a split: a partial costs 2 KB a head
+    return kb;
+}
+
+int64_t ns_mla_partial_floats(int64_t n, int64_t T, int64_t H, int sms) {
+    const int64_t kb = ns_mla_split(n, T, H, sms), ns = (n + kb - 1) / kb;
+    return ns > 1 ? T * H * ns * PS : 0;
+}
+
+int ns_launch_mla_decode(ns_gpu* g, const MlaDecodeArgs& a, const char* where) {
+    const int64_t n = a.pos0 + a.T;              // cells the last row sees
+    Params p;
+    p.q = (const __half*) a.q;
+    p.out = a.out;
+    p.part = a.part;
+    p.status = g->status_dev;
+    p.T = (int) a.T;
+    p.H = (int) a.H;
+    p.pos0 = a.pos0;
+    p.kb = ns_mla_split(n, a.T, a.H, g->sms);
+    p.ns = (int) ((n + p.kb - 1) / p.kb);
+    p.scale_log2 = a.scale * 1.4426950408889634f;
+    CUtensorMap tq, tc;
+    // Q [T][H][576]: a box = 128 heads x 64 features of one row
+    if (make_map(&tq, a.q, CR, (uint64_t) a.H, (uint64_t) a.T, CR * 2, (uint64_t) a.H * CR * 2, BM, where)) return -1;
+    // cache [n][576]: a box = 64 cells x 64 features; cells past n read as zeros
+    if (make_map(&tc, a.cache, CR, (uint64_t) n, 1, CR * 2, (uint64_t) n * CR * 2, BN, where)) return -1;
+    static bool set[64] = {};
+    if (!set[g->dev & 63]) {
+        NS_CUDA(cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL), where);
+        set[g->dev & 63] = true;
+    }
+    dim3 grid((unsigned) (2 * p.ns), (unsigned) ((a.H + BM - 1) / BM), (unsigned) a.T);
+    mla_decode_kernel<<<grid, THREADS, SMEM_TOTAL, g->compute>>>(tq, tc, p);
+    if (ns_launched(where)) return -1;
+    if (p.ns > 1) {
+        mla_merge_kernel<<<(unsigned) (a.T * a.H), 256, 0, g->compute>>>(p);
+        if (ns_launched(where)) return -1;
+    }
+    return 0;
+}

@@ -114,3 +114,27 @@ class Ops:
         _need(out, T * H * 128 * 2, "mla_prefill out")
         check(self.api, self.api.need("ns_b200_mla_prefill")(self.gpu.raw, q.ptr, q_tok, k.ptr, k_tok, v.ptr, v_tok, T, H, p0, scale, out.ptr),
               "ns_b200_mla_prefill")
+
+    # ---- absorbed MLA decode ----------------------------------------------------------------------------------------
+    def mla_decode_scratch(self, T, H, pos0):
+        return int(self.api.need("ns_b200_mla_decode_scratch")(self.gpu.raw, T, H, pos0))
+
+    def mla_decode(self, q, cache, T, H, pos0, scale, out, scratch=None):
+        """q fp16 [T][H][576], cache fp16 [n][576] -> out fp32 [T][H][512] (the middle stage of deepseek2's MLA)."""
+        _need(q, T * H * 576 * 2, "mla_decode q")
+        _need(cache, (pos0 + T) * 576 * 2, "mla_decode cache")
+        _need(out, T * H * 512 * 4, "mla_decode out")
+        sc = self.mla_decode_scratch(T, H, pos0)
+        if sc > 0:
+            _need(scratch, sc * 4, "mla_decode scratch")
+        check(self.api, self.api.need("ns_b200_mla_decode")(self.gpu.raw, q.ptr, cache.ptr, T, H, pos0, scale, out.ptr,
+                                                            scratch.ptr if scratch is not None else None), "ns_b200_mla_decode")
+
+    def ds2_mla_decode(self, q, kb, vb, cache, out, T, H, pos0, scale):
+        """deepseek2's whole decode attention: q fp32 [T][H][192], k_b [H][512][128], v_b [H][128][512] fp16 -> out fp32 [T][H][128]."""
+        _need(q, T * H * 192 * 4, "ds2_mla_decode q")
+        _need(kb, H * 512 * 128 * 2, "ds2_mla_decode k_b")
+        _need(vb, H * 128 * 512 * 2, "ds2_mla_decode v_b")
+        _need(cache, (pos0 + T) * 576 * 2, "ds2_mla_decode cache")
+        _need(out, T * H * 128 * 4, "ds2_mla_decode out")
+        check(self.api, self.api.need("ns_ds2_mla_decode")(self.gpu.raw, q.ptr, kb.ptr, vb.ptr, cache.ptr, out.ptr, T, H, pos0, scale), "ns_ds2_mla_decode")

@@ -1,0 +1,80 @@
+"""Absorbed MLA decode on the tensor path against the CPU oracle, through the C ABI.
+
+Tolerance: BASELINE's bar, |got - want| <= 2e-3 + 1e-2 |want|, against the oracle's GEMM-form numerics (q and p rounded
+to fp16: llm/deepseek2/src/engine.rs:1204-1224), against the fused kernel's fp32 numerics
+(kernels/llm/deepseek2/ds2.cpp:186-235) and against fp64."""
+import numpy as np
+import pytest
+
+from nextsycl_b200 import DevBuf
+from nextsycl_b200 import workloads as W
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+ABS, REL = 2e-3, 1e-2
+SCALE = float(1.0 / np.sqrt(192.0))
+
+
+def assert_close(got, want, what, abs_tol=ABS, rel_tol=REL):
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    assert np.isfinite(got).all(), f"{what}: non-finite output"
+    d = np.abs(got - want)
+    bad = d > abs_tol + rel_tol * np.abs(want)
+    assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} outside tolerance, max abs {d.max():.3e}"
+
+
+def run(gpu, ops, q16, cache, T, H, pos0):
+    dq, dc = DevBuf.of(gpu, q16), DevBuf.of(gpu, cache)
+    out = DevBuf(gpu, T * H * 512 * 4)
+    out.fill(0xFF)
+    n = ops.mla_decode_scratch(T, H, pos0)
+    sc = DevBuf(gpu, n * 4) if n else None
+    if sc is not None:
+        sc.fill(0xFF)
+    ops.mla_decode(dq, dc, T, H, pos0, SCALE, out, sc)
+    gpu.sync()
+    return out.read(np.float32).reshape(T, H, 512)
+
+
+@pytest.mark.parametrize("T,H,n", [(1, 128, 1), (1, 128, 100), (1, 16, 1000), (3, 128, 333), (1, 128, 5000), (2, 200, 700), (1, 128, 4096)])
+def test_mla_decode_matches_oracle(gpu, ops, T, H, n):
+    q = W.normal_f16(940, 0, (T, H, 576))
+    cache = W.normal_f16(940, 1, (n, 576), 0.5)
+    got = run(gpu, ops, q, cache, T, H, n - T)
+    qf, cb = q.astype(np.float32), cache.view(np.uint16)
+    assert_close(got, O.mla_gemm(qf, cb, T, H, 512, 64, n - T, np.float32(SCALE)), "vs GEMM-form numerics")
+    assert_close(got, O.mla_fused(qf, cb, T, H, 512, 64, n - T, np.float32(SCALE)), "vs fused-kernel numerics")
+    assert_close(got, O.mla_exact(qf, cb, T, H, 512, 64, n - T, SCALE), "vs fp64")
+
+
+def test_ds2_whole_decode(gpu, ops):
+    """ns_ds2_mla_decode: absorb, latent attention, un-absorb, against the same three stages in numpy + the oracle."""
+    T, H, n = 2, 128, 900
+    q = W.rng(941, 0).standard_normal((T, H, 192), dtype=np.float32)
+    kb = W.normal_f16(941, 1, (H, 512, 128), 0.1)
+    vb = W.normal_f16(941, 2, (H, 128, 512), 0.1)
+    cache = W.normal_f16(941, 3, (n, 576), 0.5)
+    out = DevBuf(gpu, T * H * 128 * 4)
+    ops.ds2_mla_decode(DevBuf.of(gpu, q), DevBuf.of(gpu, kb), DevBuf.of(gpu, vb), DevBuf.of(gpu, cache), out, T, H, n - T, SCALE)
+    gpu.sync()
+    got = out.read(np.float32).reshape(T, H, 128)
+    # q~ = k_b q_nope (fp32), then [q~ | q_pe] as the oracle's input (it rounds it to fp16 as the kernel does)
+    qa = np.einsum("hrc,thc->thr", kb.astype(np.float32), q[:, :, :128]).astype(np.float32)
+    qfull = np.ascontiguousarray(np.concatenate([qa, q[:, :, 128:]], axis=2))
+    u = O.mla_gemm(qfull, cache.view(np.uint16), T, H, 512, 64, n - T, np.float32(SCALE))
+    want = np.einsum("hvl,thl->thv", vb.astype(np.float64), u.astype(np.float64))
+    assert_close(got, want, "whole decode")
+
+
+@pytest.mark.parametrize("n", [32768, 131072])
+def test_config_3_full_size(gpu, ops, n):
+    """BASELINE config 3: 128 heads, latent cache ~N(0, 0.5), query ~N(0, 1), scale 1/sqrt(192). All 128 heads run on the
+    GPU; the oracle checks the first 8 (the heads are independent rows of the same tile)."""
+    T, H = 1, 128
+    q = W.normal_f16(3, 0, (T, H, 576))
+    cache = W.normal_f16(3, 1, (n, 576), 0.5)
+    got = run(gpu, ops, q, cache, T, H, n - 1)
+    qs = np.ascontiguousarray(q[:, :8].astype(np.float32))
+    assert_close(got[:, :8], O.mla_gemm(qs, cache.view(np.uint16), T, 8, 512, 64, n - 1, np.float32(SCALE)), "config 3, heads 0..7")
+    assert np.isfinite(got).all()
