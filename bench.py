@@ -1,18 +1,24 @@
 #!/usr/bin/env python
-"""Benchmark of the attention path: `python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload W]`.
+"""Benchmark of the attention path.
 
-Prints ONE JSON line (rank 0). The default workload is BASELINE config 2 as a batch: GQA decode of 8 sequences,
-1 new token each, 64 query heads, 8 key heads, head 128, 32,768 cached fp16 tokens a sequence (1 GiB of K+V on each
-GPU: every step's reads miss L2). A step is one pass of the decode path over the batch.
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME] [--no-others]
 
-  value     KV bytes the step must read / device time, inputs resident in HBM, summed over ranks (weak scaling: every
-            rank holds its own 8 sequences; there is no exchange between independent sequences)
-  e2e       the same metric through the reference's own calls with HOST buffers: per sequence ns_copy_to(q, k, v rows),
-            ns_q35_kv_store, ns_q35_attn_decode, ns_copy_from(out), one ns_sync a step
-  roofline  HBM: algorithmic bytes a launch / CUDA-event time of the launch, against the measured copy bandwidth
-  cpu_baseline / --impl reference: the CPU restatement of the reference kernel (oracle/) on the host cores
+Prints ONE JSON line (rank 0). The headline workload (`decode_c2`) is BASELINE config 2 as a batch: GQA decode of 8
+sequences, 1 new token each, 64 query / 8 key heads of 128, 32,768 cached fp16 tokens a sequence - 1 GiB of K+V per
+GPU, so every step's reads miss L2. A step is one pass of the path over the batch.
 
-The reference's SYCL kernels cannot be built here (no oneAPI toolchain), so the reference arm times the oracle port.
+  value      KV bytes the step must read / device time, inputs resident in HBM, summed over ranks (weak scaling:
+             every rank holds its own 8 sequences; independent sequences need no exchange)
+  e2e        the same metric through the reference's own calls with HOST buffers: per sequence ns_copy_to(q, k, v
+             rows) -> ns_q35_kv_store -> ns_q35_attn_decode -> ns_copy_from(out), one ns_sync a step
+  roofline   algorithmic bytes (or flops) a launch / CUDA-event time, against the measured peaks
+  cpu_baseline, --impl reference: the CPU restatement of the reference kernel (oracle/) on the host cores; the
+             reference's SYCL kernels themselves cannot be built without a oneAPI toolchain
+  others     the other BASELINE configurations, each timed the same way for a few steps: 16K and 2K causal prefill
+             (TFLOP/s), 128K and 256K decode, absorbed MLA decode at three context lengths, the bf16 MLA prefill chunk
+             (heads sharded over the ranks)
+
+`--workload NAME` makes another configuration the headline (used for profiler runs).
 """
 import argparse
 import json
@@ -92,167 +98,294 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
-# ---- the workload -----------------------------------------------------------------------------------------------------
+# ---- environment shared by the workloads ----------------------------------------------------------------------------------
 
-C2 = dict(T=1, Hq=64, Hkv=8, D=128, kv=32768, B=8)
+class Env:
+    def __init__(self):
+        from nextsycl_b200 import Gpu, Ops
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        self.dist = None
+        if self.world > 1:
+            import torch
+            import torch.distributed as dist
+            torch.cuda.set_device(self.local)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+            self.dist = dist
+            self.torch = torch
+        self.gpu = Gpu(self.local)
+        self.ops = Ops(self.gpu)
+
+    def barrier(self):
+        self.gpu.sync()
+        if self.dist:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, x):
+        if not self.dist:
+            return x
+        t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(self, fn, steps, warmup):
+        """W warm-up steps, then K steps between two stamps on the library's compute stream; barrier + sync on both
+        sides; the maximum over ranks. Returns milliseconds a step."""
+        for _ in range(warmup):
+            fn()
+        self.barrier()
+        a = self.gpu.stamp()
+        for _ in range(steps):
+            fn()
+        b = self.gpu.stamp()
+        self.gpu.sync()
+        ms = self.gpu.elapsed_ns(a, b) / 1e6
+        self.barrier()
+        return self.max_over_ranks(ms) / steps
+
+    def close(self):
+        if self.dist:
+            self.dist.destroy_process_group()
+        self.gpu.close()
 
 
-def c2_bytes_per_seq(w):
-    return 2 * w["kv"] * w["Hkv"] * w["D"] * 2          # K and V read once (the algorithmic figure)
-
-
-def make_seq(config, w, seq):
+def device_random_f16(env, nbytes, seed, sigma=1.0, bf16=False):
+    """A device buffer of `nbytes` of seeded N(0, sigma) 16-bit values: a 32 MiB host block drawn once and copied
+    end to end (the values repeat every 16 Mi elements, which no kernel here can profit from)."""
+    from nextsycl_b200 import DevBuf
     from nextsycl_b200 import workloads as W
-    return W.gqa_case(config, w["T"], w["Hq"], w["Hkv"], w["D"], w["kv"], seq=seq)
+    from nextsycl_b200.core import check
+    block_elems = min(nbytes // 2, 16 << 20)
+    blk = W.normal_bf16_bits(90, seed, (block_elems,), sigma) if bf16 else W.normal_f16(90, seed, (block_elems,), sigma)
+    buf = DevBuf(env.gpu, nbytes)
+    buf.write(blk)
+    env.gpu.sync()
+    done = block_elems * 2
+    while done < nbytes:
+        n = min(done, nbytes - done)
+        check(env.gpu.api, env.gpu.api.ns_copy_dev(env.gpu.raw, buf.ptr + done, buf.ptr, n), "copy_dev")
+        done += n
+    env.gpu.sync()
+    return buf
 
 
-def cpu_time_decode(w, seconds=6.0, seq=0):
-    """The oracle's flash-numerics decode of ONE sequence of the workload on all host threads, repeated for about
-    `seconds`; returns (bytes/s, threads, repeats)."""
+# ---- workloads: each returns (step_fn, info) where info has the algorithmic work a step ------------------------------------
+
+def wl_gqa_decode(env, T, Hq, Hkv, D, kv, B, rotate=1, real_data=True):
+    """B sequences a GPU (each its own caches); `rotate` distinct cache sets used in turn so L2 cannot hold a step's reads."""
+    from nextsycl_b200 import DevBuf
+    from nextsycl_b200 import workloads as W
+    ops = env.ops
+    sets, keep, qs = [], [], []
+    for r in range(rotate):
+        seqs = []
+        for b in range(B):
+            if real_data:
+                q, k, v, p0 = W.gqa_case(2, T, Hq, Hkv, D, kv, seq=env.rank * B * rotate + r * B + b)
+                dk, dv = DevBuf.of(env.gpu, k), DevBuf.of(env.gpu, v)
+                if r == 0:
+                    qs.append(q)
+            else:
+                dk = device_random_f16(env, Hkv * kv * D * 2, 100 + 2 * (r * B + b))
+                dv = device_random_f16(env, Hkv * kv * D * 2, 101 + 2 * (r * B + b))
+                if r == 0:
+                    qs.append(W.normal_f16(2, 50 + b, (T, Hq * D)))
+            keep += [dk, dv]
+            seqs.append((dk, dv, kv, kv - T))
+        sets.append((ops.seq_table(seqs), seqs))
+    dq = DevBuf.of(env.gpu, np.stack(qs))
+    out = DevBuf(env.gpu, B * T * Hq * D * 2)
+    scratch = DevBuf(env.gpu, max(4, 4 * ops.gqa_decode_scratch(B, T, Hq, Hkv, D, kv)))
+    i = [0]
+
+    def step():
+        ops.gqa_decode(dq, Hq * D, T * Hq * D, sets[i[0] % rotate][0], B, T, Hq, Hkv, D, kv, out, scratch)
+        i[0] += 1
+    info = {"bytes": B * 2 * kv * Hkv * D * 2, "flops": 4 * (T * (kv - T) + T * (T + 1) // 2) * Hq * D * B, "bound": "hbm", "launches": 2,
+            "keep": (keep, sets, dq, out, scratch), "qs": qs, "seqs": sets[0][1]}
+    return step, info
+
+
+def wl_prefill(env, T, Hq, Hkv, D):
+    """Causal prefill from position 0, fp16; with several ranks each takes a contiguous share of the key heads (and their
+    query heads) - no exchange. With more ranks than key heads, ranks that share a key head each take a share of its
+    query heads (its K and V replicated)."""
+    from nextsycl_b200 import DevBuf
+    w = env.world
+    if w <= Hkv:
+        hkv_r, hq_r = Hkv // w, Hq // w
+    else:
+        hkv_r, hq_r = 1, Hq // w
+    q = device_random_f16(env, T * hq_r * D * 2, 1)
+    k = device_random_f16(env, hkv_r * T * D * 2, 2)
+    v = device_random_f16(env, hkv_r * T * D * 2, 3)
+    out = DevBuf(env.gpu, T * hq_r * D * 2)
+
+    def step():
+        env.ops.gqa_prefill(0, q, hq_r * D, k, v, T, hq_r, hkv_r, D, T, 0, out)
+    keys = T * (T + 1) // 2
+    info = {"flops": 4 * keys * hq_r * D, "flops_total": 4 * keys * Hq * D, "bytes": 2 * T * hkv_r * D * 2, "bound": "tensor", "launches": 1,
+            "keep": (q, k, v, out)}
+    return step, info
+
+
+def wl_mla_decode(env, n):
+    from nextsycl_b200 import DevBuf
+    from nextsycl_b200 import workloads as W
+    q = DevBuf.of(env.gpu, W.normal_f16(3, 0, (1, 128, 576)))
+    rotate = 3 if n * 1152 < 150e6 else 2
+    caches = [device_random_f16(env, n * 1152, 10 + r, 0.5) for r in range(rotate)]
+    out = DevBuf(env.gpu, 128 * 512 * 4)
+    sc = DevBuf(env.gpu, max(4, 4 * env.ops.mla_decode_scratch(1, 128, n - 1)))
+    i = [0]
+
+    def step():
+        env.ops.mla_decode(q, caches[i[0] % rotate], 1, 128, n - 1, float(1 / np.sqrt(192.0)), out, sc)
+        i[0] += 1
+    info = {"bytes": 1152 * n, "flops": 278528 * n, "bound": "hbm+tensor", "launches": 2, "keep": (q, caches, out, sc)}
+    return step, info
+
+
+def wl_mla_prefill(env, T=4096, p0=32768, H=128):
+    """BASELINE config 4: 4,096 new rows over a 32,768-token cache, bf16, 192-wide keys / 128-wide values; the 128 heads
+    sharded over the ranks (each rank its own heads' K and V; no exchange)."""
+    from nextsycl_b200 import DevBuf
+    h = H // env.world
+    n = p0 + T
+    q = device_random_f16(env, T * h * 192 * 2, 20, bf16=True)
+    k = device_random_f16(env, n * h * 192 * 2, 21, bf16=True)
+    v = device_random_f16(env, n * h * 128 * 2, 22, bf16=True)
+    out = DevBuf(env.gpu, T * h * 128 * 2)
+
+    def step():
+        env.ops.mla_prefill(q, h * 192, k, h * 192, v, h * 128, T, h, p0, float(1 / np.sqrt(192.0)), out)
+    keys = T * p0 + T * (T + 1) // 2
+    info = {"flops": keys * h * 2 * (192 + 128), "flops_total": keys * H * 2 * (192 + 128), "bytes": n * h * (192 + 128) * 2, "bound": "tensor",
+            "launches": 1, "keep": (q, k, v, out)}
+    return step, info
+
+
+def measure(env, name, steps, warmup):
+    """Builds the workload, times it, returns a result dict (per GPU figures plus the whole-job rate)."""
+    pk = peaks()
+    if name == "decode_c2":
+        step, info = wl_gqa_decode(env, 1, 64, 8, 128, 32768, 8)
+    elif name == "decode_c2_b1":
+        step, info = wl_gqa_decode(env, 1, 64, 8, 128, 32768, 1, rotate=3)
+    elif name == "decode_128k":
+        step, info = wl_gqa_decode(env, 1, 64, 8, 128, 131072, 1, rotate=2, real_data=False)
+    elif name == "decode_c5":
+        step, info = wl_gqa_decode(env, 4, 32, 4, 128, 262144, 1, rotate=2, real_data=False)
+    elif name == "prefill_16k":
+        step, info = wl_prefill(env, 16384, 16, 4, 128)
+    elif name == "prefill_c1":
+        step, info = wl_prefill(env, 2048, 16, 4, 128)
+    elif name.startswith("mla_decode_"):
+        step, info = wl_mla_decode(env, {"4k": 4096, "32k": 32768, "131k": 131072}[name.split("_")[-1]])
+    elif name == "mla_prefill_c4":
+        step, info = wl_mla_prefill(env)
+    else:
+        raise SystemExit(f"unknown workload {name}")
+    ms = env.timed(step, steps, max(3, warmup))
+    res = {"workload": name, "ms_per_step": ms, "steps": steps}
+    if "tensor" in info["bound"]:
+        tf = info["flops"] / (ms * 1e-3) / 1e12
+        res.update({"tflops_per_gpu": tf, "frac_of_bf16_peak": tf / float(pk["bf16_tflops"]),
+                    "frac_of_bf16_sustained": tf / float(pk.get("bf16_tflops_sustained", pk["bf16_tflops"]))})
+        if "flops_total" in info:
+            res["tflops_job"] = info["flops_total"] / (ms * 1e-3) / 1e12
+    if "hbm" in info["bound"]:
+        gbs = info["bytes"] / (ms * 1e-3) / 1e9
+        res.update({"gbs_per_gpu": gbs, "frac_of_hbm_peak": gbs / float(pk["hbm_gbs"])})
+    res["_info"] = info
+    return res
+
+
+OTHERS_1GPU = [("prefill_16k", 10), ("prefill_c1", 50), ("decode_c2_b1", 50), ("decode_128k", 30), ("decode_c5", 30), ("mla_decode_4k", 50),
+               ("mla_decode_32k", 50), ("mla_decode_131k", 30), ("mla_prefill_c4", 3)]
+OTHERS_NGPU = [("prefill_16k", 10), ("mla_prefill_c4", 3)]
+
+
+def config_of(name, n):
+    texts = {
+        "decode_c2": "config 2: GQA decode, 1 new token, 64 query / 8 key heads, head 128, 32,768 cached fp16 tokens, batch 8 per GPU",
+        "prefill_16k": "16K causal GQA prefill, 16 query / 4 key heads of 128, fp16 (config 1's geometry at the target length)",
+        "prefill_c1": "config 1: causal GQA prefill, 2,048 rows, 16 query / 4 key heads of 128, fp16",
+        "decode_c2_b1": "config 2, one sequence",
+        "decode_128k": "128K GQA decode, 64 query / 8 key heads of 128, one sequence (512 MiB of K+V)",
+        "decode_c5": "config 5 on one GPU: 4 verify rows, 32 query / 4 key heads of 128, 262,144 cached tokens (512 MiB of K+V)",
+        "mla_decode_4k": "config 3: absorbed MLA decode, 128 heads, 576-wide latent cache, 4,096 cells",
+        "mla_decode_32k": "config 3, 32,768 cells",
+        "mla_decode_131k": "config 3, 131,072 cells",
+        "mla_prefill_c4": "config 4: bf16 MLA prefill chunk, 4,096 rows over 32,768 cached, 128 heads (192/128), heads sharded over ranks",
+    }
+    return {"workload": texts.get(name, name), "name": name,
+            "l2": "inputs larger than L2, or several input sets used in turn", "parallelism": f"{n} GPU(s)"}
+
+
+# ---- reference arm --------------------------------------------------------------------------------------------------------
+
+def cpu_decode_rate(seconds, steps=None, warmup=1):
+    """The oracle's flash-numerics decode of ONE sequence of config 2 on all host threads; (bytes/s, threads, repeats, s each)."""
+    from nextsycl_b200 import workloads as W
     from oracle import oracle as O
-    q, k, v, p0 = make_seq(2, w, seq)
+    T, Hq, Hkv, D, kv = 1, 64, 8, 128, 32768
+    q, k, v, p0 = W.gqa_case(2, T, Hq, Hkv, D, kv, seq=0)
     qf, kb, vb = q.astype(np.float32), k.view(np.uint16), v.view(np.uint16)
-    O.gqa_flash_decode(qf, kb, vb, w["T"], w["Hq"], w["Hkv"], w["D"], w["kv"], p0)   # warm
+    for _ in range(warmup):
+        O.gqa_flash_decode(qf, kb, vb, T, Hq, Hkv, D, kv, p0)
     n, t0 = 0, time.perf_counter()
     while True:
-        O.gqa_flash_decode(qf, kb, vb, w["T"], w["Hq"], w["Hkv"], w["D"], w["kv"], p0)
+        O.gqa_flash_decode(qf, kb, vb, T, Hq, Hkv, D, kv, p0)
         n += 1
         dt = time.perf_counter() - t0
-        if dt >= seconds:
+        if (steps is not None and n >= steps) or (steps is None and dt >= seconds):
             break
-    return c2_bytes_per_seq(w) * n / dt, O.threads(), n, dt / n
+    return 2 * kv * Hkv * D * 2 * n / dt, O.threads(), n, dt / n
 
 
 def run_reference(args):
-    """--impl reference: the reference kernel's CPU restatement on the host cores; a step = one sequence of the batch
-    (1/8 of the workload's step; the metric is a rate, so the sample size does not scale it)."""
-    w = dict(C2)
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """--impl reference: the reference kernel's CPU restatement on the host cores. A step is one sequence of the batch
+    (1/8 of the headline step); the metric is a rate, so the sample size does not scale it."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    from oracle import oracle as O
-    q, k, v, p0 = make_seq(2, w, 0)
-    qf, kb, vb = q.astype(np.float32), k.view(np.uint16), v.view(np.uint16)
-    for _ in range(args.warmup):
-        O.gqa_flash_decode(qf, kb, vb, w["T"], w["Hq"], w["Hkv"], w["D"], w["kv"], p0)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        O.gqa_flash_decode(qf, kb, vb, w["T"], w["Hq"], w["Hkv"], w["D"], w["kv"], p0)
-    dt = (time.perf_counter() - t0) / args.steps
-    gbs = c2_bytes_per_seq(w) / dt / 1e9
+    bps, cores, n, per = cpu_decode_rate(0, steps=max(1, args.steps), warmup=max(1, args.warmup))
+    gbs = bps / 1e9
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": config_of(w, args.gpus),
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": O.threads(), "kind": "port",
-                         "sample": "one sequence of the batch (134,217,728 KV bytes) a step; CPU restatement of kernels/llm/qwen35/silo/attn.cpp "
-                                   "decode numerics, OpenMP over (row, head); the SYCL reference itself cannot be built without oneAPI"},
+        "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": config_of("decode_c2", args.gpus),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": "one sequence of the batch (134,217,728 KV bytes) a step; CPU restatement of the decode numerics of "
+                                   "kernels/llm/qwen35/silo/attn.cpp, OpenMP over (row, head); the SYCL reference cannot be built without oneAPI"},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
 
 
-def config_of(w, n):
-    return {"workload": "config 2: GQA decode, 1 new token, 64 query / 8 key heads, head 128, 32,768 cached fp16 tokens, batch 8 per GPU",
-            "batch_per_gpu": w["B"], "kv_len": w["kv"], "q_heads": w["Hq"], "kv_heads": w["Hkv"], "head_dim": w["D"],
-            "l2": "inputs larger than L2 (1 GiB of K+V per GPU per step)", "parallelism": f"sequences sharded, {n} GPU(s), no exchange"}
+# ---- our arm --------------------------------------------------------------------------------------------------------------
 
-
-def run_ours(args):
-    from nextsycl_b200 import DevBuf, Gpu, HostBuf, Ops
-    w = dict(C2)
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    gpu = Gpu(local)
-    ops = Ops(gpu)
-    T, Hq, Hkv, D, kv, B = w["T"], w["Hq"], w["Hkv"], w["D"], w["kv"], w["B"]
-
-    # ---- inputs resident in HBM: B sequences with their own caches (distinct seeds per rank and sequence)
-    seqs, qs, keep = [], [], []
-    for b in range(B):
-        q, k, v, p0 = make_seq(2, w, rank * B + b)
-        qs.append(q)
-        dk, dv = DevBuf.of(gpu, k), DevBuf.of(gpu, v)
-        keep += [dk, dv]
-        seqs.append((dk, dv, kv, p0))
-    dq = DevBuf.of(gpu, np.stack(qs))
-    table = ops.seq_table(seqs)
-    out = DevBuf(gpu, B * T * Hq * D * 2)
-    scratch = DevBuf(gpu, max(4, 4 * ops.gqa_decode_scratch(B, T, Hq, Hkv, D, kv)))
-
-    def step():
-        ops.gqa_decode(dq, Hq * D, T * Hq * D, table, B, T, Hq, Hkv, D, kv, out, scratch)
-
-    def barrier():
-        gpu.sync()
-        if dist:
-            import torch
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
-        barrier()
-        a = gpu.stamp()
-        for _ in range(steps):
-            fn()
-        b = gpu.stamp()
-        gpu.sync()
-        ms = gpu.elapsed_ns(a, b) / 1e6
-        barrier()
-        if dist:
-            import torch
-            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-
-    sampler = ClockSampler(local)
-    sampler.start()
-    ms = timed(step, args.steps, max(3, args.warmup))
-    clocks = sampler.stop()
-    ms_step = ms / args.steps
-    bytes_step = B * c2_bytes_per_seq(w)
-    value = world * bytes_step / (ms_step * 1e-3) / 1e9
-
-    if args.kernel_only:
-        if rank == 0:
-            print(json.dumps({"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "ms_per_step": ms_step,
-                              "kernel_only": True, "clocks": clocks}))
-        if dist:
-            dist.destroy_process_group()
-        gpu.close()
-        return
-
-    # ---- end to end through the reference's calls, host buffers in, host buffer out
-    hq = HostBuf(gpu, B * Hq * D * 4)
-    hk = HostBuf(gpu, B * Hkv * D * 4)
-    hv = HostBuf(gpu, B * Hkv * D * 4)
-    ho = HostBuf(gpu, B * Hq * D * 4)
+def e2e_decode(env, info, steps):
+    """Config 2 through the reference's own calls from pinned host buffers; seconds a step (max over ranks)."""
+    from nextsycl_b200 import DevBuf, HostBuf
     from nextsycl_b200 import workloads as W
+    gpu, ops = env.gpu, env.ops
+    T, Hq, Hkv, D, kv, B = 1, 64, 8, 128, 32768, 8
+    seqs, qs = info["seqs"], info["qs"]
+    hq, hk, hv, ho = HostBuf(gpu, B * Hq * D * 4), HostBuf(gpu, B * Hkv * D * 4), HostBuf(gpu, B * Hkv * D * 4), HostBuf(gpu, B * Hq * D * 4)
     hq.array(np.float32)[:] = np.stack(qs).astype(np.float32).ravel()
-    hk.array(np.float32)[:] = W.rng(2, 9001 + rank).standard_normal(B * Hkv * D, dtype=np.float32)
-    hv.array(np.float32)[:] = W.rng(2, 9002 + rank).standard_normal(B * Hkv * D, dtype=np.float32)
-    dqf = DevBuf(gpu, B * Hq * D * 4)
-    dkf = DevBuf(gpu, B * Hkv * D * 4)
-    dvf = DevBuf(gpu, B * Hkv * D * 4)
-    dof = DevBuf(gpu, B * Hq * D * 4)
+    hk.array(np.float32)[:] = W.rng(2, 9001 + env.rank).standard_normal(B * Hkv * D, dtype=np.float32)
+    hv.array(np.float32)[:] = W.rng(2, 9002 + env.rank).standard_normal(B * Hkv * D, dtype=np.float32)
+    dqf, dkf, dvf, dof = DevBuf(gpu, hq.len), DevBuf(gpu, hk.len), DevBuf(gpu, hv.len), DevBuf(gpu, ho.len)
     sc1 = DevBuf(gpu, max(4, 4 * ops.attn_decode_scratch(T, Hq, Hkv, D, kv - 1)))
     api, raw = gpu.api, gpu.raw
-
     views = [(dkf.view(b * Hkv * D * 4, Hkv * D * 4), dvf.view(b * Hkv * D * 4, Hkv * D * 4), dqf.view(b * Hq * D * 4, Hq * D * 4),
               dof.view(b * Hq * D * 4, Hq * D * 4)) for b in range(B)]
 
-    def e2e_step():
+    def step():
         api.ns_copy_to(raw, dqf.ptr, hq.ptr, hq.len)
         api.ns_copy_to(raw, dkf.ptr, hk.ptr, hk.len)
         api.ns_copy_to(raw, dvf.ptr, hv.ptr, hv.len)
@@ -264,48 +397,89 @@ def run_ours(args):
         api.ns_copy_from(raw, ho.ptr, dof.ptr, ho.len)
         gpu.sync()
 
-    e2e_steps = max(5, min(args.steps, 200))
     for _ in range(3):
-        e2e_step()
-    barrier()
+        step()
+    env.barrier()
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
-    if dist:
-        import torch
-        t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_val = world * bytes_step / e2e_s / 1e9
+    for _ in range(steps):
+        step()
+    s = (time.perf_counter() - t0) / steps
+    return env.max_over_ranks(s), int(hq.len + hk.len + hv.len), int(ho.len)
 
-    if rank == 0:
-        pk = peaks()
-        hbm = float(pk["hbm_gbs"])
-        per_gpu = bytes_step / (ms_step * 1e-3) / 1e9
-        line = {
-            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": config_of(w, world),
-            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": hbm, "unit": "GB/s", "frac": per_gpu / hbm, "traffic": None,
-                         "peak_source": pk["_source"],
-                         "note": "per GPU; algorithmic bytes = 2*kv*Hkv*D*2 B a sequence x 8 sequences a launch; duration = CUDA-event time of a "
-                                 "step (the split kernel plus its merge kernel)"},
-            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": int(hq.len + hk.len + hv.len), "d2h_bytes_per_step": int(ho.len),
-                    "ms_per_step": e2e_s * 1e3,
-                    "path": "per sequence: ns_copy_to q,k,v rows (pinned) -> ns_q35_kv_store -> ns_q35_attn_decode -> ns_copy_from out; ns_sync a step"},
-            "gpu_launches": int(args.steps * 2),
-            "clocks": clocks,
-        }
+
+def run_ours(args):
+    env = Env()
+    pk = peaks()
+    name = args.workload
+    sampler = ClockSampler(env.local)
+    sampler.start()
+    res = measure(env, name, args.steps, args.warmup)
+    clocks = sampler.stop()
+    info = res.pop("_info")
+    ms = res["ms_per_step"]
+    world = env.world
+
+    if name.startswith("decode"):
+        value, unit = world * info["bytes"] / (ms * 1e-3) / 1e9, "GB/s"
+        roof = {"bound": "hbm", "achieved": res["gbs_per_gpu"], "peak": float(pk["hbm_gbs"]), "unit": "GB/s", "frac": res["frac_of_hbm_peak"],
+                "traffic": None, "peak_source": pk["_source"],
+                "note": "per GPU; algorithmic bytes = 2*kv*Hkv*D*2 B a sequence x sequences a launch; duration = CUDA-event time of a step "
+                        "(the split kernel plus its merge kernel)"}
+        scaling = "weak"
+    elif name.startswith("mla_decode"):
+        value, unit = info["bytes"] / (ms * 1e-3) / 1e9, "GB/s"
+        roof = {"bound": "hbm", "achieved": res["gbs_per_gpu"], "peak": float(pk["hbm_gbs"]), "unit": "GB/s", "frac": res["frac_of_hbm_peak"],
+                "traffic": None, "peak_source": pk["_source"], "note": "algorithmic bytes = 1,152 B a cell; flops 278,528 a cell",
+                "tensor_frac": info["flops"] / (ms * 1e-3) / 1e12 / float(pk["bf16_tflops"])}
+        scaling = "weak"
+    else:
+        value, unit = res.get("tflops_job", res["tflops_per_gpu"]), "TFLOP/s"
+        roof = {"bound": "tensor", "achieved": res["tflops_per_gpu"], "peak": float(pk["bf16_tflops"]), "unit": "TFLOP/s",
+                "frac": res["frac_of_bf16_peak"], "traffic": None, "peak_source": pk["_source"],
+                "note": "per GPU; causal-exact flops (masked tiles not counted) / CUDA-event time; burst bf16 peak"}
+        scaling = "strong"
+
+    if args.kernel_only:
+        if env.rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "ms_per_step": ms,
+                              "kernel_only": True, "config": config_of(name, world), "clocks": clocks}))
+        env.close()
+        return
+
+    line = {
+        "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "bf16" if name == "mla_prefill_c4" else "f16", "data": "synthetic",
+        "config": config_of(name, world), "roofline": roof, "gpu_launches": int(args.steps * info["launches"]), "clocks": clocks,
+    }
+    if name == "decode_c2":
+        e2e_steps = max(5, min(args.steps, 200))
+        s, h2d, d2h = e2e_decode(env, info, e2e_steps)
+        line["e2e"] = {"value": world * info["bytes"] / s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "ms_per_step": s * 1e3,
+                       "path": "per sequence: ns_copy_to q,k,v rows (pinned) -> ns_q35_kv_store -> ns_q35_attn_decode -> ns_copy_from out; ns_sync a step"}
+    del info, res
+
+    if not args.no_others:
+        others = {}
+        for oname, osteps in (OTHERS_1GPU if world == 1 else OTHERS_NGPU):
+            if oname == name:
+                continue
+            try:
+                r = measure(env, oname, osteps, 3)
+                r.pop("_info")
+                others[oname] = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in r.items() if k != "workload"}
+            except Exception as e:   # a failed extra must not take the headline with it
+                others[oname] = {"error": str(e)[:200]}
+        line["others"] = others
+
+    if env.rank == 0:
         if world == 1 and not args.no_cpu:
-            bps, cores, n, per = cpu_time_decode(w, seconds=args.cpu_seconds)
+            bps, cores, n, per = cpu_decode_rate(args.cpu_seconds)
             line["cpu_baseline"] = {"value": bps / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-                                    "sample": f"one sequence of the batch (134,217,728 KV bytes) x {n} repeats, {per * 1e3:.1f} ms each; "
+                                    "sample": f"one sequence of config 2 (134,217,728 KV bytes) x {n} repeats, {per * 1e3:.1f} ms each; "
                                               "CPU restatement of the reference decode kernel's numerics"}
         print(json.dumps(line))
-    if dist:
-        dist.destroy_process_group()
-    gpu.close()
+    env.close()
 
 
 def main():
@@ -314,9 +488,11 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode_c2")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-others", action="store_true", help="skip the other configurations")
     ap.add_argument("--cpu-seconds", type=float, default=6.0)
-    ap.add_argument("--kernel-only", action="store_true", help="device-timed leg only (no end-to-end or CPU leg): for profiler runs")
+    ap.add_argument("--kernel-only", action="store_true", help="device-timed headline only (no end-to-end, CPU or other legs): for profiler runs")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
