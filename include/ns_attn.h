@@ -116,6 +116,31 @@ int ns_ds2_mla_decode(ns_gpu* g, const float* q, const uint16_t* kb, const uint1
 int64_t ns_b200_mla_decode_scratch(ns_gpu* g, int64_t T, int64_t H, int64_t pos0);
 int ns_b200_mla_decode(ns_gpu* g, const void* q, const void* cache, int64_t T, int64_t H, int64_t pos0, float scale, float* out, float* scratch);
 
+/* One long context split over several GPUs by contiguous key ranges, with a log-sum-exp combine (no counterpart in
+ * the reference, which runs a context on one GPU and moves activations between GPUs through host memory,
+ * kernels/ns/ns.cpp:244-250). Rank r holds the keys [key_base, key_base + kv_local) of every key head in its own caches
+ * [Hkv][kv_local][D] fp16; q [T][Hq*D] fp16 is the same on all ranks; row t sees global keys 0 .. p0+t.
+ *   ns_b200_kvsplit_decode  - this rank's keys: split-KV decode, then its (O, m, l) per (row, head) is stored into slot
+ *     `rank` of EVERY rank's mailbox (mailboxes: a DEVICE array of nranks mailbox addresses as this GPU sees them -
+ *     its own and the peers' IPC-opened ones) and the epoch is published in each (release, system scope).
+ *   ns_b200_kvsplit_combine - waits on the device, polling this rank's OWN mailbox for at most wait_us microseconds,
+ *     until all ranks published `epoch`, then merges them into out [T][Hq*D] fp16. If the wait runs out the kernel
+ *     leaves, nothing is written, and the next ns_sync returns -1 ("gave up a bounded wait (code 701)").
+ * Epochs count from 1 and must increase by one per step on every rank (two buffers alternate by epoch parity, so a rank
+ * may run one step ahead of its peers, never two). A mailbox is ns_b200_kvsplit_mailbox_bytes bytes, zeroed once. */
+int64_t ns_b200_kvsplit_mailbox_bytes(int64_t nranks, int64_t T, int64_t Hq, int64_t D);
+int64_t ns_b200_kvsplit_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t kv_local);
+int ns_b200_kvsplit_decode(ns_gpu* g, const void* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                           int64_t kv_local, int64_t key_base, int64_t p0, float* scratch, int64_t rank, int64_t nranks, void* const* mailboxes,
+                           int64_t epoch);
+int ns_b200_kvsplit_combine(ns_gpu* g, const void* mailbox, int64_t nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t wait_us,
+                            void* out);
+/* Device memory shared between processes of one machine (CUDA IPC): a 64-byte handle for ptr (the start of an
+ * ns_alloc allocation), opened in another process as a peer-mapped address, closed when done. */
+int ns_b200_ipc_export(ns_gpu* g, void* ptr, void* handle64);
+int ns_b200_ipc_open(ns_gpu* g, const void* handle64, void** out);
+int ns_b200_ipc_close(ns_gpu* g, void* ptr);
+
 /* No counterpart in the reference. ns_b200_gqa_decode for callers that can neither pass scratch nor tolerate an
  * allocation: an engine whose device memory was planned to the last byte at load time, or a serving loop that must
  * not hit the device-wide synchronisation a cudaMalloc brings. The split partials go to an array built into the

@@ -2,6 +2,7 @@
 #include "kernels.cuh"
 
 #include <algorithm>
+#include <cstring>
 
 int ns_prefill_f32(ns_gpu* g, const char* name, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv,
                    int64_t D, int64_t cap, int64_t p0, float* out);
@@ -154,6 +155,85 @@ int ns_b200_gqa_decode(ns_gpu* g, const void* q, int64_t qs, int64_t q_seq, cons
     a.q_f32 = 0, a.out_f32 = 0;
     return ns_launch_gqa_decode(g, a, name);
     NS_CATCH("ns_b200_gqa_decode")
+}
+
+// ---- one long context split over several GPUs by key ranges (the log-sum-exp combine is the path's one exchange) -------
+
+int64_t ns_b200_kvsplit_mailbox_bytes(int64_t nranks, int64_t T, int64_t Hq, int64_t D) {
+    if (nranks < 1 || T < 1 || Hq < 1 || D < 1) return 0;
+    return ns_mbox_bytes((int) nranks, T * Hq, D);
+}
+
+int64_t ns_b200_kvsplit_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t kv_local) {
+    if (T < 1 || Hkv < 1 || kv_local < 1) return 0;
+    return T * Hq * ns_dec_splits(kv_local, Hkv) * (D + 2);   // every row keeps its partial, also with one split
+}
+
+int ns_b200_kvsplit_decode(ns_gpu* g, const void* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                           int64_t kv_local, int64_t key_base, int64_t p0, float* scratch, int64_t rank, int64_t nranks, void* const* mailboxes,
+                           int64_t epoch) {
+    NS_TRY
+    const char* name = "ns_b200_kvsplit_decode";
+    if (ns_enter(g, name)) return -1;
+    if (T < 1 || T > 8 || !shape_ok(Hq, Hkv, D)) return ns_fail(std::string(name) + ": 1..8 rows, heads of 128 or 256, 1..16 query heads a key head");
+    if (nranks < 1 || nranks > 64 || rank < 0 || rank >= nranks) return ns_fail(std::string(name) + ": rank within 1..64 ranks");
+    if (kv_local < 1 || kv_local >= ((int64_t) 1 << 31) || key_base < 0 || p0 < 0 || p0 + T >= ((int64_t) 1 << 40))
+        return ns_fail(std::string(name) + ": a key range of 1 .. 2^31 keys");
+    if (epoch < 1) return ns_fail(std::string(name) + ": epochs count from 1");
+    if (qs % 8 != 0 || ((uintptr_t) q & 15) != 0) return ns_fail(std::string(name) + ": query rows 16-byte aligned");
+    if (!q || !kc || !vc || !scratch || !mailboxes) return ns_fail(std::string(name) + ": a null buffer");
+    GqaDecodeArgs a{};
+    a.q = q;
+    a.qs = qs;
+    a.q_seq = 0;
+    a.seqs = nullptr;
+    a.one = ns_b200_seq{kc, vc, kv_local, p0 - key_base};   // the slice's capacity bounds what each row sees of it
+    a.out = nullptr;
+    a.part = scratch;
+    a.B = 1, a.T = T, a.Hq = Hq, a.Hkv = Hkv, a.D = D;
+    a.ns_max = ns_dec_splits(kv_local, Hkv);
+    a.q_f32 = 0, a.out_f32 = 0;
+    a.mailboxes = (float* const*) mailboxes;
+    a.rank = (int) rank;
+    a.nranks = (int) nranks;
+    a.epoch = epoch;
+    return ns_launch_gqa_decode(g, a, name);
+    NS_CATCH("ns_b200_kvsplit_decode")
+}
+
+int ns_b200_kvsplit_combine(ns_gpu* g, const void* mailbox, int64_t nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t wait_us,
+                            void* out) {
+    NS_TRY
+    const char* name = "ns_b200_kvsplit_combine";
+    if (ns_enter(g, name)) return -1;
+    if (!mailbox || !out) return ns_fail(std::string(name) + ": a null buffer");
+    if (nranks < 1 || nranks > 64 || T < 1 || T > 8 || Hq < 1 || epoch < 1) return ns_fail(std::string(name) + ": 1..64 ranks, 1..8 rows, epochs from 1");
+    if (wait_us < 1 || wait_us > 2000000) return ns_fail(std::string(name) + ": a wait of 1 us .. 2 s");
+    return ns_launch_gqa_combine(g, (const float*) mailbox, (int) nranks, T, Hq, D, epoch, wait_us * 10, out, 0, name);
+    NS_CATCH("ns_b200_kvsplit_combine")
+}
+
+int ns_b200_ipc_export(ns_gpu* g, void* ptr, void* handle64) {
+    if (ns_enter(g, "ns_b200_ipc_export")) return -1;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    if (!ptr || !handle64) return ns_fail("ns_b200_ipc_export: a null argument");
+    NS_CUDA(cudaIpcGetMemHandle((cudaIpcMemHandle_t*) handle64, ptr), "ns_b200_ipc_export");
+    return 0;
+}
+
+int ns_b200_ipc_open(ns_gpu* g, const void* handle64, void** out) {
+    if (ns_enter(g, "ns_b200_ipc_open")) return -1;
+    if (!handle64 || !out) return ns_fail("ns_b200_ipc_open: a null argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    NS_CUDA(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess), "ns_b200_ipc_open");
+    return 0;
+}
+
+int ns_b200_ipc_close(ns_gpu* g, void* ptr) {
+    if (ns_enter(g, "ns_b200_ipc_close")) return -1;
+    if (ptr) NS_CUDA(cudaIpcCloseMemHandle(ptr), "ns_b200_ipc_close");
+    return 0;
 }
 
 }  // extern "C"

@@ -59,7 +59,16 @@ struct Params {
     int T, Hq, Hkv, G, ns_max, groups;
     int q_f32, out_f32;
     float qscale;
+    // KV-split over several GPUs: every row's partial is kept (never normalised here) and the merge pushes this
+    // rank's (O, m, l) into every rank's mailbox
+    int force_part;
+    int rank, nranks;
+    float* const* mailboxes;   // device array [nranks]: each rank's mailbox as this GPU sees it (peer-mapped)
+    long long epoch;
 };
+
+// keys row t of a sequence sees: its causal length, bounded by what the cache slice holds
+__device__ __forceinline__ int64_t row_keys(const ns_b200_seq& s, int t) { return min(s.p0 + t + 1, s.cap); }
 
 // byte offset of 16-byte chunk c of row r in a tile whose rows are ROWB bytes: chunks XOR-swizzled by the row
 template <int ROWB>
@@ -120,7 +129,7 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
     // rows of one pass share a split size; where the rows' own sizes differ (a row's context crosses a step of the
     // split function) the rows go one at a time, each with its own - the same arithmetic either way
     bool same = true;
-    for (int t = t_lo; t <= t_hi; ++t) same = same && ns_dec_split(p0 + t + 1, p.Hkv) == ns_dec_split(p0 + t_lo + 1, p.Hkv);
+    for (int t = t_lo; t <= t_hi; ++t) same = same && ns_dec_split(row_keys(seq, t), p.Hkv) == ns_dec_split(row_keys(seq, t_lo), p.Hkv);
     const int npass = same ? 1 : t_hi - t_lo + 1;
 
     const uint8_t* kbase = (const uint8_t*) seq.kc + (int64_t) hk * seq.cap * ROWB;
@@ -128,8 +137,8 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
 
     for (int pass = 0; pass < npass; ++pass) {
         const int t_a = same ? t_lo : t_lo + pass, t_b = same ? t_hi : t_a;
-        const int64_t kb = ns_dec_split(p0 + t_a + 1, p.Hkv);
-        const int64_t kv_end = p0 + t_b + 1;
+        const int64_t kb = ns_dec_split(row_keys(seq, t_a), p.Hkv);
+        const int64_t kv_end = row_keys(seq, t_b);
         const int64_t jbeg = (int64_t) split * kb, jend = min(kv_end, (int64_t) (split + 1) * kb);
         if (jbeg >= jend) continue;   // the whole CTA
         const int ntiles = (int) ((jend - jbeg + KT - 1) / KT);
@@ -291,7 +300,7 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
             if (rho >= R) break;   // i ascends with r
             const int t = rho / G, gq = rho % G;
             if (t < t_a || t > t_b) continue;
-            const int64_t kv = p0 + t + 1;
+            const int64_t kv = row_keys(seq, t);
             if (jbeg >= kv) continue;   // this split holds none of the row's keys: not one of its splits
             float mx = -INFINITY;
 #pragma unroll
@@ -308,7 +317,7 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
             }
             const int hq = hk * G + gq;
             const int64_t row = ((int64_t) b * T + t) * p.Hq + hq;
-            if (ns_dec_splits(kv, p.Hkv) == 1) {
+            if (ns_dec_splits(kv, p.Hkv) == 1 && !p.force_part) {
                 const float v = L > 0.f ? A / L : 0.f;
                 if (p.out_f32) ((float*) p.out)[row * D + d] = v;
                 else ((__half*) p.out)[row * D + d] = __float2half_rn(v);
@@ -333,8 +342,8 @@ __global__ void __launch_bounds__(D) gqa_merge_kernel(const Params p) {
     const int d = threadIdx.x;
     const int hq = (int) (rh % p.Hq), t = (int) ((rh / p.Hq) % p.T), b = (int) (rh / ((int64_t) p.Hq * p.T));
     (void) hq;
-    const int64_t p0 = p.seqs ? p.seqs[b].p0 : p.one.p0;
-    const int nsr = (int) ns_dec_splits(p0 + t + 1, p.Hkv);
+    const ns_b200_seq seq = p.seqs ? p.seqs[b] : p.one;
+    const int nsr = (int) ns_dec_splits(row_keys(seq, t), p.Hkv);
     if (nsr == 1) return;
     const float* pp = p.part + rh * p.ns_max * (D + 2);
     float mx = -INFINITY;
@@ -353,6 +362,114 @@ __global__ void __launch_bounds__(D) gqa_merge_kernel(const Params p) {
     else ((__half*) p.out)[rh * D + d] = __float2half_rn(v);
 }
 
+// KV split over several GPUs, this rank's side: its key splits merged into one partial (O, m, l) per (row, head), which
+// is stored - with plain stores over NVLink - into slot `rank` of EVERY rank's mailbox; the last block to finish
+// publishes the epoch in every mailbox's flag for this rank (release at system scope). One sequence.
+template <int D>
+__global__ void __launch_bounds__(D) gqa_merge_push_kernel(const Params p) {
+    const int64_t rh = blockIdx.x;   // (t, hq)
+    const int d = threadIdx.x;
+    const int t = (int) (rh / p.Hq);
+    const ns_b200_seq seq = p.seqs ? p.seqs[0] : p.one;
+    const int64_t kv = row_keys(seq, t);
+    const int nsr = kv > 0 ? (int) ns_dec_splits(kv, p.Hkv) : 0;
+    const float* pp = p.part + rh * p.ns_max * (D + 2);
+    float mx = -INFINITY;
+    for (int k = 0; k < nsr; ++k) mx = fmaxf(mx, pp[k * (D + 2) + D]);
+    float L = 0.f, A = 0.f;
+    if (mx != -INFINITY) {
+        for (int k = 0; k < nsr; ++k) {
+            const float mk = pp[k * (D + 2) + D];
+            const float e = mk == -INFINITY ? 0.f : exp2f(mk - mx);
+            L += pp[k * (D + 2) + D + 1] * e;
+            A += pp[k * (D + 2) + d] * e;
+        }
+    }
+    const int64_t rows = (int64_t) p.T * p.Hq;
+    const int buf = (int) (p.epoch & 1);
+    for (int r = 0; r < p.nranks; ++r) {
+        float* slot = p.mailboxes[r] + ns_mbox_slot(buf, p.rank, p.nranks, rows, D) + rh * (D + 2);
+        slot[d] = A;
+        if (d == 0) {
+            slot[D] = mx;
+            slot[D + 1] = L;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (d == 0) {
+        // the counter lives in this rank's own mailbox and returns to zero for the next call
+        int* counter = reinterpret_cast<int*>(p.mailboxes[p.rank] + ns_mbox_flags_off(p.nranks, rows, D)) + 4 * p.nranks;
+        const int done = atomicAdd(counter, 1) + 1;
+        if (done == (int) gridDim.x) {
+            *counter = 0;
+            __threadfence_system();
+            for (int r = 0; r < p.nranks; ++r) {
+                long long* flag = reinterpret_cast<long long*>(p.mailboxes[r] + ns_mbox_flags_off(p.nranks, rows, D)) + buf * p.nranks + p.rank;
+                asm volatile("st.release.sys.global.s64 [%0], %1;\n" ::"l"(flag), "l"(p.epoch) : "memory");
+            }
+        }
+    }
+}
+
+struct CombineParams {
+    const float* mailbox;   // this rank's own mailbox (local memory)
+    void* out;              // [T][Hq*D] fp16 or fp32
+    int* status;
+    int nranks, D, out_f32;
+    long long rows, epoch, spins;
+};
+
+// The other side: waits - with a bounded poll of LOCAL memory - until every rank's flag shows this epoch, then merges
+// the ranks' partials (attn.cpp:352-368's formula across ranks). A wait that runs out writes status code 701 and the
+// block leaves without touching the output.
+template <int D>
+__global__ void __launch_bounds__(D) gqa_combine_kernel(const CombineParams c) {
+    __shared__ int ready;
+    const int64_t rh = blockIdx.x;
+    const int d = threadIdx.x;
+    const int buf = (int) (c.epoch & 1);
+    if (d == 0) {
+        const long long* flags = reinterpret_cast<const long long*>(c.mailbox + ns_mbox_flags_off(c.nranks, c.rows, D)) + buf * c.nranks;
+        int ok = 1;
+        for (int r = 0; r < c.nranks && ok; ++r) {
+            long long v = 0, it = 0;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.s64 %0, [%1];\n" : "=l"(v) : "l"(flags + r) : "memory");
+                if (v >= c.epoch) break;
+                if (++it > c.spins) {
+                    ok = 0;
+                    break;
+                }
+                __nanosleep(100);
+            }
+        }
+        if (!ok && c.status) {
+            *(volatile int*) c.status = 701;
+            __threadfence_system();
+        }
+        ready = ok;
+    }
+    __syncthreads();
+    if (!ready) return;
+    const float* base = c.mailbox + ns_mbox_slot(buf, 0, c.nranks, c.rows, D) + rh * (D + 2);
+    const int64_t stride = c.rows * (D + 2);
+    float mx = -INFINITY;
+    for (int r = 0; r < c.nranks; ++r) mx = fmaxf(mx, base[r * stride + D]);
+    float L = 0.f, A = 0.f;
+    if (mx != -INFINITY) {
+        for (int r = 0; r < c.nranks; ++r) {
+            const float mk = base[r * stride + D];
+            const float e = mk == -INFINITY ? 0.f : exp2f(mk - mx);
+            L += base[r * stride + D + 1] * e;
+            A += base[r * stride + d] * e;
+        }
+    }
+    const float v = L > 0.f ? A / L : 0.f;
+    if (c.out_f32) ((float*) c.out)[rh * D + d] = v;
+    else ((__half*) c.out)[rh * D + d] = __float2half_rn(v);
+}
+
 template <int D, int MT, int NSTAGE>
 int launch(ns_gpu* g, const Params& p, int64_t B, const char* where) {
     constexpr int RG = 16 * MT;
@@ -367,7 +484,10 @@ int launch(ns_gpu* g, const Params& p, int64_t B, const char* where) {
     dim3 grid((unsigned) p.ns_max, (unsigned) p.Hkv, (unsigned) (B * p.groups));
     kern<<<grid, THREADS, smem, g->compute>>>(p);
     if (ns_launched(where)) return -1;
-    if (p.ns_max > 1) {
+    if (p.mailboxes) {
+        gqa_merge_push_kernel<D><<<(unsigned) (p.T * p.Hq), D, 0, g->compute>>>(p);
+        if (ns_launched(where)) return -1;
+    } else if (p.ns_max > 1) {
         gqa_merge_kernel<D><<<(unsigned) (B * p.T * p.Hq), D, 0, g->compute>>>(p);
         if (ns_launched(where)) return -1;
     }
@@ -393,6 +513,11 @@ int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where) {
     p.q_f32 = a.q_f32;
     p.out_f32 = a.out_f32;
     p.qscale = 1.0f / sqrtf((float) a.D) * 1.4426950408889634f;
+    p.force_part = a.mailboxes ? 1 : 0;
+    p.rank = a.rank;
+    p.nranks = a.nranks;
+    p.mailboxes = a.mailboxes;
+    p.epoch = a.epoch;
     const int R = p.T * p.G;
     if (a.B * (int64_t) ((R + 15) / 16) > 65535) return ns_fail(std::string(where) + ": too many sequences for one launch");
     if (a.D == 128) {
@@ -472,4 +597,22 @@ extern "C" int ns_b200_gqa_decode_static(ns_gpu* g, const void* q, int64_t qs, i
     a.q_f32 = 0, a.out_f32 = 0;
     return ns_launch_gqa_decode(g, a, name);
     NS_CATCH("ns_b200_gqa_decode_static")
+}
+
+int ns_launch_gqa_combine(ns_gpu* g, const float* mailbox, int nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t spins, void* out,
+                          int out_f32, const char* where) {
+    CombineParams c;
+    c.mailbox = mailbox;
+    c.out = out;
+    c.status = g->status_dev;
+    c.nranks = nranks;
+    c.D = (int) D;
+    c.out_f32 = out_f32;
+    c.rows = T * Hq;
+    c.epoch = epoch;
+    c.spins = spins;
+    if (D == 128) gqa_combine_kernel<128><<<(unsigned) (T * Hq), 128, 0, g->compute>>>(c);
+    else if (D == 256) gqa_combine_kernel<256><<<(unsigned) (T * Hq), 256, 0, g->compute>>>(c);
+    else return ns_fail(std::string(where) + ": heads of 128 or 256");
+    return ns_launched(where);
 }

@@ -30,7 +30,25 @@ struct GqaDecodeArgs {
     int64_t B, T, Hq, Hkv, D;
     int64_t ns_max;            // splits the partial buffer is laid out for
     int q_f32, out_f32;
+    // KV split over several GPUs (null mailboxes: a whole sequence on this GPU)
+    float* const* mailboxes;   // device array [nranks] of mailbox bases as this GPU addresses them
+    int rank, nranks;
+    int64_t epoch;
 };
+
+// A rank's mailbox for the KV-split combine, in floats from its base: partials [2 buffers][nranks][rows][D+2], then
+// (16-float aligned) the flags [2][nranks] as 64-bit epochs and a block counter.
+__host__ __device__ inline int64_t ns_mbox_slot(int buf, int rank, int nranks, int64_t rows, int64_t D) {
+    return ((int64_t) (buf * nranks + rank) * rows) * (D + 2);
+}
+__host__ __device__ inline int64_t ns_mbox_flags_off(int nranks, int64_t rows, int64_t D) {
+    return (2 * (int64_t) nranks * rows * (D + 2) + 15) / 16 * 16;
+}
+__host__ __device__ inline int64_t ns_mbox_bytes(int nranks, int64_t rows, int64_t D) {
+    return ns_mbox_flags_off(nranks, rows, D) * 4 + 2 * (int64_t) nranks * 8 + 64;
+}
+int ns_launch_gqa_combine(ns_gpu* g, const float* mailbox, int nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t spins, void* out,
+                          int out_f32, const char* where);
 int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where);
 
 // ---- cache writers (kv_store.cu) ------------------------------------------------------------------------------------

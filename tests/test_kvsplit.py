@@ -1,0 +1,112 @@
+"""The KV-split decode across ranks.
+
+CPU part: the partition of a context into key ranges, and the handle exchange over torch.distributed (gloo, 2 ranks).
+GPU part (one GPU): all ranks' slices run one after another on the same stream, each pushing into every rank's
+mailbox, then each rank's combine - by then every flag is set, so nothing ever waits on another launch. A combine whose
+peer never published gives up its bounded wait and the next sync reports it."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from nextsycl_b200.dist import key_ranges
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_key_ranges_cover_the_context():
+    for kv, n in [(262144, 8), (262144, 1), (1000, 4), (100, 8), (65, 2), (64, 2)]:
+        r = key_ranges(kv, n)
+        assert len(r) == n and r[0][0] == 0
+        assert sum(c for _, c in r) == kv
+        for (b0, c0), (b1, _) in zip(r, r[1:]):
+            assert b1 == b0 + c0
+            assert b1 % 64 == 0 or b1 == kv
+    assert key_ranges(262144, 8)[3] == (98304, 32768)
+
+
+GLOO_SCRIPT = r"""
+import os, sys
+sys.path.insert(0, %r)
+import torch.distributed as dist
+from nextsycl_b200.dist import key_ranges
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%%s" %% sys.argv[1], rank=int(sys.argv[2]), world_size=2)
+rank = dist.get_rank()
+handle = bytes([rank]) * 64
+got = [None, None]
+dist.all_gather_object(got, handle)
+assert got[0] == bytes([0]) * 64 and got[1] == bytes([1]) * 64
+base, count = key_ranges(1000, 2)[rank]
+assert (base, count) == ((0, 512) if rank == 0 else (512, 488))
+dist.barrier()
+dist.destroy_process_group()
+print("ok", rank)
+"""
+
+
+def test_handle_exchange_over_gloo(tmp_path):
+    script = tmp_path / "gloo_ranks.py"
+    script.write_text(GLOO_SCRIPT % ROOT)
+    port = str(29500 + os.getpid() % 2000)
+    procs = [subprocess.Popen([sys.executable, str(script), port, str(r)], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(2)]
+    for p in procs:
+        out, err = p.communicate(timeout=120)
+        assert p.returncode == 0, err
+        assert out.startswith("ok")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("nranks,T,Hq,Hkv,kv", [(2, 1, 16, 2, 1000), (4, 4, 32, 4, 5000), (8, 4, 32, 4, 20000), (3, 2, 8, 2, 130)])
+def test_all_ranks_on_one_gpu_match_the_oracle(gpu, ops, nranks, T, Hq, Hkv, kv):
+    from nextsycl_b200 import DevBuf
+    from nextsycl_b200 import workloads as W
+    from nextsycl_b200.dist import KvSplit
+    from oracle import oracle as O
+    D = 128
+    q, k, v, p0 = W.gqa_case(950, T, Hq, Hkv, D, kv)
+    dq = DevBuf.of(gpu, q)
+    nbytes = KvSplit.mailbox_bytes(gpu.api, nranks, T, Hq, D)
+    boxes = [DevBuf(gpu, nbytes) for _ in range(nranks)]
+    for b in boxes:
+        b.fill(0)
+    groups = [KvSplit(gpu, r, nranks, T, Hq, D, local_mailboxes=boxes) for r in range(nranks)]
+    want = O.gqa_flash_decode(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, kv, p0)
+    keep = []
+    for step in range(2):   # two steps: both mailbox buffers, and the counter's return to zero
+        for r, (base, count) in enumerate(key_ranges(kv, nranks)):
+            kl = max(count, 1)
+            ks = np.ascontiguousarray(k[:, base:base + kl]) if count else np.zeros((Hkv, 1, D), np.float16)
+            vs = np.ascontiguousarray(v[:, base:base + kl]) if count else np.zeros((Hkv, 1, D), np.float16)
+            dk, dv = DevBuf.of(gpu, ks), DevBuf.of(gpu, vs)
+            sc = DevBuf(gpu, 4 * groups[r].scratch_floats(Hkv, kl))
+            sc.fill(0xFF)
+            keep += [dk, dv, sc]
+            # a rank without keys still publishes (an empty partial): its rows see nothing of a slice that starts past them
+            groups[r].decode(dq, Hq * D, dk, dv, Hkv, kl, base if count else kv + 8, p0, sc)
+        for r in range(nranks):
+            out = DevBuf(gpu, T * Hq * D * 2)
+            out.fill(0xFF)
+            groups[r].combine(out, wait_us=1000)
+            gpu.sync()
+            got = out.read(np.float16).reshape(T, Hq * D).astype(np.float32)
+            d = np.abs(got - want)
+            assert np.all(d <= 2e-3 + 1e-2 * np.abs(want)), (step, r, float(d.max()))
+
+
+@pytest.mark.gpu
+def test_combine_gives_up_when_a_peer_never_publishes(gpu, ops):
+    from nextsycl_b200 import DevBuf, Error
+    from nextsycl_b200.dist import KvSplit
+    T, Hq, D, nranks = 1, 8, 128, 2
+    boxes = [DevBuf(gpu, KvSplit.mailbox_bytes(gpu.api, nranks, T, Hq, D)) for _ in range(nranks)]
+    for b in boxes:
+        b.fill(0)
+    g0 = KvSplit(gpu, 0, nranks, T, Hq, D, local_mailboxes=boxes)
+    out = DevBuf(gpu, T * Hq * D * 2)
+    g0.combine(out, epoch=1, wait_us=2000)      # nobody published epoch 1
+    with pytest.raises(Error, match="bounded wait"):
+        gpu.sync()
+    gpu.sync()                                   # the report clears; the context stays usable
+    assert DevBuf.of(gpu, np.arange(4, dtype=np.float32)).read(np.float32).sum() == 6
