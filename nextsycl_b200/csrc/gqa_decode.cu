@@ -11,6 +11,7 @@
 // rows are too few for a tcgen05 tile; the kernel is HBM-bound), keep their own online softmax (quad shuffles for
 // the row max and sum) and merge once at the end through shared memory. No block-wide barrier in the key loop.
 #include "kernels.cuh"
+#include "lse_merge.cuh"
 
 namespace {
 
@@ -336,68 +337,51 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
 
 // the splits of each (sequence, row, head) merged: attn.cpp:352-368's formula; rows with one split were written by
 // the first kernel
+constexpr int MERGE_THREADS = 256;
+
 template <int D>
-__global__ void __launch_bounds__(D) gqa_merge_kernel(const Params p) {
+__global__ void __launch_bounds__(MERGE_THREADS) gqa_merge_kernel(const Params p) {
+    __shared__ float sm[lse::smem_floats<D, MERGE_THREADS>()];
     const int64_t rh = blockIdx.x;   // (b, t, hq)
-    const int d = threadIdx.x;
-    const int hq = (int) (rh % p.Hq), t = (int) ((rh / p.Hq) % p.T), b = (int) (rh / ((int64_t) p.Hq * p.T));
-    (void) hq;
+    const int t = (int) ((rh / p.Hq) % p.T), b = (int) (rh / ((int64_t) p.Hq * p.T));
     const ns_b200_seq seq = p.seqs ? p.seqs[b] : p.one;
     const int nsr = (int) ns_dec_splits(row_keys(seq, t), p.Hkv);
     if (nsr == 1) return;
-    const float* pp = p.part + rh * p.ns_max * (D + 2);
-    float mx = -INFINITY;
-    for (int k = 0; k < nsr; ++k) mx = fmaxf(mx, pp[k * (D + 2) + D]);
-    float L = 0.f, A = 0.f;
-    if (mx != -INFINITY) {
-        for (int k = 0; k < nsr; ++k) {
-            const float mk = pp[k * (D + 2) + D];
-            const float e = mk == -INFINITY ? 0.f : exp2f(mk - mx);
-            L += pp[k * (D + 2) + D + 1] * e;
-            A += pp[k * (D + 2) + d] * e;
-        }
+    float mx, L;
+    const float2 a = lse::merge_row<D, MERGE_THREADS>(p.part + rh * p.ns_max * (D + 2), D + 2, nsr, mx, L, sm);
+    if (threadIdx.x < D / 2) {
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        const int d = 2 * threadIdx.x;
+        if (p.out_f32) *reinterpret_cast<float2*>((float*) p.out + rh * D + d) = make_float2(a.x * inv, a.y * inv);
+        else *reinterpret_cast<__half2*>((__half*) p.out + rh * D + d) = __floats2half2_rn(a.x * inv, a.y * inv);
     }
-    const float v = L > 0.f ? A / L : 0.f;
-    if (p.out_f32) ((float*) p.out)[rh * D + d] = v;
-    else ((__half*) p.out)[rh * D + d] = __float2half_rn(v);
 }
 
 // KV split over several GPUs, this rank's side: its key splits merged into one partial (O, m, l) per (row, head), which
 // is stored - with plain stores over NVLink - into slot `rank` of EVERY rank's mailbox; the last block to finish
 // publishes the epoch in every mailbox's flag for this rank (release at system scope). One sequence.
 template <int D>
-__global__ void __launch_bounds__(D) gqa_merge_push_kernel(const Params p) {
+__global__ void __launch_bounds__(MERGE_THREADS) gqa_merge_push_kernel(const Params p) {
+    __shared__ float sm[lse::smem_floats<D, MERGE_THREADS>()];
     const int64_t rh = blockIdx.x;   // (t, hq)
-    const int d = threadIdx.x;
     const int t = (int) (rh / p.Hq);
     const ns_b200_seq seq = p.seqs ? p.seqs[0] : p.one;
     const int64_t kv = row_keys(seq, t);
     const int nsr = kv > 0 ? (int) ns_dec_splits(kv, p.Hkv) : 0;
-    const float* pp = p.part + rh * p.ns_max * (D + 2);
-    float mx = -INFINITY;
-    for (int k = 0; k < nsr; ++k) mx = fmaxf(mx, pp[k * (D + 2) + D]);
-    float L = 0.f, A = 0.f;
-    if (mx != -INFINITY) {
-        for (int k = 0; k < nsr; ++k) {
-            const float mk = pp[k * (D + 2) + D];
-            const float e = mk == -INFINITY ? 0.f : exp2f(mk - mx);
-            L += pp[k * (D + 2) + D + 1] * e;
-            A += pp[k * (D + 2) + d] * e;
-        }
-    }
+    float mx, L;
+    const float2 a = lse::merge_row<D, MERGE_THREADS>(p.part + rh * p.ns_max * (D + 2), D + 2, nsr, mx, L, sm);
     const int64_t rows = (int64_t) p.T * p.Hq;
     const int buf = (int) (p.epoch & 1);
-    for (int r = 0; r < p.nranks; ++r) {
-        float* slot = p.mailboxes[r] + ns_mbox_slot(buf, p.rank, p.nranks, rows, D) + rh * (D + 2);
-        slot[d] = A;
-        if (d == 0) {
-            slot[D] = mx;
-            slot[D + 1] = L;
+    if (threadIdx.x < D / 2) {
+        for (int r = 0; r < p.nranks; ++r) {
+            float* slot = p.mailboxes[r] + ns_mbox_slot(buf, p.rank, p.nranks, rows, D) + rh * (D + 2);
+            *reinterpret_cast<float2*>(slot + 2 * threadIdx.x) = a;
+            if (threadIdx.x == 0) *reinterpret_cast<float2*>(slot + D) = make_float2(mx, L);
         }
     }
     __threadfence_system();
     __syncthreads();
-    if (d == 0) {
+    if (threadIdx.x == 0) {
         // the counter lives in this rank's own mailbox and returns to zero for the next call
         int* counter = reinterpret_cast<int*>(p.mailboxes[p.rank] + ns_mbox_flags_off(p.nranks, rows, D)) + 4 * p.nranks;
         const int done = atomicAdd(counter, 1) + 1;
@@ -485,10 +469,10 @@ int launch(ns_gpu* g, const Params& p, int64_t B, const char* where) {
     kern<<<grid, THREADS, smem, g->compute>>>(p);
     if (ns_launched(where)) return -1;
     if (p.mailboxes) {
-        gqa_merge_push_kernel<D><<<(unsigned) (p.T * p.Hq), D, 0, g->compute>>>(p);
+        gqa_merge_push_kernel<D><<<(unsigned) (p.T * p.Hq), MERGE_THREADS, 0, g->compute>>>(p);
         if (ns_launched(where)) return -1;
     } else if (p.ns_max > 1) {
-        gqa_merge_kernel<D><<<(unsigned) (B * p.T * p.Hq), D, 0, g->compute>>>(p);
+        gqa_merge_kernel<D><<<(unsigned) (B * p.T * p.Hq), MERGE_THREADS, 0, g->compute>>>(p);
         if (ns_launched(where)) return -1;
     }
     return 0;

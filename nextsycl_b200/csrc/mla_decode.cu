@@ -15,6 +15,7 @@
 // Every mbarrier wait is bounded; a wait that gives up records a status code and the CTA runs to its teardown.
 #include "kernels.cuh"
 #include "tc05.cuh"
+#include "lse_merge.cuh"
 
 #include <cuda.h>
 
@@ -299,22 +300,18 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
 }
 
-// the splits of each (row, head) merged; a split past the row's cells wrote nothing and is skipped
-__global__ void __launch_bounds__(256) mla_merge_kernel(const Params p) {
+// the splits of each (row, head) merged; a split past the row's cells wrote nothing and is not read
+__global__ void __launch_bounds__(512) mla_merge_kernel(const Params p) {
+    __shared__ float sm[lse::smem_floats<L, 512>()];
     const int64_t row = blockIdx.x;   // (t, h)
     const int t = (int) (row / p.H);
     const int64_t n = p.pos0 + t + 1;
     const int nsr = (int) ((n + p.kb - 1) / p.kb);
-    const float* pp = p.part + row * p.ns * PS;
-    float mx = -INFINITY;
-    for (int k = 0; k < nsr; ++k) mx = fmaxf(mx, pp[k * PS + L]);
-    float den = 0.f;
-    for (int k = 0; k < nsr; ++k) den += pp[k * PS + L + 1] * exp2f(pp[k * PS + L] - mx);
-    const float inv = den > 0.f ? 1.0f / den : 0.f;
-    for (int d = threadIdx.x; d < L; d += blockDim.x) {
-        float a = 0.f;
-        for (int k = 0; k < nsr; ++k) a += pp[k * PS + d] * exp2f(pp[k * PS + L] - mx);
-        p.out[row * L + d] = a * inv;
+    float mx, den;
+    const float2 a = lse::merge_row<L, 512>(p.part + row * p.ns * PS, PS, nsr, mx, den, sm);
+    if (threadIdx.x < L / 2) {
+        const float inv = den > 0.f ? 1.0f / den : 0.f;
+        *reinterpret_cast<float2*>(p.out + row * L + 2 * threadIdx.x) = make_float2(a.x * inv, a.y * inv);
     }
 }
 
@@ -384,7 +381,7 @@ int ns_launch_mla_decode(ns_gpu* g, const MlaDecodeArgs& a, const char* where) {
     mla_decode_kernel<<<grid, THREADS, SMEM_TOTAL, g->compute>>>(tq, tc, p);
     if (ns_launched(where)) return -1;
     if (p.ns > 1) {
-        mla_merge_kernel<<<(unsigned) (a.T * a.H), 256, 0, g->compute>>>(p);
+        mla_merge_kernel<<<(unsigned) (a.T * a.H), 512, 0, g->compute>>>(p);
         if (ns_launched(where)) return -1;
     }
     return 0;
