@@ -110,6 +110,30 @@ int ns_b200_mla_prefill(ns_gpu* g, const void* q, int64_t q_tok, const void* k, 
 int ns_ds2_mla_decode(ns_gpu* g, const float* q, const uint16_t* kb, const uint16_t* vb, const uint16_t* cache, float* out, int64_t T, int64_t H,
                       int64_t pos0, float scale);
 
+/* kernels/llm/glm5next/glm.h:47 - dense causal absorbed MLA over fp32 latents: qa [T][H][L], c [n][L], u [T][H][L] =
+ * sum_s softmax(qa . c_s * scale) c_s over s <= pos0+t; exact two-pass softmax in fp32 (L up to 512). */
+int ns_mla_attend(ns_gpu* g, const float* qa, const float* c, float* u, int64_t T, int64_t H, int64_t L, int64_t pos0, float scale);
+/* kernels/llm/glm5next/glm.h:65-66,79-80 - MLA over each row's selection of cells of the fp16 latent cache [n][512]
+ * (or, _q8, of q8 rows: 16 fp16 scales then 512 int8 = 544 bytes): sel_cnt null or sel_cnt[t] < 0 - every earlier
+ * token; else 4 tokens of each selected pool sel[t][0 .. sel_cnt[t]) then the row's incomplete pool. qa, u fp32
+ * [T][H][512]. The reference runs this on vector units for at most 8 rows and 2,560 cells and falls back to gathers plus
+ * oneMKL GEMMs for prompt rows (llm/glm5next/src/engine.rs:1905-1938); here any number of rows takes one path: the
+ * rows' cells gathered to fp16, then the tensor-core latent-attention kernel (qa and the weights rounded to fp16). */
+int ns_mla_attend_sel(ns_gpu* g, const float* qa, const uint16_t* c, float* u, int64_t T, int64_t H, int64_t L, int64_t pos0, float scale,
+                      const int32_t* sel, const int32_t* sel_cnt, int64_t K);
+int ns_mla_attend_sel_q8(ns_gpu* g, const float* qa, const void* c, float* u, int64_t T, int64_t H, int64_t L, int64_t pos0, float scale,
+                         const int32_t* sel, const int32_t* sel_cnt, int64_t K);
+/* kernels/llm/glm5next/glm.h:58-62,70,72,76-78 - the helper steps of the reference's GEMM-form prompt MLA, under their own
+ * names: each row's cell indices and count; the masked row softmax; fp32 -> fp16; fp32 rows -> q8 latent rows; rows
+ * gathered by index from an fp16 matrix or from q8 rows. (The GEMMs between them are oneMKL calls in the reference,
+ * ns_gemm_batch_h; this library does not export a GEMM - ns_mla_attend_sel replaces the whole sequence.) */
+int ns_mla_cells(ns_gpu* g, const int32_t* sel, const int32_t* sel_cnt, int64_t T, int64_t K, int64_t pos0, int32_t* idx, int32_t* n, int64_t NC);
+int ns_softmax_masked(ns_gpu* g, float* S, int64_t R, int64_t H, int64_t NC, const int32_t* n, float scale);
+int ns_to_f16(ns_gpu* g, const float* x, uint16_t* y, int64_t n);
+int ns_to_q8row(ns_gpu* g, const float* x, void* y, int64_t n, int64_t L);
+int ns_gather_q8_h(ns_gpu* g, const void* src, const int32_t* idx, uint16_t* out, int64_t n, int64_t L);
+int ns_gather_h(ns_gpu* g, const uint16_t* src, const int32_t* idx, uint16_t* out, int64_t n, int64_t C);
+
 /* The middle stage alone (BASELINE's absorbed-MLA decode): q [T][H][576] fp16 = absorbed query (512) then rotated
  * part (64); cache [n][576] fp16; out u [T][H][512] fp32. scratch: ns_b200_mla_decode_scratch floats (it depends on
  * the GPU's SM count, hence the handle), 0 when the row is not split. */

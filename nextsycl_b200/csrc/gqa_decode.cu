@@ -45,6 +45,11 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -90,8 +95,10 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint8_t* w_s = smem + RG * ROWB + warp * (NSTAGE * 2 * TILE);
 
-    const int split = blockIdx.x, hk = blockIdx.y;
-    const int b = blockIdx.z / p.groups, rg = blockIdx.z % p.groups;
+    // the row groups of one (split, key head) are neighbours in the grid: they run at the same time, and the second
+    // to read a key tile finds it in L2
+    const int split = blockIdx.x / p.groups, rg = blockIdx.x % p.groups, hk = blockIdx.y;
+    const int b = blockIdx.z;
     const ns_b200_seq seq = p.seqs ? p.seqs[b] : p.one;
     const int T = p.T, G = p.G, R = T * G, row0 = rg * RG;
     const int64_t p0 = seq.p0;
@@ -145,13 +152,14 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
         const int ntiles = (int) ((jend - jbeg + KT - 1) / KT);
 
         // this thread's rows: (mt, lane/4) and 8 below; a row outside the pass sees no key
-        int64_t lim[MT][2];
+        int lim_rel[MT][2];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const int rho = row0 + mt * 16 + hh * 8 + (lane >> 2), t = rho / G;
-                lim[mt][hh] = (rho < R && t >= t_a && t <= t_b) ? p0 + t : -1;
+                const int64_t last = (rho < R && t >= t_a && t <= t_b) ? min(p0 + t, jend - 1) : jbeg - 1;
+                lim_rel[mt][hh] = (int) max(last - jbeg, (int64_t) -1);
             }
 
         float o[MT][NT][4];
@@ -222,40 +230,53 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
             }
             // ---- mask, online softmax (a row's 16 scores sit in its quad: 4 a lane)
             uint32_t pf[MT][4];
+            float cs[MT][2];
+            bool moved = false;
+            const int rel0 = (int) (j0 - jbeg);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
-                    const int64_t last = min(lim[mt][hh], jend - 1);
+                    const int last = lim_rel[mt][hh];   // the row's last visible key, relative to the split's first
                     float x[4];
                     float mx = -INFINITY;
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int nt = e >> 1;
-                        const int64_t key = j0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+                        const int key = rel0 + nt * 8 + 2 * (lane & 3) + (e & 1);
                         x[e] = key <= last ? s[mt][nt][hh * 2 + (e & 1)] : -INFINITY;
                         mx = fmaxf(mx, x[e]);
                     }
                     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
                     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                     const float mo = m[mt][hh], mn = fmaxf(mo, mx);
-                    const float c = mn == -INFINITY ? 1.0f : exp2f(mo - mn);
+                    const float ref = mn == -INFINITY ? 0.f : mn;   // nothing seen yet: every weight below is 2^-inf = 0
+                    const float c = mo == mn ? 1.0f : ex2_approx(mo - ref);
                     float pv[4], sum = 0.f;
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        pv[e] = x[e] == -INFINITY ? 0.f : exp2f(x[e] - mn);
+                        pv[e] = ex2_approx(x[e] - ref);
                         sum += pv[e];
                     }
                     l[mt][hh] = l[mt][hh] * c + sum;   // this lane's share; the quad's shares are added at the end
                     m[mt][hh] = mn;
                     pf[mt][hh] = pack_h2(pv[0], pv[1]);       // keys 0..7 of the tile -> A fragment k 0..7
                     pf[mt][2 + hh] = pack_h2(pv[2], pv[3]);   // keys 8..15 -> k 8..15
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        o[mt][nt][hh * 2] *= c;
-                        o[mt][nt][hh * 2 + 1] *= c;
-                    }
+                    cs[mt][hh] = c;
+                    moved = moved || c != 1.0f;
                 }
+            }
+            // the running maxima settle after a few tiles: O is rescaled only when some row's maximum moved
+            if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            o[mt][nt][hh * 2] *= cs[mt][hh];
+                            o[mt][nt][hh * 2 + 1] *= cs[mt][hh];
+                        }
             }
             // ---- O += P V
 #pragma unroll
@@ -465,7 +486,7 @@ int launch(ns_gpu* g, const Params& p, int64_t B, const char* where) {
         NS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem), where);
         set[g->dev & 63] = true;
     }
-    dim3 grid((unsigned) p.ns_max, (unsigned) p.Hkv, (unsigned) (B * p.groups));
+    dim3 grid((unsigned) (p.ns_max * p.groups), (unsigned) p.Hkv, (unsigned) B);
     kern<<<grid, THREADS, smem, g->compute>>>(p);
     if (ns_launched(where)) return -1;
     if (p.mailboxes) {
@@ -503,12 +524,13 @@ int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where) {
     p.mailboxes = a.mailboxes;
     p.epoch = a.epoch;
     const int R = p.T * p.G;
-    if (a.B * (int64_t) ((R + 15) / 16) > 65535) return ns_fail(std::string(where) + ": too many sequences for one launch");
+    if (a.B > 65535) return ns_fail(std::string(where) + ": too many sequences for one launch");
     if (a.D == 128) {
         if (R <= 16) {
             p.groups = 1;
             return launch<128, 1, 3>(g, p, a.B, where);
         }
+        // 32-row CTAs: measured faster than pairs of 16-row CTAs sharing tiles through L2 (119 vs 142 us on 512 MiB)
         p.groups = (R + 31) / 32;
         return launch<128, 2, 3>(g, p, a.B, where);
     }

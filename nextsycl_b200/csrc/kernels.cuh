@@ -77,12 +77,16 @@ int ns_launch_flash_prefill(ns_gpu* g, const FlashPrefillArgs& a, const char* wh
 
 // ---- absorbed MLA decode on tcgen05 (mla_decode.cu) --------------------------------------------------------------------
 struct MlaDecodeArgs {
-    const void* q;        // [T][H][576] fp16: the absorbed query (512) then the rotated part (64)
-    const void* cache;    // [n][576] fp16, n >= pos0 + T
-    float* out;           // [T][H][512] fp32
-    float* part;          // ns_mla_partial_floats floats (may be null when that is 0)
+    const void* q;            // [T][H][512 + rope] fp16: the absorbed query, then the rotated part
+    const void* cache;        // cells [n][512 + rope] fp16 - one matrix for all rows, or one per row (cache_rows_apart > 0)
+    float* out;               // [T][H][512] fp32
+    float* part;              // ns_mla_partial_floats floats (may be null when that is 0)
     int64_t T, H, pos0;
     float scale;
+    int rope;                 // 64 (deepseek2's 576-wide rows) or 0 (glm5next's 512-wide rows)
+    int64_t n_max;            // the most cells any row attends to (sizes the grid and the partials)
+    const int* counts;        // device [T]: cells each row attends to; null: pos0 + t + 1 (causal over one shared cache)
+    int64_t cache_rows_apart; // elements between the rows' own cell matrices; 0: one shared cache
 };
 // cells a key split / floats of partials for rows that see up to n cells, on a GPU of `sms` SMs
 int64_t ns_mla_split(int64_t n, int64_t T, int64_t H, int sms);

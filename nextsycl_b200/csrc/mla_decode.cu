@@ -22,24 +22,29 @@
 namespace {
 using namespace tc05;
 
-constexpr int L = 512, R = 64, CR = L + R;     // latent, rotated, row width
+constexpr int L = 512;                         // latent width; a cache row is CR = 512 + rotated part (64 or 0)
 constexpr int BM = 128;                        // heads a tile
 constexpr int BN = 64;                         // cells a tile
 constexpr int NSTAGE = 2;
 constexpr int QT = 256;                        // features of Q kept in tensor memory
-constexpr int QS = CR - QT;                    // features of Q kept in shared memory (320)
 constexpr int DVH = 256;                       // output columns a CTA
 constexpr int THREADS = 192;
 constexpr int PS = 516;                        // floats a partial row: O[512], m, l, 2 pad
 constexpr float RESCALE_LOG2 = 8.0f;
 
 constexpr int O_COL = 0, Q_COL = 256, S_COL = 384;   // tensor-memory columns; S buffers at 384 and 448
-constexpr int TILE_BYTES = BN * CR * 2;              // 73,728
-constexpr int QS_BYTES = BM * QS * 2;                // 81,920
-constexpr int SMEM_TOTAL = 1024 + QS_BYTES + NSTAGE * TILE_BYTES + 512;
+template <int CR>
+struct Geo {
+    static constexpr int QS = CR - QT;                       // features of Q kept in shared memory (320 or 256)
+    static constexpr int TILE_BYTES = BN * CR * 2;           // 73,728 or 65,536
+    static constexpr int QS_BYTES = BM * QS * 2;             // 81,920 or 65,536
+    static constexpr int SMEM_TOTAL = 1024 + QS_BYTES + NSTAGE * TILE_BYTES + 512;
+};
 
 struct Params {
-    const __half* q;       // [T][H][576] fp16
+    const __half* q;       // [T][H][CR] fp16
+    const int* counts;     // per row: cells it attends to (null: pos0 + t + 1)
+    int zmul;              // 1: row t has its own cell matrix (third tensor-map coordinate t); 0: one shared cache
     float* out;            // [T][H][512]
     float* part;           // [T][H][ns][PS]
     int* status;
@@ -48,8 +53,10 @@ struct Params {
     float scale_log2;
 };
 
+template <int CR>
 __global__ void __launch_bounds__(THREADS, 1)
 mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_c, const Params p) {
+    constexpr int QS = Geo<CR>::QS, TILE_BYTES = Geo<CR>::TILE_BYTES, QS_BYTES = Geo<CR>::QS_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
     uint8_t* q_s = smem;                       // 5 chunks of [128 heads][64 features]
@@ -69,7 +76,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int tid = threadIdx.x, warp = tid >> 5;
     const int hv = blockIdx.x & 1, split = blockIdx.x >> 1;
     const int h0 = blockIdx.y * BM, t = blockIdx.z;
-    const int64_t n = p.pos0 + t + 1;                       // cells this row sees
+    const int64_t n = p.counts ? (int64_t) p.counts[t] : p.pos0 + t + 1;   // cells this row sees
     const int64_t jbeg = (int64_t) split * p.kb, jend = min(n, (int64_t) (split + 1) * p.kb);
     const int ntiles = jbeg < jend ? (int) ((jend - jbeg + BN - 1) / BN) : 0;
     if (ntiles == 0) return;                                // the whole CTA: this split holds none of the row's cells
@@ -113,7 +120,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (!ok) break;
                 mbar_expect_tx(smem_u32(c_full + s), TILE_BYTES);
                 uint8_t* dst = c_s + s * TILE_BYTES;
-                for (int c = 0; c < CR / 64; ++c) tma_load_3d(smem_u32(dst + c * (BN * 128)), &tm_c, c * 64, (int) (jbeg + (int64_t) j * BN), 0, smem_u32(c_full + s));
+                for (int c = 0; c < CR / 64; ++c) tma_load_3d(smem_u32(dst + c * (BN * 128)), &tm_c, c * 64, (int) (jbeg + (int64_t) j * BN), t * p.zmul, smem_u32(c_full + s));
             }
         }
     } else if (warp == 5) {
@@ -139,22 +146,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
                 mma_commit(smem_u32(s_full + (j & 1)));
             };
-            if (ok) ok = mbar_wait(smem_u32(c_full + 0), 0, abort_flag, p.status, 503);
-            if (ok) {
-                fence_after_sync();
-                issue_qk(0);
-            }
-            for (int j = 0; j < ntiles && ok; ++j) {
+            auto issue_pv = [&](int j) {
                 const int s = j % NSTAGE;
-                if (j + 1 < ntiles) {
-                    ok = mbar_wait(smem_u32(c_full + (j + 1) % NSTAGE), (uint32_t) ((j + 1) / NSTAGE) & 1, abort_flag, p.status, 504);
-                    if (!ok) break;
-                    fence_after_sync();
-                    issue_qk(j + 1);
-                }
-                ok = mbar_wait(smem_u32(p_full + (j & 1)), (uint32_t) (j >> 1) & 1, abort_flag, p.status, 505);
-                if (!ok) break;
-                fence_after_sync();
                 // the value operand: this CTA's 4 chunks of the same tile, MN-major; 16 cells a step
                 const uint32_t vb = smem_u32(c_s + s * TILE_BYTES) + (uint32_t) (hv * (DVH / 64) * (BN * 128));
                 const uint32_t pa = tmem + (uint32_t) (S_COL + (j & 1) * BN);
@@ -166,6 +159,39 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 mma_commit(smem_u32(c_empty + s));
                 mma_commit(smem_u32(pv_done));
                 if (j == ntiles - 1) mma_commit(smem_u32(o_final));
+            };
+            // The two products are issued in whatever order their inputs arrive: S(qk) as soon as its tile has landed
+            // (and the S buffer it overwrites has been consumed: P(qk-2) V(qk-2) issued), P(pv) V(pv) as soon as the
+            // softmax published P(pv). A fixed order would queue P(j) V(j) - which frees tile j's stage for the next
+            // load - behind S(j+1), which waits for a load that was itself waiting for a stage.
+            int qk = 0, pv = 0;
+            uint32_t idle = 0;
+            while (ok && pv < ntiles) {
+                bool did = false;
+                if (qk < ntiles && qk - pv < 2 && mbar_try(smem_u32(c_full + qk % NSTAGE), (uint32_t) (qk / NSTAGE) & 1)) {
+                    fence_after_sync();
+                    issue_qk(qk);
+                    ++qk;
+                    did = true;
+                }
+                if (pv < qk && mbar_try(smem_u32(p_full + (pv & 1)), (uint32_t) (pv >> 1) & 1)) {
+                    fence_after_sync();
+                    issue_pv(pv);
+                    ++pv;
+                    did = true;
+                }
+                if (did) {
+                    idle = 0;
+                } else if (*abort_flag || ++idle > WAIT_LIMIT) {
+                    if (!*abort_flag) {
+                        *abort_flag = 1;
+                        if (p.status) {
+                            *(volatile int*) p.status = 504;
+                            __threadfence_system();
+                        }
+                    }
+                    ok = false;
+                }
             }
         }
     } else {
@@ -305,7 +331,7 @@ __global__ void __launch_bounds__(512) mla_merge_kernel(const Params p) {
     __shared__ float sm[lse::smem_floats<L, 512>()];
     const int64_t row = blockIdx.x;   // (t, h)
     const int t = (int) (row / p.H);
-    const int64_t n = p.pos0 + t + 1;
+    const int64_t n = p.counts ? (int64_t) p.counts[t] : p.pos0 + t + 1;
     const int nsr = (int) ((n + p.kb - 1) / p.kb);
     float mx, den;
     const float2 a = lse::merge_row<L, 512>(p.part + row * p.ns * PS, PS, nsr, mx, den, sm);
@@ -354,10 +380,14 @@ int64_t ns_mla_partial_floats(int64_t n, int64_t T, int64_t H, int sms) {
     return ns > 1 ? T * H * ns * PS : 0;
 }
 
-int ns_launch_mla_decode(ns_gpu* g, const MlaDecodeArgs& a, const char* where) {
-    const int64_t n = a.pos0 + a.T;              // cells the last row sees
+namespace {
+template <int CR>
+int launch(ns_gpu* g, const MlaDecodeArgs& a, const char* where) {
+    const int64_t n = a.n_max;                   // the most cells any row sees
     Params p;
     p.q = (const __half*) a.q;
+    p.counts = a.counts;
+    p.zmul = a.cache_rows_apart > 0 ? 1 : 0;
     p.out = a.out;
     p.part = a.part;
     p.status = g->status_dev;
@@ -368,21 +398,31 @@ int ns_launch_mla_decode(ns_gpu* g, const MlaDecodeArgs& a, const char* where) {
     p.ns = (int) ((n + p.kb - 1) / p.kb);
     p.scale_log2 = a.scale * 1.4426950408889634f;
     CUtensorMap tq, tc;
-    // Q [T][H][576]: a box = 128 heads x 64 features of one row
+    // Q [T][H][CR]: a box = 128 heads x 64 features of one row
     if (make_map(&tq, a.q, CR, (uint64_t) a.H, (uint64_t) a.T, CR * 2, (uint64_t) a.H * CR * 2, BM, where)) return -1;
-    // cache [n][576]: a box = 64 cells x 64 features; cells past n read as zeros
-    if (make_map(&tc, a.cache, CR, (uint64_t) n, 1, CR * 2, (uint64_t) n * CR * 2, BN, where)) return -1;
+    // cells [Z][n][CR]: a box = 64 cells x 64 features; cells past n read as zeros
+    const uint64_t z = p.zmul ? (uint64_t) a.T : 1, zs = p.zmul ? (uint64_t) a.cache_rows_apart * 2 : (uint64_t) n * CR * 2;
+    if (make_map(&tc, a.cache, CR, (uint64_t) n, z, CR * 2, zs, BN, where)) return -1;
+    auto kern = mla_decode_kernel<CR>;
     static bool set[64] = {};
     if (!set[g->dev & 63]) {
-        NS_CUDA(cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL), where);
+        NS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<CR>::SMEM_TOTAL), where);
         set[g->dev & 63] = true;
     }
     dim3 grid((unsigned) (2 * p.ns), (unsigned) ((a.H + BM - 1) / BM), (unsigned) a.T);
-    mla_decode_kernel<<<grid, THREADS, SMEM_TOTAL, g->compute>>>(tq, tc, p);
+    kern<<<grid, THREADS, Geo<CR>::SMEM_TOTAL, g->compute>>>(tq, tc, p);
     if (ns_launched(where)) return -1;
     if (p.ns > 1) {
         mla_merge_kernel<<<(unsigned) (a.T * a.H), 512, 0, g->compute>>>(p);
         if (ns_launched(where)) return -1;
     }
     return 0;
+}
+
+}  // namespace
+
+int ns_launch_mla_decode(ns_gpu* g, const MlaDecodeArgs& a, const char* where) {
+    if (a.rope == 64) return launch<576>(g, a, where);
+    if (a.rope == 0) return launch<512>(g, a, where);
+    return ns_fail(std::string(where) + ": a rotated part of 64 or none");
 }

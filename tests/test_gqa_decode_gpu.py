@@ -101,14 +101,15 @@ def test_kv_store_then_decode(gpu, ops):
     v = W.rng(924, 1).standard_normal((T, Hkv * D), dtype=np.float32)
     kc, vc = DevBuf(gpu, Hkv * cap * D * 2), DevBuf(gpu, Hkv * cap * D * 2)
     kc.fill(0), vc.fill(0)
-    ops.kv_store(DevBuf.of(gpu, k), Hkv * D, DevBuf.of(gpu, v), Hkv * D, T, Hkv, D, cap, p0, kc, vc)
+    dkr, dvr = DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+    ops.kv_store(dkr, Hkv * D, dvr, Hkv * D, T, Hkv, D, cap, p0, kc, vc)
     hk, hv = np.zeros((Hkv, cap, D), np.uint16), np.zeros((Hkv, cap, D), np.uint16)
     O.kv_store(k, v, T, Hkv, D, cap, p0, hk, hv)
     assert np.array_equal(kc.read(np.uint16).reshape(Hkv, cap, D), hk)      # bit-exact: one rounding to fp16
     assert np.array_equal(vc.read(np.uint16).reshape(Hkv, cap, D), hv)
     from nextsycl_b200 import Error
     with pytest.raises(Error, match="capacity"):
-        ops.kv_store(DevBuf.of(gpu, k), Hkv * D, DevBuf.of(gpu, v), Hkv * D, T, Hkv, D, cap, cap - 1, kc, vc)
+        ops.kv_store(dkr, Hkv * D, dvr, Hkv * D, T, Hkv, D, cap, cap - 1, kc, vc)
 
 
 def test_argument_errors(gpu, ops):
