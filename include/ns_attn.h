@@ -69,6 +69,15 @@ int64_t ns_nhs_attn_decode_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D
 int ns_nhs_attn_decode(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
                        int64_t cap, int64_t p0, float* out, float* scratch);
 
+/* kernels/llm/qwen35/q35.h:47-52 - what is queued on the GPU's queue between begin and end is recorded (it does not
+ * run), finished by end, replayed by launch as one submission, released by free. Here a CUDA graph captured from the
+ * compute stream. Calls that take positions by value bake them in; the native entry points read lengths and step numbers
+ * from device memory so that a recorded step stays valid. */
+int ns_q35_graph_begin(ns_gpu* g, void** out);
+int ns_q35_graph_end(ns_gpu* g, void* h);
+int ns_q35_graph_launch(ns_gpu* g, void* h);
+void ns_q35_graph_free(void* h);
+
 /* ================= 2. native entry points ================= */
 
 /* One sequence of a decode batch, resident in device memory: its caches ([Hkv][cap][D] fp16 each), their capacity in
@@ -151,13 +160,15 @@ int ns_b200_mla_decode(ns_gpu* g, const void* q, const void* cache, int64_t T, i
  *     until all ranks published `epoch`, then merges them into out [T][Hq*D] fp16. If the wait runs out the kernel
  *     leaves, nothing is written, and the next ns_sync returns -1 ("gave up a bounded wait (code 701)").
  * Epochs count from 1 and must increase by one per step on every rank (two buffers alternate by epoch parity, so a rank
- * may run one step ahead of its peers, never two). A mailbox is ns_b200_kvsplit_mailbox_bytes bytes, zeroed once. */
+ * may run one step ahead of its peers, never two). With epoch 0 in both calls the step number is kept in the rank's own
+ * mailbox and advanced by the combine, so the pair can be recorded once (ns_q35_graph_begin/end) and replayed.
+ * A mailbox is ns_b200_kvsplit_mailbox_bytes bytes, zeroed once. */
 int64_t ns_b200_kvsplit_mailbox_bytes(int64_t nranks, int64_t T, int64_t Hq, int64_t D);
 int64_t ns_b200_kvsplit_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t kv_local);
 int ns_b200_kvsplit_decode(ns_gpu* g, const void* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
                            int64_t kv_local, int64_t key_base, int64_t p0, float* scratch, int64_t rank, int64_t nranks, void* const* mailboxes,
                            int64_t epoch);
-int ns_b200_kvsplit_combine(ns_gpu* g, const void* mailbox, int64_t nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t wait_us,
+int ns_b200_kvsplit_combine(ns_gpu* g, void* mailbox, int64_t nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t wait_us,
                             void* out);
 /* Device memory shared between processes of one machine (CUDA IPC): a 64-byte handle for ptr (the start of an
  * ns_alloc allocation), opened in another process as a peer-mapped address, closed when done. */

@@ -89,6 +89,10 @@ ATTN = {
     "ns_b200_mla_decode": (C.c_int, [vp, vp, vp, i64, i64, i64, C.c_float, vp, vp]),
     "ns_b200_gqa_decode_scratch": (i64, [i64, i64, i64, i64, i64, i64]),
     "ns_b200_gqa_decode": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, i64, vp, vp]),
+    "ns_q35_graph_begin": (C.c_int, [vp, C.POINTER(vp)]),
+    "ns_q35_graph_end": (C.c_int, [vp, vp]),
+    "ns_q35_graph_launch": (C.c_int, [vp, vp]),
+    "ns_q35_graph_free": (None, [vp]),
     "ns_b200_kvsplit_mailbox_bytes": (i64, [i64, i64, i64, i64]),
     "ns_b200_kvsplit_scratch": (i64, [i64, i64, i64, i64, i64]),
     "ns_b200_kvsplit_decode": (C.c_int, [vp, vp, i64, vp, vp, i64, i64, i64, i64, i64, i64, i64, vp, i64, i64, vp, i64]),

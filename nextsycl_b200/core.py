@@ -71,10 +71,36 @@ class Gpu:
         check(self.api, self.api.ns_elapsed(self.raw, t0, t1, C.byref(ns)), "reading stamps")
         return ns.value
 
+    def record(self, fn):
+        """Records what `fn` queues on the compute stream (it does not run) and returns a Graph to replay it."""
+        h = C.c_void_p()
+        check(self.api, self.api.need("ns_q35_graph_begin")(self.raw, C.byref(h)), "starting a recording")
+        try:
+            fn()
+        finally:
+            rc = self.api.need("ns_q35_graph_end")(self.raw, h)
+        check(self.api, rc, "finishing a recording")
+        return Graph(self, h)
+
     def stream(self):
         """The compute cudaStream_t as an integer (ns_gpu_queue returns a pointer to it)."""
         p = self.api.ns_gpu_queue(self.raw)
         return C.cast(p, C.POINTER(C.c_void_p))[0]
+
+
+class Graph:
+    """A recorded stretch of the compute stream (ns_q35_graph_*)."""
+
+    def __init__(self, gpu, handle):
+        self.gpu, self.h = gpu, handle
+
+    def launch(self):
+        check(self.gpu.api, self.gpu.api.ns_q35_graph_launch(self.gpu.raw, self.h), "replaying a recording")
+
+    def free(self):
+        if self.h:
+            self.gpu.api.ns_q35_graph_free(self.h)
+            self.h = None
 
 
 class DevBuf:

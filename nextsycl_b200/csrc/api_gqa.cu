@@ -179,7 +179,7 @@ int ns_b200_kvsplit_decode(ns_gpu* g, const void* q, int64_t qs, const void* kc,
     if (nranks < 1 || nranks > 64 || rank < 0 || rank >= nranks) return ns_fail(std::string(name) + ": rank within 1..64 ranks");
     if (kv_local < 1 || kv_local >= ((int64_t) 1 << 31) || key_base < 0 || p0 < 0 || p0 + T >= ((int64_t) 1 << 40))
         return ns_fail(std::string(name) + ": a key range of 1 .. 2^31 keys");
-    if (epoch < 1) return ns_fail(std::string(name) + ": epochs count from 1");
+    if (epoch < 0) return ns_fail(std::string(name) + ": epochs count from 1 (0: the mailbox's own counter)");
     if (qs % 8 != 0 || ((uintptr_t) q & 15) != 0) return ns_fail(std::string(name) + ": query rows 16-byte aligned");
     if (!q || !kc || !vc || !scratch || !mailboxes) return ns_fail(std::string(name) + ": a null buffer");
     GqaDecodeArgs a{};
@@ -201,15 +201,15 @@ int ns_b200_kvsplit_decode(ns_gpu* g, const void* q, int64_t qs, const void* kc,
     NS_CATCH("ns_b200_kvsplit_decode")
 }
 
-int ns_b200_kvsplit_combine(ns_gpu* g, const void* mailbox, int64_t nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t wait_us,
+int ns_b200_kvsplit_combine(ns_gpu* g, void* mailbox, int64_t nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t wait_us,
                             void* out) {
     NS_TRY
     const char* name = "ns_b200_kvsplit_combine";
     if (ns_enter(g, name)) return -1;
     if (!mailbox || !out) return ns_fail(std::string(name) + ": a null buffer");
-    if (nranks < 1 || nranks > 64 || T < 1 || T > 8 || Hq < 1 || epoch < 1) return ns_fail(std::string(name) + ": 1..64 ranks, 1..8 rows, epochs from 1");
+    if (nranks < 1 || nranks > 64 || T < 1 || T > 8 || Hq < 1 || epoch < 0) return ns_fail(std::string(name) + ": 1..64 ranks, 1..8 rows, epochs from 1");
     if (wait_us < 1 || wait_us > 2000000) return ns_fail(std::string(name) + ": a wait of 1 us .. 2 s");
-    return ns_launch_gqa_combine(g, (const float*) mailbox, (int) nranks, T, Hq, D, epoch, wait_us * 10, out, 0, name);
+    return ns_launch_gqa_combine(g, (float*) mailbox, (int) nranks, T, Hq, D, epoch, wait_us * 10, out, 0, name);
     NS_CATCH("ns_b200_kvsplit_combine")
 }
 

@@ -392,7 +392,10 @@ __global__ void __launch_bounds__(MERGE_THREADS) gqa_merge_push_kernel(const Par
     float mx, L;
     const float2 a = lse::merge_row<D, MERGE_THREADS>(p.part + rh * p.ns_max * (D + 2), D + 2, nsr, mx, L, sm);
     const int64_t rows = (int64_t) p.T * p.Hq;
-    const int buf = (int) (p.epoch & 1);
+    // epoch 0: the step number lives in this rank's own mailbox (the combine advances it), so a recorded graph of the
+    // step can be replayed
+    const long long epoch = p.epoch ? p.epoch : *ns_mbox_epoch(p.mailboxes[p.rank], p.nranks, rows, D) + 1;
+    const int buf = (int) (epoch & 1);
     if (threadIdx.x < D / 2) {
         for (int r = 0; r < p.nranks; ++r) {
             float* slot = p.mailboxes[r] + ns_mbox_slot(buf, p.rank, p.nranks, rows, D) + rh * (D + 2);
@@ -411,14 +414,14 @@ __global__ void __launch_bounds__(MERGE_THREADS) gqa_merge_push_kernel(const Par
             __threadfence_system();
             for (int r = 0; r < p.nranks; ++r) {
                 long long* flag = reinterpret_cast<long long*>(p.mailboxes[r] + ns_mbox_flags_off(p.nranks, rows, D)) + buf * p.nranks + p.rank;
-                asm volatile("st.release.sys.global.s64 [%0], %1;\n" ::"l"(flag), "l"(p.epoch) : "memory");
+                asm volatile("st.release.sys.global.s64 [%0], %1;\n" ::"l"(flag), "l"(epoch) : "memory");
             }
         }
     }
 }
 
 struct CombineParams {
-    const float* mailbox;   // this rank's own mailbox (local memory)
+    float* mailbox;         // this rank's own mailbox (local memory)
     void* out;              // [T][Hq*D] fp16 or fp32
     int* status;
     int nranks, D, out_f32;
@@ -433,7 +436,9 @@ __global__ void __launch_bounds__(D) gqa_combine_kernel(const CombineParams c) {
     __shared__ int ready;
     const int64_t rh = blockIdx.x;
     const int d = threadIdx.x;
-    const int buf = (int) (c.epoch & 1);
+    long long* epoch_slot = ns_mbox_epoch(c.mailbox, c.nranks, c.rows, D);
+    const long long epoch = c.epoch ? c.epoch : *epoch_slot + 1;
+    const int buf = (int) (epoch & 1);
     if (d == 0) {
         const long long* flags = reinterpret_cast<const long long*>(c.mailbox + ns_mbox_flags_off(c.nranks, c.rows, D)) + buf * c.nranks;
         int ok = 1;
@@ -441,7 +446,7 @@ __global__ void __launch_bounds__(D) gqa_combine_kernel(const CombineParams c) {
             long long v = 0, it = 0;
             for (;;) {
                 asm volatile("ld.acquire.sys.global.s64 %0, [%1];\n" : "=l"(v) : "l"(flags + r) : "memory");
-                if (v >= c.epoch) break;
+                if (v >= epoch) break;
                 if (++it > c.spins) {
                     ok = 0;
                     break;
@@ -456,6 +461,17 @@ __global__ void __launch_bounds__(D) gqa_combine_kernel(const CombineParams c) {
         ready = ok;
     }
     __syncthreads();
+    if (c.epoch == 0) {
+        // the last block to have read the step number advances it (every block read it before arriving here)
+        if (d == 0) {
+            int* counter = reinterpret_cast<int*>(c.mailbox + ns_mbox_flags_off(c.nranks, c.rows, D)) + 4 * c.nranks + 1;
+            if (atomicAdd(counter, 1) + 1 == (int) gridDim.x) {
+                *counter = 0;
+                if (ready) *epoch_slot = epoch;
+                __threadfence();
+            }
+        }
+    }
     if (!ready) return;
     const float* base = c.mailbox + ns_mbox_slot(buf, 0, c.nranks, c.rows, D) + rh * (D + 2);
     const int64_t stride = c.rows * (D + 2);
@@ -605,7 +621,7 @@ extern "C" int ns_b200_gqa_decode_static(ns_gpu* g, const void* q, int64_t qs, i
     NS_CATCH("ns_b200_gqa_decode_static")
 }
 
-int ns_launch_gqa_combine(ns_gpu* g, const float* mailbox, int nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t spins, void* out,
+int ns_launch_gqa_combine(ns_gpu* g, float* mailbox, int nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t spins, void* out,
                           int out_f32, const char* where) {
     CombineParams c;
     c.mailbox = mailbox;

@@ -47,7 +47,11 @@ __host__ __device__ inline int64_t ns_mbox_flags_off(int nranks, int64_t rows, i
 __host__ __device__ inline int64_t ns_mbox_bytes(int nranks, int64_t rows, int64_t D) {
     return ns_mbox_flags_off(nranks, rows, D) * 4 + 2 * (int64_t) nranks * 8 + 64;
 }
-int ns_launch_gqa_combine(ns_gpu* g, const float* mailbox, int nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t spins, void* out,
+// after the flags: two block counters (ints), then the rank's own step number (used when a call passes epoch 0)
+__host__ __device__ inline long long* ns_mbox_epoch(float* mailbox, int nranks, int64_t rows, int64_t D) {
+    return reinterpret_cast<long long*>(reinterpret_cast<int*>(mailbox + ns_mbox_flags_off(nranks, rows, D)) + 4 * nranks + 2);
+}
+int ns_launch_gqa_combine(ns_gpu* g, float* mailbox, int nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t spins, void* out,
                           int out_f32, const char* where);
 int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where);
 

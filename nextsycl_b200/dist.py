@@ -72,6 +72,8 @@ class KvSplit:
         if epoch is None:
             self.epoch += 1
             epoch = self.epoch
+        elif epoch == 0:
+            self.device_epochs = True   # the mailbox counts the steps itself (a recorded step can be replayed)
         api = self.gpu.api
         check(api, api.need("ns_b200_kvsplit_decode")(self.gpu.raw, q.ptr, qs, kc.ptr, vc.ptr, self.T, self.Hq, Hkv, self.D, kv_local, key_base, p0,
                                                       scratch.ptr, self.rank, self.nranks, self.table.ptr, epoch), "ns_b200_kvsplit_decode")
@@ -79,8 +81,10 @@ class KvSplit:
 
     def combine(self, out, epoch=None, wait_us=200000):
         api = self.gpu.api
-        check(api, api.need("ns_b200_kvsplit_combine")(self.gpu.raw, self.mailbox.ptr, self.nranks, self.T, self.Hq, self.D,
-                                                       self.epoch if epoch is None else epoch, wait_us, out.ptr), "ns_b200_kvsplit_combine")
+        if epoch is None:
+            epoch = 0 if getattr(self, "device_epochs", False) else self.epoch
+        check(api, api.need("ns_b200_kvsplit_combine")(self.gpu.raw, self.mailbox.ptr, self.nranks, self.T, self.Hq, self.D, epoch, wait_us, out.ptr),
+              "ns_b200_kvsplit_combine")
 
     def close(self):
         api = self.gpu.api

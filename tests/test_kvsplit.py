@@ -110,3 +110,36 @@ def test_combine_gives_up_when_a_peer_never_publishes(gpu, ops):
         gpu.sync()
     gpu.sync()                                   # the report clears; the context stays usable
     assert DevBuf.of(gpu, np.arange(4, dtype=np.float32)).read(np.float32).sum() == 6
+
+
+@pytest.mark.gpu
+def test_recorded_step_replays_with_device_epochs(gpu, ops):
+    """One rank's step (slice decode + push + combine) recorded with ns_q35_graph_begin/end and replayed: the step number
+    lives in the mailbox, so every replay is a new epoch on alternating buffers."""
+    from nextsycl_b200 import DevBuf
+    from nextsycl_b200 import workloads as W
+    from nextsycl_b200.dist import KvSplit
+    from oracle import oracle as O
+    T, Hq, Hkv, D, kv = 4, 32, 4, 128, 3000
+    q, k, v, p0 = W.gqa_case(951, T, Hq, Hkv, D, kv)
+    dq, dk, dv = DevBuf.of(gpu, q), DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+    box = DevBuf(gpu, KvSplit.mailbox_bytes(gpu.api, 1, T, Hq, D))
+    box.fill(0)
+    grp = KvSplit(gpu, 0, 1, T, Hq, D, local_mailboxes=[box])
+    sc = DevBuf(gpu, 4 * grp.scratch_floats(Hkv, kv))
+    out = DevBuf(gpu, T * Hq * D * 2)
+
+    def one():
+        grp.decode(dq, Hq * D, dk, dv, Hkv, kv, 0, p0, sc, epoch=0)
+        grp.combine(out, epoch=0, wait_us=1000)
+    one()                      # first call outside any recording (it sets kernel attributes)
+    gpu.sync()
+    graph = gpu.record(one)
+    want = O.gqa_flash_decode(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, kv, p0)
+    for rep in range(3):
+        out.fill(0xFF)
+        graph.launch()
+        gpu.sync()
+        got = out.read(np.float16).reshape(T, Hq * D).astype(np.float32)
+        assert np.all(np.abs(got - want) <= 2e-3 + 1e-2 * np.abs(want)), rep
+    graph.free()
