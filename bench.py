@@ -173,7 +173,7 @@ def device_random_f16(env, nbytes, seed, sigma=1.0, bf16=False):
 
 # ---- workloads: each returns (step_fn, info) where info has the algorithmic work a step ------------------------------------
 
-def wl_gqa_decode(env, T, Hq, Hkv, D, kv, B, rotate=1, real_data=True):
+def wl_gqa_decode(env, T, Hq, Hkv, D, kv, B, rotate=1, real_data=True, graph=False):
     """B sequences a GPU (each its own caches); `rotate` distinct cache sets used in turn so L2 cannot hold a step's reads."""
     from nextsycl_b200 import DevBuf
     from nextsycl_b200 import workloads as W
@@ -200,8 +200,20 @@ def wl_gqa_decode(env, T, Hq, Hkv, D, kv, B, rotate=1, real_data=True):
     scratch = DevBuf(env.gpu, max(4, 4 * ops.gqa_decode_scratch(B, T, Hq, Hkv, D, kv)))
     i = [0]
 
+    def one(r):
+        ops.gqa_decode(dq, Hq * D, T * Hq * D, sets[r][0], B, T, Hq, Hkv, D, kv, out, scratch)
+    if graph:
+        # the call reads its lengths from device memory, so a recorded step stays valid: replayed as one submission
+        one(0)
+        env.gpu.sync()
+        graphs = [env.gpu.record(lambda r=r: one(r)) for r in range(rotate)]
+        keep.append(graphs)
+
     def step():
-        ops.gqa_decode(dq, Hq * D, T * Hq * D, sets[i[0] % rotate][0], B, T, Hq, Hkv, D, kv, out, scratch)
+        if graph:
+            graphs[i[0] % rotate].launch()
+        else:
+            one(i[0] % rotate)
         i[0] += 1
     info = {"bytes": B * 2 * kv * Hkv * D * 2, "flops": 4 * (T * (kv - T) + T * (T + 1) // 2) * Hq * D * B, "bound": "hbm", "launches": 2,
             "keep": (keep, sets, dq, out, scratch), "qs": qs, "seqs": sets[0][1]}
@@ -241,10 +253,16 @@ def wl_mla_decode(env, n):
     sc = DevBuf(env.gpu, max(4, 4 * env.ops.mla_decode_scratch(1, 128, n - 1)))
     i = [0]
 
+    def one(r):
+        env.ops.mla_decode(q, caches[r], 1, 128, n - 1, float(1 / np.sqrt(192.0)), out, sc)
+    one(0)
+    env.gpu.sync()
+    graphs = [env.gpu.record(lambda r=r: one(r)) for r in range(rotate)]
+
     def step():
-        env.ops.mla_decode(q, caches[i[0] % rotate], 1, 128, n - 1, float(1 / np.sqrt(192.0)), out, sc)
+        graphs[i[0] % rotate].launch()
         i[0] += 1
-    info = {"bytes": 1152 * n, "flops": 278528 * n, "bound": "hbm+tensor", "launches": 2, "keep": (q, caches, out, sc)}
+    info = {"bytes": 1152 * n, "flops": 278528 * n, "bound": "hbm+tensor", "launches": 2, "keep": (q, caches, out, sc, graphs)}
     return step, info
 
 
@@ -319,11 +337,11 @@ def measure(env, name, steps, warmup):
     if name == "decode_c2":
         step, info = wl_gqa_decode(env, 1, 64, 8, 128, 32768, 8)
     elif name == "decode_c2_b1":
-        step, info = wl_gqa_decode(env, 1, 64, 8, 128, 32768, 1, rotate=3)
+        step, info = wl_gqa_decode(env, 1, 64, 8, 128, 32768, 1, rotate=3, graph=True)
     elif name == "decode_128k":
-        step, info = wl_gqa_decode(env, 1, 64, 8, 128, 131072, 1, rotate=2, real_data=False)
+        step, info = wl_gqa_decode(env, 1, 64, 8, 128, 131072, 1, rotate=2, real_data=False, graph=True)
     elif name == "decode_c5":
-        step, info = wl_gqa_decode(env, 4, 32, 4, 128, 262144, 1, rotate=2, real_data=False)
+        step, info = wl_gqa_decode(env, 4, 32, 4, 128, 262144, 1, rotate=2, real_data=False, graph=True)
     elif name == "decode_c5_split":
         step, info = wl_kvsplit_decode(env)
     elif name == "prefill_16k":
