@@ -91,6 +91,7 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
     constexpr int NT = D / 8;            // output n-tiles
     constexpr int KS = D / 16;           // k-steps of S = Q K^T
     extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int row_flag[8];
     uint8_t* q_s = smem;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint8_t* w_s = smem + RG * ROWB + warp * (NSTAGE * 2 * TILE);
@@ -316,40 +317,55 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
                     *reinterpret_cast<float2*>(os + ((size_t) (warp * RG + r)) * D + nt * 8 + 2 * (lane & 3)) =
                         make_float2(o[mt][nt][hh * 2], o[mt][nt][hh * 2 + 1]);
             }
+        // per row of the pass (at most 8): does this split hold any of its keys, and is it the row's only split - worked
+        // out once by one thread each (64-bit divisions are long instruction sequences), not per output element
+        if (tid < 8) {
+            const int t = t_a + tid;
+            int f = 0;
+            if (t <= t_b) {
+                const int64_t kv = row_keys(seq, t);
+                if (jbeg < kv) f = (ns_dec_splits(kv, p.Hkv) == 1 && !p.force_part) ? 2 : 1;
+            }
+            row_flag[tid] = f;   // 0: not one of the row's splits, 1: partial, 2: the row's output
+        }
         __syncthreads();
-        for (int i = tid; i < RG * D; i += THREADS) {
-            const int r = i / D, d = i % D, rho = row0 + r;
-            if (rho >= R) break;   // i ascends with r
-            const int t = rho / G, gq = rho % G;
+        for (int r = warp; r < RG; r += WARPS) {   // a warp a row: 32 lanes x D/32 features
+            const int rho = row0 + r;
+            if (rho >= R) break;
+            const int t = rho / G, gq = rho - t * G;
             if (t < t_a || t > t_b) continue;
-            const int64_t kv = row_keys(seq, t);
-            if (jbeg >= kv) continue;   // this split holds none of the row's keys: not one of its splits
+            const int flag = row_flag[t - t_a];
+            if (flag == 0) continue;
             float mx = -INFINITY;
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, ms[w * RG + r]);
-            float L = 0.f, A = 0.f;
-            if (mx != -INFINITY) {
+            float e[WARPS], L = 0.f;
 #pragma unroll
-                for (int w = 0; w < WARPS; ++w) {
-                    const float mw = ms[w * RG + r];
-                    const float e = mw == -INFINITY ? 0.f : exp2f(mw - mx);
-                    L += ls[w * RG + r] * e;
-                    A += os[((size_t) (w * RG + r)) * D + d] * e;
-                }
+            for (int w = 0; w < WARPS; ++w) {
+                const float mw = ms[w * RG + r];
+                e[w] = (mw == -INFINITY || mx == -INFINITY) ? 0.f : ex2_approx(mw - mx);
+                L += ls[w * RG + r] * e[w];
             }
             const int hq = hk * G + gq;
             const int64_t row = ((int64_t) b * T + t) * p.Hq + hq;
-            if (ns_dec_splits(kv, p.Hkv) == 1 && !p.force_part) {
-                const float v = L > 0.f ? A / L : 0.f;
-                if (p.out_f32) ((float*) p.out)[row * D + d] = v;
-                else ((__half*) p.out)[row * D + d] = __float2half_rn(v);
-            } else {
-                float* pr = p.part + (row * p.ns_max + split) * (D + 2);
-                pr[d] = A;
-                if (d == 0) {
-                    pr[D] = mx;
-                    pr[D + 1] = L;
+            const float inv = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+            for (int k = 0; k < D / 32; ++k) {
+                const int d = k * 32 + lane;
+                float A = 0.f;
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) A += os[((size_t) (w * RG + r)) * D + d] * e[w];
+                if (flag == 2) {
+                    if (p.out_f32) ((float*) p.out)[row * D + d] = A * inv;
+                    else ((__half*) p.out)[row * D + d] = __float2half_rn(A * inv);
+                } else {
+                    p.part[(row * p.ns_max + split) * (D + 2) + d] = A;
                 }
+            }
+            if (flag == 1 && lane == 0) {
+                float* pr = p.part + (row * p.ns_max + split) * (D + 2);
+                pr[D] = mx;
+                pr[D + 1] = L;
             }
         }
         __syncthreads();   // the merge buffer is stage memory again for the next pass

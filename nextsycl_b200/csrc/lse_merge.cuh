@@ -61,7 +61,20 @@ __device__ __forceinline__ float2 merge_row(const float* __restrict__ pp, int PS
     L = block_sum<THREADS>(l_loc, red);   // its barriers also publish w
     const int g = tid / LANES, lane = tid % LANES;
     float2 a = make_float2(0.f, 0.f);
-    for (int k = g; k < nsr; k += GROUPS) {
+    // 8 splits' loads in flight at a time (an un-unrolled loop waits out every load's latency in turn)
+    int k = g;
+    for (; k + 7 * GROUPS < nsr; k += 8 * GROUPS) {
+        float2 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const float2*>(pp + (size_t) (k + u * GROUPS) * PS + 2 * lane);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float e = w[k + u * GROUPS];
+            a.x += v[u].x * e;
+            a.y += v[u].y * e;
+        }
+    }
+    for (; k < nsr; k += GROUPS) {
         const float e = w[k];
         const float2 v = *reinterpret_cast<const float2*>(pp + (size_t) k * PS + 2 * lane);
         a.x += v.x * e;

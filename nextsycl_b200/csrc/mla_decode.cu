@@ -182,7 +182,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
                 if (did) {
                     idle = 0;
-                } else if (*abort_flag || ++idle > WAIT_LIMIT) {
+                    continue;
+                }
+                __nanosleep(40);   // an idle poll must not take issue slots from the softmax warps on this scheduler
+                if (*abort_flag || ++idle > WAIT_LIMIT) {
                     if (!*abort_flag) {
                         *abort_flag = 1;
                         if (p.status) {
