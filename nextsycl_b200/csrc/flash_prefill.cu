@@ -394,9 +394,11 @@ int launch(ns_gpu* g, const FlashPrefillArgs& a, const char* where) {
 
 int ns_launch_flash_prefill(ns_gpu* g, const FlashPrefillArgs& a, const char* where) {
     if (a.T <= 0) return 0;
-    // two row blocks a CTA once there are rows for them (flash_prefill2.cu); NS_B200_PREFILL_1BLOCK keeps the one-block kernel
-    static const bool one_block = getenv("NS_B200_PREFILL_1BLOCK") != nullptr;
-    if (a.Dqk == 128 && a.Dv == 128 && a.T > 128 && !one_block) return ns_launch_flash_prefill2(g, a, where);
+    // NS_B200_PREFILL_2BLOCK=1 selects the variant with two row blocks a CTA (flash_prefill2.cu). It is correct but was
+    // measured slower at 16K (769 against 1,007 TFLOP/s): the softmax is bound by the SM's instruction issue rate, which
+    // two softmax warpgroups share, not by latency.
+    static const bool two_block = getenv("NS_B200_PREFILL_2BLOCK") != nullptr;
+    if (a.Dqk == 128 && a.Dv == 128 && a.T > 128 && two_block) return ns_launch_flash_prefill2(g, a, where);
     if (a.Dqk == 128 && a.Dv == 128 && !a.bf16) return launch<128, 128, 128, 2, 0>(g, a, where);
     if (a.Dqk == 128 && a.Dv == 128 && a.bf16) return launch<128, 128, 128, 2, 1>(g, a, where);
     if (a.Dqk == 192 && a.Dv == 128 && a.bf16) return launch<192, 128, 128, 2, 1>(g, a, where);
