@@ -344,6 +344,8 @@ def measure(env, name, steps, warmup):
         step, info = wl_gqa_decode(env, 4, 32, 4, 128, 262144, 1, rotate=2, real_data=False, graph=True)
     elif name == "decode_c5_split":
         step, info = wl_kvsplit_decode(env)
+    elif name.startswith("decode_split_kv"):      # decode_split_kv<tokens>: the same with another context length
+        step, info = wl_kvsplit_decode(env, kv=int(name[len("decode_split_kv"):]))
     elif name == "prefill_16k":
         step, info = wl_prefill(env, 16384, 16, 4, 128)
     elif name == "prefill_c1":

@@ -430,7 +430,9 @@ __global__ void __launch_bounds__(MERGE_THREADS) gqa_merge_push_kernel(const Par
             __threadfence_system();
             for (int r = 0; r < p.nranks; ++r) {
                 long long* flag = reinterpret_cast<long long*>(p.mailboxes[r] + ns_mbox_flags_off(p.nranks, rows, D)) + buf * p.nranks + p.rank;
-                asm volatile("st.release.sys.global.s64 [%0], %1;\n" ::"l"(flag), "l"(epoch) : "memory");
+                // the fence above is the release; a release on each of these stores would wait out an NVLink round trip
+                // per rank, one after the other
+                asm volatile("st.relaxed.sys.global.s64 [%0], %1;\n" ::"l"(flag), "l"(epoch) : "memory");
             }
         }
     }

@@ -130,18 +130,20 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             constexpr uint32_t idesc_pv = idesc_f16(BM, DVH, 0, 0, 1);
             bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, p.status, 501);
             if (ok) ok = mbar_wait(smem_u32(qt_full), 0, abort_flag, p.status, 502);
+            // descriptors: everything but the start address is fixed, and the address field (bits 0..13, in 16-byte units)
+            // cannot carry into the next field for any shared-memory address, so a step is one 32-bit add
+            const uint64_t q_desc0 = smem_desc_sw128(smem_u32(q_s), 16, 1024);
             auto issue_qk = [&](int j) {
-                const uint32_t cb = smem_u32(c_s + (j % NSTAGE) * TILE_BYTES), qb = smem_u32(q_s);
+                const uint64_t c_desc0 = smem_desc_sw128(smem_u32(c_s + (j % NSTAGE) * TILE_BYTES), 16, 1024);
                 const uint32_t d = tmem + (uint32_t) (S_COL + (j & 1) * BN);
 #pragma unroll
                 for (int k = 0; k < CR / 16; ++k) {
-                    const uint64_t bd = smem_desc_sw128(cb + (k / 4) * (BN * 128) + (k % 4) * 32, 16, 1024);
+                    const uint64_t bd = c_desc0 + (uint64_t) (((k / 4) * (BN * 128) + (k % 4) * 32) >> 4);
                     if (k < QT / 16) {
                         mma_ts(d, tmem + (uint32_t) (Q_COL + k * 8), bd, idesc_qk, k > 0);
                     } else {
                         const int ks = k - QT / 16;
-                        const uint64_t ad = smem_desc_sw128(qb + (ks / 4) * (BM * 128) + (ks % 4) * 32, 16, 1024);
-                        mma_ss(d, ad, bd, idesc_qk, 1);
+                        mma_ss(d, q_desc0 + (uint64_t) (((ks / 4) * (BM * 128) + (ks % 4) * 32) >> 4), bd, idesc_qk, 1);
                     }
                 }
                 mma_commit(smem_u32(s_full + (j & 1)));
@@ -149,13 +151,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             auto issue_pv = [&](int j) {
                 const int s = j % NSTAGE;
                 // the value operand: this CTA's 4 chunks of the same tile, MN-major; 16 cells a step
-                const uint32_t vb = smem_u32(c_s + s * TILE_BYTES) + (uint32_t) (hv * (DVH / 64) * (BN * 128));
+                const uint64_t v_desc0 = smem_desc_sw128(smem_u32(c_s + s * TILE_BYTES) + (uint32_t) (hv * (DVH / 64) * (BN * 128)), BN * 128, 1024);
                 const uint32_t pa = tmem + (uint32_t) (S_COL + (j & 1) * BN);
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k) {
-                    const uint64_t bd = smem_desc_sw128(vb + k * (16 * 128), BN * 128, 1024);
-                    mma_ts(tmem + (uint32_t) O_COL, pa + (uint32_t) (k * 8), bd, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-                }
+                for (int k = 0; k < BN / 16; ++k)
+                    mma_ts(tmem + (uint32_t) O_COL, pa + (uint32_t) (k * 8), v_desc0 + (uint64_t) ((k * (16 * 128)) >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
                 mma_commit(smem_u32(c_empty + s));
                 mma_commit(smem_u32(pv_done));
                 if (j == ntiles - 1) mma_commit(smem_u32(o_final));
@@ -168,16 +168,17 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             uint32_t idle = 0;
             while (ok && pv < ntiles) {
                 bool did = false;
-                if (qk < ntiles && qk - pv < 2 && mbar_try(smem_u32(c_full + qk % NSTAGE), (uint32_t) (qk / NSTAGE) & 1)) {
-                    fence_after_sync();
-                    issue_qk(qk);
-                    ++qk;
-                    did = true;
-                }
+                // P V first: it is short, and it frees a tile stage for the next load
                 if (pv < qk && mbar_try(smem_u32(p_full + (pv & 1)), (uint32_t) (pv >> 1) & 1)) {
                     fence_after_sync();
                     issue_pv(pv);
                     ++pv;
+                    did = true;
+                }
+                if (qk < ntiles && qk - pv < 2 && mbar_try(smem_u32(c_full + qk % NSTAGE), (uint32_t) (qk / NSTAGE) & 1)) {
+                    fence_after_sync();
+                    issue_qk(qk);
+                    ++qk;
                     did = true;
                 }
                 if (did) {
@@ -300,19 +301,30 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const int64_t row = (int64_t) t * p.H + h0 + r;
             const bool direct = p.ns == 1;
             const float inv = direct ? (l > 0.f ? 1.0f / l : 0.f) : 1.0f;
-            float* dst = direct ? p.out + row * L + hv * DVH : p.part + (row * p.ns + split) * PS + hv * DVH;
-#pragma unroll
+            // A thread holds one row of O; written as it lies, a warp's store would touch 32 rows. Each 32-column chunk
+            // goes through a padded [32][33] tile in shared memory (the tile stages are idle by now), so that a warp
+            // instruction writes 128 contiguous bytes of one row.
+            float* tile = reinterpret_cast<float*>(c_s) + warp * (32 * 33);
+            const int lane = tid & 31;
+            const int64_t row_w = (int64_t) t * p.H + h0 + warp * 32;   // the warp's first row
+            const int rows_w = max(0, min(32, p.H - (h0 + warp * 32)));
+#pragma unroll 1
             for (int c = 0; c < DVH / 32; ++c) {
                 uint32_t v[32];
                 tmem_ld32(tmem + lane_base + (uint32_t) (O_COL + c * 32), v);
                 tmem_wait_ld();
-                if (head_live) {
 #pragma unroll
-                    for (int e = 0; e < 8; ++e)
-                        reinterpret_cast<float4*>(dst + c * 32)[e] =
-                            make_float4(__uint_as_float(v[4 * e]) * inv, __uint_as_float(v[4 * e + 1]) * inv, __uint_as_float(v[4 * e + 2]) * inv,
-                                        __uint_as_float(v[4 * e + 3]) * inv);
+                for (int e = 0; e < 32; ++e) tile[lane * 33 + e] = __uint_as_float(v[e]) * inv;
+                __syncwarp();
+                float* dst0 = direct ? p.out + row_w * L + hv * DVH : p.part + (row_w * p.ns + split) * PS + hv * DVH;
+                const int64_t dst_row = direct ? L : (int64_t) p.ns * PS;
+                if (rows_w == 32) {
+#pragma unroll
+                    for (int rr = 0; rr < 32; ++rr) dst0[rr * dst_row + c * 32 + lane] = tile[rr * 33 + lane];
+                } else {
+                    for (int rr = 0; rr < rows_w; ++rr) dst0[rr * dst_row + c * 32 + lane] = tile[rr * 33 + lane];
                 }
+                __syncwarp();
             }
             if (head_live && !direct && hv == 0) {
                 float* st = p.part + (row * p.ns + split) * PS + L;

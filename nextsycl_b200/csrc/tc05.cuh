@@ -75,6 +75,11 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int 
                  : "memory");
 }
 
+// the same box only as far as L2: no shared memory, no barrier - a later tma_load_3d of it finds it there
+__device__ __forceinline__ void tma_prefetch_3d(const void* tmap, int x, int y, int z) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n" ::"l"(tmap), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
 // ---- tensor memory ---------------------------------------------------------------------------------------------------
 // one whole warp; ncols a power of two >= 32; the base address lands in *slot (shared memory)
 __device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t ncols) {
