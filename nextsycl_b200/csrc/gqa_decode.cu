@@ -45,6 +45,11 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// A kernel that follows another on the stream and starts with pdl_wait(): its blocks may be placed on SMs while the
+// first kernel drains, and run once that kernel has completed and its writes are visible (programmatic dependent launch).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -98,6 +103,7 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
 
     // the row groups of one (split, key head) are neighbours in the grid: they run at the same time, and the second
     // to read a key tile finds it in L2
+    pdl_launch_dependents();   // the merge kernel's blocks may take SMs as they free up; they wait for this grid to finish
     const int split = blockIdx.x / p.groups, rg = blockIdx.x % p.groups, hk = blockIdx.y;
     const int b = blockIdx.z;
     const ns_b200_seq seq = p.seqs ? p.seqs[b] : p.one;
@@ -379,6 +385,7 @@ constexpr int MERGE_THREADS = 256;
 template <int D>
 __global__ void __launch_bounds__(MERGE_THREADS) gqa_merge_kernel(const Params p) {
     __shared__ float sm[lse::smem_floats<D, MERGE_THREADS>()];
+    pdl_wait();   // the split kernel's partials
     const int64_t rh = blockIdx.x;   // (b, t, hq)
     const int t = (int) ((rh / p.Hq) % p.T), b = (int) (rh / ((int64_t) p.Hq * p.T));
     const ns_b200_seq seq = p.seqs ? p.seqs[b] : p.one;
@@ -400,6 +407,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) gqa_merge_kernel(const Params p
 template <int D>
 __global__ void __launch_bounds__(MERGE_THREADS) gqa_merge_push_kernel(const Params p) {
     __shared__ float sm[lse::smem_floats<D, MERGE_THREADS>()];
+    pdl_wait();   // the split kernel's partials
     const int64_t rh = blockIdx.x;   // (t, hq)
     const int t = (int) (rh / p.Hq);
     const ns_b200_seq seq = p.seqs ? p.seqs[0] : p.one;
@@ -509,6 +517,21 @@ __global__ void __launch_bounds__(D) gqa_combine_kernel(const CombineParams c) {
     else ((__half*) c.out)[rh * D + d] = __float2half_rn(v);
 }
 
+template <class K, class P>
+cudaError_t launch_dependent(K kernel, unsigned blocks, unsigned threads, cudaStream_t stream, const P& params) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, params);
+}
+
 template <int D, int MT, int NSTAGE>
 int launch(ns_gpu* g, const Params& p, int64_t B, const char* where) {
     constexpr int RG = 16 * MT;
@@ -524,10 +547,10 @@ int launch(ns_gpu* g, const Params& p, int64_t B, const char* where) {
     kern<<<grid, THREADS, smem, g->compute>>>(p);
     if (ns_launched(where)) return -1;
     if (p.mailboxes) {
-        gqa_merge_push_kernel<D><<<(unsigned) (p.T * p.Hq), MERGE_THREADS, 0, g->compute>>>(p);
+        NS_CUDA(launch_dependent(gqa_merge_push_kernel<D>, (unsigned) (p.T * p.Hq), MERGE_THREADS, g->compute, p), where);
         if (ns_launched(where)) return -1;
     } else if (p.ns_max > 1) {
-        gqa_merge_kernel<D><<<(unsigned) (B * p.T * p.Hq), MERGE_THREADS, 0, g->compute>>>(p);
+        NS_CUDA(launch_dependent(gqa_merge_kernel<D>, (unsigned) (B * p.T * p.Hq), MERGE_THREADS, g->compute, p), where);
         if (ns_launched(where)) return -1;
     }
     return 0;
