@@ -143,6 +143,25 @@ int ns_to_q8row(ns_gpu* g, const float* x, void* y, int64_t n, int64_t L);
 int ns_gather_q8_h(ns_gpu* g, const void* src, const int32_t* idx, uint16_t* out, int64_t n, int64_t L);
 int ns_gather_h(ns_gpu* g, const uint16_t* src, const int32_t* idx, uint16_t* out, int64_t n, int64_t C);
 
+/* kernels/llm/deepseek41/silo/ds41.h:28-36 - deepseek41's MQA with heads of 512 where a key is its own value. A row at
+ * position p = pos0 + t reads its last min(window, p+1) raw keys from the ring (fp16 [R][512], slot pos % R) and then the
+ * compressed cells it sees (comp fp16 [n][512], j < (p+1)/ratio; with sel [T][K], the K it lists once it sees more than
+ * K); sinks [H] joins each head's softmax denominator only. q, out fp32 [T][H][512]. The reference has a vector-unit
+ * kernel (silo/ds41.cpp:139-229, at most ~12K cells a row) and an XMX one (silo/attn.cpp:64-310, H a multiple of 8);
+ * both names run the same path here for any H and any cell count: the rows' cells gathered to dense fp16 in bounded
+ * blocks of rows, then the tensor-core latent-attention kernel with the XMX kernel's numerics (q scaled by
+ * scale*log2(e) and rounded to fp16, exp2, fp16 weights) and the sink folded into its normalisation (attn.cpp:266-285).
+ * A sel index outside [0, (p+1)/ratio) is clamped into it rather than read. */
+int ns_ds41_attend(ns_gpu* g, const float* q, const uint16_t* raw, int64_t R, const uint16_t* comp, int64_t ratio, const int32_t* sel, int64_t K,
+                   const float* sinks, float* out, int64_t T, int64_t H, int64_t pos0, int64_t window, float scale);
+int ns_ds41_attend_xmx_supported(int64_t H, int64_t D);   /* 1 when D == 512 (the reference also wants H % 8 == 0) */
+int ns_ds41_attend_xmx(ns_gpu* g, const float* q, const uint16_t* raw, int64_t R, const uint16_t* comp, int64_t ratio, const int32_t* sel, int64_t K,
+                       const float* sinks, float* out, int64_t T, int64_t H, int64_t pos0, int64_t window, float scale);
+/* silo/ds41.cpp:116-133 - the writers of those caches: T fp32 rows [T][D] into ring slots (pos0 + t) % R as fp16; n fp32
+ * rows into rows j0.. of an fp16 matrix */
+int ns_ds41_ring_put(ns_gpu* g, const float* kv, uint16_t* ring, int64_t T, int64_t pos0, int64_t R, int64_t D);
+int ns_ds41_rows_f16(ns_gpu* g, const float* x, uint16_t* cache, int64_t n, int64_t j0, int64_t D);
+
 /* The middle stage alone (BASELINE's absorbed-MLA decode): q [T][H][576] fp16 = absorbed query (512) then rotated
  * part (64); cache [n][576] fp16; out u [T][H][512] fp32. scratch: ns_b200_mla_decode_scratch floats (it depends on
  * the GPU's SM count, hence the handle), 0 when the row is not split. */

@@ -85,6 +85,11 @@ ATTN = {
     "ns_to_q8row": (C.c_int, [vp, vp, vp, i64, i64]),
     "ns_gather_q8_h": (C.c_int, [vp, vp, vp, vp, i64, i64]),
     "ns_gather_h": (C.c_int, [vp, vp, vp, vp, i64, i64]),
+    "ns_ds41_attend": (C.c_int, [vp, vp, vp, i64, vp, i64, vp, i64, vp, vp, i64, i64, i64, i64, C.c_float]),
+    "ns_ds41_attend_xmx_supported": (C.c_int, [i64, i64]),
+    "ns_ds41_attend_xmx": (C.c_int, [vp, vp, vp, i64, vp, i64, vp, i64, vp, vp, i64, i64, i64, i64, C.c_float]),
+    "ns_ds41_ring_put": (C.c_int, [vp, vp, vp, i64, i64, i64, i64]),
+    "ns_ds41_rows_f16": (C.c_int, [vp, vp, vp, i64, i64, i64]),
     "ns_b200_mla_decode_scratch": (i64, [vp, i64, i64, i64]),
     "ns_b200_mla_decode": (C.c_int, [vp, vp, vp, i64, i64, i64, C.c_float, vp, vp]),
     "ns_b200_gqa_decode_scratch": (i64, [i64, i64, i64, i64, i64, i64]),

@@ -228,7 +228,7 @@ int attend_sel(ns_gpu* g, const char* name, const float* qa, const void* c, bool
         void* kept = nullptr;
         if (ns_kept(g, (size_t) (q_bytes + part * 4), &kept)) return -1;
         to_f16_kernel<<<1024, 256, 0, g->compute>>>(qa, (__half*) kept, T * H * Lw);
-        MlaDecodeArgs a{kept, c, u, part ? (float*) ((uint8_t*) kept + q_bytes) : nullptr, T, H, pos0, scale, 0, pos0 + T, nullptr, 0};
+        MlaDecodeArgs a{kept, c, u, part ? (float*) ((uint8_t*) kept + q_bytes) : nullptr, T, H, pos0, scale, 0, pos0 + T, nullptr, 0, nullptr};
         return ns_launch_mla_decode(g, a, name);
     }
     // a row reads its selected pools' cells and its incomplete pool, or (count < 0) every earlier token up to 2,560
@@ -249,7 +249,7 @@ int attend_sel(ns_gpu* g, const char* name, const float* qa, const void* c, bool
     if (q8) mla_gather_kernel<true><<<grid, 256, 0, g->compute>>>(c, sel, sel_cnt, K, pos0, NC, stage, counts);
     else mla_gather_kernel<false><<<grid, 256, 0, g->compute>>>(c, sel, sel_cnt, K, pos0, NC, stage, counts);
     if (ns_launched(name)) return -1;
-    MlaDecodeArgs a{q16, stage, u, pbuf, T, H, pos0, scale, 0, NC, counts, NC * Lw};
+    MlaDecodeArgs a{q16, stage, u, pbuf, T, H, pos0, scale, 0, NC, counts, NC * Lw, nullptr};
     return ns_launch_mla_decode(g, a, name);
 }
 

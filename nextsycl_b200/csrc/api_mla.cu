@@ -79,7 +79,7 @@ int ns_b200_mla_decode(ns_gpu* g, const void* q, const void* cache, int64_t T, i
     if (((uintptr_t) q & 15) != 0 || ((uintptr_t) cache & 15) != 0 || ((uintptr_t) out & 15) != 0 || ((uintptr_t) scratch & 15) != 0)
         return ns_fail(std::string(name) + ": buffers 16-byte aligned");
     if (ns_mla_partial_floats(pos0 + T, T, H, g->sms) > 0 && !scratch) return ns_fail(std::string(name) + ": no scratch");
-    MlaDecodeArgs a{q, cache, out, scratch, T, H, pos0, scale, 64, pos0 + T, nullptr, 0};
+    MlaDecodeArgs a{q, cache, out, scratch, T, H, pos0, scale, 64, pos0 + T, nullptr, 0, nullptr};
     return ns_launch_mla_decode(g, a, name);
     NS_CATCH("ns_b200_mla_decode")
 }
@@ -104,7 +104,7 @@ int ns_ds2_mla_decode(ns_gpu* g, const float* q, const uint16_t* kb, const uint1
     float* part = part_floats ? (float*) ((uint8_t*) kept + qa_bytes + u_bytes) : nullptr;
     mla_absorb_kernel<<<(unsigned) (T * H), 256, 0, g->compute>>>(q, (const __half*) kb, qa, (int) T, (int) H);
     if (ns_launched(name)) return -1;
-    MlaDecodeArgs a{qa, cache, u, part, T, H, pos0, scale, 64, pos0 + T, nullptr, 0};
+    MlaDecodeArgs a{qa, cache, u, part, T, H, pos0, scale, 64, pos0 + T, nullptr, 0, nullptr};
     if (ns_launch_mla_decode(g, a, name)) return -1;
     mla_unabsorb_kernel<<<(unsigned) (T * H), 256, 0, g->compute>>>(u, (const __half*) vb, out, (int) T, (int) H);
     return ns_launched(name);

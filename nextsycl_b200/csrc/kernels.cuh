@@ -93,6 +93,7 @@ struct MlaDecodeArgs {
     int64_t n_max;            // the most cells any row attends to (sizes the grid and the partials)
     const int* counts;        // device [T]: cells each row attends to; null: pos0 + t + 1 (causal over one shared cache)
     int64_t cache_rows_apart; // elements between the rows' own cell matrices; 0: one shared cache
+    const float* sinks;       // device [H] or null: a per-head sink (natural-log units) that joins the denominator only
 };
 // cells a key split / floats of partials for rows that see up to n cells, on a GPU of `sms` SMs
 int64_t ns_mla_split(int64_t n, int64_t T, int64_t H, int sms);

@@ -43,6 +43,7 @@ struct Geo {
 
 struct Params {
     const __half* q;       // [T][H][CR] fp16
+    const float* sinks;    // per head, natural-log units, or null: a sink joins the denominator only (deepseek41)
     const int* counts;     // per row: cells it attends to (null: pos0 + t + 1)
     int zmul;              // 1: row t has its own cell matrix (third tensor-map coordinate t); 0: one shared cache
     float* out;            // [T][H][512]
@@ -300,7 +301,17 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             fence_after_sync();
             const int64_t row = (int64_t) t * p.H + h0 + r;
             const bool direct = p.ns == 1;
-            const float inv = direct ? (l > 0.f ? 1.0f / l : 0.f) : 1.0f;
+            float inv = 1.0f;
+            if (direct) {
+                // with a sink s: out = O 2^(m - mx) / (l 2^(m - mx) + 2^(s - mx)), mx = max(m, s) (kernels/llm/deepseek41/silo/attn.cpp:266-285)
+                float f = 1.0f, den = l;
+                if (p.sinks && head_live) {
+                    const float sk = p.sinks[h0 + r] * 1.4426950408889634f, mx = fmaxf(m_ref, sk);
+                    f = ex2(m_ref - mx);
+                    den = l * f + ex2(sk - mx);
+                }
+                inv = den > 0.f ? f / den : 0.f;
+            }
             // A thread holds one row of O; written as it lies, a warp's store would touch 32 rows. Each 32-column chunk
             // goes through a padded [32][33] tile in shared memory (the tile stages are idle by now), so that a warp
             // instruction writes 128 contiguous bytes of one row.
@@ -351,7 +362,13 @@ __global__ void __launch_bounds__(512) mla_merge_kernel(const Params p) {
     float mx, den;
     const float2 a = lse::merge_row<L, 512>(p.part + row * p.ns * PS, PS, nsr, mx, den, sm);
     if (threadIdx.x < L / 2) {
-        const float inv = den > 0.f ? 1.0f / den : 0.f;
+        float f = 1.0f;
+        if (p.sinks) {
+            const float sk = p.sinks[row % p.H] * 1.4426950408889634f, m2 = fmaxf(mx, sk);
+            f = mx == -INFINITY ? 0.f : exp2f(mx - m2);
+            den = den * f + exp2f(sk - m2);
+        }
+        const float inv = den > 0.f ? f / den : 0.f;
         *reinterpret_cast<float2*>(p.out + row * L + 2 * threadIdx.x) = make_float2(a.x * inv, a.y * inv);
     }
 }
@@ -402,6 +419,7 @@ int launch(ns_gpu* g, const MlaDecodeArgs& a, const char* where) {
     Params p;
     p.q = (const __half*) a.q;
     p.counts = a.counts;
+    p.sinks = a.sinks;
     p.zmul = a.cache_rows_apart > 0 ? 1 : 0;
     p.out = a.out;
     p.part = a.part;

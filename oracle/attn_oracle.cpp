@@ -606,6 +606,94 @@ void orc_mla_dec512(const float* qa, const void* cv, float* u, int64_t T, int64_
     }
 }
 
+// ---- deepseek41: MQA over a window ring and compressed cells, with sinks ------------------------------------------
+
+// ns_ds41_attend. A row at position p = pos0+t reads n_raw = min(window, p+1) raw keys from the ring [R][512] (slot
+// (p - n_raw + 1 + i) % R) and then compressed cells comp [n][512]: the first vis = (p+1)/ratio of them, or - when sel is
+// given and vis > K - the K cells sel[t][0..K) (kernels/llm/deepseek41/silo/attn.cpp:83-94). A key is its own value.
+// The sink of a head joins the denominator only.
+//   mode 0, the vector kernel (kernels/llm/deepseek41/silo/ds41.cpp:139-229): fp32 q, scores (q . c) * scale, the
+//     maximum starts from the sink, natural exp, denominator sum + exp(sink - mx).
+//   mode 1, the XMX kernel (silo/attn.cpp:64-259 and the merge :266-285): q scaled by scale*log2(e) and rounded to fp16,
+//     chunks of 16 cells ascending, exp2, weights rounded to fp16 for the numerator, then
+//     out = O 2^(m - mx) / (l 2^(m - mx) + 2^(sink*log2e - mx)), mx = max(m, sink*log2e).
+void orc_ds41_attend(const float* q, const uint16_t* raw, int64_t R, const uint16_t* comp, int64_t ratio, const int32_t* sel, int64_t K,
+                     const float* sinks, float* out, int64_t T, int64_t H, int64_t pos0, int64_t window, float scale, int mode) {
+    const int64_t D = 512;
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+    for (int64_t t = 0; t < T; ++t) {
+        for (int64_t h = 0; h < H; ++h) {
+            const int64_t p = pos0 + t;
+            const int64_t n_raw = std::min<int64_t>(window, p + 1);
+            const int64_t vis = comp ? (p + 1) / ratio : 0;
+            const bool pick = sel && vis > K;
+            const int64_t n = n_raw + (pick ? K : vis);
+            auto cell = [&](int64_t i) -> const uint16_t* {
+                if (i < n_raw) return raw + ((p - n_raw + 1 + i) % R) * D;
+                const int64_t k = i - n_raw;
+                return comp + (pick ? (int64_t) sel[t * K + k] : k) * D;
+            };
+            const float* qr = q + (t * H + h) * D;
+            float* o = out + (t * H + h) * D;
+            if (mode == 0) {
+                std::vector<float> sc((size_t) n), acc((size_t) D, 0.f);
+                float mx = sinks[h];
+                for (int64_t i = 0; i < n; ++i) {
+                    const uint16_t* c = cell(i);
+                    float d = 0.f;
+                    for (int64_t r = 0; r < D; ++r) d += qr[r] * h2f(c[r]);
+                    sc[i] = d * scale;
+                    mx = std::fmax(mx, sc[i]);
+                }
+                float sum = 0.f;
+                for (int64_t i = 0; i < n; ++i) {
+                    sc[i] = std::exp(sc[i] - mx);
+                    sum += sc[i];
+                }
+                sum += std::exp(sinks[h] - mx);
+                for (int64_t i = 0; i < n; ++i) {
+                    const uint16_t* c = cell(i);
+                    for (int64_t r = 0; r < D; ++r) acc[r] += sc[i] * h2f(c[r]);
+                }
+                for (int64_t r = 0; r < D; ++r) o[r] = acc[r] / sum;
+            } else {
+                std::vector<float> qh((size_t) D), O((size_t) D, 0.f);
+                for (int64_t r = 0; r < D; ++r) qh[r] = round_h(qr[r] * (scale * LOG2E));
+                float m = NEG_INF, l = 0.f;
+                for (int64_t j0 = 0; j0 < n; j0 += 16) {
+                    float s[16], mxc = NEG_INF;
+                    for (int c = 0; c < 16; ++c) {
+                        s[c] = NEG_INF;
+                        if (j0 + c < n) {
+                            const uint16_t* cc = cell(j0 + c);
+                            float d = 0.f;
+                            for (int64_t r = 0; r < D; ++r) d += qh[r] * h2f(cc[r]);
+                            s[c] = d;
+                        }
+                        mxc = std::fmax(mxc, s[c]);
+                    }
+                    const float mn = std::fmax(m, mxc), cf = mn == NEG_INF ? 1.f : std::exp2(m - mn);
+                    for (int64_t r = 0; r < D; ++r) O[r] *= cf;
+                    float sum = 0.f;
+                    for (int c = 0; c < 16; ++c) {
+                        if (s[c] == NEG_INF) continue;
+                        const float pv = std::exp2(s[c] - mn);
+                        sum += pv;
+                        const float pr = round_h(pv);
+                        const uint16_t* cc = cell(j0 + c);
+                        for (int64_t r = 0; r < D; ++r) O[r] += pr * h2f(cc[r]);
+                    }
+                    l = l * cf + sum;
+                    m = mn;
+                }
+                const float sk = sinks[h] * LOG2E, mx = std::fmax(m, sk);
+                const float f = std::exp2(m - mx), den = l * f + std::exp2(sk - mx);
+                for (int64_t r = 0; r < D; ++r) o[r] = O[r] * f / den;
+            }
+        }
+    }
+}
+
 // ---- cache writers -----------------------------------------------------------------------------------------------
 
 // ns_q35_kv_store (kernels/llm/qwen35/q35.cpp:573-588): fp32 rows k [T][ks], v [T][vs] -> fp16 caches [Hkv][cap][D]

@@ -169,3 +169,12 @@ def merge(part, rows, ns, D, PS, sinks=None):
     out = np.empty((rows, D), np.float32)
     lib().orc_merge(_f(part), i64(rows), i64(ns), i64(D), i64(PS), None if sinks is None else _f(sinks), _f(out))
     return out
+
+
+def ds41_attend(q, raw, R, comp, ratio, sel, K, sinks, T, H, pos0, window, scale, mode=1):
+    """deepseek41's MQA-512 with sinks. q fp32 [T, H, 512]; raw uint16 [R, 512]; comp uint16 [n, 512] or None; sel int32
+    [T, K] or None; sinks fp32 [H]. mode 0: the vector kernel's numerics, 1: the XMX kernel's."""
+    out = np.empty((T, H, 512), np.float32)
+    lib().orc_ds41_attend(_f(q), _h(raw), i64(R), None if comp is None else _h(comp), i64(ratio), None if sel is None else sel.ctypes.data_as(_pi),
+                          i64(K), _f(sinks), _f(out), i64(T), i64(H), i64(pos0), i64(window), C.c_float(scale), C.c_int(mode))
+    return out

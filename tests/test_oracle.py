@@ -166,3 +166,49 @@ def test_known_answers():
         c = g[name + "_c"].view(np.uint16)
         assert np.allclose(O.mla_fused(g[name + "_q"], c, T, H, 512, 64, pos0, sc), g[name + "_fused"], rtol=0, atol=1e-6)
         assert np.allclose(O.mla_gemm(g[name + "_q"], c, T, H, 512, 64, pos0, sc), g[name + "_gemm"], rtol=0, atol=1e-6)
+
+
+def ds41_numpy(q, raw, R, comp, ratio, sel, K, sinks, T, H, pos0, window, scale):
+    """The attention of reference/deepseek41/ds41ref.py:241-250 (scores, the maximum with the sink, exp, a denominator that
+    also holds exp(sink - m)) over the cells kernels/llm/deepseek41/silo/attn.cpp:83-94 lists for a row, in float64."""
+    out = np.zeros((T, H, 512))
+    for t in range(T):
+        p = pos0 + t
+        n_raw = min(window, p + 1)
+        cells = [raw[(p - n_raw + 1 + i) % R] for i in range(n_raw)]
+        vis = (p + 1) // ratio if comp is not None else 0
+        if sel is not None and vis > K:
+            cells += [comp[j] for j in sel[t]]
+        else:
+            cells += [comp[j] for j in range(vis)]
+        kk = np.stack(cells).view(np.float16).astype(np.float64)
+        s = q[t].astype(np.float64) @ kk.T * scale
+        m = np.maximum(s.max(-1), sinks)
+        pr = np.exp(s - m[:, None])
+        out[t] = (pr @ kk) / (pr.sum(-1) + np.exp(sinks - m))[:, None]
+    return out
+
+
+@pytest.mark.parametrize("T,pos0,window,R,ncomp,ratio,K", [(1, 5, 8, 8, 0, 4, 0), (1, 300, 128, 128, 75, 4, 0), (2, 299, 64, 96, 75, 4, 16),
+                                                           (3, 0, 16, 16, 0, 4, 0)])
+def test_ds41_attend_both_numerics(T, pos0, window, R, ncomp, ratio, K):
+    H = 8
+    rng = W.rng(970, T * 1000 + pos0)
+    q = rng.standard_normal((T, H, 512), dtype=np.float32)
+    raw = O.to_f16_bits(0.5 * rng.standard_normal((R, 512), dtype=np.float32))
+    comp = O.to_f16_bits(0.5 * rng.standard_normal((ncomp, 512), dtype=np.float32)) if ncomp else None
+    sel = None
+    if K:
+        sel = np.stack([np.sort(rng.choice((pos0 + t + 1) // ratio, size=K, replace=False)) for t in range(T)]).astype(np.int32)
+    sinks = rng.standard_normal(H).astype(np.float32)
+    scale = np.float32(512 ** -0.5)
+    want = ds41_numpy(q, raw, R, comp, ratio, sel, K, sinks, T, H, pos0, window, scale)
+    vec = O.ds41_attend(q, raw, R, comp, ratio, sel, K, sinks, T, H, pos0, window, scale, mode=0)
+    xmx = O.ds41_attend(q, raw, R, comp, ratio, sel, K, sinks, T, H, pos0, window, scale, mode=1)
+    assert np.abs(vec - want).max() < 1e-5
+    assert close(xmx, want)
+    # a sink far below every score leaves a plain softmax; far above, it takes the whole denominator
+    low = O.ds41_attend(q, raw, R, comp, ratio, sel, K, np.full(H, -1e4, np.float32), T, H, pos0, window, scale, mode=1)
+    high = O.ds41_attend(q, raw, R, comp, ratio, sel, K, np.full(H, 1e4, np.float32), T, H, pos0, window, scale, mode=1)
+    assert close(low, ds41_numpy(q, raw, R, comp, ratio, sel, K, np.full(H, -1e4), T, H, pos0, window, scale))
+    assert np.abs(high).max() < 1e-30
