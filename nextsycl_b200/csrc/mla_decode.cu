@@ -32,6 +32,28 @@ constexpr int THREADS = 192;
 constexpr int PS = 516;                        // floats a partial row: O[512], m, l, 2 pad
 constexpr float RESCALE_LOG2 = 8.0f;
 
+#ifdef NS_MLA_TRACE
+__device__ long long g_trace[16384];
+__device__ __forceinline__ void trace(int kind, int j) {
+    if (blockIdx.x != NS_MLA_TRACE && kind != 0 && kind != 6 && kind != 7 && kind != 10 && kind != 11) return;
+    j = blockIdx.x;
+    const unsigned long long i = atomicAdd((unsigned long long*) &g_trace[0], 1ull);
+    if (i >= 4000) return;
+    long long gt;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+    g_trace[2 + 2 * i] = ((long long) kind << 32) | (unsigned) j;
+    g_trace[3 + 2 * i] = gt;
+}
+#define TRACE(k, j) trace(k, j)
+#else
+#define TRACE(k, j)
+#endif
+
+// Programmatic dependent launch: the merge kernel's blocks may be placed on SMs as this kernel's CTAs leave; they run
+// once this grid has completed and its partials are visible.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
 constexpr int O_COL = 0, Q_COL = 256, S_COL = 384;   // tensor-memory columns; S buffers at 384 and 448
 template <int CR>
 struct Geo {
@@ -106,6 +128,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    if (tid == 0) TRACE(0, 0);
+    pdl_launch_dependents();
 
     if (warp == 4) {
         // ================= TMA producer =================
@@ -130,7 +154,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             constexpr uint32_t idesc_qk = idesc_f16(BM, BN, 0, 0, 0);
             constexpr uint32_t idesc_pv = idesc_f16(BM, DVH, 0, 0, 1);
             bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, p.status, 501);
+            TRACE(8, 0);
             if (ok) ok = mbar_wait(smem_u32(qt_full), 0, abort_flag, p.status, 502);
+            TRACE(9, 0);
             // descriptors: everything but the start address is fixed, and the address field (bits 0..13, in 16-byte units)
             // cannot carry into the next field for any shared-memory address, so a step is one 32-bit add
             const uint64_t q_desc0 = smem_desc_sw128(smem_u32(q_s), 16, 1024);
@@ -172,12 +198,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 // P V first: it is short, and it frees a tile stage for the next load
                 if (pv < qk && mbar_try(smem_u32(p_full + (pv & 1)), (uint32_t) (pv >> 1) & 1)) {
                     fence_after_sync();
+                    TRACE(3, pv);
                     issue_pv(pv);
                     ++pv;
                     did = true;
                 }
                 if (qk < ntiles && qk - pv < 2 && mbar_try(smem_u32(c_full + qk % NSTAGE), (uint32_t) (qk / NSTAGE) & 1)) {
                     fence_after_sync();
+                    TRACE(2, qk);
                     issue_qk(qk);
                     ++qk;
                     did = true;
@@ -227,6 +255,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(s_full + (j & 1)), (uint32_t) (j >> 1) & 1, abort_flag, p.status, 601));
             if (!ok) break;
             fence_after_sync();
+            if (tid == 0) TRACE(4, j);
             const uint32_t s_addr = tmem + lane_base + (uint32_t) (S_COL + (j & 1) * BN);
             float s[BN];
 #pragma unroll
@@ -291,12 +320,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tmem_wait_st();
             fence_before_sync();
             mbar_arrive(smem_u32(p_full + (j & 1)));
+            if (tid == 0) TRACE(5, j);
         }
         // ---- epilogue: this half of O, and (from the half-0 CTA) the row's m and l
         // (pv_done cannot serve here: a parity wait only tells the current phase from the one before it, and this thread
         // has not followed its phases; o_final completes exactly once, after the last product)
         if (ok) ok = mbar_wait(smem_u32(o_final), 0, abort_flag, p.status, 603);
         ok = __all_sync(0xffffffffu, ok);
+        if (tid == 0) TRACE(6, 0);
         if (ok) {
             fence_after_sync();
             const int64_t row = (int64_t) t * p.H + h0 + r;
@@ -312,28 +343,35 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
                 inv = den > 0.f ? f / den : 0.f;
             }
-            // A thread holds one row of O; written as it lies, a warp's store would touch 32 rows. Each 32-column chunk
-            // goes through a padded [32][33] tile in shared memory (the tile stages are idle by now), so that a warp
-            // instruction writes 128 contiguous bytes of one row.
-            float* tile = reinterpret_cast<float*>(c_s) + warp * (32 * 33);
-            const int lane = tid & 31;
+            // A thread holds one row of O; written as it lies, a warp's store would touch 32 rows. Each block of 64
+            // columns goes through a padded [32][68] tile in shared memory (the tile stages are idle by now), so that a
+            // warp instruction writes 256 contiguous bytes of each of two rows, 16 bytes a lane.
+            float* tile = reinterpret_cast<float*>(c_s) + warp * (32 * 68);
+            const int lane = tid & 31, half = lane >> 4, l16 = lane & 15;
             const int64_t row_w = (int64_t) t * p.H + h0 + warp * 32;   // the warp's first row
             const int rows_w = max(0, min(32, p.H - (h0 + warp * 32)));
+            float* dst0 = direct ? p.out + row_w * L + hv * DVH : p.part + (row_w * p.ns + split) * PS + hv * DVH;
+            const int64_t dst_row = direct ? L : (int64_t) p.ns * PS;
 #pragma unroll 1
-            for (int c = 0; c < DVH / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem + lane_base + (uint32_t) (O_COL + c * 32), v);
+            for (int c = 0; c < DVH / 64; ++c) {
+                uint32_t v0[32], v1[32];
+                tmem_ld32(tmem + lane_base + (uint32_t) (O_COL + c * 64), v0);
+                tmem_ld32(tmem + lane_base + (uint32_t) (O_COL + c * 64 + 32), v1);
                 tmem_wait_ld();
+                float4* trow = reinterpret_cast<float4*>(tile + lane * 68);
 #pragma unroll
-                for (int e = 0; e < 32; ++e) tile[lane * 33 + e] = __uint_as_float(v[e]) * inv;
+                for (int e = 0; e < 8; ++e) {
+                    trow[e] = make_float4(__uint_as_float(v0[4 * e]) * inv, __uint_as_float(v0[4 * e + 1]) * inv, __uint_as_float(v0[4 * e + 2]) * inv,
+                                          __uint_as_float(v0[4 * e + 3]) * inv);
+                    trow[8 + e] = make_float4(__uint_as_float(v1[4 * e]) * inv, __uint_as_float(v1[4 * e + 1]) * inv, __uint_as_float(v1[4 * e + 2]) * inv,
+                                              __uint_as_float(v1[4 * e + 3]) * inv);
+                }
                 __syncwarp();
-                float* dst0 = direct ? p.out + row_w * L + hv * DVH : p.part + (row_w * p.ns + split) * PS + hv * DVH;
-                const int64_t dst_row = direct ? L : (int64_t) p.ns * PS;
-                if (rows_w == 32) {
 #pragma unroll
-                    for (int rr = 0; rr < 32; ++rr) dst0[rr * dst_row + c * 32 + lane] = tile[rr * 33 + lane];
-                } else {
-                    for (int rr = 0; rr < rows_w; ++rr) dst0[rr * dst_row + c * 32 + lane] = tile[rr * 33 + lane];
+                for (int rr = 0; rr < 32; rr += 2) {
+                    const int ri = rr + half;
+                    if (ri < rows_w)
+                        *reinterpret_cast<float4*>(dst0 + ri * dst_row + c * 64 + l16 * 4) = *reinterpret_cast<const float4*>(tile + ri * 68 + l16 * 4);
                 }
                 __syncwarp();
             }
@@ -344,6 +382,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
         }
     }
+    if (tid == 0) TRACE(7, 0);
     fence_before_sync();
     __syncthreads();
     if (warp == 5) {
@@ -352,16 +391,72 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
 }
 
-// the splits of each (row, head) merged; a split past the row's cells wrote nothing and is not read
-__global__ void __launch_bounds__(512) mla_merge_kernel(const Params p) {
-    __shared__ float sm[lse::smem_floats<L, 512>()];
+// The splits of each (row, head) merged (a split past the row's cells wrote nothing and is not read): a block takes one
+// half of the 512 columns, 8 groups of 64 lanes x 16 bytes; group g takes the splits k = g, g + 8, ... with 10 loads in
+// flight a thread, the first of them issued before the weights are known.
+constexpr int MERGE_THREADS = 512, MERGE_GROUPS = 8, MERGE_FLIGHT = 10;
+__global__ void __launch_bounds__(MERGE_THREADS) mla_merge_kernel(const Params p) {
+    __shared__ float w_s[lse::MAX_SPLITS];
+    __shared__ float red[32];
+    __shared__ float4 acc_s[MERGE_THREADS];
     const int64_t row = blockIdx.x;   // (t, h)
     const int t = (int) (row / p.H);
+    const int tid = threadIdx.x, g = tid >> 6, lane = tid & 63;
+    pdl_wait();   // the split kernel's partials
     const int64_t n = p.counts ? (int64_t) p.counts[t] : p.pos0 + t + 1;
     const int nsr = (int) ((n + p.kb - 1) / p.kb);
-    float mx, den;
-    const float2 a = lse::merge_row<L, 512>(p.part + row * p.ns * PS, PS, nsr, mx, den, sm);
-    if (threadIdx.x < L / 2) {
+    if (threadIdx.x == 0) TRACE(10, 0);
+    const float* pp = p.part + row * p.ns * PS;
+    const float* src = pp + blockIdx.y * DVH + lane * 4;
+    float4 v[MERGE_FLIGHT];
+#pragma unroll
+    for (int u = 0; u < MERGE_FLIGHT; ++u) {
+        const int k = g + MERGE_GROUPS * u;
+        v[u] = k < nsr ? *reinterpret_cast<const float4*>(src + (size_t) k * PS) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    // a thread's own split's (m, l) travel with the first loads; splits past the block's width (rare) are re-read
+    float2 ml0 = make_float2(-INFINITY, 0.f);
+    if (tid < nsr) ml0 = *reinterpret_cast<const float2*>(pp + (size_t) tid * PS + L);
+    float m_loc = ml0.x;
+    for (int k = tid + MERGE_THREADS; k < nsr; k += MERGE_THREADS) m_loc = fmaxf(m_loc, pp[(size_t) k * PS + L]);
+    float mx = lse::block_max<MERGE_THREADS>(m_loc, red);
+    float l_loc = 0.f;
+    if (tid < nsr) {
+        const float e = (ml0.x == -INFINITY || mx == -INFINITY) ? 0.f : exp2f(ml0.x - mx);
+        w_s[tid] = e;
+        l_loc = ml0.y * e;
+    }
+    for (int k = tid + MERGE_THREADS; k < nsr; k += MERGE_THREADS) {
+        const float mk = pp[(size_t) k * PS + L];
+        const float e = (mk == -INFINITY || mx == -INFINITY) ? 0.f : exp2f(mk - mx);
+        w_s[k] = e;
+        l_loc += pp[(size_t) k * PS + L + 1] * e;
+    }
+    float den = lse::block_sum<MERGE_THREADS>(l_loc, red);   // its barriers also publish w_s
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k0 = 0; k0 < nsr; k0 += MERGE_GROUPS * MERGE_FLIGHT) {
+        if (k0 > 0) {
+#pragma unroll
+            for (int u = 0; u < MERGE_FLIGHT; ++u) {
+                const int k = k0 + g + MERGE_GROUPS * u;
+                v[u] = k < nsr ? *reinterpret_cast<const float4*>(src + (size_t) k * PS) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < MERGE_FLIGHT; ++u) {
+            const int k = k0 + g + MERGE_GROUPS * u;
+            const float e = k < nsr ? w_s[k] : 0.f;
+            a.x += v[u].x * e, a.y += v[u].y * e, a.z += v[u].z * e, a.w += v[u].w * e;
+        }
+    }
+    acc_s[tid] = a;
+    __syncthreads();
+    if (g == 0) {
+#pragma unroll
+        for (int gg = 1; gg < MERGE_GROUPS; ++gg) {
+            const float4 o = acc_s[gg * 64 + lane];
+            a.x += o.x, a.y += o.y, a.z += o.z, a.w += o.w;
+        }
         float f = 1.0f;
         if (p.sinks) {
             const float sk = p.sinks[row % p.H] * 1.4426950408889634f, m2 = fmaxf(mx, sk);
@@ -369,9 +464,20 @@ __global__ void __launch_bounds__(512) mla_merge_kernel(const Params p) {
             den = den * f + exp2f(sk - m2);
         }
         const float inv = den > 0.f ? f / den : 0.f;
-        *reinterpret_cast<float2*>(p.out + row * L + 2 * threadIdx.x) = make_float2(a.x * inv, a.y * inv);
+        *reinterpret_cast<float4*>(p.out + row * L + blockIdx.y * DVH + lane * 4) = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
     }
+    if (threadIdx.x == 0) TRACE(11, 0);
 }
+
+#ifdef NS_MLA_TRACE
+}
+extern "C" void ns_debug_trace_reset() {
+    long long z = 0;
+    cudaMemcpyToSymbol(g_trace, &z, 8);
+}
+extern "C" void ns_debug_trace(long long* dst) { cudaMemcpyFromSymbol(dst, g_trace, sizeof(long long) * 8192); }
+namespace {
+#endif
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -430,6 +536,7 @@ int launch(ns_gpu* g, const MlaDecodeArgs& a, const char* where) {
     p.kb = ns_mla_split(n, a.T, a.H, g->sms);
     p.ns = (int) ((n + p.kb - 1) / p.kb);
     p.scale_log2 = a.scale * 1.4426950408889634f;
+    if (p.ns > lse::MAX_SPLITS) return ns_fail(std::string(where) + ": more key splits than the merge holds");
     CUtensorMap tq, tc;
     // Q [T][H][CR]: a box = 128 heads x 64 features of one row
     if (make_map(&tq, a.q, CR, (uint64_t) a.H, (uint64_t) a.T, CR * 2, (uint64_t) a.H * CR * 2, BM, where)) return -1;
@@ -446,8 +553,16 @@ int launch(ns_gpu* g, const MlaDecodeArgs& a, const char* where) {
     kern<<<grid, THREADS, Geo<CR>::SMEM_TOTAL, g->compute>>>(tq, tc, p);
     if (ns_launched(where)) return -1;
     if (p.ns > 1) {
-        mla_merge_kernel<<<(unsigned) (a.T * a.H), 512, 0, g->compute>>>(p);
-        if (ns_launched(where)) return -1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned) (a.T * a.H), 2);
+        cfg.blockDim = dim3(MERGE_THREADS);
+        cfg.stream = g->compute;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        NS_CUDA(cudaLaunchKernelEx(&cfg, mla_merge_kernel, p), where);
     }
     return 0;
 }
