@@ -24,6 +24,8 @@ static const char* kEngines[] = {
     "ns_gather_h",
     // deepseek2
     "ns_ds2_mla_decode",
+    // qwen35 quantised caches
+    "ns_q35_kv_store_q", "ns_q35_fwht32",
     // deepseek41
     "ns_ds41_attend", "ns_ds41_attend_xmx_supported", "ns_ds41_attend_xmx", "ns_ds41_ring_put", "ns_ds41_rows_f16",
     // native

@@ -49,13 +49,26 @@ int ns_q35_attn_prompt_kv(ns_gpu* g, int kt, const float* q, int64_t qs, const v
 
 /* kernels/llm/qwen35/silo/silo.h:49-59 - decode rows (1..8), each at its own position p0+t; a row's result is the same
  * whatever rows share its pass. `_supported` is widened from the reference's (D 256, 6 heads a key head) to D 128 / 256
- * with 1..16 query heads a key head. kt: cache form, 0 = fp16 (the only one this build takes). */
+ * with 1..16 query heads a key head. kt (both _kv entry points): the cache's form, 0 fp16, 1 q8_0, 2 q4_0 (heads of 256;
+ * rows as ns_q35_kv_store_q writes them). A quantised cache is first expanded - the rows the pass reads, to exactly the
+ * fp16 values the reference's reader kv_load8 produces (silo/attn.cpp:49-78) - into a buffer the library keeps, then the
+ * fp16 kernels run: the same results as the reference's numerics give, at the cost of one more pass over the cache. */
 int ns_q35_attn_decode_supported(int64_t T, int64_t Hq, int64_t Hkv, int64_t D);
 int64_t ns_q35_attn_decode_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0);
 int ns_q35_attn_decode(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
                        int64_t cap, int64_t p0, float* out, float* scratch);
 int ns_q35_attn_decode_kv(ns_gpu* g, int kt, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv,
                           int64_t D, int64_t cap, int64_t p0, float* out, float* scratch);
+
+/* kernels/llm/qwen35/q35.h:39-46 - the quantised caches' writer and rotation. ns_q35_kv_store_q: fp32 rows k, v
+ * [T][Hkv*256] into caches [Hkv][cap][272 or 144 bytes] as q8_0 (kt 1: 256 int8 then 8 fp16 scales) or q4_0 (kt 2: 8
+ * blocks of 16 bytes, value j low / j+16 high, then 8 fp16 scales; ggml's quantize_row_q4_0), q35.cpp:281-326.
+ * ns_q35_fwht32: each block of 32 of rows x [rows][n] (stride floats apart) through the normalised 32-point
+ * Walsh-Hadamard transform, its own inverse (q35.cpp:328-348): the rotation applied to q and k (and undone on the output
+ * for v) when a quantised cache is rotated. */
+int ns_q35_kv_store_q(ns_gpu* g, int kt, const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hkv, int64_t D, int64_t cap,
+                      int64_t p0, void* kc, void* vc);
+int ns_q35_fwht32(ns_gpu* g, float* x, int64_t rows, int64_t n, int64_t stride);
 
 /* kernels/llm/nemotronh/nh.h:39-44 and silo/nhs.h:63-69 - the same kernels under the nemotronh engine's names (D 128) */
 int64_t ns_nh_attn_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0);

@@ -61,9 +61,22 @@ int ns_q35_attn_prompt(ns_gpu* g, const float* q, int64_t qs, const void* kc, co
 int ns_q35_attn_prompt_kv(ns_gpu* g, int kt, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv,
                           int64_t D, int64_t cap, int64_t p0, float* out) {
     NS_TRY
-    if (kt != 0) return ns_fail("ns_q35_attn_prompt_kv: a cache form 0 (half); q8_0 and q4_0 caches are not built in this library");
-    if (!ns_q35_attn_prompt_supported(T, Hq, Hkv, D)) return ns_fail("ns_q35_attn_prompt_kv: more than 8 rows, heads of 128 or 256");
-    return ns_prefill_f32(g, "ns_q35_attn_prompt_kv", q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out);
+    const char* name = "ns_q35_attn_prompt_kv";
+    if (!ns_q35_attn_prompt_supported(T, Hq, Hkv, D)) return ns_fail(std::string(name) + ": more than 8 rows, heads of 128 or 256");
+    if (kt == 0) return ns_prefill_f32(g, name, q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out);
+    // q8_0 / q4_0 caches (heads of 256): expanded to the fp16 values the reference's reader produces (silo/attn.cpp:49-78)
+    // in a kept buffer [Hkv][p0+T][256] each; a prompt pass is bound by its products, so the extra pass over the cache is small
+    if (kt != 1 && kt != 2) return ns_fail(std::string(name) + ": a cache form 0 (half), 1 (q8_0) or 2 (q4_0)");
+    if (ns_enter(g, name)) return -1;
+    if (D != 256) return ns_fail(std::string(name) + ": quantised caches have heads of 256");
+    if (!kc || !vc || p0 < 0 || p0 + T > cap) return ns_fail(std::string(name) + ": past the cache's capacity");
+    const int64_t n = p0 + T, one = (Hkv * n * 256 * 2 + 255) / 256 * 256;
+    void* kept = nullptr;
+    if (ns_kept_kv(g, (size_t) (2 * one), &kept)) return -1;
+    void* kh = kept;
+    void* vh = (uint8_t*) kept + one;
+    if (ns_launch_kv_dequant(g, kt, kc, Hkv, cap, n, kh, name) || ns_launch_kv_dequant(g, kt, vc, Hkv, cap, n, vh, name)) return -1;
+    return ns_prefill_f32(g, name, q, qs, kh, vh, T, Hq, Hkv, D, n, p0, out);
     NS_CATCH("ns_q35_attn_prompt_kv")
 }
 

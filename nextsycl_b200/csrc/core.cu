@@ -59,6 +59,26 @@ int ns_kept(ns_gpu* g, size_t bytes, void** out) {
     return 0;
 }
 
+int ns_kept_kv(ns_gpu* g, size_t bytes, void** out) {
+    std::lock_guard<std::mutex> lk(g->mu);
+    if (g->kept_kv_bytes < bytes) {
+        if (g->kept_kv) {
+            NS_CUDA(cudaStreamSynchronize(g->compute), "ns_kept_kv");
+            cudaFree(g->kept_kv);
+            g->kept_kv = nullptr;
+            g->kept_kv_bytes = 0;
+        }
+        const size_t want = (bytes + (size_t) (1 << 20) - 1) / (1 << 20) * (1 << 20);
+        if (cudaMalloc(&g->kept_kv, want) != cudaSuccess) {
+            cudaGetLastError();
+            return ns_fail("device allocation of " + std::to_string(want) + " bytes failed");
+        }
+        g->kept_kv_bytes = want;
+    }
+    *out = g->kept_kv;
+    return 0;
+}
+
 extern "C" {
 
 const char* ns_last_error(void) { return g_err.c_str(); }
@@ -136,6 +156,7 @@ void ns_gpu_close(ns_gpu* g) {
     for (cudaEvent_t e : g->ring)
         if (e) cudaEventDestroy(e);
     if (g->kept) cudaFree(g->kept);
+    if (g->kept_kv) cudaFree(g->kept_kv);
     if (g->status_host) cudaFreeHost(g->status_host);
     cudaStreamDestroy(g->compute);
     cudaStreamDestroy(g->lane[0]);

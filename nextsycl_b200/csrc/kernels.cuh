@@ -59,6 +59,9 @@ int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where);
 int ns_launch_kv_store(ns_gpu* g, const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hkv, int64_t D, int64_t cap, int64_t p0,
                        void* kc, void* vc);
 
+// rows [0, n) of each head of a quantised cache (kt 1: q8_0, 2: q4_0; heads of 256) as fp16 [Hkv][n][256] (kv_quant.cu)
+int ns_launch_kv_dequant(ns_gpu* g, int kt, const void* c, int64_t Hkv, int64_t cap, int64_t n, void* out, const char* where);
+
 // fp32 rows -> 16-bit rows scaled by `scale` (one rounding, as the reference stages its queries: silo/attn.cpp:147)
 int ns_launch_scale_to_f16(ns_gpu* g, const float* src, int64_t src_row, void* dst, int64_t dst_row, int64_t rows, int64_t cols, float scale);
 

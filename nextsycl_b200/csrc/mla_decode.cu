@@ -32,22 +32,6 @@ constexpr int THREADS = 192;
 constexpr int PS = 516;                        // floats a partial row: O[512], m, l, 2 pad
 constexpr float RESCALE_LOG2 = 8.0f;
 
-#ifdef NS_MLA_TRACE
-__device__ long long g_trace[16384];
-__device__ __forceinline__ void trace(int kind, int j) {
-    if (blockIdx.x != NS_MLA_TRACE && kind != 0 && kind != 6 && kind != 7 && kind != 10 && kind != 11) return;
-    j = blockIdx.x;
-    const unsigned long long i = atomicAdd((unsigned long long*) &g_trace[0], 1ull);
-    if (i >= 4000) return;
-    long long gt;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-    g_trace[2 + 2 * i] = ((long long) kind << 32) | (unsigned) j;
-    g_trace[3 + 2 * i] = gt;
-}
-#define TRACE(k, j) trace(k, j)
-#else
-#define TRACE(k, j)
-#endif
 
 // Programmatic dependent launch: the merge kernel's blocks may be placed on SMs as this kernel's CTAs leave; they run
 // once this grid has completed and its partials are visible.
@@ -128,7 +112,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    if (tid == 0) TRACE(0, 0);
     pdl_launch_dependents();
 
     if (warp == 4) {
@@ -154,9 +137,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             constexpr uint32_t idesc_qk = idesc_f16(BM, BN, 0, 0, 0);
             constexpr uint32_t idesc_pv = idesc_f16(BM, DVH, 0, 0, 1);
             bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, p.status, 501);
-            TRACE(8, 0);
             if (ok) ok = mbar_wait(smem_u32(qt_full), 0, abort_flag, p.status, 502);
-            TRACE(9, 0);
             // descriptors: everything but the start address is fixed, and the address field (bits 0..13, in 16-byte units)
             // cannot carry into the next field for any shared-memory address, so a step is one 32-bit add
             const uint64_t q_desc0 = smem_desc_sw128(smem_u32(q_s), 16, 1024);
@@ -198,14 +179,12 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 // P V first: it is short, and it frees a tile stage for the next load
                 if (pv < qk && mbar_try(smem_u32(p_full + (pv & 1)), (uint32_t) (pv >> 1) & 1)) {
                     fence_after_sync();
-                    TRACE(3, pv);
                     issue_pv(pv);
                     ++pv;
                     did = true;
                 }
                 if (qk < ntiles && qk - pv < 2 && mbar_try(smem_u32(c_full + qk % NSTAGE), (uint32_t) (qk / NSTAGE) & 1)) {
                     fence_after_sync();
-                    TRACE(2, qk);
                     issue_qk(qk);
                     ++qk;
                     did = true;
@@ -255,7 +234,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(s_full + (j & 1)), (uint32_t) (j >> 1) & 1, abort_flag, p.status, 601));
             if (!ok) break;
             fence_after_sync();
-            if (tid == 0) TRACE(4, j);
             const uint32_t s_addr = tmem + lane_base + (uint32_t) (S_COL + (j & 1) * BN);
             float s[BN];
 #pragma unroll
@@ -320,14 +298,12 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tmem_wait_st();
             fence_before_sync();
             mbar_arrive(smem_u32(p_full + (j & 1)));
-            if (tid == 0) TRACE(5, j);
         }
         // ---- epilogue: this half of O, and (from the half-0 CTA) the row's m and l
         // (pv_done cannot serve here: a parity wait only tells the current phase from the one before it, and this thread
         // has not followed its phases; o_final completes exactly once, after the last product)
         if (ok) ok = mbar_wait(smem_u32(o_final), 0, abort_flag, p.status, 603);
         ok = __all_sync(0xffffffffu, ok);
-        if (tid == 0) TRACE(6, 0);
         if (ok) {
             fence_after_sync();
             const int64_t row = (int64_t) t * p.H + h0 + r;
@@ -382,7 +358,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
         }
     }
-    if (tid == 0) TRACE(7, 0);
     fence_before_sync();
     __syncthreads();
     if (warp == 5) {
@@ -405,7 +380,6 @@ __global__ void __launch_bounds__(MERGE_THREADS) mla_merge_kernel(const Params p
     pdl_wait();   // the split kernel's partials
     const int64_t n = p.counts ? (int64_t) p.counts[t] : p.pos0 + t + 1;
     const int nsr = (int) ((n + p.kb - 1) / p.kb);
-    if (threadIdx.x == 0) TRACE(10, 0);
     const float* pp = p.part + row * p.ns * PS;
     const float* src = pp + blockIdx.y * DVH + lane * 4;
     float4 v[MERGE_FLIGHT];
@@ -466,18 +440,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) mla_merge_kernel(const Params p
         const float inv = den > 0.f ? f / den : 0.f;
         *reinterpret_cast<float4*>(p.out + row * L + blockIdx.y * DVH + lane * 4) = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
     }
-    if (threadIdx.x == 0) TRACE(11, 0);
 }
 
-#ifdef NS_MLA_TRACE
-}
-extern "C" void ns_debug_trace_reset() {
-    long long z = 0;
-    cudaMemcpyToSymbol(g_trace, &z, 8);
-}
-extern "C" void ns_debug_trace(long long* dst) { cudaMemcpyFromSymbol(dst, g_trace, sizeof(long long) * 8192); }
-namespace {
-#endif
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);

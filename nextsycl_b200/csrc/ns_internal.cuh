@@ -24,6 +24,8 @@ struct ns_gpu {
     int64_t next_ticket = 0;
     void* kept = nullptr;                // grow-only staging buffer (compat entry points: fp32 -> fp16 queries)
     size_t kept_bytes = 0;
+    void* kept_kv = nullptr;             // a second one: quantised caches expanded to fp16 for the tensor-core kernels
+    size_t kept_kv_bytes = 0;
     int* status_host = nullptr;          // one word of mapped pinned memory: a kernel whose bounded wait gave up writes its code
     int* status_dev = nullptr;           // the same word as the device sees it; ns_sync reports and clears it
 };
@@ -46,6 +48,7 @@ int ns_enter(ns_gpu* g, const char* where);
 // the kept staging buffer grown to at least `bytes` (stream-ordered with the compute stream: growth frees the old
 // buffer only after the stream has drained)
 int ns_kept(ns_gpu* g, size_t bytes, void** out);
+int ns_kept_kv(ns_gpu* g, size_t bytes, void** out);
 // after a kernel launch: surfaces a launch-configuration error as -1
 int ns_launched(const char* where);
 

@@ -694,6 +694,93 @@ void orc_ds41_attend(const float* q, const uint16_t* raw, int64_t R, const uint1
     }
 }
 
+// ---- quantised caches (heads of 256): kernels/llm/qwen35/q35.cpp:281-326, reader silo/attn.cpp:49-78 --------------------
+// A head's row: q8_0 (kt 1) 256 int8 values then 8 fp16 scales = 272 bytes; q4_0 (kt 2) 8 blocks of 16 bytes (byte j of a
+// block: value j low nibble, value j + 16 high) then 8 fp16 scales = 144 bytes. Blocks of 32 values.
+static inline int64_t q_row_bytes(int kt) { return kt == 1 ? 272 : 144; }
+
+static void quant_block(int kt, const float* x, uint8_t* row, int b) {
+    if (kt == 1) {
+        float amax = 0.0f;
+        for (int j = 0; j < 32; ++j) amax = std::fmax(amax, std::fabs(x[j]));
+        const float d = amax / 127.0f, id = d != 0.0f ? 1.0f / d : 0.0f;
+        for (int j = 0; j < 32; ++j) row[b * 32 + j] = (uint8_t) (int8_t) std::round(x[j] * id);   // half away from zero
+        const uint16_t dh = f2h(d);
+        std::memcpy(row + 256 + 2 * b, &dh, 2);
+    } else {
+        // ggml's quantize_row_q4_0: the value of the largest magnitude (the first of a tie), d = it / -8
+        float m = 0.0f, am = 0.0f;
+        for (int j = 0; j < 32; ++j)
+            if (std::fabs(x[j]) > am) {
+                am = std::fabs(x[j]);
+                m = x[j];
+            }
+        const float d = m / -8.0f, id = d != 0.0f ? 1.0f / d : 0.0f;
+        for (int j = 0; j < 16; ++j) {
+            const int lo = std::min(15, (int) (x[j] * id + 8.5f)), hi = std::min(15, (int) (x[j + 16] * id + 8.5f));
+            row[b * 16 + j] = (uint8_t) (lo | (hi << 4));
+        }
+        const uint16_t dh = f2h(d);
+        std::memcpy(row + 128 + 2 * b, &dh, 2);
+    }
+}
+
+// ns_q35_kv_store_q: rows k, v [T][Hkv*256] fp32 (ks, vs floats apart) into the quantised caches [Hkv][cap][row bytes]
+void orc_kv_store_q(int kt, const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hkv, int64_t cap, int64_t p0, uint8_t* kc,
+                    uint8_t* vc) {
+    const int64_t rb = q_row_bytes(kt);
+    for (int64_t t = 0; t < T; ++t)
+        for (int64_t h = 0; h < Hkv; ++h)
+            for (int b = 0; b < 8; ++b) {
+                quant_block(kt, k + t * ks + h * 256 + b * 32, kc + (h * cap + p0 + t) * rb, b);
+                quant_block(kt, v + t * vs + h * 256 + b * 32, vc + (h * cap + p0 + t) * rb, b);
+            }
+}
+
+// What kv_load8<KT> hands the tensor cores (silo/attn.cpp:49-78): value = half((float) q * (float) d). Rows [0, n) of each
+// head of a cache [Hkv][cap][row bytes] to fp16 [Hkv][n][256].
+void orc_kv_dequant(int kt, const uint8_t* c, int64_t Hkv, int64_t cap, int64_t n, uint16_t* out) {
+    const int64_t rb = q_row_bytes(kt);
+#pragma omp parallel for collapse(2)
+    for (int64_t h = 0; h < Hkv; ++h)
+        for (int64_t j = 0; j < n; ++j) {
+            const uint8_t* row = c + (h * cap + j) * rb;
+            uint16_t* o = out + (h * n + j) * 256;
+            for (int i = 0; i < 256; ++i) {
+                const int b = i / 32, e = i % 32;
+                uint16_t dh;
+                float q;
+                if (kt == 1) {
+                    std::memcpy(&dh, row + 256 + 2 * b, 2);
+                    q = (float) (int8_t) row[i];
+                } else {
+                    std::memcpy(&dh, row + 128 + 2 * b, 2);
+                    const uint8_t byte = row[b * 16 + (e & 15)];
+                    q = (float) ((int) ((e < 16 ? byte : byte >> 4) & 15) - 8);
+                }
+                o[i] = f2h(q * h2f(dh));
+            }
+        }
+}
+
+// ns_q35_fwht32 (q35.cpp:328-348): each block of 32 of rows [rows][n] through a normalised Walsh-Hadamard transform
+void orc_fwht32(float* x, int64_t rows, int64_t n, int64_t stride) {
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t b = 0; b < n / 32; ++b) {
+            float* p = x + r * stride + b * 32;
+            float v[32];
+            for (int i = 0; i < 32; ++i) v[i] = p[i];
+            for (int o = 1; o < 32; o <<= 1)
+                for (int i = 0; i < 32; ++i)
+                    if (!(i & o)) {
+                        const float a = v[i], c = v[i + o];
+                        v[i] = a + c;
+                        v[i + o] = a - c;
+                    }
+            for (int i = 0; i < 32; ++i) p[i] = v[i] * 0.17677669529663687f;
+        }
+}
+
 // ---- cache writers -----------------------------------------------------------------------------------------------
 
 // ns_q35_kv_store (kernels/llm/qwen35/q35.cpp:573-588): fp32 rows k [T][ks], v [T][vs] -> fp16 caches [Hkv][cap][D]

@@ -178,3 +178,27 @@ def ds41_attend(q, raw, R, comp, ratio, sel, K, sinks, T, H, pos0, window, scale
     lib().orc_ds41_attend(_f(q), _h(raw), i64(R), None if comp is None else _h(comp), i64(ratio), None if sel is None else sel.ctypes.data_as(_pi),
                           i64(K), _f(sinks), _f(out), i64(T), i64(H), i64(pos0), i64(window), C.c_float(scale), C.c_int(mode))
     return out
+
+
+def q_row_bytes(kt):
+    return {0: 512, 1: 272, 2: 144}[kt]
+
+
+def kv_store_q(kt, k, v, T, Hkv, cap, p0, kc, vc):
+    """fp32 rows k, v [T, Hkv*256] into quantised caches kc, vc uint8 [Hkv, cap, row bytes] (kt 1: q8_0, 2: q4_0)."""
+    u8 = C.POINTER(C.c_uint8)
+    lib().orc_kv_store_q(C.c_int(kt), _f(k), i64(k.shape[1]), _f(v), i64(v.shape[1]), i64(T), i64(Hkv), i64(cap), i64(p0), kc.ctypes.data_as(u8),
+                         vc.ctypes.data_as(u8))
+
+
+def kv_dequant(kt, c, Hkv, cap, n):
+    """Rows [0, n) of each head of a quantised cache as the fp16 values the reference's reader produces -> uint16 [Hkv, n, 256]."""
+    out = np.empty((Hkv, n, 256), np.uint16)
+    lib().orc_kv_dequant(C.c_int(kt), c.ctypes.data_as(C.POINTER(C.c_uint8)), i64(Hkv), i64(cap), i64(n), _h(out))
+    return out
+
+
+def fwht32(x):
+    """In place: each block of 32 of the rows of x [rows, n] fp32 through the normalised Walsh-Hadamard transform."""
+    lib().orc_fwht32(_f(x), i64(x.shape[0]), i64(x.shape[1]), i64(x.shape[1]))
+    return x

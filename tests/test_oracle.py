@@ -212,3 +212,55 @@ def test_ds41_attend_both_numerics(T, pos0, window, R, ncomp, ratio, K):
     high = O.ds41_attend(q, raw, R, comp, ratio, sel, K, np.full(H, 1e4, np.float32), T, H, pos0, window, scale, mode=1)
     assert close(low, ds41_numpy(q, raw, R, comp, ratio, sel, K, np.full(H, -1e4), T, H, pos0, window, scale))
     assert np.abs(high).max() < 1e-30
+
+
+@pytest.mark.parametrize("kt", [1, 2])
+def test_quantised_cache_rows(kt):
+    """kernels/llm/qwen35/q35.cpp:281-326 and silo/attn.cpp:49-78 restated in numpy: blocks of 32, llama.cpp's q8_0 / q4_0
+    with the scales behind the values; the reader's value is half(q * d)."""
+    T, Hkv, cap, p0 = 5, 2, 16, 3
+    rng = W.rng(975, kt)
+    k = rng.standard_normal((T, Hkv * 256), dtype=np.float32)
+    v = (3.0 * rng.standard_normal((T, Hkv * 256), dtype=np.float32)).astype(np.float32)
+    k[0, :32] = 0.0                      # an all-zero block: scale 0, values 0 (q8_0) or 8 (q4_0)
+    k[1, 32:64] = np.float32(-2.5)       # a constant block
+    rb = O.q_row_bytes(kt)
+    kc = np.zeros((Hkv, cap, rb), np.uint8)
+    vc = np.zeros((Hkv, cap, rb), np.uint8)
+    O.kv_store_q(kt, k, v, T, Hkv, cap, p0, kc, vc)
+    for src, cache in ((k, kc), (v, vc)):
+        x = src.reshape(T, Hkv, 8, 32)
+        for t in range(T):
+            for h in range(Hkv):
+                row = cache[h, p0 + t]
+                for b in range(8):
+                    xb = x[t, h, b]
+                    if kt == 1:
+                        d = np.float32(np.abs(xb).max()) / np.float32(127.0)
+                        inv = np.float32(1.0) / d if d != 0 else np.float32(0.0)
+                        y = xb * inv
+                        want = (np.sign(y) * np.floor(np.abs(y) + np.float32(0.5))).astype(np.int8)   # round half away from zero
+                        assert np.array_equal(row[b * 32:(b + 1) * 32].view(np.int8), want)
+                        assert row[256 + 2 * b:258 + 2 * b].view(np.float16)[0] == np.float16(d)
+                    else:
+                        m = xb[np.argmax(np.abs(xb))] if np.abs(xb).max() > 0 else np.float32(0.0)
+                        d = np.float32(m) / np.float32(-8.0)
+                        inv = np.float32(1.0) / d if d != 0 else np.float32(0.0)
+                        qv = np.minimum(15, (xb * inv + np.float32(8.5)).astype(np.int32))
+                        want = (qv[:16] | (qv[16:] << 4)).astype(np.uint8)
+                        assert np.array_equal(row[b * 16:(b + 1) * 16], want)
+                        assert row[128 + 2 * b:130 + 2 * b].view(np.float16)[0] == np.float16(d)
+        deq = O.kv_dequant(kt, cache, Hkv, cap, cap).view(np.float16).astype(np.float32)
+        back = deq[:, p0:p0 + T].transpose(1, 0, 2).reshape(T, Hkv, 8, 32)
+        # a block is within half a step of its scale (q8_0), a step (q4_0: the codes stop at 15), plus the fp16 rounding of the scale
+        step = np.abs(x).max(-1, keepdims=True) / (127.0 if kt == 1 else 8.0)
+        assert np.all(np.abs(back - x) <= (0.51 if kt == 1 else 1.01) * step + 1e-3 * np.abs(x).max())
+    assert np.all(kc[:, :p0] == 0) and np.all(kc[:, p0 + T:] == 0)
+
+
+def test_fwht32_is_its_own_inverse():
+    x = W.rng(976, 0).standard_normal((7, 256), dtype=np.float32)
+    y = O.fwht32(x.copy())
+    h = np.array([[(-1) ** bin(i & j).count("1") for j in range(32)] for i in range(32)], np.float64) / np.sqrt(32.0)
+    assert np.allclose(y.reshape(7, 8, 32), x.reshape(7, 8, 32).astype(np.float64) @ h, atol=1e-5)
+    assert np.allclose(O.fwht32(y.copy()), x, atol=1e-5)
