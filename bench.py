@@ -220,6 +220,46 @@ def wl_gqa_decode(env, T, Hq, Hkv, D, kv, B, rotate=1, real_data=True, graph=Fal
     return step, info
 
 
+def wl_gqa_decode_q35(env, kt, kv=131072):
+    """One decode row of the qwen35 geometry (24 query / 4 key heads of 256) over a cache of form kt (0 fp16, 1 q8_0, 2 q4_0)
+    through the reference's own symbol ns_q35_attn_decode_kv; the caches are written by ns_q35_kv_store[_q] from seeded rows.
+    Two cache sets used in turn; a step is a recorded graph (the call takes its position by value)."""
+    from nextsycl_b200 import DevBuf
+    from nextsycl_b200 import workloads as W
+    from nextsycl_b200.core import check
+    api, gpu = env.gpu.api, env.gpu
+    T, Hq, Hkv, D = 1, 24, 4, 256
+    rb = {0: 512, 1: 272, 2: 144}[kt]
+    blk = 4096
+    rows = [DevBuf.of(gpu, W.normal_f32(6, 10 + i, (blk, Hkv * D))) for i in range(2)]
+    sets = []
+    for r in range(2):
+        kc, vc = DevBuf(gpu, Hkv * kv * rb), DevBuf(gpu, Hkv * kv * rb)
+        for p0 in range(0, kv, blk):
+            if kt == 0:
+                check(api, api.ns_q35_kv_store(gpu.raw, rows[r].ptr, Hkv * D, rows[1 - r].ptr, Hkv * D, blk, Hkv, D, kv, p0, kc.ptr, vc.ptr), "kv_store")
+            else:
+                check(api, api.ns_q35_kv_store_q(gpu.raw, kt, rows[r].ptr, Hkv * D, rows[1 - r].ptr, Hkv * D, blk, Hkv, D, kv, p0, kc.ptr, vc.ptr), "kv_store_q")
+        sets.append((kc, vc))
+    q = DevBuf.of(gpu, W.normal_f32(6, 1, (T, Hq * D)))
+    out = DevBuf(gpu, T * Hq * D * 4)
+    scratch = DevBuf(gpu, max(4, 4 * int(api.ns_q35_attn_decode_scratch(T, Hq, Hkv, D, kv - T))))
+
+    def one(r):
+        check(api, api.ns_q35_attn_decode_kv(gpu.raw, kt, q.ptr, Hq * D, sets[r][0].ptr, sets[r][1].ptr, T, Hq, Hkv, D, kv, kv - T, out.ptr, scratch.ptr), "decode_kv")
+    one(0)
+    gpu.sync()
+    graphs = [gpu.record(lambda r=r: one(r)) for r in range(2)]
+    i = [0]
+
+    def step():
+        graphs[i[0] % 2].launch()
+        i[0] += 1
+    info = {"bytes": 2 * kv * Hkv * rb, "bound": "hbm", "launches": 2, "keep": (rows, sets, q, out, scratch, graphs),
+            "tokens_bytes_f16": 2 * kv * Hkv * 512}
+    return step, info
+
+
 def wl_prefill(env, T, Hq, Hkv, D):
     """Causal prefill from position 0, fp16; with several ranks each takes a contiguous share of the key heads (and their
     query heads) - no exchange. With more ranks than key heads, ranks that share a key head each take a share of its
@@ -346,6 +386,8 @@ def measure(env, name, steps, warmup):
         step, info = wl_kvsplit_decode(env)
     elif name.startswith("decode_split_kv"):      # decode_split_kv<tokens>: the same with another context length
         step, info = wl_kvsplit_decode(env, kv=int(name[len("decode_split_kv"):]))
+    elif name.startswith("decode_q35_"):
+        step, info = wl_gqa_decode_q35(env, {"f16": 0, "q8": 1, "q4": 2}[name.split("_")[-1]])
     elif name == "prefill_16k":
         step, info = wl_prefill(env, 16384, 16, 4, 128)
     elif name == "prefill_c1":
@@ -369,11 +411,14 @@ def measure(env, name, steps, warmup):
         res.update({"gbs_per_gpu": gbs, "frac_of_hbm_peak": gbs / float(pk["hbm_gbs"])})
         if "bytes_total" in info:
             res["gbs_job"] = info["bytes_total"] / (ms * 1e-3) / 1e9
+        if "tokens_bytes_f16" in info:   # a quantised cache: the same tokens as so many fp16 bytes a second
+            res["f16_equivalent_gbs"] = info["tokens_bytes_f16"] / (ms * 1e-3) / 1e9
     res["_info"] = info
     return res
 
 
-OTHERS_1GPU = [("prefill_16k", 10), ("prefill_c1", 50), ("decode_c2_b1", 50), ("decode_128k", 30), ("decode_c5", 30), ("mla_decode_4k", 50),
+OTHERS_1GPU = [("prefill_16k", 10), ("prefill_c1", 50), ("decode_c2_b1", 50), ("decode_128k", 30), ("decode_c5", 30), ("decode_q35_f16", 30),
+               ("decode_q35_q8", 30), ("decode_q35_q4", 30), ("mla_decode_4k", 50),
                ("mla_decode_32k", 50), ("mla_decode_131k", 30), ("mla_prefill_c4", 3)]
 OTHERS_NGPU = [("decode_c5_split", 50), ("prefill_16k", 10), ("mla_prefill_c4", 3)]
 
@@ -386,6 +431,9 @@ def config_of(name, n):
         "decode_c2_b1": "config 2, one sequence",
         "decode_128k": "128K GQA decode, 64 query / 8 key heads of 128, one sequence (512 MiB of K+V)",
         "decode_c5": "config 5 on one GPU: 4 verify rows, 32 query / 4 key heads of 128, 262,144 cached tokens (512 MiB of K+V)",
+        "decode_q35_f16": "qwen35 geometry: 1 decode row, 24 query / 4 key heads of 256, 131,072 cached tokens, fp16 caches (ns_q35_attn_decode_kv)",
+        "decode_q35_q8": "the same over q8_0 caches (272-byte rows)",
+        "decode_q35_q4": "the same over q4_0 caches (144-byte rows)",
         "decode_c5_split": "config 5 over the ranks: 262,144 cached tokens split by key ranges, partials pushed over NVLink and combined (strong scaling)",
         "mla_decode_4k": "config 3: absorbed MLA decode, 128 heads, 576-wide latent cache, 4,096 cells",
         "mla_decode_32k": "config 3, 32,768 cells",

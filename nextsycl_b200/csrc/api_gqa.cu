@@ -21,7 +21,7 @@ int64_t decode_ns_max(int64_t T, int64_t Hkv, int64_t p0) {
 
 // rows 1..8 at p0.., fp32 in and out, one sequence: what ns_q35_attn_decode and its namesakes share
 int decode_f32(ns_gpu* g, const char* name, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv,
-               int64_t D, int64_t cap, int64_t p0, float* out, float* scratch) {
+               int64_t D, int64_t cap, int64_t p0, float* out, float* scratch, int kt = 0) {
     if (ns_enter(g, name)) return -1;
     if (T < 1 || T > 8 || !shape_ok(Hq, Hkv, D)) return ns_fail(std::string(name) + ": 1..8 rows, heads of 128 or 256, 1..16 query heads a key head");
     if (p0 < 0 || p0 + T > cap) return ns_fail(std::string(name) + ": past the cache's capacity");
@@ -41,6 +41,7 @@ int decode_f32(ns_gpu* g, const char* name, const float* q, int64_t qs, const vo
     a.B = 1, a.T = T, a.Hq = Hq, a.Hkv = Hkv, a.D = D;
     a.ns_max = ns;
     a.q_f32 = 1, a.out_f32 = 1;
+    a.kt = kt;
     return ns_launch_gqa_decode(g, a, name);
 }
 
@@ -101,21 +102,13 @@ int ns_q35_attn_decode_kv(ns_gpu* g, int kt, const float* q, int64_t qs, const v
                           int64_t D, int64_t cap, int64_t p0, float* out, float* scratch) {
     NS_TRY
     if (kt == 0) return decode_f32(g, "ns_q35_attn_decode_kv", q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out, scratch);
-    // q8_0 / q4_0 caches (heads of 256): the rows the pass reads, as the fp16 values the reference's reader hands its
-    // tensor cores (silo/attn.cpp:49-78), into a kept buffer [Hkv][p0+T][256] each; then the fp16 kernels
+    // q8_0 / q4_0 caches (heads of 256): the decode kernel streams the rows as they lie and expands each tile in shared
+    // memory to the fp16 values the reference's reader hands its tensor cores (silo/attn.cpp:49-78)
     const char* name = "ns_q35_attn_decode_kv";
     if (kt != 1 && kt != 2) return ns_fail(std::string(name) + ": a cache form 0 (half), 1 (q8_0) or 2 (q4_0)");
-    if (ns_enter(g, name)) return -1;
-    if (T <= 0) return 0;
     if (D != 256) return ns_fail(std::string(name) + ": quantised caches have heads of 256");
-    if (!kc || !vc || Hkv < 1 || p0 < 0 || p0 + T > cap) return ns_fail(std::string(name) + ": past the cache's capacity");
-    const int64_t n = p0 + T, one = (Hkv * n * 256 * 2 + 255) / 256 * 256;
-    void* kept = nullptr;
-    if (ns_kept_kv(g, (size_t) (2 * one), &kept)) return -1;
-    void* kh = kept;
-    void* vh = (uint8_t*) kept + one;
-    if (ns_launch_kv_dequant(g, kt, kc, Hkv, cap, n, kh, name) || ns_launch_kv_dequant(g, kt, vc, Hkv, cap, n, vh, name)) return -1;
-    return decode_f32(g, name, q, qs, kh, vh, T, Hq, Hkv, D, n, p0, out, scratch);
+    if (((uintptr_t) kc & 15) != 0 || ((uintptr_t) vc & 15) != 0) return ns_fail(std::string(name) + ": caches 16-byte aligned");
+    return decode_f32(g, name, q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out, scratch, kt);
     NS_CATCH("ns_q35_attn_decode_kv")
 }
 

@@ -87,19 +87,62 @@ __device__ __forceinline__ uint32_t swz(int r, int c) {
     return (uint32_t) (r * ROWB + ((c ^ (r & 7)) << 4));
 }
 
-template <int D, int MT, int NSTAGE>
-__global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
+// ---- quantised caches (heads of 256; kernels/llm/qwen35/silo/attn.cpp:44-78): a head's row is q8_0 - 256 int8 then 8
+// fp16 scales, 272 bytes - or q4_0 - 8 blocks of 16 bytes (byte j: value j low nibble, value j + 16 high) then 8 fp16
+// scales, 144 bytes. Features 8c .. 8c+7 of a row as the 8 halves the reference's reader produces, half(float(q) *
+// float(d)): q becomes an exact half by placing its (biased) byte in the mantissa of 1024 and subtracting the bias, and
+// the half product of two halves is the exact product rounded once, as the reference's float product rounded to half is.
+template <int QF>
+__host__ __device__ constexpr int raw_row_bytes(int D) { return QF == 0 ? D * 2 : QF == 1 ? D + D / 16 : D / 2 + D / 16; }
+
+__device__ __forceinline__ uint32_t scaled_pair(uint32_t biased, uint32_t sel, __half2 bias, __half2 d2) {
+    const uint32_t w = __byte_perm(biased, 0x64646464u, sel);   // halves (1024 + b_lo, 1024 + b_hi)
+    __half2 h = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&w), bias), d2);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+template <int QF>
+__device__ __forceinline__ uint4 dequant8(const uint8_t* row, int c) {
+    if (QF == 1) {
+        const uint2 w = *reinterpret_cast<const uint2*>(row + 8 * c);
+        const __half2 d2 = __half2half2(*reinterpret_cast<const __half*>(row + 256 + 2 * (c >> 2)));
+        const __half2 bias = __floats2half2_rn(1152.f, 1152.f);   // 1024 + 128: the byte holds q + 128
+        const uint32_t x = w.x ^ 0x80808080u, y = w.y ^ 0x80808080u;
+        return make_uint4(scaled_pair(x, 0x4140, bias, d2), scaled_pair(x, 0x4342, bias, d2), scaled_pair(y, 0x4140, bias, d2),
+                          scaled_pair(y, 0x4342, bias, d2));
+    } else {
+        const int blk = c >> 2, sub = c & 3;
+        const uint2 w = *reinterpret_cast<const uint2*>(row + blk * 16 + (sub & 1) * 8);
+        const __half2 d2 = __half2half2(*reinterpret_cast<const __half*>(row + 128 + 2 * blk));
+        const __half2 bias = __floats2half2_rn(1032.f, 1032.f);   // 1024 + 8: the nibble holds q + 8
+        const int sh = sub >= 2 ? 4 : 0;
+        const uint32_t x = (w.x >> sh) & 0x0F0F0F0Fu, y = (w.y >> sh) & 0x0F0F0F0Fu;
+        return make_uint4(scaled_pair(x, 0x4140, bias, d2), scaled_pair(x, 0x4342, bias, d2), scaled_pair(y, 0x4140, bias, d2),
+                          scaled_pair(y, 0x4342, bias, d2));
+    }
+}
+
+// QF: the caches' form, 0 fp16, 1 q8_0, 2 q4_0. A quantised tile travels as it lies (cp.async of the raw rows into a ring
+// of raw stages) and is expanded by its warp into one fp16 tile just before each product reads it: the keys for S, then
+// the values, into the same 8 KB, for P V. The expansion is some 700 dependent instructions a tile and a warp, so these
+// instances are sized for two CTAs an SM (two warps a scheduler to hide each other's latencies).
+template <int D, int MT, int NSTAGE, int QF>
+__global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(const Params p) {
     constexpr int RG = 16 * MT;          // query rows a CTA
     constexpr int ROWB = D * 2;          // bytes a key row
     constexpr int CPR = ROWB / 16;       // 16-byte chunks a row
     constexpr int TILE = KT * ROWB;      // bytes a K (or V) tile
     constexpr int NT = D / 8;            // output n-tiles
     constexpr int KS = D / 16;           // k-steps of S = Q K^T
+    constexpr int RAWB = raw_row_bytes<QF>(D);      // bytes a key row as the cache holds it
+    constexpr int RAW_CPR = RAWB / 16;
+    constexpr int RAW_TILE = KT * RAWB;
+    constexpr int WARP_BYTES = QF == 0 ? NSTAGE * 2 * TILE : TILE + NSTAGE * 2 * RAW_TILE;
+    static_assert(QF == 0 || D == 256, "quantised caches have heads of 256: a row's 32 chunks are a warp's lanes");
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int row_flag[8];
     uint8_t* q_s = smem;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    uint8_t* w_s = smem + RG * ROWB + warp * (NSTAGE * 2 * TILE);
+    uint8_t* w_s = smem + RG * ROWB + warp * WARP_BYTES;   // fp16: NSTAGE (K, V) tile pairs; quantised: one fp16 tile, then NSTAGE raw pairs
 
     // the row groups of one (split, key head) are neighbours in the grid: they run at the same time, and the second
     // to read a key tile finds it in L2
@@ -147,8 +190,8 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
     for (int t = t_lo; t <= t_hi; ++t) same = same && ns_dec_split(row_keys(seq, t), p.Hkv) == ns_dec_split(row_keys(seq, t_lo), p.Hkv);
     const int npass = same ? 1 : t_hi - t_lo + 1;
 
-    const uint8_t* kbase = (const uint8_t*) seq.kc + (int64_t) hk * seq.cap * ROWB;
-    const uint8_t* vbase = (const uint8_t*) seq.vc + (int64_t) hk * seq.cap * ROWB;
+    const uint8_t* kbase = (const uint8_t*) seq.kc + (int64_t) hk * seq.cap * RAWB;
+    const uint8_t* vbase = (const uint8_t*) seq.vc + (int64_t) hk * seq.cap * RAWB;
 
     for (int pass = 0; pass < npass; ++pass) {
         const int t_a = same ? t_lo : t_lo + pass, t_b = same ? t_hi : t_a;
@@ -185,15 +228,31 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
         auto issue = [&](int tile, int stage) {
             if (tile < ntiles) {
                 const int64_t j0 = jbeg + (int64_t) tile * KT;
-                uint8_t* ks = w_s + stage * (2 * TILE);
-                uint8_t* vs = ks + TILE;
+                if (QF == 0) {
+                    uint8_t* ks = w_s + stage * (2 * TILE);
+                    uint8_t* vs = ks + TILE;
 #pragma unroll
-                for (int i = 0; i < KT * CPR / 32; ++i) {
-                    const int idx = i * 32 + lane, r = idx / CPR, c = idx % CPR;
-                    const bool ok = j0 + r < jend;
-                    const int64_t off = ok ? (j0 + r) * ROWB + c * 16 : 0;
-                    cp_async16(smem_u32(ks + swz<ROWB>(r, c)), kbase + off, ok);
-                    cp_async16(smem_u32(vs + swz<ROWB>(r, c)), vbase + off, ok);
+                    for (int i = 0; i < KT * CPR / 32; ++i) {
+                        const int idx = i * 32 + lane, r = idx / CPR, c = idx % CPR;
+                        const bool ok = j0 + r < jend;
+                        const int64_t off = ok ? (j0 + r) * ROWB + c * 16 : 0;
+                        cp_async16(smem_u32(ks + swz<ROWB>(r, c)), kbase + off, ok);
+                        cp_async16(smem_u32(vs + swz<ROWB>(r, c)), vbase + off, ok);
+                    }
+                } else {
+                    uint8_t* kr = w_s + TILE + stage * (2 * RAW_TILE);
+                    uint8_t* vr = kr + RAW_TILE;
+#pragma unroll
+                    for (int i = 0; i < (KT * RAW_CPR + 31) / 32; ++i) {
+                        const int idx = i * 32 + lane;
+                        if (idx < KT * RAW_CPR) {
+                            const int r = idx / RAW_CPR, c = idx % RAW_CPR;
+                            const bool ok = j0 + r < jend;   // a row past the split: zeros (scale 0)
+                            const int64_t off = ok ? (j0 + r) * RAWB + c * 16 : 0;
+                            cp_async16(smem_u32(kr + r * RAWB + c * 16), kbase + off, ok);
+                            cp_async16(smem_u32(vr + r * RAWB + c * 16), vbase + off, ok);
+                        }
+                    }
                 }
             }
             cp_async_commit();
@@ -211,8 +270,15 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
             }
             cp_async_wait<NSTAGE - 1>();
             __syncwarp();
-            const uint8_t* ks = w_s + stage * (2 * TILE);
-            const uint8_t* vs = ks + TILE;
+            const uint8_t* ks = QF == 0 ? w_s + stage * (2 * TILE) : w_s;
+            const uint8_t* vs = QF == 0 ? ks + TILE : w_s;
+            if (QF != 0) {
+                // the raw keys expanded into the warp's fp16 tile: row i, a lane one 16-byte chunk of it
+                const uint8_t* kr = w_s + TILE + stage * (2 * RAW_TILE);
+#pragma unroll 8
+                for (int i = 0; i < KT; ++i) *reinterpret_cast<uint4*>(w_s + swz<ROWB>(i, lane)) = dequant8<QF>(kr + i * RAWB, lane);
+                __syncwarp();
+            }
             const int64_t j0 = jbeg + (int64_t) tile * KT;
 
             // ---- S = Q K^T: MT x (16 rows x 16 keys)
@@ -284,6 +350,14 @@ __global__ void __launch_bounds__(THREADS) gqa_decode_kernel(const Params p) {
                             o[mt][nt][hh * 2] *= cs[mt][hh];
                             o[mt][nt][hh * 2 + 1] *= cs[mt][hh];
                         }
+            }
+            if (QF != 0) {
+                // the keys are consumed: the values take their place
+                __syncwarp();
+                const uint8_t* vr = w_s + TILE + stage * (2 * RAW_TILE) + RAW_TILE;
+#pragma unroll 8
+                for (int i = 0; i < KT; ++i) *reinterpret_cast<uint4*>(w_s + swz<ROWB>(i, lane)) = dequant8<QF>(vr + i * RAWB, lane);
+                __syncwarp();
             }
             // ---- O += P V
 #pragma unroll
@@ -532,12 +606,14 @@ cudaError_t launch_dependent(K kernel, unsigned blocks, unsigned threads, cudaSt
     return cudaLaunchKernelEx(&cfg, kernel, params);
 }
 
-template <int D, int MT, int NSTAGE>
+template <int D, int MT, int NSTAGE, int QF = 0>
 int launch(ns_gpu* g, const Params& p, int64_t B, const char* where) {
     constexpr int RG = 16 * MT;
-    constexpr size_t smem = (size_t) RG * D * 2 + (size_t) WARPS * NSTAGE * 2 * KT * D * 2;
+    constexpr size_t tile = (size_t) KT * D * 2, raw_tile = (size_t) KT * raw_row_bytes<QF>(D);
+    constexpr size_t smem = (size_t) RG * D * 2 + (size_t) WARPS * (QF == 0 ? NSTAGE * 2 * tile : tile + NSTAGE * 2 * raw_tile);
+    static_assert(QF == 0 || 2 * (smem + 1024) <= 227 * 1024, "two CTAs of a quantised instance share an SM");
     static_assert(smem >= (size_t) RG * D * 2 + (size_t) WARPS * RG * (D + 2) * 4, "the merge buffer fits the stage memory");
-    auto kern = gqa_decode_kernel<D, MT, NSTAGE>;
+    auto kern = gqa_decode_kernel<D, MT, NSTAGE, QF>;
     static bool set[64] = {};
     if (!set[g->dev & 63]) {
         NS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem), where);
@@ -582,6 +658,11 @@ int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where) {
     p.epoch = a.epoch;
     const int R = p.T * p.G;
     if (a.B > 65535) return ns_fail(std::string(where) + ": too many sequences for one launch");
+    if (a.kt != 0) {
+        if (a.D != 256 || (a.kt != 1 && a.kt != 2)) return ns_fail(std::string(where) + ": quantised caches are q8_0 (1) or q4_0 (2) with heads of 256");
+        p.groups = (R + 15) / 16;
+        return a.kt == 1 ? launch<256, 1, 2, 1>(g, p, a.B, where) : launch<256, 1, 3, 2>(g, p, a.B, where);
+    }
     if (a.D == 128) {
         if (R <= 16) {
             p.groups = 1;

@@ -34,6 +34,7 @@ struct GqaDecodeArgs {
     float* const* mailboxes;   // device array [nranks] of mailbox bases as this GPU addresses them
     int rank, nranks;
     int64_t epoch;
+    int kt = 0;                // the caches' form: 0 fp16, 1 q8_0, 2 q4_0 (heads of 256; rows of 272 / 144 bytes)
 };
 
 // A rank's mailbox for the KV-split combine, in floats from its base: partials [2 buffers][nranks][rows][D+2], then

@@ -20,6 +20,14 @@ def normal_f16(config, tensor, shape, sigma=1.0):
     return x.astype(np.float16)
 
 
+def normal_f32(config, tensor, shape, sigma=1.0):
+    """fp32 array of N(0, sigma) values."""
+    x = rng(config, tensor).standard_normal(shape, dtype=np.float32)
+    if sigma != 1.0:
+        x *= np.float32(sigma)
+    return x
+
+
 def normal_bf16_bits(config, tensor, shape, sigma=1.0):
     """bf16 bit patterns (uint16) of N(0, sigma) values, round to nearest even."""
     x = rng(config, tensor).standard_normal(shape, dtype=np.float32)
