@@ -417,6 +417,10 @@ def measure(env, name, steps, warmup):
     return res
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, per launch and GPU, from the ncu captures summarised under
+# profiles/ (a profiler's figure, constant for a workload; not measured by this script)
+NCU_TRAFFIC = {"decode_c2": 1.073912e9 + 12.0e6, "mla_decode_32k": 37.96e6 + 0.07e6, "decode_q35_q8": 285.29e6 + 3.9e6}
+
 OTHERS_1GPU = [("prefill_16k", 10), ("prefill_c1", 50), ("decode_c2_b1", 50), ("decode_128k", 30), ("decode_c5", 30), ("decode_q35_f16", 30),
                ("decode_q35_q8", 30), ("decode_q35_q4", 30), ("mla_decode_4k", 50),
                ("mla_decode_32k", 50), ("mla_decode_131k", 30), ("mla_prefill_c4", 3)]
@@ -580,14 +584,14 @@ def run_ours(args):
     if name.startswith("decode"):
         value, unit = info.get("bytes_total", world * info["bytes"]) / (ms * 1e-3) / 1e9, "GB/s"
         roof = {"bound": "hbm", "achieved": res["gbs_per_gpu"], "peak": float(pk["hbm_gbs"]), "unit": "GB/s", "frac": res["frac_of_hbm_peak"],
-                "traffic": None, "peak_source": pk["_source"],
+                "traffic": NCU_TRAFFIC.get(name), "peak_source": pk["_source"],
                 "note": "per GPU; algorithmic bytes = 2*kv*Hkv*D*2 B a sequence x sequences a launch; duration = CUDA-event time of a step "
                         "(the split kernel plus its merge kernel)"}
         scaling = "strong" if "bytes_total" in info else "weak"
     elif name.startswith("mla_decode"):
         value, unit = info["bytes"] / (ms * 1e-3) / 1e9, "GB/s"
         roof = {"bound": "hbm", "achieved": res["gbs_per_gpu"], "peak": float(pk["hbm_gbs"]), "unit": "GB/s", "frac": res["frac_of_hbm_peak"],
-                "traffic": None, "peak_source": pk["_source"], "note": "algorithmic bytes = 1,152 B a cell; flops 278,528 a cell",
+                "traffic": NCU_TRAFFIC.get(name), "peak_source": pk["_source"], "note": "algorithmic bytes = 1,152 B a cell; flops 278,528 a cell",
                 "tensor_frac": info["flops"] / (ms * 1e-3) / 1e12 / float(pk["bf16_tflops"])}
         scaling = "weak"
     else:

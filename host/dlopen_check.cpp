@@ -24,6 +24,8 @@ static const char* kEngines[] = {
     "ns_gather_h",
     // deepseek2
     "ns_ds2_mla_decode",
+    // qwen35: the step before attention
+    "ns_q35_qk_norm_rope", "ns_q35_qk_norm_rope_pos", "ns_q35_rope", "ns_b200_qkv_prepare",
     // qwen35 quantised caches
     "ns_q35_kv_store_q", "ns_q35_fwht32",
     // deepseek41

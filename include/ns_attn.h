@@ -70,6 +70,18 @@ int ns_q35_kv_store_q(ns_gpu* g, int kt, const float* k, int64_t ks, const float
                       int64_t p0, void* kc, void* vc);
 int ns_q35_fwht32(ns_gpu* g, float* x, int64_t rows, int64_t n, int64_t stride);
 
+/* kernels/llm/qwen35/q35.h:16-24,59-61 - the step before attention. Per (row t, head h): x = src[t*ss + h*hs .. + D] RMS-normed
+ * (weight w [D], eps), then rotate-half rotary positions on its first n_rot features (pairs i, i + n_rot/2; angle (p0 + t)
+ * theta^(-2i / n_rot)), into dst[t*ds + h*D]. _pos: each row at its own positions pos [T][3] (t, h, w), pair k turning by
+ * the one Qwen3-VL's interleaved sections (s0, s1, s2) choose. ns_q35_rope: the same without the norm. fp32 throughout;
+ * src and dst may be the same rows. */
+int ns_q35_qk_norm_rope(ns_gpu* g, const float* src, int64_t ss, int64_t hs, float* dst, int64_t ds, int64_t T, int64_t H, int64_t D, const float* w,
+                        float eps, int64_t n_rot, float theta, int64_t p0);
+int ns_q35_qk_norm_rope_pos(ns_gpu* g, const float* src, int64_t ss, int64_t hs, float* dst, int64_t ds, int64_t T, int64_t H, int64_t D, const float* w,
+                            float eps, int64_t n_rot, float theta, const int32_t* pos, int64_t s0, int64_t s1, int64_t s2);
+int ns_q35_rope(ns_gpu* g, const float* src, int64_t ss, int64_t hs, float* dst, int64_t ds, int64_t T, int64_t H, int64_t D, int64_t n_rot, float theta,
+                int64_t p0);
+
 /* kernels/llm/nemotronh/nh.h:39-44 and silo/nhs.h:63-69 - the same kernels under the nemotronh engine's names (D 128) */
 int64_t ns_nh_attn_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0);
 int ns_nh_attn(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t cap,
@@ -101,6 +113,15 @@ typedef struct ns_b200_seq {
     int64_t cap;
     int64_t p0;
 } ns_b200_seq;
+
+/* A layer's projected rows made ready for attention in one launch (the reference queues ns_q35_qk_norm_rope for q, for k,
+ * and ns_q35_kv_store: llm/qwen35/src/engine.rs:1553-1585): q [T][Hq*D] (qs floats apart) and k [T][Hkv*D] (ks apart) are
+ * RMS-normed per head (weights wq, wk [D]; null: no norm) and rotated at positions p0 + t; q leaves as fp16 rows q_out
+ * [T][Hq*D] (what ns_b200_gqa_decode / ns_b200_gqa_prefill read), k and v [T][Hkv*D] (vs apart) land in the fp16 caches
+ * [Hkv][cap][D] at positions p0 .. p0+T-1. The arithmetic is that of the three calls it replaces. */
+int ns_b200_qkv_prepare(ns_gpu* g, const float* q, int64_t qs, const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hq, int64_t Hkv,
+                        int64_t D, const float* wq, const float* wk, float eps, int64_t n_rot, float theta, int64_t p0, int64_t cap, void* q_out, void* kc,
+                        void* vc);
 
 /* Split-KV GQA decode of a batch (replaces one ns_q35_attn_decode call per sequence, llm/qwen35/src/engine.rs:1535,
  * 1596-1600). q [B][T][Hq*D] fp16 (qs elements between rows, q_seq between sequences), seqs a DEVICE array [B],

@@ -1,0 +1,146 @@
+// pre_attn.cu: the step before attention - RMS norm of each head of q and k, rotary positions, and the writes that feed
+// the attention kernels (kernels/llm/qwen35/q35.cpp:220-279,350-385,573-588). The reference runs it as three or four
+// launches a layer (norm+rope of q, of k, the cache store); ns_b200_qkv_prepare is the same arithmetic in one launch,
+// with q leaving as the fp16 rows the native attention entry points read and k, v landing in the fp16 caches.
+#include "kernels.cuh"
+
+namespace {
+
+// Row x [D] of one (row, head), a warp: RMS norm (w null: none), rotate-half over the first n_rot features (pair (i, i +
+// n_rot/2) by angle p * theta^(-2i/n_rot)), then `put(i, value)` for every feature. Both features of a pair are read
+// before either is written, so src and dst may be the same rows.
+template <class Put>
+__device__ __forceinline__ void norm_rope_row(const float* __restrict__ x, int64_t D, const float* __restrict__ w, float eps, int64_t n_rot, float theta,
+                                              float p_t, const int32_t* pos3, int64_t s0, int64_t s1, int64_t s2, Put put) {
+    const int lane = threadIdx.x & 31;
+    float inv = 1.0f;
+    if (w) {
+        float s = 0.0f;
+        for (int64_t i = lane; i < D; i += 32) s += x[i] * x[i];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        inv = rsqrtf(s / (float) D + eps);
+    }
+    const int64_t half_rot = n_rot / 2, sect = s0 + s1 + s2;
+    for (int64_t i = lane; i < half_rot; i += 32) {
+        float p = p_t;
+        if (pos3) {
+            const int64_t sec = i % sect;
+            const int c = (sec % 3 == 1 && sec < 3 * s1) ? 1 : (sec % 3 == 2 && sec < 3 * s2) ? 2 : 0;
+            p = (float) pos3[c];
+        }
+        // the frequency as the correctly rounded float of theta^e, e the reference's float exponent: at position 100,000 one
+        // unit in the last place of the frequency is 0.008 rad of angle
+        const float a = p * (float) pow((double) theta, (double) (-2.0f * (float) i / (float) n_rot));
+        float sn, c_;
+        sincosf(a, &sn, &c_);
+        const float lo = w ? x[i] * inv * w[i] : x[i], hi = w ? x[i + half_rot] * inv * w[i + half_rot] : x[i + half_rot];
+        put(i, lo * c_ - hi * sn);
+        put(i + half_rot, hi * c_ + lo * sn);
+    }
+    for (int64_t i = n_rot + lane; i < D; i += 32) put(i, w ? x[i] * inv * w[i] : x[i]);
+}
+
+__global__ void __launch_bounds__(256) norm_rope_kernel(const float* __restrict__ src, int64_t ss, int64_t hs, float* __restrict__ dst, int64_t ds, int64_t T,
+                                                        int64_t H, int64_t D, const float* __restrict__ w, float eps, int64_t n_rot, float theta, int64_t p0,
+                                                        const int32_t* __restrict__ pos, int64_t s0, int64_t s1, int64_t s2) {
+    const int64_t th = (int64_t) blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (th >= T * H) return;
+    const int64_t t = th / H, h = th % H;
+    float* y = dst + t * ds + h * D;
+    norm_rope_row(src + t * ss + h * hs, D, w, eps, n_rot, theta, (float) (p0 + t), pos ? pos + 3 * t : nullptr, s0, s1, s2,
+                  [&](int64_t i, float v) { y[i] = v; });
+}
+
+// one launch for a layer's q, k, v rows: heads [0, Hq) are q (norm wq, rope) -> q_out fp16 [T][Hq*D]; heads [Hq, Hq+Hkv) are
+// k (norm wk, rope) -> the key cache at position p0 + t; heads [Hq+Hkv, Hq+2Hkv) are v -> the value cache, unchanged
+__global__ void __launch_bounds__(256) qkv_prepare_kernel(const float* __restrict__ q, int64_t qs, const float* __restrict__ k, int64_t ks,
+                                                          const float* __restrict__ v, int64_t vs, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                                                          const float* __restrict__ wq, const float* __restrict__ wk, float eps, int64_t n_rot, float theta,
+                                                          int64_t p0, int64_t cap, __half* __restrict__ q_out, __half* __restrict__ kc,
+                                                          __half* __restrict__ vc) {
+    const int64_t HT = Hq + 2 * Hkv, th = (int64_t) blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (th >= T * HT) return;
+    const int64_t t = th / HT, h = th % HT;
+    const int lane = threadIdx.x & 31;
+    if (h < Hq) {
+        __half* y = q_out + (t * Hq + h) * D;
+        norm_rope_row(q + t * qs + h * D, D, wq, eps, n_rot, theta, (float) (p0 + t), nullptr, 0, 0, 0, [&](int64_t i, float x) { y[i] = __float2half_rn(x); });
+    } else if (h < Hq + Hkv) {
+        const int64_t hk = h - Hq;
+        __half* y = kc + (hk * cap + p0 + t) * D;
+        norm_rope_row(k + t * ks + hk * D, D, wk, eps, n_rot, theta, (float) (p0 + t), nullptr, 0, 0, 0, [&](int64_t i, float x) { y[i] = __float2half_rn(x); });
+    } else {
+        const int64_t hk = h - Hq - Hkv;
+        const float* x = v + t * vs + hk * D;
+        __half* y = vc + (hk * cap + p0 + t) * D;
+        for (int64_t i = lane; i < D; i += 32) y[i] = __float2half_rn(x[i]);
+    }
+}
+
+int check_rope(const char* name, int64_t D, int64_t n_rot) {
+    if (D < 2 || D % 16 != 0 || n_rot < 0 || n_rot > D || n_rot % 2) return ns_fail(std::string(name) + ": D a multiple of 16, n_rot even and at most D");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ns_q35_qk_norm_rope(ns_gpu* g, const float* src, int64_t ss, int64_t hs, float* dst, int64_t ds, int64_t T, int64_t H, int64_t D, const float* w,
+                        float eps, int64_t n_rot, float theta, int64_t p0) {
+    NS_TRY
+    const char* name = "ns_q35_qk_norm_rope";
+    if (ns_enter(g, name)) return -1;
+    if (T <= 0) return 0;
+    if (check_rope(name, D, n_rot)) return -1;
+    if (!src || !dst || !w || H < 1) return ns_fail(std::string(name) + ": a null buffer");
+    norm_rope_kernel<<<(unsigned) ((T * H + 7) / 8), 256, 0, g->compute>>>(src, ss, hs, dst, ds, T, H, D, w, eps, n_rot, theta, p0, nullptr, 0, 0, 0);
+    return ns_launched(name);
+    NS_CATCH("ns_q35_qk_norm_rope")
+}
+
+int ns_q35_qk_norm_rope_pos(ns_gpu* g, const float* src, int64_t ss, int64_t hs, float* dst, int64_t ds, int64_t T, int64_t H, int64_t D, const float* w,
+                            float eps, int64_t n_rot, float theta, const int32_t* pos, int64_t s0, int64_t s1, int64_t s2) {
+    NS_TRY
+    const char* name = "ns_q35_qk_norm_rope_pos";
+    if (ns_enter(g, name)) return -1;
+    if (T <= 0) return 0;
+    if (check_rope(name, D, n_rot)) return -1;
+    if (s0 < 0 || s1 < 0 || s2 < 0 || s0 + s1 + s2 <= 0) return ns_fail(std::string(name) + ": sections");
+    if (!src || !dst || !w || !pos || H < 1) return ns_fail(std::string(name) + ": a null buffer");
+    norm_rope_kernel<<<(unsigned) ((T * H + 7) / 8), 256, 0, g->compute>>>(src, ss, hs, dst, ds, T, H, D, w, eps, n_rot, theta, 0, pos, s0, s1, s2);
+    return ns_launched(name);
+    NS_CATCH("ns_q35_qk_norm_rope_pos")
+}
+
+int ns_q35_rope(ns_gpu* g, const float* src, int64_t ss, int64_t hs, float* dst, int64_t ds, int64_t T, int64_t H, int64_t D, int64_t n_rot, float theta,
+                int64_t p0) {
+    NS_TRY
+    const char* name = "ns_q35_rope";
+    if (ns_enter(g, name)) return -1;
+    if (T <= 0) return 0;
+    if (check_rope(name, D, n_rot)) return -1;
+    if (!src || !dst || H < 1) return ns_fail(std::string(name) + ": a null buffer");
+    norm_rope_kernel<<<(unsigned) ((T * H + 7) / 8), 256, 0, g->compute>>>(src, ss, hs, dst, ds, T, H, D, nullptr, 0.f, n_rot, theta, p0, nullptr, 0, 0, 0);
+    return ns_launched(name);
+    NS_CATCH("ns_q35_rope")
+}
+
+int ns_b200_qkv_prepare(ns_gpu* g, const float* q, int64_t qs, const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hq, int64_t Hkv,
+                        int64_t D, const float* wq, const float* wk, float eps, int64_t n_rot, float theta, int64_t p0, int64_t cap, void* q_out, void* kc,
+                        void* vc) {
+    NS_TRY
+    const char* name = "ns_b200_qkv_prepare";
+    if (ns_enter(g, name)) return -1;
+    if (T <= 0) return 0;
+    if (check_rope(name, D, n_rot)) return -1;
+    if (Hq < 1 || Hkv < 1 || !q || !k || !v || !q_out || !kc || !vc) return ns_fail(std::string(name) + ": a null buffer");
+    if (p0 < 0 || p0 + T > cap) return ns_fail(std::string(name) + ": past the cache's capacity");
+    qkv_prepare_kernel<<<(unsigned) ((T * (Hq + 2 * Hkv) + 7) / 8), 256, 0, g->compute>>>(q, qs, k, ks, v, vs, T, Hq, Hkv, D, wq, wk, eps, n_rot, theta, p0, cap,
+                                                                                          (__half*) q_out, (__half*) kc, (__half*) vc);
+    return ns_launched(name);
+    NS_CATCH("ns_b200_qkv_prepare")
+}
+
+}  // extern "C"

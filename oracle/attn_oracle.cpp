@@ -781,6 +781,48 @@ void orc_fwht32(float* x, int64_t rows, int64_t n, int64_t stride) {
         }
 }
 
+// ---- the step before attention: RMS norm and rotary positions of q and k (kernels/llm/qwen35/q35.cpp:220-254,256-279,350-385)
+// Per (row t, head h): x = src[t*ss + h*hs .. + D]; with w: x * rsqrt(mean(x^2) + eps) * w (the squares summed as the
+// reference's 16 lanes do: lane l takes i = l, l+16, ..; the lanes' sums added in order); then rotate-half over the first
+// n_rot features: pair (i, i + n_rot/2) turned by angle pos * theta^(-2i/n_rot); into dst[t*ds + h*D]. pos = p0 + t, or
+// with pos3 [T][3] the one of (t, h, w) that pair k's interleaved section picks (sections s0, s1, s2).
+void orc_qk_norm_rope(const float* src, int64_t ss, int64_t hs, float* dst, int64_t ds, int64_t T, int64_t H, int64_t D, const float* w, float eps,
+                      int64_t n_rot, float theta, int64_t p0, const int32_t* pos3, int64_t s0, int64_t s1, int64_t s2) {
+    const int64_t half_rot = n_rot / 2, sect = s0 + s1 + s2;
+    for (int64_t t = 0; t < T; ++t)
+        for (int64_t h = 0; h < H; ++h) {
+            const float* x = src + t * ss + h * hs;
+            float* y = dst + t * ds + h * D;
+            float inv = 1.0f;
+            if (w) {
+                float lane[16] = {};
+                for (int64_t i = 0; i < D; ++i) lane[i % 16] += x[i] * x[i];
+                float sum = 0.0f;
+                for (int l = 0; l < 16; ++l) sum += lane[l];
+                inv = 1.0f / std::sqrt(sum / (float) D + eps);
+            }
+            std::vector<float> v((size_t) D);
+            for (int64_t i = 0; i < D; ++i) v[i] = w ? x[i] * inv * w[i] : x[i];
+            for (int64_t i = 0; i < D; ++i) {
+                if (i >= n_rot) {
+                    y[i] = v[i];
+                    continue;
+                }
+                const int64_t k = i < half_rot ? i : i - half_rot;
+                float p = (float) (p0 + t);
+                if (pos3) {
+                    const int64_t sec = k % sect;
+                    const int c = (sec % 3 == 1 && sec < 3 * s1) ? 1 : (sec % 3 == 2 && sec < 3 * s2) ? 2 : 0;
+                    p = (float) pos3[t * 3 + c];
+                }
+                const float a = p * std::pow(theta, -2.0f * (float) k / (float) n_rot);
+                const float c_ = std::cos(a), sn = std::sin(a);
+                const float other = v[i < half_rot ? i + half_rot : i - half_rot];
+                y[i] = i < half_rot ? v[i] * c_ - other * sn : v[i] * c_ + other * sn;
+            }
+        }
+}
+
 // ---- cache writers -----------------------------------------------------------------------------------------------
 
 // ns_q35_kv_store (kernels/llm/qwen35/q35.cpp:573-588): fp32 rows k [T][ks], v [T][vs] -> fp16 caches [Hkv][cap][D]

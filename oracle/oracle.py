@@ -202,3 +202,12 @@ def fwht32(x):
     """In place: each block of 32 of the rows of x [rows, n] fp32 through the normalised Walsh-Hadamard transform."""
     lib().orc_fwht32(_f(x), i64(x.shape[0]), i64(x.shape[1]), i64(x.shape[1]))
     return x
+
+
+def qk_norm_rope(x, T, H, D, w, eps, n_rot, theta, p0=0, pos3=None, sections=(0, 0, 0)):
+    """x fp32 [T, H*D] -> fp32 [T, H*D]: RMS norm (w None: none) then rotate-half rotary positions over the first n_rot features."""
+    y = np.empty((T, H * D), np.float32)
+    lib().orc_qk_norm_rope(_f(x), i64(x.shape[1]), i64(D), _f(y), i64(H * D), i64(T), i64(H), i64(D), None if w is None else _f(w), C.c_float(eps),
+                           i64(n_rot), C.c_float(theta), i64(p0), None if pos3 is None else pos3.ctypes.data_as(_pi), i64(sections[0]), i64(sections[1]),
+                           i64(sections[2]))
+    return y

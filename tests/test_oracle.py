@@ -264,3 +264,28 @@ def test_fwht32_is_its_own_inverse():
     h = np.array([[(-1) ** bin(i & j).count("1") for j in range(32)] for i in range(32)], np.float64) / np.sqrt(32.0)
     assert np.allclose(y.reshape(7, 8, 32), x.reshape(7, 8, 32).astype(np.float64) @ h, atol=1e-5)
     assert np.allclose(O.fwht32(y.copy()), x, atol=1e-5)
+
+
+def test_qk_norm_rope_against_numpy():
+    """kernels/llm/qwen35/q35.cpp:220-254 in float64 numpy: RMS norm, then rotate-half over the first n_rot features."""
+    T, H, D, n_rot, theta, eps, p0 = 5, 3, 128, 64, 1e6, 1e-6, 1000
+    x = W.rng(977, 0).standard_normal((T, H * D), dtype=np.float32)
+    w = (1.0 + 0.1 * W.rng(977, 1).standard_normal(D, dtype=np.float32)).astype(np.float32)
+    y = O.qk_norm_rope(x, T, H, D, w, eps, n_rot, theta, p0)
+    xd = x.astype(np.float64).reshape(T, H, D)
+    v = xd / np.sqrt((xd ** 2).mean(-1, keepdims=True) + eps) * w
+    k = np.arange(n_rot // 2)
+    ang = (p0 + np.arange(T))[:, None] * theta ** (-2.0 * k / n_rot)
+    c, s = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+    want = v.copy()
+    want[..., :n_rot // 2] = v[..., :n_rot // 2] * c - v[..., n_rot // 2:n_rot] * s
+    want[..., n_rot // 2:n_rot] = v[..., n_rot // 2:n_rot] * c + v[..., :n_rot // 2] * s
+    assert np.abs(y.reshape(T, H, D) - want).max() < 2e-3      # fp32 angles at position 1,000: ~1e-4 rad
+    # positions given per row, all three equal: the same as the plain form at that position
+    pos3 = np.repeat((p0 + np.arange(T, dtype=np.int32))[:, None], 3, 1).copy()
+    assert np.array_equal(O.qk_norm_rope(x, T, H, D, w, eps, n_rot, theta, 0, pos3, (11, 11, 10)), y)
+    # without weights: the rotation alone keeps each pair's length
+    r = O.qk_norm_rope(x, T, H, D, None, 0.0, n_rot, theta, p0).reshape(T, H, D)
+    xr = x.reshape(T, H, D)
+    assert np.allclose(r[..., :32] ** 2 + r[..., 32:64] ** 2, xr[..., :32] ** 2 + xr[..., 32:64] ** 2, rtol=1e-4, atol=1e-6)
+    assert np.array_equal(r[..., n_rot:], xr[..., n_rot:])
