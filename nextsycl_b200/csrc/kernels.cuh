@@ -99,7 +99,6 @@ struct MlaDecodeArgs {
     int64_t cache_rows_apart; // elements between the rows' own cell matrices; 0: one shared cache
     const float* sinks;       // device [H] or null: a per-head sink (natural-log units) that joins the denominator only
 };
-// cells a key split / floats of partials for rows that see up to n cells, on a GPU of `sms` SMs
-int64_t ns_mla_split(int64_t n, int64_t T, int64_t H, int sms);
+// floats of partials for a pass of T rows that see up to n cells, on a GPU of `sms` SMs
 int64_t ns_mla_partial_floats(int64_t n, int64_t T, int64_t H, int sms);
 int ns_launch_mla_decode(ns_gpu* g, const MlaDecodeArgs& a, const char* where);

@@ -47,6 +47,20 @@ struct Geo {
     static constexpr int SMEM_TOTAL = 1024 + QS_BYTES + NSTAGE * TILE_BYTES + 512;
 };
 
+// Cells a key split for a row that sees n cells, when `units` (head tiles x rows sharing the launch) such rows are to fill
+// `sms` SMs once with pairs of CTAs: whole tiles, at least two of them (a partial costs 2 KB a head).
+__host__ __device__ inline int64_t mla_split(int64_t n, int64_t units, int sms) {
+    int64_t want = sms / (2 * units);
+    if (want < 1) want = 1;
+    int64_t kb = (n + want - 1) / want;
+    kb = (kb + BN - 1) / BN * BN;
+    return kb < 2 * BN ? 2 * BN : kb;
+}
+// Decode widths (at most 8 rows, as the reference's decode kernels): a row's split size comes from its own cells alone,
+// so a row of a verify pass sums exactly as the one-row pass at its position does
+// (kernels/llm/deepseek41/silo/attn.cpp:316-319). More rows: one size for the pass, from its longest row.
+constexpr int64_t DECODE_ROWS = 8;
+
 struct Params {
     const __half* q;       // [T][H][CR] fp16
     const float* sinks;    // per head, natural-log units, or null: a sink joins the denominator only (deepseek41)
@@ -55,7 +69,8 @@ struct Params {
     float* out;            // [T][H][512]
     float* part;           // [T][H][ns][PS]
     int* status;
-    int T, H, ns;
+    int T, H, ns;          // ns: splits the partials are laid out for
+    int per_row, units, sms;   // per_row: each row's split size from its own cells (mla_split(n, units, sms)); else kb
     int64_t pos0, kb;      // cells a split
     float scale_log2;
 };
@@ -84,7 +99,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int hv = blockIdx.x & 1, split = blockIdx.x >> 1;
     const int h0 = blockIdx.y * BM, t = blockIdx.z;
     const int64_t n = p.counts ? (int64_t) p.counts[t] : p.pos0 + t + 1;   // cells this row sees
-    const int64_t jbeg = (int64_t) split * p.kb, jend = min(n, (int64_t) (split + 1) * p.kb);
+    const int64_t kb = p.per_row ? mla_split(n, p.units, p.sms) : p.kb;
+    const int64_t jbeg = (int64_t) split * kb, jend = min(n, (int64_t) (split + 1) * kb);
     const int ntiles = jbeg < jend ? (int) ((jend - jbeg + BN - 1) / BN) : 0;
     if (ntiles == 0) return;                                // the whole CTA: this split holds none of the row's cells
 
@@ -307,7 +323,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (ok) {
             fence_after_sync();
             const int64_t row = (int64_t) t * p.H + h0 + r;
-            const bool direct = p.ns == 1;
+            const bool direct = n <= kb;   // the row's only split: normalised and written as the result
             float inv = 1.0f;
             if (direct) {
                 // with a sink s: out = O 2^(m - mx) / (l 2^(m - mx) + 2^(s - mx)), mx = max(m, s) (kernels/llm/deepseek41/silo/attn.cpp:266-285)
@@ -379,7 +395,9 @@ __global__ void __launch_bounds__(MERGE_THREADS) mla_merge_kernel(const Params p
     const int tid = threadIdx.x, g = tid >> 6, lane = tid & 63;
     pdl_wait();   // the split kernel's partials
     const int64_t n = p.counts ? (int64_t) p.counts[t] : p.pos0 + t + 1;
-    const int nsr = (int) ((n + p.kb - 1) / p.kb);
+    const int64_t kb = p.per_row ? mla_split(n, p.units, p.sms) : p.kb;
+    const int nsr = (int) ((n + kb - 1) / kb);
+    if (nsr <= 1) return;   // the whole block: the row's one split wrote the result itself
     const float* pp = p.part + row * p.ns * PS;
     const float* src = pp + blockIdx.y * DVH + lane * 4;
     float4 v[MERGE_FLIGHT];
@@ -467,18 +485,27 @@ int make_map(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_
 
 }  // namespace
 
-int64_t ns_mla_split(int64_t n, int64_t T, int64_t H, int sms) {
-    const int64_t tiles = (H + BM - 1) / BM * T;
-    int64_t want = sms / (2 * tiles);           // splits that fill the SMs once
-    if (want < 1) want = 1;
-    int64_t kb = (n + want - 1) / want;
-    kb = (kb + BN - 1) / BN * BN;
-    if (kb < 2 * BN) kb = 2 * BN;               // at least two tiles a split: a partial costs 2 KB a head
-    return kb;
+// the split size of a pass of T rows whose longest row sees n cells, and the splits its partials are laid out for
+static void mla_layout(int64_t n, int64_t T, int64_t H, int sms, int& per_row, int& units, int64_t& kb, int64_t& ns) {
+    const int64_t head_tiles = (H + BM - 1) / BM;
+    per_row = T <= DECODE_ROWS ? 1 : 0;
+    units = (int) (per_row ? head_tiles : head_tiles * T);
+    kb = mla_split(n, units, sms);
+    if (per_row) {
+        // every row's own count is at most n: its splits number at most sms / (2 units), and at most n / 128 rounded up
+        int64_t want = sms / (2 * units);
+        if (want < 1) want = 1;
+        ns = std::min<int64_t>(want, (n + 2 * BN - 1) / (2 * BN));
+        if (ns < 1) ns = 1;
+    } else {
+        ns = (n + kb - 1) / kb;
+    }
 }
 
 int64_t ns_mla_partial_floats(int64_t n, int64_t T, int64_t H, int sms) {
-    const int64_t kb = ns_mla_split(n, T, H, sms), ns = (n + kb - 1) / kb;
+    int per_row, units;
+    int64_t kb, ns;
+    mla_layout(n, T, H, sms, per_row, units, kb, ns);
     return ns > 1 ? T * H * ns * PS : 0;
 }
 
@@ -497,8 +524,11 @@ int launch(ns_gpu* g, const MlaDecodeArgs& a, const char* where) {
     p.T = (int) a.T;
     p.H = (int) a.H;
     p.pos0 = a.pos0;
-    p.kb = ns_mla_split(n, a.T, a.H, g->sms);
-    p.ns = (int) ((n + p.kb - 1) / p.kb);
+    int64_t ns = 1;
+    mla_layout(n, a.T, a.H, g->sms, p.per_row, p.units, p.kb, ns);
+    p.ns = (int) ns;
+    p.sms = g->sms;
+    if (p.ns > 1 && !a.part) return ns_fail(std::string(where) + ": no scratch for the key splits");
     p.scale_log2 = a.scale * 1.4426950408889634f;
     if (p.ns > lse::MAX_SPLITS) return ns_fail(std::string(where) + ": more key splits than the merge holds");
     CUtensorMap tq, tc;

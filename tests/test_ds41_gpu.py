@@ -82,15 +82,22 @@ def test_sink_limits(gpu):
     assert np.abs(got).max() < 1e-30
 
 
-def test_a_row_alone_agrees_with_its_pass(gpu):
-    """Row t of a pass of T rows against the same position run alone: the same cells; the key splits may differ, so the
-    two agree to the rounding of the fp16 weights, not bit for bit."""
+def test_a_row_of_a_verify_pass_equals_the_one_row_pass(gpu):
+    """Decode widths (at most 8 rows): a row's split size comes from its own cells, so row t of a pass equals the same
+    position run alone bit for bit (kernels/llm/deepseek41/silo/attn.cpp:316-319)."""
     T, H, pos0, window, R, ratio, K = 3, 64, 5000, 128, 128, 4, 256
     q, raw, comp, sel, sinks = case(991, T, H, pos0, window, R, ratio, K)
     whole = run(gpu, gpu.api.ns_ds41_attend_xmx, q, raw, R, comp, ratio, sel, K, sinks, T, H, pos0, window)
     for t in range(T):
         alone = run(gpu, gpu.api.ns_ds41_attend_xmx, q[t:t + 1].copy(), raw, R, comp, ratio, sel[t:t + 1].copy(), K, sinks, 1, H, pos0 + t, window)
-        close(alone[0], whole[t], abs_tol=5e-4, rel_tol=1e-2)
+        assert np.array_equal(alone[0], whole[t])
+    # rows whose cell counts differ (no picks: every compressed cell): 8 rows across a step of the compressed count
+    T, pos0 = 8, 4090
+    q, raw, comp, _, sinks = case(994, T, H, pos0, window, R, ratio, 0)
+    whole = run(gpu, gpu.api.ns_ds41_attend_xmx, q, raw, R, comp, ratio, None, 0, sinks, T, H, pos0, window)
+    for t in (0, 5, 7):
+        alone = run(gpu, gpu.api.ns_ds41_attend_xmx, q[t:t + 1].copy(), raw, R, comp, ratio, None, 0, sinks, 1, H, pos0 + t, window)
+        assert np.array_equal(alone[0], whole[t])
 
 
 def test_rejects_bad_arguments(gpu):

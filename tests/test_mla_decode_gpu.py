@@ -78,3 +78,20 @@ def test_config_3_full_size(gpu, ops, n):
     qs = np.ascontiguousarray(q[:, :8].astype(np.float32))
     assert_close(got[:, :8], O.mla_gemm(qs, cache.view(np.uint16), T, 8, 512, 64, n - 1, np.float32(SCALE)), "config 3, heads 0..7")
     assert np.isfinite(got).all()
+
+
+def test_a_verify_row_equals_the_one_row_pass(gpu, ops):
+    """At decode widths a row's key splits come from its own cell count alone: row t of a pass of T rows is the one-row
+    pass at its position, bit for bit (the property kernels/llm/deepseek41/silo/attn.cpp:316-319 states for its decode)."""
+    T, H, n = 4, 128, 9000
+    q = W.normal_f16(941, 0, (T, H, 576))
+    cache = W.normal_f16(941, 1, (n, 576), 0.5)
+    whole = run(gpu, ops, q, cache, T, H, n - T)
+    for t in range(T):
+        alone = run(gpu, ops, q[t:t + 1].copy(), cache, 1, H, n - T + t)
+        assert np.array_equal(alone[0], whole[t])
+    # more rows than a decode pass: one split size for the pass; still within tolerance of the oracle
+    T = 12
+    q = W.normal_f16(941, 2, (T, H, 576))
+    got = run(gpu, ops, q, cache, T, H, n - T)
+    assert_close(got, O.mla_gemm(q.astype(np.float32), cache.view(np.uint16), T, H, 512, 64, n - T, np.float32(SCALE)), "12 rows")
