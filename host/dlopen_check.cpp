@@ -23,7 +23,7 @@ static const char* kEngines[] = {
     "ns_mla_attend", "ns_mla_attend_sel", "ns_mla_attend_sel_q8", "ns_mla_cells", "ns_softmax_masked", "ns_to_f16", "ns_to_q8row", "ns_gather_q8_h",
     "ns_gather_h",
     // deepseek2
-    "ns_ds2_mla_decode",
+    "ns_ds2_mla_decode", "ns_ds2_rope", "ns_ds2_kv_store",
     // qwen35: the step before attention
     "ns_q35_qk_norm_rope", "ns_q35_qk_norm_rope_pos", "ns_q35_rope", "ns_b200_qkv_prepare",
     // qwen35 quantised caches

@@ -82,6 +82,16 @@ int ns_q35_qk_norm_rope_pos(ns_gpu* g, const float* src, int64_t ss, int64_t hs,
 int ns_q35_rope(ns_gpu* g, const float* src, int64_t ss, int64_t hs, float* dst, int64_t ds, int64_t T, int64_t H, int64_t D, int64_t n_rot, float theta,
                 int64_t p0);
 
+/* kernels/llm/deepseek2/ds2.h:20-31 - deepseek2's step before attention. ns_ds2_rope: YaRN rotary positions (ggml's
+ * rope_yarn, pairs of adjacent values) in place on x: T rows `row` floats apart, H heads `head` apart, the rotated part
+ * n_dims values from float `off` of each head, row t at position pos0 + t; `out` (nullable) also receives the rotated part.
+ * ns_ds2_kv_store: the latent cache's rows pos0 .. pos0+T-1 (fp16 [L + R] each) from kv [T][L + R] fp32 - the first L
+ * RMS-normed with w (eps), the last R rotated as ns_ds2_rope does at the row's position. */
+int ns_ds2_rope(ns_gpu* g, float* x, int64_t T, int64_t H, int64_t row, int64_t head, int64_t off, int64_t n_dims, int64_t pos0, float freq_base,
+                float freq_scale, float ext_factor, float mscale, float corr0, float corr1, float* out, int64_t out_row, int64_t out_head);
+int ns_ds2_kv_store(ns_gpu* g, const float* kv, const float* w, float eps, uint16_t* cache, int64_t T, int64_t L, int64_t R, int64_t pos0, float freq_base,
+                    float freq_scale, float ext_factor, float mscale, float corr0, float corr1);
+
 /* kernels/llm/nemotronh/nh.h:39-44 and silo/nhs.h:63-69 - the same kernels under the nemotronh engine's names (D 128) */
 int64_t ns_nh_attn_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0);
 int ns_nh_attn(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t cap,

@@ -4,6 +4,9 @@
 // with q leaving as the fp16 rows the native attention entry points read and k, v landing in the fp16 caches.
 #include "kernels.cuh"
 
+#include <algorithm>
+#include <cmath>
+
 namespace {
 
 // Row x [D] of one (row, head), a warp: RMS norm (w null: none), rotate-half over the first n_rot features (pair (i, i +
@@ -78,6 +81,80 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const float* __restric
     }
 }
 
+// deepseek2 (kernels/llm/deepseek2/ds2.cpp:15-34): cos and sin of pair i0 (of n_dims) at position p as ggml's rope cache
+// computes them - the angle by repeated products from the position, YaRN's ramp between the interpolated and the
+// extrapolated angle, mscale on both. Every product and sum is a single rounding, in the reference's order.
+__device__ __forceinline__ void yarn_cs(float p, int i0, float theta_scale, float freq_scale, float ext_factor, float mscale, float corr0, float corr1,
+                                        float& c, float& s) {
+    float theta_extrap = p;
+    for (int k = 0; k < i0 / 2; ++k) theta_extrap = __fmul_rn(theta_extrap, theta_scale);
+    const float theta_interp = __fmul_rn(freq_scale, theta_extrap);
+    float theta = theta_interp;
+    if (ext_factor != 0.0f) {
+        const float y = __fdiv_rn(__fsub_rn((float) (i0 / 2), corr0), fmaxf(0.001f, __fsub_rn(corr1, corr0)));
+        const float ramp_mix = __fmul_rn(__fsub_rn(1.0f, fminf(1.0f, fmaxf(0.0f, y))), ext_factor);
+        theta = __fadd_rn(__fmul_rn(theta_interp, __fsub_rn(1.0f, ramp_mix)), __fmul_rn(theta_extrap, ramp_mix));
+    }
+    float sn, cs;
+    sincosf(theta, &sn, &cs);
+    c = __fmul_rn(cs, mscale);
+    s = __fmul_rn(sn, mscale);
+}
+
+// ds2.cpp:58-83: adjacent pairs of the rotated part of each head, in place (and into `out`)
+__global__ void ds2_rope_kernel(float* __restrict__ x, int64_t T, int64_t H, int64_t row, int64_t head, int64_t off, int64_t n_dims, int64_t pos0,
+                                float theta_scale, float freq_scale, float ext_factor, float mscale, float corr0, float corr1, float* __restrict__ out,
+                                int64_t out_row, int64_t out_head) {
+    const int64_t pairs = n_dims / 2, total = T * H * pairs;
+    for (int64_t id = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; id < total; id += (int64_t) gridDim.x * blockDim.x) {
+        const int64_t i = id % pairs, h = (id / pairs) % H, t = id / (pairs * H);
+        const int i0 = (int) (2 * i);
+        float c, s;
+        yarn_cs((float) (pos0 + t), i0, theta_scale, freq_scale, ext_factor, mscale, corr0, corr1, c, s);
+        float* v = x + t * row + h * head + off + i0;
+        const float x0 = v[0], x1 = v[1];
+        const float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)), y1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+        v[0] = y0, v[1] = y1;
+        if (out) {
+            float* o = out + t * out_row + h * out_head + i0;
+            o[0] = y0, o[1] = y1;
+        }
+    }
+}
+
+// ds2.cpp:85-112: a block a token: the first L values RMS-normed with w, the last R rotated, into the fp16 cache row
+__global__ void __launch_bounds__(256) ds2_kv_store_kernel(const float* __restrict__ kv, const float* __restrict__ w, float eps, __half* __restrict__ cache,
+                                                           int64_t L, int64_t R, int64_t pos0, float theta_scale, float freq_scale, float ext_factor,
+                                                           float mscale, float corr0, float corr1) {
+    __shared__ float red[8];
+    const int64_t t = blockIdx.x;
+    const int lid = threadIdx.x;
+    const float* xr = kv + t * (L + R);
+    float ss = 0.f;
+    for (int64_t i = lid; i < L; i += 256) ss += xr[i] * xr[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((lid & 31) == 0) red[lid >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) tot += red[k];
+    const float inv = 1.f / sqrtf(tot / (float) L + eps);
+    __half* o = cache + (pos0 + t) * (L + R);
+    for (int64_t i = lid; i < L; i += 256) o[i] = __float2half_rn(xr[i] * inv * w[i]);
+    for (int64_t i = lid; i < R / 2; i += 256) {
+        const int i0 = (int) (2 * i);
+        float c, s;
+        yarn_cs((float) (pos0 + t), i0, theta_scale, freq_scale, ext_factor, mscale, corr0, corr1, c, s);
+        const float x0 = xr[L + i0], x1 = xr[L + i0 + 1];
+        o[L + i0] = __float2half_rn(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
+        o[L + i0 + 1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
+    }
+}
+
+// the reference's float power theta_scale = freq_base^(-2 / n_dims), as the correctly rounded float
+float theta_scale_of(float freq_base, int64_t n_dims) { return (float) pow((double) freq_base, (double) (-2.0f / (float) n_dims)); }
+
 int check_rope(const char* name, int64_t D, int64_t n_rot) {
     if (D < 2 || D % 16 != 0 || n_rot < 0 || n_rot > D || n_rot % 2) return ns_fail(std::string(name) + ": D a multiple of 16, n_rot even and at most D");
     return 0;
@@ -125,6 +202,34 @@ int ns_q35_rope(ns_gpu* g, const float* src, int64_t ss, int64_t hs, float* dst,
     norm_rope_kernel<<<(unsigned) ((T * H + 7) / 8), 256, 0, g->compute>>>(src, ss, hs, dst, ds, T, H, D, nullptr, 0.f, n_rot, theta, p0, nullptr, 0, 0, 0);
     return ns_launched(name);
     NS_CATCH("ns_q35_rope")
+}
+
+int ns_ds2_rope(ns_gpu* g, float* x, int64_t T, int64_t H, int64_t row, int64_t head, int64_t off, int64_t n_dims, int64_t pos0, float freq_base,
+                float freq_scale, float ext_factor, float mscale, float corr0, float corr1, float* out, int64_t out_row, int64_t out_head) {
+    NS_TRY
+    if (ns_enter(g, "ns_ds2_rope")) return -1;
+    if (T <= 0 || H <= 0 || n_dims <= 0) return 0;
+    if (n_dims % 2 != 0) return ns_fail("ns_ds2_rope: an even rotated width");
+    if (!x || pos0 < 0) return ns_fail("ns_ds2_rope: a null buffer");
+    const int64_t total = T * H * (n_dims / 2);
+    ds2_rope_kernel<<<(unsigned) std::min<int64_t>(4096, (total + 255) / 256), 256, 0, g->compute>>>(x, T, H, row, head, off, n_dims, pos0,
+                                                                                                    theta_scale_of(freq_base, n_dims), freq_scale, ext_factor,
+                                                                                                    mscale, corr0, corr1, out, out_row, out_head);
+    return ns_launched("ns_ds2_rope");
+    NS_CATCH("ns_ds2_rope")
+}
+
+int ns_ds2_kv_store(ns_gpu* g, const float* kv, const float* w, float eps, uint16_t* cache, int64_t T, int64_t L, int64_t R, int64_t pos0, float freq_base,
+                    float freq_scale, float ext_factor, float mscale, float corr0, float corr1) {
+    NS_TRY
+    if (ns_enter(g, "ns_ds2_kv_store")) return -1;
+    if (T <= 0) return 0;
+    if (R % 2 != 0 || R < 0 || L < 1) return ns_fail("ns_ds2_kv_store: an even rotated width");
+    if (!kv || !w || !cache || pos0 < 0) return ns_fail("ns_ds2_kv_store: a null buffer");
+    ds2_kv_store_kernel<<<(unsigned) T, 256, 0, g->compute>>>(kv, w, eps, (__half*) cache, L, R, pos0, theta_scale_of(freq_base, R > 0 ? R : 2), freq_scale,
+                                                             ext_factor, mscale, corr0, corr1);
+    return ns_launched("ns_ds2_kv_store");
+    NS_CATCH("ns_ds2_kv_store")
 }
 
 int ns_b200_qkv_prepare(ns_gpu* g, const float* q, int64_t qs, const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hq, int64_t Hkv,

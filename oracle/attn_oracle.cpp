@@ -823,6 +823,68 @@ void orc_qk_norm_rope(const float* src, int64_t ss, int64_t hs, float* dst, int6
         }
 }
 
+// ---- deepseek2: YaRN rotary positions and the latent cache's writer (kernels/llm/deepseek2/ds2.cpp:15-34,58-112) ----------
+// cos and sin of pair i0 (of n_dims) at position p as ggml's rope cache computes them: the angle by repeated products
+static void yarn_cs(float p, int i0, int n_dims, float freq_base, float freq_scale, float ext_factor, float mscale, float corr0, float corr1, float& c,
+                    float& s) {
+    const float theta_scale = std::pow(freq_base, -2.0f / (float) n_dims);
+    float theta_extrap = p;
+    for (int k = 0; k < i0 / 2; ++k) theta_extrap *= theta_scale;
+    const float theta_interp = freq_scale * theta_extrap;
+    float theta = theta_interp;
+    if (ext_factor != 0.0f) {
+        const float y = ((float) (i0 / 2) - corr0) / std::fmax(0.001f, corr1 - corr0);
+        const float ramp_mix = (1.0f - std::fmin(1.0f, std::fmax(0.0f, y))) * ext_factor;
+        theta = theta_interp * (1 - ramp_mix) + theta_extrap * ramp_mix;
+    }
+    c = std::cos(theta) * mscale;
+    s = std::sin(theta) * mscale;
+}
+
+// ns_ds2_rope: adjacent pairs of the n_dims values from float `off` of each head, in place; `out` (nullable) gets them too
+void orc_ds2_rope(float* x, int64_t T, int64_t H, int64_t row, int64_t head, int64_t off, int64_t n_dims, int64_t pos0, float freq_base, float freq_scale,
+                  float ext_factor, float mscale, float corr0, float corr1, float* out, int64_t out_row, int64_t out_head) {
+    for (int64_t t = 0; t < T; ++t)
+        for (int64_t h = 0; h < H; ++h)
+            for (int64_t i = 0; i < n_dims / 2; ++i) {
+                const int i0 = (int) (2 * i);
+                float c, s;
+                yarn_cs((float) (pos0 + t), i0, (int) n_dims, freq_base, freq_scale, ext_factor, mscale, corr0, corr1, c, s);
+                float* v = x + t * row + h * head + off + i0;
+                const float x0 = v[0], x1 = v[1];
+                const float y0 = x0 * c - x1 * s, y1 = x0 * s + x1 * c;
+                v[0] = y0, v[1] = y1;
+                if (out) {
+                    out[t * out_row + h * out_head + i0] = y0;
+                    out[t * out_row + h * out_head + i0 + 1] = y1;
+                }
+            }
+}
+
+// ns_ds2_kv_store: kv [T][L+R] fp32 -> cache rows pos0.. fp16: the first L RMS-normed with w (the squares summed as the
+// reference's 256 work-items do, item l taking i = l, l+256, ..; their sums added in order), the last R rotated
+void orc_ds2_kv_store(const float* kv, const float* w, float eps, uint16_t* cache, int64_t T, int64_t L, int64_t R, int64_t pos0, float freq_base,
+                      float freq_scale, float ext_factor, float mscale, float corr0, float corr1) {
+    for (int64_t t = 0; t < T; ++t) {
+        const float* xr = kv + t * (L + R);
+        float item[256] = {};
+        for (int64_t i = 0; i < L; ++i) item[i % 256] += xr[i] * xr[i];
+        float ss = 0.f;
+        for (int l = 0; l < 256; ++l) ss += item[l];
+        const float inv = 1.f / std::sqrt(ss / (float) L + eps);
+        uint16_t* o = cache + (pos0 + t) * (L + R);
+        for (int64_t i = 0; i < L; ++i) o[i] = f2h(xr[i] * inv * w[i]);
+        for (int64_t i = 0; i < R / 2; ++i) {
+            const int i0 = (int) (2 * i);
+            float c, s;
+            yarn_cs((float) (pos0 + t), i0, (int) R, freq_base, freq_scale, ext_factor, mscale, corr0, corr1, c, s);
+            const float x0 = xr[L + i0], x1 = xr[L + i0 + 1];
+            o[L + i0] = f2h(x0 * c - x1 * s);
+            o[L + i0 + 1] = f2h(x0 * s + x1 * c);
+        }
+    }
+}
+
 // ---- cache writers -----------------------------------------------------------------------------------------------
 
 // ns_q35_kv_store (kernels/llm/qwen35/q35.cpp:573-588): fp32 rows k [T][ks], v [T][vs] -> fp16 caches [Hkv][cap][D]

@@ -211,3 +211,18 @@ def qk_norm_rope(x, T, H, D, w, eps, n_rot, theta, p0=0, pos3=None, sections=(0,
                            i64(n_rot), C.c_float(theta), i64(p0), None if pos3 is None else pos3.ctypes.data_as(_pi), i64(sections[0]), i64(sections[1]),
                            i64(sections[2]))
     return y
+
+
+def ds2_rope(x, T, H, row, head, off, n_dims, pos0, freq_base, freq_scale, ext_factor, mscale, corr0, corr1, out=None, out_row=0, out_head=0):
+    """YaRN rotary positions in place on x (fp32, flat); `out` (fp32, flat) also receives the rotated part."""
+    f = C.c_float
+    lib().orc_ds2_rope(_f(x), i64(T), i64(H), i64(row), i64(head), i64(off), i64(n_dims), i64(pos0), f(freq_base), f(freq_scale), f(ext_factor), f(mscale),
+                       f(corr0), f(corr1), None if out is None else _f(out), i64(out_row), i64(out_head))
+    return x
+
+
+def ds2_kv_store(kv, w, eps, cache, T, L, R, pos0, freq_base, freq_scale, ext_factor, mscale, corr0, corr1):
+    """kv fp32 [T, L+R] into rows pos0.. of the latent cache (uint16 [n, L+R]): L RMS-normed with w, R rotated."""
+    f = C.c_float
+    lib().orc_ds2_kv_store(_f(kv), _f(w), f(eps), _h(cache), i64(T), i64(L), i64(R), i64(pos0), f(freq_base), f(freq_scale), f(ext_factor), f(mscale), f(corr0),
+                           f(corr1))

@@ -105,3 +105,50 @@ def test_fused_prepare_equals_the_three_calls(gpu):
     close(got_k, want_k, abs_tol=2e-3, rel_tol=2e-3)    # one fp16 rounding apart at most
     assert api.ns_b200_qkv_prepare(gpu.raw, dq.ptr, Hq * D, dk.ptr, Hkv * D, dv.ptr, Hkv * D, T, Hq, Hkv, D, dwq.ptr, dwk.ptr, eps, n_rot, theta, cap - 2, cap,
                                    q16.ptr, kc2.ptr, vc2.ptr) == -1
+
+
+YARN = dict(freq_base=np.float32(10000.0), freq_scale=np.float32(0.025), ext_factor=np.float32(1.0), mscale=np.float32(1.0 + 0.1 * np.log(40.0)),
+            corr0=np.float32(10.0), corr1=np.float32(23.0))
+
+
+@pytest.mark.parametrize("ext", [0.0, 1.0])
+def test_ds2_rope(gpu, ext):
+    """deepseek2's q rows [T][H][128 nope | 64 rope]: the rope part of each head turned in place and copied out."""
+    api = gpu.api
+    T, H, head, off, n_dims, pos0 = 4, 16, 192, 128, 64, 3000
+    x = W.rng(1340, 0).standard_normal((T, H * head), dtype=np.float32)
+    y = dict(YARN, ext_factor=np.float32(ext))
+    dx, dout = DevBuf.of(gpu, x), DevBuf(gpu, T * H * n_dims * 4)
+    check(api, api.ns_ds2_rope(gpu.raw, dx.ptr, T, H, H * head, head, off, n_dims, pos0, y["freq_base"], y["freq_scale"], y["ext_factor"], y["mscale"],
+                               y["corr0"], y["corr1"], dout.ptr, H * n_dims, n_dims), "ns_ds2_rope")
+    gpu.sync()
+    want, wout = x.copy().ravel(), np.zeros(T * H * n_dims, np.float32)
+    O.ds2_rope(want, T, H, H * head, head, off, n_dims, pos0, *[float(y[k]) for k in ("freq_base", "freq_scale", "ext_factor", "mscale", "corr0", "corr1")],
+               out=wout, out_row=H * n_dims, out_head=n_dims)
+    # the angle is built from identical single-rounded products on both sides; sin / cos differ by the libraries' last places
+    ulp = (pos0 + T) * 2.0 ** -23 * 5.0
+    close(dx.read(np.float32), want, abs_tol=1e-5 + ulp)
+    close(dout.read(np.float32), wout, abs_tol=1e-5 + ulp)
+    got = dx.read(np.float32).reshape(T, H, head)
+    assert np.array_equal(got[..., :off], x.reshape(T, H, head)[..., :off])      # the nope part is untouched
+
+
+def test_ds2_kv_store(gpu):
+    api = gpu.api
+    T, L, R, pos0, n = 6, 512, 64, 1021, 1100
+    kv = W.rng(1350, 0).standard_normal((T, L + R), dtype=np.float32)
+    w = (1.0 + 0.1 * W.rng(1350, 1).standard_normal(L, dtype=np.float32)).astype(np.float32)
+    before = W.rng(1350, 2).integers(0, 1 << 15, size=(n, L + R), dtype=np.uint16)
+    dkv, dw, dc = DevBuf.of(gpu, kv), DevBuf.of(gpu, w), DevBuf.of(gpu, before)
+    y = YARN
+    check(api, api.ns_ds2_kv_store(gpu.raw, dkv.ptr, dw.ptr, np.float32(1e-6), dc.ptr, T, L, R, pos0, y["freq_base"], y["freq_scale"], y["ext_factor"], y["mscale"],
+                                   y["corr0"], y["corr1"]), "ns_ds2_kv_store")
+    gpu.sync()
+    want = before.copy()
+    O.ds2_kv_store(kv, w, 1e-6, want, T, L, R, pos0, *[float(y[k]) for k in ("freq_base", "freq_scale", "ext_factor", "mscale", "corr0", "corr1")])
+    got = dc.read(np.uint16).reshape(n, L + R)
+    assert np.array_equal(got[:pos0], before[:pos0]) and np.array_equal(got[pos0 + T:], before[pos0 + T:])
+    # fp16 rows one rounding apart at most: the norm's sum order and sin / cos differ in the last place
+    close(got[pos0:pos0 + T].view(np.float16), want[pos0:pos0 + T].view(np.float16), abs_tol=2e-3, rel_tol=2e-3)
+    # a cache written here is what the decode kernel reads: the row count and layout of ns_ds2_mla_decode's cache
+    assert got.shape[1] == 576
