@@ -201,6 +201,15 @@ int ns_ds41_attend(ns_gpu* g, const float* q, const uint16_t* raw, int64_t R, co
 int ns_ds41_attend_xmx_supported(int64_t H, int64_t D);   /* 1 when D == 512 (the reference also wants H % 8 == 0) */
 int ns_ds41_attend_xmx(ns_gpu* g, const float* q, const uint16_t* raw, int64_t R, const uint16_t* comp, int64_t ratio, const int32_t* sel, int64_t K,
                        const float* sinks, float* out, int64_t T, int64_t H, int64_t pos0, int64_t window, float scale);
+/* kernels/llm/deepseek41/silo/ds41.h:76-79,90-93 (k41.cpp:616-662,776-808) - either side of that attention.
+ * ns_ds41_kv_post: a layer's window keys kv [T][D] (D <= 512) RMS-normed by w, the last rd values rotated at their
+ * positions (YaRN, adjacent pairs), then the model's E4M3 simulation in blocks of 32 (a power-of-two scale a block);
+ * kv keeps the simulated values and ring slot (pos0 + t) % R receives them as fp16.
+ * ns_ds41_att_post: the attention's output x [T][H][D]: each head's last rd values rotated back, then the same simulation. */
+int ns_ds41_kv_post(ns_gpu* g, float* kv, const float* w, int64_t T, int64_t D, float eps, int64_t rd, int64_t pos0, float freq_base, float freq_scale,
+                    float ext_factor, float mscale, float corr0, float corr1, uint16_t* ring, int64_t R);
+int ns_ds41_att_post(ns_gpu* g, float* x, int64_t T, int64_t H, int64_t D, int64_t rd, int64_t pos0, float freq_base, float freq_scale, float ext_factor,
+                     float mscale, float corr0, float corr1);
 /* silo/ds41.cpp:116-133 - the writers of those caches: T fp32 rows [T][D] into ring slots (pos0 + t) % R as fp16; n fp32
  * rows into rows j0.. of an fp16 matrix */
 int ns_ds41_ring_put(ns_gpu* g, const float* kv, uint16_t* ring, int64_t T, int64_t pos0, int64_t R, int64_t D);

@@ -152,6 +152,96 @@ __global__ void __launch_bounds__(256) ds2_kv_store_kernel(const float* __restri
     }
 }
 
+// deepseek41's E4M3 simulation (kernels/llm/deepseek41/silo/k41.cpp:16-35): a block of 32 values shares a power-of-two
+// scale from its largest magnitude; each value becomes the nearest E4M3FN value (ties to even) times the scale
+__device__ __forceinline__ float pow2_ceil(float x) {
+    int e;
+    const float m = frexpf(x, &e);
+    if (m == 0.5f) e -= 1;
+    return ldexpf(1.0f, e);
+}
+__device__ __forceinline__ float e4m3_round(float x) {
+    const float a = fabsf(x);
+    if (a == 0.f) return x;
+    int e;
+    frexpf(a, &e);
+    int be = e - 1;
+    if (be < -6) be = -6;
+    const float step = ldexpf(1.0f, be - 3);
+    float q = __fmul_rn(rintf(__fdiv_rn(a, step)), step);
+    q = fminf(q, 448.f);
+    return x < 0 ? -q : q;
+}
+// v of the 32 lanes of a warp = one block
+__device__ __forceinline__ float e4m3_sim_warp(float v) {
+    float amax = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float sc = pow2_ceil(__fdiv_rn(fmaxf(amax, 1e-4f), 448.f));
+    return __fmul_rn(e4m3_round(fminf(fmaxf(__fdiv_rn(v, sc), -448.f), 448.f)), sc);
+}
+
+// k41.cpp:616-662: a block a token, D <= 512
+__global__ void __launch_bounds__(256) ds41_kv_post_kernel(float* __restrict__ kv, const float* __restrict__ w, int64_t D, float eps, int64_t rd, int64_t pos0,
+                                                           float theta_scale, float freq_scale, float ext_factor, float mscale, float corr0, float corr1,
+                                                           __half* __restrict__ ring, int64_t R) {
+    __shared__ float y[512];
+    __shared__ float red[8];
+    const int64_t t = blockIdx.x;
+    const int lid = threadIdx.x;
+    float* xr = kv + t * D;
+    float s = 0.f;
+    for (int64_t c = lid; c < D; c += 256) s += xr[c] * xr[c];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((lid & 31) == 0) red[lid >> 5] = s;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) tot += red[k];
+    const float inv = 1.f / sqrtf(tot / (float) D + eps);
+    for (int64_t c = lid; c < D; c += 256) y[c] = xr[c] * inv * w[c];
+    __syncthreads();
+    const int64_t off = D - rd;
+    if (lid < rd / 2) {
+        const int i0 = 2 * lid;
+        float cs, sn;
+        yarn_cs((float) (pos0 + t), i0, theta_scale, freq_scale, ext_factor, mscale, corr0, corr1, cs, sn);
+        const float x0 = y[off + i0], x1 = y[off + i0 + 1];
+        y[off + i0] = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+        y[off + i0 + 1] = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
+    }
+    __syncthreads();
+    for (int64_t c0 = 0; c0 < D; c0 += 256) {
+        const int64_t c = c0 + lid;
+        const bool in = c < D;               // D is a multiple of 32: a warp is all in or all out
+        const float q = e4m3_sim_warp(in ? y[c] : 0.f);
+        if (in) {
+            xr[c] = q;
+            ring[((pos0 + t) % R) * D + c] = __float2half_rn(q);
+        }
+    }
+}
+
+// k41.cpp:776-808: x [T][H][D]; a warp a block of 32 consecutive values; a pair's other value from the neighbouring lane
+__global__ void __launch_bounds__(128) ds41_att_post_kernel(float* __restrict__ x, int64_t n, int64_t H, int64_t D, int64_t rd, int64_t pos0,
+                                                            float theta_scale, float freq_scale, float ext_factor, float mscale, float corr0, float corr1) {
+    const int64_t i = (int64_t) blockIdx.x * 128 + threadIdx.x;
+    const bool in = i < n;                   // n is a multiple of 32: a warp is all in or all out
+    float v = in ? x[i] : 0.f;
+    const int64_t c = i % D, off = D - rd;
+    const float o = __shfl_xor_sync(0xffffffffu, v, 1);
+    if (in && c >= off) {
+        const int i0 = (int) ((c - off) & ~int64_t(1));
+        float cs, sn;
+        yarn_cs((float) (pos0 + i / (H * D)), i0, theta_scale, freq_scale, ext_factor, mscale, corr0, corr1, cs, sn);
+        sn = -sn;
+        v = (c - off) % 2 == 0 ? __fsub_rn(__fmul_rn(v, cs), __fmul_rn(o, sn)) : __fadd_rn(__fmul_rn(o, sn), __fmul_rn(v, cs));
+    }
+    const float q = e4m3_sim_warp(v);
+    if (in) x[i] = q;
+}
+
 // the reference's float power theta_scale = freq_base^(-2 / n_dims), as the correctly rounded float
 float theta_scale_of(float freq_base, int64_t n_dims) { return (float) pow((double) freq_base, (double) (-2.0f / (float) n_dims)); }
 
@@ -230,6 +320,33 @@ int ns_ds2_kv_store(ns_gpu* g, const float* kv, const float* w, float eps, uint1
                                                              ext_factor, mscale, corr0, corr1);
     return ns_launched("ns_ds2_kv_store");
     NS_CATCH("ns_ds2_kv_store")
+}
+
+int ns_ds41_kv_post(ns_gpu* g, float* kv, const float* w, int64_t T, int64_t D, float eps, int64_t rd, int64_t pos0, float freq_base, float freq_scale,
+                    float ext_factor, float mscale, float corr0, float corr1, uint16_t* ring, int64_t R) {
+    NS_TRY
+    if (ns_enter(g, "ns_ds41_kv_post")) return -1;
+    if (T <= 0) return 0;
+    if (D < 32 || D % 32 != 0 || D > 512 || rd < 0 || rd % 2 != 0 || rd > D) return ns_fail("ns_ds41_kv_post: a row of at most 512 in blocks of 32");
+    if (!kv || !w || !ring || R < 1 || pos0 < 0) return ns_fail("ns_ds41_kv_post: a null buffer");
+    ds41_kv_post_kernel<<<(unsigned) T, 256, 0, g->compute>>>(kv, w, D, eps, rd, pos0, theta_scale_of(freq_base, rd > 0 ? rd : 2), freq_scale, ext_factor, mscale,
+                                                             corr0, corr1, (__half*) ring, R);
+    return ns_launched("ns_ds41_kv_post");
+    NS_CATCH("ns_ds41_kv_post")
+}
+
+int ns_ds41_att_post(ns_gpu* g, float* x, int64_t T, int64_t H, int64_t D, int64_t rd, int64_t pos0, float freq_base, float freq_scale, float ext_factor,
+                     float mscale, float corr0, float corr1) {
+    NS_TRY
+    if (ns_enter(g, "ns_ds41_att_post")) return -1;
+    if (T <= 0 || H <= 0) return 0;
+    if (D < 32 || D % 32 != 0 || rd < 0 || rd % 2 != 0 || rd > D) return ns_fail("ns_ds41_att_post: rows in blocks of 32");
+    if (!x || pos0 < 0) return ns_fail("ns_ds41_att_post: a null buffer");
+    const int64_t n = T * H * D;
+    ds41_att_post_kernel<<<(unsigned) ((n + 127) / 128), 128, 0, g->compute>>>(x, n, H, D, rd, pos0, theta_scale_of(freq_base, rd > 0 ? rd : 2), freq_scale,
+                                                                              ext_factor, mscale, corr0, corr1);
+    return ns_launched("ns_ds41_att_post");
+    NS_CATCH("ns_ds41_att_post")
 }
 
 int ns_b200_qkv_prepare(ns_gpu* g, const float* q, int64_t qs, const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hq, int64_t Hkv,

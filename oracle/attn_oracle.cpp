@@ -885,6 +885,82 @@ void orc_ds2_kv_store(const float* kv, const float* w, float eps, uint16_t* cach
     }
 }
 
+// ---- deepseek41: the window key's writer and the attention output's post step (kernels/llm/deepseek41/silo/k41.cpp:16-35,
+// 250-270,616-662,776-808): YaRN rotation of a row's last rd values, then the model's E4M3 simulation in blocks of 32
+static float pow2_ceil(float x) {   // 2^ceil(log2 x), x > 0
+    int e;
+    const float m = std::frexp(x, &e);
+    if (m == 0.5f) e -= 1;
+    return std::ldexp(1.0f, e);
+}
+static float e4m3_round(float x) {   // the nearest E4M3FN value (ties to even), |x| <= 448
+    const float a = std::fabs(x);
+    if (a == 0.f) return x;
+    int e;
+    std::frexp(a, &e);
+    int be = e - 1;
+    if (be < -6) be = -6;
+    const float step = std::ldexp(1.0f, be - 3);
+    float q = std::rint(a / step) * step;
+    q = std::fmin(q, 448.f);
+    return x < 0 ? -q : q;
+}
+static void e4m3_sim32(const float* v, float* out) {   // a block of 32: a power-of-two scale from its largest magnitude
+    float amax = 0.f;
+    for (int j = 0; j < 32; ++j) amax = std::fmax(amax, std::fabs(v[j]));
+    const float sc = pow2_ceil(std::fmax(amax, 1e-4f) / 448.f);
+    for (int j = 0; j < 32; ++j) out[j] = e4m3_round(std::fmin(std::fmax(v[j] / sc, -448.f), 448.f)) * sc;
+}
+
+// ns_ds41_kv_post: kv [T][D] RMS-normed by w (256 items' partial sums, added in order), the last rd values rotated at
+// pos0 + t, the E4M3 simulation in 32s; kv keeps the simulated values, the ring slot (pos0 + t) % R gets them as fp16
+void orc_ds41_kv_post(float* kv, const float* w, int64_t T, int64_t D, float eps, int64_t rd, int64_t pos0, float freq_base, float freq_scale,
+                      float ext_factor, float mscale, float corr0, float corr1, uint16_t* ring, int64_t R) {
+    for (int64_t t = 0; t < T; ++t) {
+        float* xr = kv + t * D;
+        float item[256] = {};
+        for (int64_t c = 0; c < D; ++c) item[c % 256] += xr[c] * xr[c];
+        float s = 0.f;
+        for (int l = 0; l < 256; ++l) s += item[l];
+        const float inv = 1.f / std::sqrt(s / (float) D + eps);
+        std::vector<float> y((size_t) D);
+        for (int64_t c = 0; c < D; ++c) y[c] = xr[c] * inv * w[c];
+        const int64_t off = D - rd;
+        for (int64_t i = 0; i < rd / 2; ++i) {
+            const int i0 = (int) (2 * i);
+            float cs, sn;
+            yarn_cs((float) (pos0 + t), i0, (int) rd, freq_base, freq_scale, ext_factor, mscale, corr0, corr1, cs, sn);
+            const float x0 = y[off + i0], x1 = y[off + i0 + 1];
+            y[off + i0] = x0 * cs - x1 * sn;
+            y[off + i0 + 1] = x0 * sn + x1 * cs;
+        }
+        for (int64_t c0 = 0; c0 < D; c0 += 32) {
+            e4m3_sim32(y.data() + c0, xr + c0);
+            for (int j = 0; j < 32; ++j) ring[((pos0 + t) % R) * D + c0 + j] = f2h(xr[c0 + j]);
+        }
+    }
+}
+
+// ns_ds41_att_post: x [T][H][D], each head's last rd values rotated back at the row's position, then the simulation in 32s
+void orc_ds41_att_post(float* x, int64_t T, int64_t H, int64_t D, int64_t rd, int64_t pos0, float freq_base, float freq_scale, float ext_factor,
+                       float mscale, float corr0, float corr1) {
+    const int64_t off = D - rd;
+    for (int64_t t = 0; t < T; ++t)
+        for (int64_t h = 0; h < H; ++h) {
+            float* xr = x + (t * H + h) * D;
+            std::vector<float> y(xr, xr + D);
+            for (int64_t c = off; c < D; ++c) {
+                const int i0 = (int) ((c - off) & ~int64_t(1));
+                float cs, sn;
+                yarn_cs((float) (pos0 + t), i0, (int) rd, freq_base, freq_scale, ext_factor, mscale, corr0, corr1, cs, sn);
+                sn = -sn;
+                const float v = xr[c], o = xr[c ^ 1];   // off is even (D a multiple of 32, rd even): the pair's other value
+                y[c] = (c - off) % 2 == 0 ? v * cs - o * sn : o * sn + v * cs;
+            }
+            for (int64_t c0 = 0; c0 < D; c0 += 32) e4m3_sim32(y.data() + c0, xr + c0);
+        }
+}
+
 // ---- cache writers -----------------------------------------------------------------------------------------------
 
 // ns_q35_kv_store (kernels/llm/qwen35/q35.cpp:573-588): fp32 rows k [T][ks], v [T][vs] -> fp16 caches [Hkv][cap][D]

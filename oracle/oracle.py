@@ -226,3 +226,15 @@ def ds2_kv_store(kv, w, eps, cache, T, L, R, pos0, freq_base, freq_scale, ext_fa
     f = C.c_float
     lib().orc_ds2_kv_store(_f(kv), _f(w), f(eps), _h(cache), i64(T), i64(L), i64(R), i64(pos0), f(freq_base), f(freq_scale), f(ext_factor), f(mscale), f(corr0),
                            f(corr1))
+
+
+def ds41_kv_post(kv, w, T, D, eps, rd, pos0, yarn, ring, R):
+    """In place on kv fp32 [T, D] and into ring (uint16 [R, D]); yarn = (freq_base, freq_scale, ext_factor, mscale, corr0, corr1)."""
+    f = C.c_float
+    lib().orc_ds41_kv_post(_f(kv), _f(w), i64(T), i64(D), f(eps), i64(rd), i64(pos0), *[f(v) for v in yarn], _h(ring), i64(R))
+
+
+def ds41_att_post(x, T, H, D, rd, pos0, yarn):
+    """In place on x fp32 [T, H, D]."""
+    f = C.c_float
+    lib().orc_ds41_att_post(_f(x), i64(T), i64(H), i64(D), i64(rd), i64(pos0), *[f(v) for v in yarn])

@@ -152,3 +152,54 @@ def test_ds2_kv_store(gpu):
     close(got[pos0:pos0 + T].view(np.float16), want[pos0:pos0 + T].view(np.float16), abs_tol=2e-3, rel_tol=2e-3)
     # a cache written here is what the decode kernel reads: the row count and layout of ns_ds2_mla_decode's cache
     assert got.shape[1] == 576
+
+
+def sim_close(got, want, what):
+    """Values on the E4M3 grid: equal but for the few whose input sat next to a rounding boundary (the norm's sum order and
+    sin / cos differ in the last place between the two sides), and those within one grid step (an eighth of the value)."""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    assert np.isfinite(got).all(), what
+    same = got == want
+    assert same.mean() > 0.995, f"{what}: {1 - same.mean():.4f} of the values differ"
+    assert np.all(np.abs(got - want) <= 0.13 * np.abs(want) + 2e-6), what
+
+
+def test_ds41_kv_post(gpu):
+    api = gpu.api
+    T, D, rd, pos0, R = 9, 512, 64, 250, 128      # slots 250 % 128 = 122 .. wrap past 127
+    kv = W.rng(1360, 0).standard_normal((T, D), dtype=np.float32)
+    w = (1.0 + 0.1 * W.rng(1360, 1).standard_normal(D, dtype=np.float32)).astype(np.float32)
+    before = W.rng(1360, 2).integers(0, 1 << 15, size=(R, D), dtype=np.uint16)
+    yarn = [float(YARN[k]) for k in ("freq_base", "freq_scale", "ext_factor", "mscale", "corr0", "corr1")]
+    dkv, dw, dr = DevBuf.of(gpu, kv), DevBuf.of(gpu, w), DevBuf.of(gpu, before)
+    check(api, api.ns_ds41_kv_post(gpu.raw, dkv.ptr, dw.ptr, T, D, np.float32(1e-6), rd, pos0, *[np.float32(v) for v in yarn], dr.ptr, R), "ns_ds41_kv_post")
+    gpu.sync()
+    want_kv, want_ring = kv.copy(), before.copy()
+    O.ds41_kv_post(want_kv, w, T, D, 1e-6, rd, pos0, yarn, want_ring, R)
+    got_kv, got_ring = dkv.read(np.float32).reshape(T, D), dr.read(np.uint16).reshape(R, D)
+    sim_close(got_kv, want_kv, "kv")
+    slots = [(pos0 + t) % R for t in range(T)]
+    others = [s for s in range(R) if s not in slots]
+    assert np.array_equal(got_ring[others], before[others])
+    assert np.array_equal(got_ring[slots].view(np.float16), got_kv.astype(np.float16))    # the ring holds what kv keeps
+    # every value is on the E4M3 grid of its block: value / scale has at most 4 significant bits
+    blocks = got_kv.reshape(T, D // 32, 32).astype(np.float64)
+    sc = 2.0 ** np.ceil(np.log2(np.maximum(np.abs(blocks).max(-1, keepdims=True), 1e-4) / 448.0))
+    m, _ = np.frexp(blocks / sc)
+    assert np.all(m * 16 == np.round(m * 16))
+
+
+def test_ds41_att_post(gpu):
+    api = gpu.api
+    T, H, D, rd, pos0 = 3, 8, 512, 64, 777
+    x = W.rng(1370, 0).standard_normal((T, H, D), dtype=np.float32)
+    yarn = [float(YARN[k]) for k in ("freq_base", "freq_scale", "ext_factor", "mscale", "corr0", "corr1")]
+    dx = DevBuf.of(gpu, x)
+    check(api, api.ns_ds41_att_post(gpu.raw, dx.ptr, T, H, D, rd, pos0, *[np.float32(v) for v in yarn]), "ns_ds41_att_post")
+    gpu.sync()
+    want = x.copy()
+    O.ds41_att_post(want, T, H, D, rd, pos0, yarn)
+    got = dx.read(np.float32).reshape(T, H, D)
+    sim_close(got, want, "att_post")
+    assert np.array_equal(got[..., :D - rd - 32], want[..., :D - rd - 32])      # blocks without rotated values: exact
+    assert api.ns_ds41_att_post(gpu.raw, dx.ptr, T, H, 500, rd, pos0, *[np.float32(v) for v in yarn]) == -1
