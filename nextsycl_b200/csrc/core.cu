@@ -137,6 +137,8 @@ int ns_gpu_open(int index, ns_gpu** out) {
         *g->status_host = 0;
         e = cudaHostGetDevicePointer((void**) &g->status_dev, g->status_host, 0);
     }
+    if (e == cudaSuccess) e = cudaMalloc((void**) &g->dec_sync, 2 * NS_DEC_SYNC_SLOTS * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(g->dec_sync, 0, 2 * NS_DEC_SYNC_SLOTS * sizeof(unsigned int));
     if (e != cudaSuccess) {
         delete g;
         return ns_cuda(e, "ns_gpu_open");
@@ -157,6 +159,7 @@ void ns_gpu_close(ns_gpu* g) {
         if (e) cudaEventDestroy(e);
     if (g->kept) cudaFree(g->kept);
     if (g->kept_kv) cudaFree(g->kept_kv);
+    if (g->dec_sync) cudaFree(g->dec_sync);
     if (g->status_host) cudaFreeHost(g->status_host);
     cudaStreamDestroy(g->compute);
     cudaStreamDestroy(g->lane[0]);
@@ -314,6 +317,7 @@ int ns_sync(ns_gpu* g) {
     if (g->status_host && *(volatile int*) g->status_host != 0) {
         const int code = *(volatile int*) g->status_host;
         *(volatile int*) g->status_host = 0;
+        if (g->dec_sync) cudaMemset(g->dec_sync, 0, 2 * NS_DEC_SYNC_SLOTS * sizeof(unsigned int));   // counters a failed step may have left set
         return ns_fail("ns_sync: a kernel gave up a bounded wait (code " + std::to_string(code) + "); its output is not valid");
     }
     return 0;

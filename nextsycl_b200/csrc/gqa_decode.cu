@@ -76,6 +76,10 @@ struct Params {
     int rank, nranks;
     float* const* mailboxes;   // device array [nranks]: each rank's mailbox as this GPU sees it (peer-mapped)
     long long epoch;
+    // completion counters (null: the merge waits for the whole split grid instead): sync[(b, key head)] counts the split
+    // kernel's CTAs of that pair that have written their partials, sync[NS_DEC_SYNC_SLOTS + ...] the merge blocks done with them
+    unsigned int* sync;
+    int* status;
 };
 
 // keys row t of a sequence sees: its causal length, bounded by what the cache slice holds
@@ -450,6 +454,51 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
         }
         __syncthreads();   // the merge buffer is stage memory again for the next pass
     }
+    if (p.sync) {
+        // this CTA's partials are written: one more of its (sequence, key head)'s splits is ready for the merge
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) atomicAdd(p.sync + (b * p.Hkv + hk), 1u);
+    }
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* ptr) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.u32 %0, [%1];\n" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+// A merge block's way in and out when the split kernel counts its CTAs. In: wait (bounded) until every split CTA of the
+// block's (sequence, key head) has written - the block was placed while the split kernel's last CTAs still ran, so pairs
+// that finished early are merged under that tail. Out: the last merge block of the pair returns both counters to zero.
+constexpr unsigned int MERGE_WAIT_LIMIT = 1u << 21;
+__device__ __forceinline__ void merge_enter(const Params& p, int b, int hk) {
+    if (threadIdx.x == 0) {
+        const unsigned int expect = (unsigned int) (p.ns_max * p.groups);
+        const unsigned int* c = p.sync + (b * p.Hkv + hk);
+        unsigned int i = 0;
+        while (ld_acquire_gpu(c) < expect) {
+            if (++i > MERGE_WAIT_LIMIT) {
+                if (p.status) {
+                    *(volatile int*) p.status = 801;
+                    __threadfence_system();
+                }
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+    __syncthreads();
+}
+__device__ __forceinline__ void merge_leave(const Params& p, int b, int hk) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int* done = p.sync + NS_DEC_SYNC_SLOTS + (b * p.Hkv + hk);
+        if (atomicAdd(done, 1u) + 1u == (unsigned int) (p.T * p.G)) {
+            p.sync[b * p.Hkv + hk] = 0u;
+            *done = 0u;
+            __threadfence();
+        }
+    }
 }
 
 // the splits of each (sequence, row, head) merged: attn.cpp:352-368's formula; rows with one split were written by
@@ -459,12 +508,17 @@ constexpr int MERGE_THREADS = 256;
 template <int D>
 __global__ void __launch_bounds__(MERGE_THREADS) gqa_merge_kernel(const Params p) {
     __shared__ float sm[lse::smem_floats<D, MERGE_THREADS>()];
-    pdl_wait();   // the split kernel's partials
     const int64_t rh = blockIdx.x;   // (b, t, hq)
     const int t = (int) ((rh / p.Hq) % p.T), b = (int) (rh / ((int64_t) p.Hq * p.T));
+    const int hk = (int) (rh % p.Hq) / p.G;
+    if (p.sync) merge_enter(p, b, hk);
+    else pdl_wait();   // the split kernel's partials
     const ns_b200_seq seq = p.seqs ? p.seqs[b] : p.one;
     const int nsr = (int) ns_dec_splits(row_keys(seq, t), p.Hkv);
-    if (nsr == 1) return;
+    if (nsr == 1) {
+        if (p.sync) merge_leave(p, b, hk);
+        return;
+    }
     float mx, L;
     const float2 a = lse::merge_row<D, MERGE_THREADS>(p.part + rh * p.ns_max * (D + 2), D + 2, nsr, mx, L, sm);
     if (threadIdx.x < D / 2) {
@@ -473,6 +527,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) gqa_merge_kernel(const Params p
         if (p.out_f32) *reinterpret_cast<float2*>((float*) p.out + rh * D + d) = make_float2(a.x * inv, a.y * inv);
         else *reinterpret_cast<__half2*>((__half*) p.out + rh * D + d) = __floats2half2_rn(a.x * inv, a.y * inv);
     }
+    if (p.sync) merge_leave(p, b, hk);
 }
 
 // KV split over several GPUs, this rank's side: its key splits merged into one partial (O, m, l) per (row, head), which
@@ -656,6 +711,9 @@ int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where) {
     p.nranks = a.nranks;
     p.mailboxes = a.mailboxes;
     p.epoch = a.epoch;
+    // the counted hand-over to the merge: one sequence-and-key-head pair a counter; the KV-split path keeps the plain dependent
+    p.sync = (!a.mailboxes && a.ns_max > 1 && a.B * a.Hkv <= NS_DEC_SYNC_SLOTS) ? g->dec_sync : nullptr;
+    p.status = g->status_dev;
     const int R = p.T * p.G;
     if (a.B > 65535) return ns_fail(std::string(where) + ": too many sequences for one launch");
     if (a.kt != 0) {

@@ -38,6 +38,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 template <int D, int THREADS>
 __host__ __device__ constexpr int smem_floats() { return MAX_SPLITS + 32 + THREADS * 2; }
 
+// The partials are read past L1 (ld.global.cg): a merge block may run while other split CTAs still write rows that share
+// a cache line with its own, and a line an earlier block of the same SM pulled into L1 would be stale.
 // One (row, head) by a block of THREADS threads: nsr (<= MAX_SPLITS) partial rows PS floats apart from pp. Every
 // thread gets mx and L; threads tid < D/2 get the merged pair (A[2 tid], A[2 tid + 1]).
 template <int D, int THREADS>
@@ -49,14 +51,14 @@ __device__ __forceinline__ float2 merge_row(const float* __restrict__ pp, int PS
     float2* acc_s = reinterpret_cast<float2*>(sm + MAX_SPLITS + 32);   // [THREADS]
     const int tid = threadIdx.x;
     float m_loc = -INFINITY;
-    for (int k = tid; k < nsr; k += THREADS) m_loc = fmaxf(m_loc, pp[(size_t) k * PS + D]);
+    for (int k = tid; k < nsr; k += THREADS) m_loc = fmaxf(m_loc, __ldcg(pp + (size_t) k * PS + D));
     mx = block_max<THREADS>(m_loc, red);
     float l_loc = 0.f;
     for (int k = tid; k < nsr; k += THREADS) {
-        const float mk = pp[(size_t) k * PS + D];
+        const float mk = __ldcg(pp + (size_t) k * PS + D);
         const float e = (mk == -INFINITY || mx == -INFINITY) ? 0.f : exp2f(mk - mx);
         w[k] = e;
-        l_loc += pp[(size_t) k * PS + D + 1] * e;
+        l_loc += __ldcg(pp + (size_t) k * PS + D + 1) * e;
     }
     L = block_sum<THREADS>(l_loc, red);   // its barriers also publish w
     const int g = tid / LANES, lane = tid % LANES;
@@ -66,7 +68,7 @@ __device__ __forceinline__ float2 merge_row(const float* __restrict__ pp, int PS
     for (; k + 7 * GROUPS < nsr; k += 8 * GROUPS) {
         float2 v[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const float2*>(pp + (size_t) (k + u * GROUPS) * PS + 2 * lane);
+        for (int u = 0; u < 8; ++u) v[u] = __ldcg(reinterpret_cast<const float2*>(pp + (size_t) (k + u * GROUPS) * PS + 2 * lane));
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const float e = w[k + u * GROUPS];
@@ -76,7 +78,7 @@ __device__ __forceinline__ float2 merge_row(const float* __restrict__ pp, int PS
     }
     for (; k < nsr; k += GROUPS) {
         const float e = w[k];
-        const float2 v = *reinterpret_cast<const float2*>(pp + (size_t) k * PS + 2 * lane);
+        const float2 v = __ldcg(reinterpret_cast<const float2*>(pp + (size_t) k * PS + 2 * lane));
         a.x += v.x * e;
         a.y += v.y * e;
     }

@@ -14,6 +14,9 @@
 // One opened GPU: a device ordinal, the compute stream every kernel and ordered copy goes to, two copy lanes
 // (ns_stream_copy), and the ticket ring. Buffers the library keeps for the process (query staging, counters) hang off
 // it and are freed by ns_gpu_close.
+// (sequence, key head) pairs the decode kernels' completion counters cover; larger batches use the plain dependent merge
+constexpr int NS_DEC_SYNC_SLOTS = 65536;
+
 struct ns_gpu {
     int dev = 0;
     int sms = 0;
@@ -24,6 +27,7 @@ struct ns_gpu {
     int64_t next_ticket = 0;
     void* kept = nullptr;                // grow-only staging buffer (compat entry points: fp32 -> fp16 queries)
     size_t kept_bytes = 0;
+    unsigned int* dec_sync = nullptr;    // 2 x NS_DEC_SYNC_SLOTS counters: decode CTAs done / merge blocks done, per (sequence, key head)
     void* kept_kv = nullptr;             // a second one: quantised caches expanded to fp16 for the tensor-core kernels
     size_t kept_kv_bytes = 0;
     int* status_host = nullptr;          // one word of mapped pinned memory: a kernel whose bounded wait gave up writes its code
