@@ -50,37 +50,49 @@ __device__ __forceinline__ float2 merge_row(const float* __restrict__ pp, int PS
     float* red = sm + MAX_SPLITS;        // [32]
     float2* acc_s = reinterpret_cast<float2*>(sm + MAX_SPLITS + 32);   // [THREADS]
     const int tid = threadIdx.x;
-    float m_loc = -INFINITY;
-    for (int k = tid; k < nsr; k += THREADS) m_loc = fmaxf(m_loc, __ldcg(pp + (size_t) k * PS + D));
+    const int g = tid / LANES, lane = tid % LANES;
+    // the first 8 splits' values are requested before the weights are known, and a thread's own split's (m, l) with them:
+    // one memory latency instead of three in a row
+    float2 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int k = g + u * GROUPS;
+        v[u] = k < nsr ? __ldcg(reinterpret_cast<const float2*>(pp + (size_t) k * PS + 2 * lane)) : make_float2(0.f, 0.f);
+    }
+    float2 ml0 = make_float2(-INFINITY, 0.f);
+    if (tid < nsr) ml0 = __ldcg(reinterpret_cast<const float2*>(pp + (size_t) tid * PS + D));
+    float m_loc = ml0.x;
+    for (int k = tid + THREADS; k < nsr; k += THREADS) m_loc = fmaxf(m_loc, __ldcg(pp + (size_t) k * PS + D));
     mx = block_max<THREADS>(m_loc, red);
     float l_loc = 0.f;
-    for (int k = tid; k < nsr; k += THREADS) {
+    if (tid < nsr) {
+        const float e = (ml0.x == -INFINITY || mx == -INFINITY) ? 0.f : exp2f(ml0.x - mx);
+        w[tid] = e;
+        l_loc = ml0.y * e;
+    }
+    for (int k = tid + THREADS; k < nsr; k += THREADS) {
         const float mk = __ldcg(pp + (size_t) k * PS + D);
         const float e = (mk == -INFINITY || mx == -INFINITY) ? 0.f : exp2f(mk - mx);
         w[k] = e;
         l_loc += __ldcg(pp + (size_t) k * PS + D + 1) * e;
     }
     L = block_sum<THREADS>(l_loc, red);   // its barriers also publish w
-    const int g = tid / LANES, lane = tid % LANES;
     float2 a = make_float2(0.f, 0.f);
-    // 8 splits' loads in flight at a time (an un-unrolled loop waits out every load's latency in turn)
-    int k = g;
-    for (; k + 7 * GROUPS < nsr; k += 8 * GROUPS) {
-        float2 v[8];
+    for (int k0 = 0; k0 < nsr; k0 += 8 * GROUPS) {
+        if (k0 > 0) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = __ldcg(reinterpret_cast<const float2*>(pp + (size_t) (k + u * GROUPS) * PS + 2 * lane));
+            for (int u = 0; u < 8; ++u) {
+                const int k = k0 + g + u * GROUPS;
+                v[u] = k < nsr ? __ldcg(reinterpret_cast<const float2*>(pp + (size_t) k * PS + 2 * lane)) : make_float2(0.f, 0.f);
+            }
+        }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            const float e = w[k + u * GROUPS];
+            const int k = k0 + g + u * GROUPS;
+            const float e = k < nsr ? w[k] : 0.f;
             a.x += v[u].x * e;
             a.y += v[u].y * e;
         }
-    }
-    for (; k < nsr; k += GROUPS) {
-        const float e = w[k];
-        const float2 v = __ldcg(reinterpret_cast<const float2*>(pp + (size_t) k * PS + 2 * lane));
-        a.x += v.x * e;
-        a.y += v.y * e;
     }
     if (GROUPS > 1) {
         acc_s[tid] = a;
