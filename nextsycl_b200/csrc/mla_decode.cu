@@ -50,11 +50,12 @@ struct Geo {
 // Cells a key split for a row that sees n cells, when `units` (head tiles x rows sharing the launch) such rows are to fill
 // `sms` SMs once with pairs of CTAs: whole tiles, at least two of them (a partial costs 2 KB a head).
 __host__ __device__ inline int64_t mla_split(int64_t n, int64_t units, int sms) {
-    int64_t want = sms / (2 * units);
+    // cell counts are below 2^31 (the callers check): 32-bit divisions, which the device does in a few instructions
+    uint32_t want = (uint32_t) sms / (2u * (uint32_t) units);
     if (want < 1) want = 1;
-    int64_t kb = (n + want - 1) / want;
+    uint32_t kb = ((uint32_t) n + want - 1) / want;
     kb = (kb + BN - 1) / BN * BN;
-    return kb < 2 * BN ? 2 * BN : kb;
+    return kb < 2 * BN ? 2 * BN : (int64_t) kb;
 }
 // Decode widths (at most 8 rows, as the reference's decode kernels): a row's split size comes from its own cells alone,
 // so a row of a verify pass sums exactly as the one-row pass at its position does
@@ -396,7 +397,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) mla_merge_kernel(const Params p
     pdl_wait();   // the split kernel's partials
     const int64_t n = p.counts ? (int64_t) p.counts[t] : p.pos0 + t + 1;
     const int64_t kb = p.per_row ? mla_split(n, p.units, p.sms) : p.kb;
-    const int nsr = (int) ((n + kb - 1) / kb);
+    const int nsr = (int) (((uint32_t) n + (uint32_t) kb - 1) / (uint32_t) kb);
     if (nsr <= 1) return;   // the whole block: the row's one split wrote the result itself
     const float* pp = p.part + row * p.ns * PS;
     const float* src = pp + blockIdx.y * DVH + lane * 4;
@@ -491,6 +492,7 @@ static void mla_layout(int64_t n, int64_t T, int64_t H, int sms, int& per_row, i
     per_row = T <= DECODE_ROWS ? 1 : 0;
     units = (int) (per_row ? head_tiles : head_tiles * T);
     kb = mla_split(n, units, sms);
+    if (T == 1) per_row = 0;   // one row: its own size is the pass's size, and the kernel need not work it out
     if (per_row) {
         // every row's own count is at most n: its splits number at most sms / (2 units), and at most n / 128 rounded up
         int64_t want = sms / (2 * units);
