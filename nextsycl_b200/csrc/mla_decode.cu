@@ -137,7 +137,12 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_c);
             mbar_expect_tx(smem_u32(q_full), QS_BYTES);
-            for (int c = 0; c < QS / 64; ++c) tma_load_3d(smem_u32(q_s + c * (BM * 128)), &tm_q, QT + c * 64, h0, t, smem_u32(q_full));
+            // every CTA of the grid reads the same Q: each starts at another chunk, so that at any instant the requests spread
+            // over more L2 lines than one chunk's
+            for (int cc = 0; cc < QS / 64; ++cc) {
+                const int c = (cc + split) % (QS / 64);
+                tma_load_3d(smem_u32(q_s + c * (BM * 128)), &tm_q, QT + c * 64, h0, t, smem_u32(q_full));
+            }
             bool ok = true;
             for (int j = 0; j < ntiles && ok; ++j) {
                 const int s = j % NSTAGE;
@@ -232,7 +237,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         {
             const uint4* src = reinterpret_cast<const uint4*>(p.q + ((int64_t) t * p.H + (head_live ? h0 + r : 0)) * CR);
 #pragma unroll
-            for (int c = 0; c < QT / 64; ++c) {
+            for (int cc = 0; cc < QT / 64; ++cc) {
+                const int c = (cc + split) & (QT / 64 - 1);   // as above: the CTAs start at different chunks
                 uint32_t w[32];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
