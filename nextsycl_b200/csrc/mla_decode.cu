@@ -259,13 +259,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             fence_after_sync();
             const uint32_t s_addr = tmem + lane_base + (uint32_t) (S_COL + (j & 1) * BN);
             float s[BN];
-#pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(s_addr + c * 32, v);
+            {
+                // both halves of the row requested before the one wait
+                uint32_t v0[32], v1[32];
+                tmem_ld32(s_addr, v0);
+                tmem_ld32(s_addr + 32, v1);
                 tmem_wait_ld();
 #pragma unroll
-                for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(v[e]);
+                for (int e = 0; e < 32; ++e) s[e] = __uint_as_float(v0[e]), s[32 + e] = __uint_as_float(v1[e]);
             }
             const int64_t c0 = jbeg + (int64_t) j * BN;
             if (c0 + BN > jend) {
