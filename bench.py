@@ -270,16 +270,20 @@ def wl_prefill(env, T, Hq, Hkv, D):
         hkv_r, hq_r = Hkv // w, Hq // w
     else:
         hkv_r, hq_r = 1, Hq // w
-    q = device_random_f16(env, T * hq_r * D * 2, 1)
-    k = device_random_f16(env, hkv_r * T * D * 2, 2)
-    v = device_random_f16(env, hkv_r * T * D * 2, 3)
-    out = DevBuf(env.gpu, T * hq_r * D * 2)
+    # input sets used in turn so that together they hold 300 MB (q, k, v and the output of a set are touched once a step)
+    set_bytes = 2 * T * hq_r * D * 2 + 2 * hkv_r * T * D * 2
+    rotate = int(os.environ.get("NS_BENCH_PREFILL_SETS", 0)) or max(2, -(-300_000_000 // set_bytes))
+    sets = [(device_random_f16(env, T * hq_r * D * 2, 1 + 3 * r), device_random_f16(env, hkv_r * T * D * 2, 2 + 3 * r),
+             device_random_f16(env, hkv_r * T * D * 2, 3 + 3 * r), DevBuf(env.gpu, T * hq_r * D * 2)) for r in range(rotate)]
+    i = [0]
 
     def step():
+        q, k, v, out = sets[i[0] % rotate]
+        i[0] += 1
         env.ops.gqa_prefill(0, q, hq_r * D, k, v, T, hq_r, hkv_r, D, T, 0, out)
     keys = T * (T + 1) // 2
     info = {"flops": 4 * keys * hq_r * D, "flops_total": 4 * keys * Hq * D, "bytes": 2 * T * hkv_r * D * 2, "bound": "tensor", "launches": 1,
-            "keep": (q, k, v, out)}
+            "keep": sets}
     return step, info
 
 
@@ -287,8 +291,10 @@ def wl_mla_decode(env, n):
     from nextsycl_b200 import DevBuf
     from nextsycl_b200 import workloads as W
     q = DevBuf.of(env.gpu, W.normal_f16(3, 0, (1, 128, 576)))
-    rotate = 3 if n * 1152 < 150e6 else 2
-    caches = [device_random_f16(env, n * 1152, 10 + r, 0.5) for r in range(rotate)]
+    # as many cache sets, used in turn, as hold 300 MB together: between two uses of a set more than twice the 126 MB L2 has gone by
+    rotate = max(2, -(-300_000_000 // (n * 1152)))
+    whole = device_random_f16(env, rotate * n * 1152, 10, 0.5)
+    caches = [whole.view(r * n * 1152, n * 1152) for r in range(rotate)]
     out = DevBuf(env.gpu, 128 * 512 * 4)
     sc = DevBuf(env.gpu, max(4, 4 * env.ops.mla_decode_scratch(1, 128, n - 1)))
     i = [0]
@@ -302,7 +308,7 @@ def wl_mla_decode(env, n):
     def step():
         graphs[i[0] % rotate].launch()
         i[0] += 1
-    info = {"bytes": 1152 * n, "flops": 278528 * n, "bound": "hbm+tensor", "launches": 2, "keep": (q, caches, out, sc, graphs)}
+    info = {"bytes": 1152 * n, "flops": 278528 * n, "bound": "hbm+tensor", "launches": 2, "keep": (q, whole, caches, out, sc, graphs)}
     return step, info
 
 
