@@ -171,3 +171,23 @@ def test_full_size_config_2(gpu, ops, B):
     got = out.read(np.float16).reshape(B, T, Hq * D).astype(np.float32)
     for b in range(B):
         assert_close(got[b], want[b], f"sequence {b}")
+
+
+def test_full_size_config_5(gpu, ops):
+    """BASELINE config 5 on one GPU at full size: 4 verify rows, 32 query / 4 key heads of 128, 262,144 cached tokens
+    (512 MiB of K and V). Each row against the oracle's flash numerics, and row t against the one-row pass at its position
+    (bit for bit: a row's splits come from its own length)."""
+    T, Hq, Hkv, D, kv = 4, 32, 4, 128, 262144
+    q, k, v, p0 = W.gqa_case(5, T, Hq, Hkv, D, kv)
+    dk, dv, dq = DevBuf.of(gpu, k), DevBuf.of(gpu, v), DevBuf.of(gpu, q)
+    out = DevBuf(gpu, T * Hq * D * 2)
+    sc = DevBuf(gpu, 4 * ops.gqa_decode_scratch(1, T, Hq, Hkv, D, kv))
+    ops.gqa_decode(dq, Hq * D, T * Hq * D, ops.seq_table([(dk, dv, kv, p0)]), 1, T, Hq, Hkv, D, kv, out, sc)
+    got = out.read(np.float16).reshape(T, Hq * D)
+    want = O.gqa_flash_decode(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, kv, p0)
+    assert_close(got.astype(np.float32), want, "config 5")
+    one = DevBuf(gpu, Hq * D * 2)
+    for t in (0, T - 1):
+        dq1 = DevBuf.of(gpu, q[t:t + 1].copy())
+        ops.gqa_decode(dq1, Hq * D, Hq * D, ops.seq_table([(dk, dv, kv, p0 + t)]), 1, 1, Hq, Hkv, D, kv, one, sc)
+        assert np.array_equal(one.read(np.float16).reshape(Hq * D).view(np.uint16), got[t].view(np.uint16)), f"row {t}"

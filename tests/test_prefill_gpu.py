@@ -155,3 +155,61 @@ def test_config_1_full_size(gpu, ops):
     got = out.read(np.float16).reshape(T, Hq * D).astype(np.float32)
     qf = q.astype(np.float32)
     assert_close(got, O.attn_tc(qf, k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, D, T, 0, np.float32(1 / np.sqrt(D)), kind=0), "config 1")
+
+
+def test_16k_rows_sampled(gpu, ops):
+    """The 16K target length (config 1's geometry): the whole pass on the GPU, rows sampled across the length - first and
+    last of a 128-row block, block edges, the last row - each against the oracle run for that row alone."""
+    T, Hq, Hkv, D = 16384, 16, 4, 128
+    q = W.normal_f16(1, 700, (T, Hq * D))
+    k = W.normal_f16(1, 701, (Hkv, T, D))
+    v = W.normal_f16(1, 702, (Hkv, T, D))
+    dq, dk, dv = DevBuf.of(gpu, q), DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+    out = DevBuf(gpu, T * Hq * D * 2)
+    ops.gqa_prefill(0, dq, Hq * D, dk, dv, T, Hq, Hkv, D, T, 0, out)
+    gpu.sync()
+    got = out.read(np.float16).reshape(T, Hq * D).astype(np.float32)
+    kb, vb = k.view(np.uint16), v.view(np.uint16)
+    for r in (0, 1, 127, 128, 4095, 4096, 9999, 16255, 16383):
+        want = O.attn_tc(q[r:r + 1].astype(np.float32), kb, vb, 1, Hq, Hkv, D, D, T, r, np.float32(1 / np.sqrt(D)), kind=0)
+        assert_close(got[r:r + 1], want, f"row {r}")
+
+
+def _repeat_on_device(gpu, blk, nbytes):
+    """A device buffer of nbytes holding the host block end to end (element i = blk[i mod len])."""
+    from nextsycl_b200.core import check
+    buf = DevBuf(gpu, nbytes)
+    buf.write(blk)
+    gpu.sync()
+    done = blk.nbytes
+    while done < nbytes:
+        n = min(done, nbytes - done)
+        check(gpu.api, gpu.api.ns_copy_dev(gpu.raw, buf.ptr + done, buf.ptr, n), "copy_dev")
+        done += n
+    gpu.sync()
+    return buf
+
+
+def test_config_4_full_size_sampled(gpu, ops):
+    """BASELINE config 4 at full size: 4,096 bf16 rows over 32,768 cached tokens, 128 heads of 192 / 128 (3 GB of K and V,
+    filled on the device from seeded 32 MiB blocks). (row, head) pairs sampled across the chunk, each against the oracle
+    run for that row and head alone on the same values."""
+    T, H, p0 = 4096, 128, 32768
+    n = p0 + T
+    L = 16 << 20
+    qblk, kblk, vblk = (W.normal_bf16_bits(4, 800 + i, (L,)) for i in range(3))
+    dq = _repeat_on_device(gpu, qblk, T * H * 192 * 2)
+    dk = _repeat_on_device(gpu, kblk, n * H * 192 * 2)
+    dv = _repeat_on_device(gpu, vblk, n * H * 128 * 2)
+    out = DevBuf(gpu, T * H * 128 * 2)
+    sc = 1 / np.sqrt(192.0)
+    ops.mla_prefill(dq, H * 192, dk, H * 192, dv, H * 128, T, H, p0, sc, out)
+    gpu.sync()
+    got = O.from_bf16_bits(out.read(np.uint16).reshape(T, H, 128))
+    j = np.arange(n, dtype=np.int64)[:, None]
+    for r, h in ((0, 0), (1, 77), (2047, 127), (2048, 5), (4095, 64)):
+        kh = kblk[(j * H * 192 + h * 192 + np.arange(192)[None, :]) % L][None]     # [1][n][192]
+        vh = vblk[(j * H * 128 + h * 128 + np.arange(128)[None, :]) % L][None]
+        qh = O.from_bf16_bits(qblk[(r * H * 192 + h * 192 + np.arange(192)) % L])[None]
+        want = O.attn_tc(np.ascontiguousarray(qh), np.ascontiguousarray(kh), np.ascontiguousarray(vh), 1, 1, 1, 192, 128, n, p0 + r, np.float32(sc), kind=1)
+        assert_close(got[r, h][None], want, f"row {r} head {h}", abs_tol=4e-3, rel_tol=2e-2)
