@@ -312,6 +312,37 @@ def wl_mla_decode(env, n):
     return step, info
 
 
+def wl_ds2_decode(env, n):
+    """The reference's whole deepseek2 decode op for one row (ns_ds2_mla_decode: absorb q through k_b, the latent attention of
+    config 3, out through v_b), fp32 rows in and out, 128 heads; cache sets in turn as in wl_mla_decode."""
+    from nextsycl_b200 import DevBuf
+    from nextsycl_b200 import workloads as W
+    from nextsycl_b200.core import check
+    api, gpu = env.gpu.api, env.gpu
+    H = 128
+    q = DevBuf.of(gpu, W.normal_f32(3, 40, (1, H * 192)))
+    kb = DevBuf.of(gpu, W.normal_f16(3, 41, (H, 512, 128), 0.09))
+    vb = DevBuf.of(gpu, W.normal_f16(3, 42, (H, 128, 512), 0.05))
+    rotate = max(2, -(-300_000_000 // (n * 1152)))
+    whole = device_random_f16(env, rotate * n * 1152, 43, 0.5)
+    caches = [whole.view(r * n * 1152, n * 1152) for r in range(rotate)]
+    out = DevBuf(gpu, H * 128 * 4)
+
+    def one(r):
+        check(api, api.ns_ds2_mla_decode(gpu.raw, q.ptr, kb.ptr, vb.ptr, caches[r].ptr, out.ptr, 1, H, n - 1, np.float32(1 / np.sqrt(192.0))), "ns_ds2_mla_decode")
+    one(0)
+    gpu.sync()
+    graphs = [gpu.record(lambda r=r: one(r)) for r in range(rotate)]
+    i = [0]
+
+    def step():
+        graphs[i[0] % rotate].launch()
+        i[0] += 1
+    info = {"bytes": 1152 * n + 2 * H * 512 * 128 * 2, "flops": 278528 * n + 4 * H * 512 * 128, "bound": "hbm+tensor", "launches": 4,
+            "keep": (q, kb, vb, whole, caches, out, graphs)}
+    return step, info
+
+
 def wl_mla_prefill(env, T=4096, p0=32768, H=128):
     """BASELINE config 4: 4,096 new rows over a 32,768-token cache, bf16, 192-wide keys / 128-wide values; the 128 heads
     sharded over the ranks (each rank its own heads' K and V; no exchange)."""
@@ -398,6 +429,8 @@ def measure(env, name, steps, warmup):
         step, info = wl_prefill(env, 16384, 16, 4, 128)
     elif name == "prefill_c1":
         step, info = wl_prefill(env, 2048, 16, 4, 128)
+    elif name == "ds2_decode_32k":
+        step, info = wl_ds2_decode(env, 32768)
     elif name.startswith("mla_decode_"):
         step, info = wl_mla_decode(env, {"4k": 4096, "32k": 32768, "131k": 131072}[name.split("_")[-1]])
     elif name == "mla_prefill_c4":
@@ -429,7 +462,7 @@ NCU_TRAFFIC = {"decode_c2": 1.073912e9 + 12.0e6, "mla_decode_32k": 37.96e6 + 0.0
 
 OTHERS_1GPU = [("prefill_16k", 10), ("prefill_c1", 50), ("decode_c2_b1", 50), ("decode_128k", 30), ("decode_c5", 30), ("decode_q35_f16", 30),
                ("decode_q35_q8", 30), ("decode_q35_q4", 30), ("mla_decode_4k", 50),
-               ("mla_decode_32k", 50), ("mla_decode_131k", 30), ("mla_prefill_c4", 3)]
+               ("mla_decode_32k", 50), ("mla_decode_131k", 30), ("ds2_decode_32k", 50), ("mla_prefill_c4", 3)]
 OTHERS_NGPU = [("decode_c5_split", 50), ("prefill_16k", 10), ("mla_prefill_c4", 3)]
 
 
@@ -445,6 +478,7 @@ def config_of(name, n):
         "decode_q35_q8": "the same over q8_0 caches (272-byte rows)",
         "decode_q35_q4": "the same over q4_0 caches (144-byte rows)",
         "decode_c5_split": "config 5 over the ranks: 262,144 cached tokens split by key ranges, partials pushed over NVLink and combined (strong scaling)",
+        "ds2_decode_32k": "ns_ds2_mla_decode, the reference's whole decode op around config 3's attention: fp32 q [128 x 192] absorbed through k_b, 32,768 cells, out through v_b",
         "mla_decode_4k": "config 3: absorbed MLA decode, 128 heads, 576-wide latent cache, 4,096 cells",
         "mla_decode_32k": "config 3, 32,768 cells",
         "mla_decode_131k": "config 3, 131,072 cells",
@@ -594,7 +628,7 @@ def run_ours(args):
                 "note": "per GPU; algorithmic bytes = 2*kv*Hkv*D*2 B a sequence x sequences a launch; duration = CUDA-event time of a step "
                         "(the split kernel plus its merge kernel)"}
         scaling = "strong" if "bytes_total" in info else "weak"
-    elif name.startswith("mla_decode"):
+    elif name.startswith("mla_decode") or name.startswith("ds2_decode"):
         value, unit = info["bytes"] / (ms * 1e-3) / 1e9, "GB/s"
         roof = {"bound": "hbm", "achieved": res["gbs_per_gpu"], "peak": float(pk["hbm_gbs"]), "unit": "GB/s", "frac": res["frac_of_hbm_peak"],
                 "traffic": NCU_TRAFFIC.get(name), "peak_source": pk["_source"], "note": "algorithmic bytes = 1,152 B a cell; flops 278,528 a cell",

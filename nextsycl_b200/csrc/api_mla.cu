@@ -7,50 +7,85 @@ namespace {
 constexpr int L = 512, R = 64, NOPE = 128, V = 128, KL = NOPE + R, CR = L + R;
 
 // q~[t,h,:512] = k_b[h] . q_nope[t,h] (k_b [H][512][128] fp16, fp32 sums: ds2.cpp:176-183), the rotated 64 copied
-// behind it; written as fp16 [T][H][576], the operand of the tensor-core stage. One warp a (t, h, 4 output rows).
+// behind it; written as fp16 [T][H][576], the operand of the tensor-core stage.
+// 8 warps a block, a warp a row of the weight matrix at a time, ROWS_IN_FLIGHT rows' loads issued before the first is used
+// (one row a time waits out a memory latency a row: 20 us for the 16.8 MB of k_b).
+constexpr int ABSORB_SPLIT = 4;        // blocks a (row, head): 128 of k_b's 512 rows each
 __global__ void __launch_bounds__(256) mla_absorb_kernel(const float* __restrict__ q, const __half* __restrict__ kb, __half* __restrict__ qa, int T, int H) {
     __shared__ float qn[NOPE];
-    const int th = blockIdx.x, h = th % H;
+    const int th = blockIdx.x / ABSORB_SPLIT, part = blockIdx.x % ABSORB_SPLIT, h = th % H;
     const float* qr = q + (int64_t) th * KL;
     if (threadIdx.x < NOPE) qn[threadIdx.x] = qr[threadIdx.x];
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     __half* dst = qa + (int64_t) th * CR;
-    for (int r = warp; r < L; r += 8) {
-        const uint2 w = reinterpret_cast<const uint2*>(kb + ((int64_t) h * L + r) * NOPE)[lane];   // 4 halves a lane
-        const __half2* hh = reinterpret_cast<const __half2*>(&w);
-        const float2 a = __half22float2(hh[0]), b = __half22float2(hh[1]);
-        float acc = a.x * qn[lane * 4] + a.y * qn[lane * 4 + 1] + b.x * qn[lane * 4 + 2] + b.y * qn[lane * 4 + 3];
+    const float q0 = qn[lane * 4], q1 = qn[lane * 4 + 1], q2 = qn[lane * 4 + 2], q3 = qn[lane * 4 + 3];
+    constexpr int ROWS = L / ABSORB_SPLIT / 8;   // rows a warp: 16
+    const int r0 = part * (L / ABSORB_SPLIT) + warp * ROWS;
+    uint2 w[ROWS];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (lane == 0) dst[r] = __float2half_rn(acc);
+    for (int i = 0; i < ROWS; ++i) w[i] = reinterpret_cast<const uint2*>(kb + ((int64_t) h * L + r0 + i) * NOPE)[lane];   // 4 halves a lane
+    float acc[ROWS];
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) {
+        const __half2* hh = reinterpret_cast<const __half2*>(&w[i]);
+        const float2 a = __half22float2(hh[0]), b = __half22float2(hh[1]);
+        acc[i] = a.x * q0 + a.y * q1 + b.x * q2 + b.y * q3;
     }
-    if (threadIdx.x < R) dst[L + threadIdx.x] = __float2half_rn(qr[NOPE + threadIdx.x]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+    if (lane < ROWS) {
+        float v = acc[0];
+#pragma unroll
+        for (int i = 1; i < ROWS; ++i) v = lane == i ? acc[i] : v;
+        dst[r0 + lane] = __float2half_rn(v);
+    }
+    if (part == 0 && threadIdx.x < R) dst[L + threadIdx.x] = __float2half_rn(qr[NOPE + threadIdx.x]);
 }
 
-// out[t,h,:128] = v_b[h] . u[t,h] (v_b [H][128][512] fp16, fp32 sums: ds2.cpp:237-255). One warp an output value.
+// out[t,h,:128] = v_b[h] . u[t,h] (v_b [H][128][512] fp16, fp32 sums: ds2.cpp:237-255). A warp 4 rows of v_b at a time.
+constexpr int UNABSORB_SPLIT = 4;      // blocks a (row, head): 32 of v_b's 128 rows each
 __global__ void __launch_bounds__(256) mla_unabsorb_kernel(const float* __restrict__ u, const __half* __restrict__ vb, float* __restrict__ out, int T, int H) {
     __shared__ float us[L];
-    const int th = blockIdx.x, h = th % H;
+    const int th = blockIdx.x / UNABSORB_SPLIT, part = blockIdx.x % UNABSORB_SPLIT, h = th % H;
     for (int i = threadIdx.x; i < L; i += blockDim.x) us[i] = u[(int64_t) th * L + i];
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int r = warp; r < V; r += 8) {
-        const uint4* vr = reinterpret_cast<const uint4*>(vb + ((int64_t) h * V + r) * L);
-        float acc = 0.f;
+    constexpr int ROWS = V / UNABSORB_SPLIT / 8;   // rows a warp: 4
+    const int r0 = part * (V / UNABSORB_SPLIT) + warp * ROWS;
+    uint4 w[ROWS][2];
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) {
+        const uint4* vr = reinterpret_cast<const uint4*>(vb + ((int64_t) h * V + r0 + i) * L);
+        w[i][0] = vr[lane];
+        w[i][1] = vr[32 + lane];
+    }
+    float acc[ROWS];
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) {
+        float a = 0.f;
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
-            const uint4 w = vr[k * 32 + lane];
-            const __half2* hh = reinterpret_cast<const __half2*>(&w);
+            const __half2* hh = reinterpret_cast<const __half2*>(&w[i][k]);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float2 x = __half22float2(hh[e]);
-                acc += x.x * us[(k * 32 + lane) * 8 + 2 * e] + x.y * us[(k * 32 + lane) * 8 + 2 * e + 1];
+                a += x.x * us[(k * 32 + lane) * 8 + 2 * e] + x.y * us[(k * 32 + lane) * 8 + 2 * e + 1];
             }
         }
+        acc[i] = a;
+    }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (lane == 0) out[(int64_t) th * V + r] = acc;
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+    if (lane < ROWS) {
+        float v = acc[0];
+#pragma unroll
+        for (int i = 1; i < ROWS; ++i) v = lane == i ? acc[i] : v;
+        out[(int64_t) th * V + r0 + lane] = v;
     }
 }
 
@@ -102,11 +137,11 @@ int ns_ds2_mla_decode(ns_gpu* g, const float* q, const uint16_t* kb, const uint1
     __half* qa = (__half*) kept;
     float* u = (float*) ((uint8_t*) kept + qa_bytes);
     float* part = part_floats ? (float*) ((uint8_t*) kept + qa_bytes + u_bytes) : nullptr;
-    mla_absorb_kernel<<<(unsigned) (T * H), 256, 0, g->compute>>>(q, (const __half*) kb, qa, (int) T, (int) H);
+    mla_absorb_kernel<<<(unsigned) (T * H * ABSORB_SPLIT), 256, 0, g->compute>>>(q, (const __half*) kb, qa, (int) T, (int) H);
     if (ns_launched(name)) return -1;
     MlaDecodeArgs a{qa, cache, u, part, T, H, pos0, scale, 64, pos0 + T, nullptr, 0, nullptr};
     if (ns_launch_mla_decode(g, a, name)) return -1;
-    mla_unabsorb_kernel<<<(unsigned) (T * H), 256, 0, g->compute>>>(u, (const __half*) vb, out, (int) T, (int) H);
+    mla_unabsorb_kernel<<<(unsigned) (T * H * UNABSORB_SPLIT), 256, 0, g->compute>>>(u, (const __half*) vb, out, (int) T, (int) H);
     return ns_launched(name);
     NS_CATCH("ns_ds2_mla_decode")
 }
