@@ -27,7 +27,7 @@ static const char* kEngines[] = {
     // qwen35: the step before attention
     "ns_q35_qk_norm_rope", "ns_q35_qk_norm_rope_pos", "ns_q35_rope", "ns_b200_qkv_prepare",
     // qwen35 quantised caches
-    "ns_q35_kv_store_q", "ns_q35_fwht32",
+    "ns_q35_kv_store_q", "ns_q35_fwht32", "ns_q35_attn_probs",
     // deepseek41
     "ns_ds41_attend", "ns_ds41_attend_xmx_supported", "ns_ds41_attend_xmx", "ns_ds41_ring_put", "ns_ds41_rows_f16", "ns_ds41_kv_post", "ns_ds41_att_post",
     // native

@@ -60,6 +60,12 @@ int ns_q35_attn_decode(ns_gpu* g, const float* q, int64_t qs, const void* kc, co
 int ns_q35_attn_decode_kv(ns_gpu* g, int kt, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv,
                           int64_t D, int64_t cap, int64_t p0, float* out, float* scratch);
 
+/* kernels/llm/qwen35/q35.h:34-38 - one query row q [Hq*D] over the first n keys of the key cache (its form kt: 0 fp16, 1 q8_0,
+ * 2 q4_0; heads of 256): each head's softmax weights (scale 1/sqrt(D)), per key their mean over the heads (mode 0) or their
+ * largest (mode 1), ADDED to out [n]; scratch [Hq][2] receives each head's (maximum, sum). */
+int ns_q35_attn_probs(ns_gpu* g, int kt, const float* q, const void* kc, int64_t Hq, int64_t Hkv, int64_t D, int64_t cap, int64_t n, int mode,
+                      float* scratch, float* out);
+
 /* kernels/llm/qwen35/q35.h:39-46 - the quantised caches' writer and rotation. ns_q35_kv_store_q: fp32 rows k, v
  * [T][Hkv*256] into caches [Hkv][cap][272 or 144 bytes] as q8_0 (kt 1: 256 int8 then 8 fp16 scales) or q4_0 (kt 2: 8
  * blocks of 16 bytes, value j low / j+16 high, then 8 fp16 scales; ggml's quantize_row_q4_0), q35.cpp:281-326.

@@ -961,6 +961,56 @@ void orc_ds41_att_post(float* x, int64_t T, int64_t H, int64_t D, int64_t rd, in
         }
 }
 
+// ---- ns_q35_attn_probs (kernels/llm/qwen35/q35.cpp:464-506): one query row's softmax weights over the cache's first n keys
+// (its form kt: 0 half, 1 q8_0, 2 q4_0; heads of 256; the value of a quantised element is float(q) * float(d), q35.cpp:19-25),
+// per key their mean over the heads (mode 0) or their largest (mode 1), added to out [n]; scratch [Hq][2] gets (max, sum)
+void orc_q35_attn_probs(int kt, const float* q, const uint8_t* kc, int64_t Hq, int64_t Hkv, int64_t cap, int64_t n, int mode, float* scratch, float* out) {
+    const int64_t D = 256, G = Hq / Hkv, rb = kt == 0 ? 512 : kt == 1 ? 272 : 144;
+    const float scale = 1.0f / std::sqrt((float) D);
+    std::vector<float> S((size_t) (Hq * n));
+#pragma omp parallel for collapse(2)
+    for (int64_t h = 0; h < Hq; ++h)
+        for (int64_t j = 0; j < n; ++j) {
+            const uint8_t* row = kc + ((h / G) * cap + j) * rb;
+            float acc = 0.0f;
+            for (int64_t i = 0; i < D; ++i) {
+                float v;
+                if (kt == 0) {
+                    uint16_t b;
+                    std::memcpy(&b, row + 2 * i, 2);
+                    v = h2f(b);
+                } else {
+                    const int blk = (int) (i / 32), e = (int) (i % 32);
+                    uint16_t db;
+                    std::memcpy(&db, row + (kt == 1 ? 256 : 128) + 2 * blk, 2);
+                    const float d = h2f(db);
+                    if (kt == 1) v = (float) (int8_t) row[i] * d;
+                    else {
+                        const uint8_t w = row[blk * 16 + (e & 15)];
+                        v = (float) ((int) (e < 16 ? w & 15 : w >> 4) - 8) * d;
+                    }
+                }
+                acc += q[h * D + i] * v;
+            }
+            S[h * n + j] = acc * scale;
+        }
+    for (int64_t h = 0; h < Hq; ++h) {
+        float m = NEG_INF, z = 0.0f;
+        for (int64_t j = 0; j < n; ++j) m = std::fmax(m, S[h * n + j]);
+        for (int64_t j = 0; j < n; ++j) z += std::exp(S[h * n + j] - m);
+        scratch[h * 2] = m;
+        scratch[h * 2 + 1] = z;
+    }
+    for (int64_t j = 0; j < n; ++j) {
+        float acc = 0.0f;
+        for (int64_t h = 0; h < Hq; ++h) {
+            const float p = std::exp(S[h * n + j] - scratch[h * 2]) / scratch[h * 2 + 1];
+            acc = mode == 1 ? std::fmax(acc, p) : acc + p / (float) Hq;
+        }
+        out[j] += acc;
+    }
+}
+
 // ---- cache writers -----------------------------------------------------------------------------------------------
 
 // ns_q35_kv_store (kernels/llm/qwen35/q35.cpp:573-588): fp32 rows k [T][ks], v [T][vs] -> fp16 caches [Hkv][cap][D]

@@ -238,3 +238,10 @@ def ds41_att_post(x, T, H, D, rd, pos0, yarn):
     """In place on x fp32 [T, H, D]."""
     f = C.c_float
     lib().orc_ds41_att_post(_f(x), i64(T), i64(H), i64(D), i64(rd), i64(pos0), *[f(v) for v in yarn])
+
+
+def q35_attn_probs(kt, q, kc, Hq, Hkv, cap, n, mode, out):
+    """One query row q fp32 [Hq*256] over the first n keys of a cache of form kt (uint8 view); adds to out fp32 [n]; -> scratch [Hq, 2]."""
+    scratch = np.zeros((Hq, 2), np.float32)
+    lib().orc_q35_attn_probs(C.c_int(kt), _f(q), kc.ctypes.data_as(C.POINTER(C.c_uint8)), i64(Hq), i64(Hkv), i64(cap), i64(n), C.c_int(mode), _f(scratch), _f(out))
+    return scratch

@@ -118,3 +118,33 @@ def test_rejects(gpu):
     assert api.ns_q35_kv_store_q(gpu.raw, 1, dk.ptr, 512, dv.ptr, 512, 2, 2, 256, 8, 7, c.ptr, c.ptr) == -1    # past the capacity
     q = DevBuf(gpu, 24 * 256 * 4)
     assert api.ns_q35_attn_decode_kv(gpu.raw, 5, q.ptr, 24 * 256, c.ptr, c.ptr, 1, 24, 4, 256, 8, 0, q.ptr, None) == -1
+
+
+@pytest.mark.parametrize("kt,mode", [(0, 0), (1, 0), (2, 1), (0, 1)])
+def test_attn_probs(gpu, kt, mode):
+    """ns_q35_attn_probs against the oracle (kernels/llm/qwen35/q35.cpp:464-506 restated): fp32 arithmetic, the sums in
+    another order: 1e-6 absolute on weights that sum to one, 1e-4 relative."""
+    api = gpu.api
+    Hq, Hkv, cap, n = 12, 2, 700, 650
+    rb = O.q_row_bytes(kt)
+    k, v = rows(1280 + kt, cap, Hkv)
+    if kt == 0:
+        kc = np.ascontiguousarray(k.reshape(cap, Hkv, 256).transpose(1, 0, 2)).astype(np.float16).view(np.uint8).reshape(Hkv, cap, 512)
+        dkc = DevBuf.of(gpu, kc)
+    else:
+        dkc, _ = store(gpu, kt, k, v, cap, Hkv, cap, 0)
+        kc = dkc.read(np.uint8).reshape(Hkv, cap, rb)
+    q = W.rng(1285, kt).standard_normal(Hq * 256, dtype=np.float32)
+    before = W.rng(1286, 0).random(n, dtype=np.float32)
+    dq, dout, dsc = DevBuf.of(gpu, q), DevBuf.of(gpu, before), DevBuf(gpu, Hq * 2 * 4)
+    check(api, api.ns_q35_attn_probs(gpu.raw, kt, dq.ptr, dkc.ptr, Hq, Hkv, 256, cap, n, mode, dsc.ptr, dout.ptr), "ns_q35_attn_probs")
+    gpu.sync()
+    want = before.copy()
+    wsc = O.q35_attn_probs(kt, q, kc, Hq, Hkv, cap, n, mode, want)
+    got = dout.read(np.float32)
+    assert np.all(np.abs(got - want) <= 1e-6 + 1e-4 * np.abs(want)), float(np.abs(got - want).max())
+    gsc = dsc.read(np.float32).reshape(Hq, 2)
+    assert np.allclose(gsc, wsc, rtol=1e-4, atol=1e-5)
+    if mode == 0:
+        assert abs(float((got - before).sum()) - 1.0) < 1e-3      # the heads' mean weights sum to one over the keys
+    assert api.ns_q35_attn_probs(gpu.raw, kt, dq.ptr, dkc.ptr, Hq, Hkv, 128, cap, n, mode, dsc.ptr, dout.ptr) == -1
