@@ -21,7 +21,7 @@ static const char* kEngines[] = {
     "ns_nhs_attn_decode_scratch", "ns_nhs_attn_decode",
     // glm5next
     "ns_mla_attend", "ns_mla_attend_sel", "ns_mla_attend_sel_q8", "ns_mla_cells", "ns_softmax_masked", "ns_to_f16", "ns_to_q8row", "ns_gather_q8_h",
-    "ns_gather_h",
+    "ns_gather_h", "ns_idx_pool", "ns_idx_score", "ns_topk",
     // deepseek2
     "ns_ds2_mla_decode", "ns_ds2_rope", "ns_ds2_kv_store",
     // qwen35: the step before attention

@@ -221,6 +221,18 @@ int ns_ds41_att_post(ns_gpu* g, float* x, int64_t T, int64_t H, int64_t D, int64
 int ns_ds41_ring_put(ns_gpu* g, const float* kv, uint16_t* ring, int64_t T, int64_t pos0, int64_t R, int64_t D);
 int ns_ds41_rows_f16(ns_gpu* g, const float* x, uint16_t* cache, int64_t n, int64_t j0, int64_t D);
 
+/* kernels/llm/glm5next/glm.h:47-55 - the DSA lightning indexer that produces `sel` for the selections above.
+ * ns_idx_pool: the pooled keys of the pools (4 consecutive tokens) completed by tokens [pos0, pos0+T): pooled[j][c] =
+ * sum_m softmax_m(ig_m[c] + ape[m][c]) ik_m[c] (ik, ig [T][D]; ape [4][D]; pooled indexed by pool); members before pos0
+ * come from ring [8][2D] (ik | ig at slot pos % 8), which then takes this pass's last tokens.
+ * ns_idx_score: from S [T*H][n] = iq . pooled^T (the caller's GEMM) and w [T][H]: score[r][j0+jj] = sum_h relu(S[r*H+h][jj])
+ * w[r][h] for the pools row r sees (j < (pos0+r+1)/4), else -inf; score rows ld floats apart.
+ * ns_topk: per row the K highest of score[r][0, n) into sel[r][0, K) in ascending position; ties at the K-th value go to the
+ * lowest positions; the same selection every run. With K > n the n positions fill the front of the row and the rest stays. */
+int ns_idx_pool(ns_gpu* g, float* ring, const float* ik, const float* ig, const float* ape, float* pooled, int64_t pos0, int64_t T, int64_t D);
+int ns_idx_score(ns_gpu* g, const float* S, const float* w, float* score, int64_t T, int64_t H, int64_t j0, int64_t n, int64_t ld, int64_t pos0);
+int ns_topk(ns_gpu* g, const float* score, int32_t* sel, int64_t T, int64_t n, int64_t ld, int64_t K);
+
 /* The middle stage alone (BASELINE's absorbed-MLA decode): q [T][H][576] fp16 = absorbed query (512) then rotated
  * part (64); cache [n][576] fp16; out u [T][H][512] fp32. scratch: ns_b200_mla_decode_scratch floats (it depends on
  * the GPU's SM count, hence the handle), 0 when the row is not split. */

@@ -93,6 +93,9 @@ ATTN = {
     "ns_ds41_att_post": (C.c_int, [vp, vp, i64, i64, i64, i64, i64, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float]),
     "ns_ds2_rope": (C.c_int, [vp, vp, i64, i64, i64, i64, i64, i64, i64, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, vp, i64, i64]),
     "ns_ds2_kv_store": (C.c_int, [vp, vp, vp, C.c_float, vp, i64, i64, i64, i64, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float]),
+    "ns_idx_pool": (C.c_int, [vp, vp, vp, vp, vp, vp, i64, i64, i64]),
+    "ns_idx_score": (C.c_int, [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64]),
+    "ns_topk": (C.c_int, [vp, vp, vp, i64, i64, i64, i64]),
     "ns_q35_attn_probs": (C.c_int, [vp, C.c_int, vp, vp, i64, i64, i64, i64, i64, C.c_int, vp, vp]),
     "ns_q35_kv_store_q": (C.c_int, [vp, C.c_int, vp, i64, vp, i64, i64, i64, i64, i64, i64, vp, vp]),
     "ns_q35_fwht32": (C.c_int, [vp, vp, i64, i64, i64]),

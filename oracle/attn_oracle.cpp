@@ -1011,6 +1011,75 @@ void orc_q35_attn_probs(int kt, const float* q, const uint8_t* kc, int64_t Hq, i
     }
 }
 
+// ---- glm5next's DSA indexer (kernels/llm/glm5next/glm.cpp:876-1015): pooled keys, pool scores, the K best pools a row ----
+// ns_idx_pool: the pools completed by tokens [pos0, pos0+T): pooled[j][c] = sum_m softmax_m(ig_m[c] + ape[m][c]) ik_m[c] over
+// the pool's 4 members (positions 4j+m); a member before pos0 comes from ring [8][2D] (ik | ig at slot pos % 8); then the
+// ring takes this pass's last (up to 8) tokens.
+void orc_idx_pool(float* ring, const float* ik, const float* ig, const float* ape, float* pooled, int64_t pos0, int64_t T, int64_t D) {
+    const int64_t j_lo = pos0 / 4, j_hi = (pos0 + T) / 4;
+    for (int64_t j = j_lo; j < j_hi; ++j)
+        for (int64_t c = 0; c < D; ++c) {
+            float lg[4], kv[4], mx = NEG_INF;
+            for (int m = 0; m < 4; ++m) {
+                const int64_t p = 4 * j + m;
+                const float* k = p >= pos0 ? ik + (p - pos0) * D : ring + (p % 8) * 2 * D;
+                const float* gg = p >= pos0 ? ig + (p - pos0) * D : ring + (p % 8) * 2 * D + D;
+                kv[m] = k[c];
+                lg[m] = gg[c] + ape[m * D + c];
+                mx = std::fmax(mx, lg[m]);
+            }
+            float sum = 0.f, acc = 0.f;
+            for (int m = 0; m < 4; ++m) {
+                const float e = std::exp(lg[m] - mx);
+                sum += e;
+                acc += e * kv[m];
+            }
+            pooled[j * D + c] = acc / sum;   // pooled is the whole pooled-key matrix: pool j's row
+        }
+    const int64_t first = std::max<int64_t>(pos0, pos0 + T - 8);
+    for (int64_t p = first; p < pos0 + T; ++p)
+        for (int64_t c = 0; c < D; ++c) {
+            ring[(p % 8) * 2 * D + c] = ik[(p - pos0) * D + c];
+            ring[(p % 8) * 2 * D + D + c] = ig[(p - pos0) * D + c];
+        }
+}
+
+// ns_idx_score: S [T*H][n] (heads as rows), w [T][H]: score[r][j0+jj] = sum_h relu(S[r*H+h][jj]) w[r][h] for the pools row r
+// sees (j < (pos0+r+1)/4), else -inf; score rows ld floats apart
+void orc_idx_score(const float* S, const float* w, float* score, int64_t T, int64_t H, int64_t j0, int64_t n, int64_t ld, int64_t pos0) {
+    for (int64_t r = 0; r < T; ++r)
+        for (int64_t jj = 0; jj < n; ++jj) {
+            const int64_t j = j0 + jj, nv = (pos0 + r + 1) / 4;
+            float sc = NEG_INF;
+            if (j < nv) {
+                sc = 0.f;
+                for (int64_t h = 0; h < H; ++h) sc += std::fmax(S[(r * H + h) * n + jj], 0.f) * w[r * H + h];
+            }
+            score[r * ld + j] = sc;
+        }
+}
+
+// ns_topk: per row the K highest of score[r][0, n) into sel[r][0, K) in ascending position; ties at the K-th value go to
+// the lowest positions. Order by the float's order-preserving key (sign bit flipped, negatives complemented).
+void orc_topk(const float* score, int32_t* sel, int64_t T, int64_t n, int64_t ld, int64_t K) {
+    for (int64_t r = 0; r < T; ++r) {
+        std::vector<std::pair<uint32_t, int32_t>> v((size_t) n);
+        for (int64_t j = 0; j < n; ++j) {
+            uint32_t u;
+            std::memcpy(&u, score + r * ld + j, 4);
+            v[j] = {(u & 0x80000000u) ? ~u : (u | 0x80000000u), (int32_t) j};
+        }
+        std::sort(v.begin(), v.end(), [](const std::pair<uint32_t, int32_t>& a, const std::pair<uint32_t, int32_t>& b) {
+            return a.first != b.first ? a.first > b.first : a.second < b.second;
+        });
+        const int64_t k = std::min(K, n);
+        std::vector<int32_t> pos((size_t) k);
+        for (int64_t i = 0; i < k; ++i) pos[i] = v[i].second;
+        std::sort(pos.begin(), pos.end());
+        for (int64_t i = 0; i < k; ++i) sel[r * K + i] = pos[i];
+    }
+}
+
 // ---- cache writers -----------------------------------------------------------------------------------------------
 
 // ns_q35_kv_store (kernels/llm/qwen35/q35.cpp:573-588): fp32 rows k [T][ks], v [T][vs] -> fp16 caches [Hkv][cap][D]

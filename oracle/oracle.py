@@ -245,3 +245,21 @@ def q35_attn_probs(kt, q, kc, Hq, Hkv, cap, n, mode, out):
     scratch = np.zeros((Hq, 2), np.float32)
     lib().orc_q35_attn_probs(C.c_int(kt), _f(q), kc.ctypes.data_as(C.POINTER(C.c_uint8)), i64(Hq), i64(Hkv), i64(cap), i64(n), C.c_int(mode), _f(scratch), _f(out))
     return scratch
+
+
+def idx_pool(ring, ik, ig, ape, pooled, pos0, T, D):
+    """Writes rows pos0//4 .. (pos0+T)//4 - 1 of pooled (fp32 [pools, D], indexed by pool); ring fp32 [8, 2D] is read, then updated."""
+    lib().orc_idx_pool(_f(ring), _f(ik), _f(ig), _f(ape), _f(pooled), i64(pos0), i64(T), i64(D))
+
+
+def idx_score(S, w, score, T, H, j0, n, pos0):
+    """S fp32 [T*H, n], w fp32 [T, H]; writes score[r, j0:j0+n] (score fp32 [T, ld])."""
+    lib().orc_idx_score(_f(S), _f(w), _f(score), i64(T), i64(H), i64(j0), i64(n), i64(score.shape[1]), i64(pos0))
+
+
+def topk(score, n, K):
+    """score fp32 [T, ld] -> sel int32 [T, K] (entries past min(K, n) stay -1)."""
+    T = score.shape[0]
+    sel = np.full((T, K), -1, np.int32)
+    lib().orc_topk(_f(score), sel.ctypes.data_as(_pi), i64(T), i64(n), i64(score.shape[1]), i64(K))
+    return sel

@@ -289,3 +289,17 @@ def test_qk_norm_rope_against_numpy():
     xr = x.reshape(T, H, D)
     assert np.allclose(r[..., :32] ** 2 + r[..., 32:64] ** 2, xr[..., :32] ** 2 + xr[..., 32:64] ** 2, rtol=1e-4, atol=1e-6)
     assert np.array_equal(r[..., n_rot:], xr[..., n_rot:])
+
+
+def test_topk_selection_rule():
+    """kernels/llm/glm5next/glm.cpp:940-1015: the K highest a row, ties at the K-th value to the lowest positions, ascending."""
+    rng = W.rng(978, 0)
+    T, n, ld, K = 3, 500, 512, 37
+    score = np.full((T, ld), 123.0, np.float32)
+    score[:, :n] = np.round(rng.standard_normal((T, n), dtype=np.float32) * 4) / 4      # many ties
+    score[1, :50] = -np.inf
+    sel = O.topk(score, n, K)
+    for r in range(T):
+        order = np.lexsort((np.arange(n), -score[r, :n].astype(np.float64)))           # value descending, then position ascending
+        assert np.array_equal(sel[r], np.sort(order[:K]))
+    assert np.array_equal(O.topk(score, 20, 30)[0, :20], np.arange(20)) and np.all(O.topk(score, 20, 30)[0, 20:] == -1)
