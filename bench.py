@@ -3,7 +3,7 @@
 
     python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME] [--no-others]
 
-Prints ONE JSON line (rank 0). The headline workload (`decode_c2`) is BASELINE config 2 as a batch: GQA decode of 8
+Prints ONE JSON line (rank 0). The headline workload (`decode_c2`) is benchmark configuration 2 as a batch: GQA decode of 8
 sequences, 1 new token each, 64 query / 8 key heads of 128, 32,768 cached fp16 tokens a sequence - 1 GiB of K+V per
 GPU, so every step's reads miss L2. A step is one pass of the path over the batch.
 
@@ -14,7 +14,7 @@ GPU, so every step's reads miss L2. A step is one pass of the path over the batc
   roofline   algorithmic bytes (or flops) a launch / CUDA-event time, against the measured peaks
   cpu_baseline, --impl reference: the CPU restatement of the reference kernel (oracle/) on the host cores; the
              reference's SYCL kernels themselves cannot be built without a oneAPI toolchain
-  others     the other BASELINE configurations, each timed the same way for a few steps: 16K and 2K causal prefill
+  others     the other benchmark configurations, each timed the same way for a few steps: 16K and 2K causal prefill
              (TFLOP/s), 128K and 256K decode, absorbed MLA decode at three context lengths, the bf16 MLA prefill chunk
              (heads sharded over the ranks)
 
@@ -344,7 +344,7 @@ def wl_ds2_decode(env, n):
 
 
 def wl_mla_prefill(env, T=4096, p0=32768, H=128):
-    """BASELINE config 4: 4,096 new rows over a 32,768-token cache, bf16, 192-wide keys / 128-wide values; the 128 heads
+    """benchmark configuration 4: 4,096 new rows over a 32,768-token cache, bf16, 192-wide keys / 128-wide values; the 128 heads
     sharded over the ranks (each rank its own heads' K and V; no exchange)."""
     from nextsycl_b200 import DevBuf
     h = H // env.world
@@ -363,7 +363,7 @@ def wl_mla_prefill(env, T=4096, p0=32768, H=128):
 
 
 def wl_kvsplit_decode(env, T=4, Hq=32, Hkv=4, D=128, kv=262144):
-    """BASELINE config 5 over the ranks: each rank holds kv/N keys of every key head; a step is this rank's split-KV
+    """benchmark configuration 5 over the ranks: each rank holds kv/N keys of every key head; a step is this rank's split-KV
     decode, the push of its partial into every rank's mailbox over NVLink, and the combine of what arrived in its own
     (strong scaling: the context is fixed, the ranks share it)."""
     from nextsycl_b200 import DevBuf

@@ -233,7 +233,7 @@ int ns_idx_pool(ns_gpu* g, float* ring, const float* ik, const float* ig, const 
 int ns_idx_score(ns_gpu* g, const float* S, const float* w, float* score, int64_t T, int64_t H, int64_t j0, int64_t n, int64_t ld, int64_t pos0);
 int ns_topk(ns_gpu* g, const float* score, int32_t* sel, int64_t T, int64_t n, int64_t ld, int64_t K);
 
-/* The middle stage alone (BASELINE's absorbed-MLA decode): q [T][H][576] fp16 = absorbed query (512) then rotated
+/* The middle stage alone (the benchmark's absorbed-MLA decode): q [T][H][576] fp16 = absorbed query (512) then rotated
  * part (64); cache [n][576] fp16; out u [T][H][512] fp32. scratch: ns_b200_mla_decode_scratch floats (it depends on
  * the GPU's SM count, hence the handle), 0 when the row is not split. */
 int64_t ns_b200_mla_decode_scratch(ns_gpu* g, int64_t T, int64_t H, int64_t pos0);

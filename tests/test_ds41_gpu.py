@@ -1,7 +1,7 @@
 """The deepseek41 engine's attention symbols on the GPU against the CPU oracle (kernels/llm/deepseek41/silo/attn.cpp and
 silo/ds41.cpp restated), through the C ABI. Tolerance: |got - want| <= 2e-3 + 1e-2 |want| against both of the reference's
 numerics (its XMX kernel's, which this path shares: fp16 q and weights, exp2; and its vector kernel's fp32 ones - the bar
-BASELINE sets for fp16 tensor-core numerics); bit-exact for the two cache writers."""
+the benchmark sets for fp16 tensor-core numerics); bit-exact for the two cache writers."""
 import numpy as np
 import pytest
 

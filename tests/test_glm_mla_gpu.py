@@ -1,6 +1,6 @@
 """The glm5next engine's MLA symbols on the GPU against the CPU oracle (kernels/llm/glm5next/glm.cpp restated), through
 the C ABI. Tolerance: |got - want| <= 2e-3 + 1e-2 |want| for the tensor-core path (fp16 q and weights, where the
-reference's vector kernels keep fp32: the bar BASELINE sets for fp16 tensor-core numerics); 1e-5 for the fp32 kernel;
+reference's vector kernels keep fp32: the bar the benchmark sets for fp16 tensor-core numerics); 1e-5 for the fp32 kernel;
 bit-exact for the integer / fp16 helper kernels."""
 import numpy as np
 import pytest

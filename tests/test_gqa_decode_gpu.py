@@ -1,6 +1,6 @@
 """GQA split-KV decode on the GPU against the CPU oracle, through the C ABI.
 
-Tolerance: BASELINE's bar for this path, max-abs 2e-3 / max-rel 1e-2 against the reference numerics (the oracle's
+Tolerance: the benchmark's bar for this path, max-abs 2e-3 / max-rel 1e-2 against the reference numerics (the oracle's
 flash mode restates kernels/llm/qwen35/silo/attn.cpp), checked as |got - want| <= 2e-3 + 1e-2 |want|; the fp64 exact
 result is reported beside it with the same bar."""
 import numpy as np
@@ -154,7 +154,7 @@ def test_native_batch_fp16(gpu, ops):
 
 @pytest.mark.parametrize("B", [1, 2])
 def test_full_size_config_2(gpu, ops, B):
-    """BASELINE config 2 at full size: 64 query heads, 8 key heads, 32,768 cached tokens, batch of sequences."""
+    """benchmark configuration 2 at full size: 64 query heads, 8 key heads, 32,768 cached tokens, batch of sequences."""
     T, Hq, Hkv, D, kv = 1, 64, 8, 128, 32768
     seqs, want, qs, keep = [], [], [], []
     for b in range(B):
@@ -174,7 +174,7 @@ def test_full_size_config_2(gpu, ops, B):
 
 
 def test_full_size_config_5(gpu, ops):
-    """BASELINE config 5 on one GPU at full size: 4 verify rows, 32 query / 4 key heads of 128, 262,144 cached tokens
+    """benchmark configuration 5 on one GPU at full size: 4 verify rows, 32 query / 4 key heads of 128, 262,144 cached tokens
     (512 MiB of K and V). Each row against the oracle's flash numerics, and row t against the one-row pass at its position
     (bit for bit: a row's splits come from its own length)."""
     T, Hq, Hkv, D, kv = 4, 32, 4, 128, 262144

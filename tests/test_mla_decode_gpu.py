@@ -1,6 +1,6 @@
 """Absorbed MLA decode on the tensor path against the CPU oracle, through the C ABI.
 
-Tolerance: BASELINE's bar, |got - want| <= 2e-3 + 1e-2 |want|, against the oracle's GEMM-form numerics (q and p rounded
+Tolerance: the benchmark's bar, |got - want| <= 2e-3 + 1e-2 |want|, against the oracle's GEMM-form numerics (q and p rounded
 to fp16: llm/deepseek2/src/engine.rs:1204-1224), against the fused kernel's fp32 numerics
 (kernels/llm/deepseek2/ds2.cpp:186-235) and against fp64."""
 import numpy as np
@@ -69,7 +69,7 @@ def test_ds2_whole_decode(gpu, ops):
 
 @pytest.mark.parametrize("n", [32768, 131072])
 def test_config_3_full_size(gpu, ops, n):
-    """BASELINE config 3: 128 heads, latent cache ~N(0, 0.5), query ~N(0, 1), scale 1/sqrt(192). All 128 heads run on the
+    """benchmark configuration 3: 128 heads, latent cache ~N(0, 0.5), query ~N(0, 1), scale 1/sqrt(192). All 128 heads run on the
     GPU; the oracle checks the first 8 (the heads are independent rows of the same tile)."""
     T, H = 1, 128
     q = W.normal_f16(3, 0, (T, H, 576))

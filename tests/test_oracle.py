@@ -11,7 +11,7 @@ from nextsycl_b200 import workloads as W
 from oracle import oracle as O
 
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "oracle_kat.npz")
-# BASELINE tolerance for fp16 tensor-core numerics against exact arithmetic
+# the benchmark's tolerance for fp16 tensor-core numerics against exact arithmetic
 ABS, REL = 2e-3, 1e-2
 
 

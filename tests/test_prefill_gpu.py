@@ -1,6 +1,6 @@
 """Causal flash prefill on the tensor path (tcgen05 / tensor memory / TMA) against the CPU oracle, through the C ABI.
 
-Tolerance: BASELINE's bar, |got - want| <= 2e-3 + 1e-2 |want| against the reference numerics (the oracle's flash mode
+Tolerance: the benchmark's bar, |got - want| <= 2e-3 + 1e-2 |want| against the reference numerics (the oracle's flash mode
 restates kernels/llm/qwen35/silo/attn.cpp) and against fp64. bf16 cases (no reference kernel exists for them) are
 held to the same bar against the oracle's bf16 tensor-core numerics and to 2e-2 absolute against fp64."""
 import numpy as np
@@ -123,7 +123,7 @@ def test_head_256(gpu, ops):
 
 
 def test_mla_prefill_bf16_192_128(gpu, ops):
-    """BASELINE config 4's geometry at a small size: 192-wide keys (128 nope + 64 rope), 128-wide values, bf16,
+    """benchmark configuration 4's geometry at a small size: 192-wide keys (128 nope + 64 rope), 128-wide values, bf16,
     token-major tensors, a chunk appended to cached tokens."""
     T, H, p0 = 130, 3, 100
     n = p0 + T
@@ -145,7 +145,7 @@ def test_mla_prefill_bf16_192_128(gpu, ops):
 
 
 def test_config_1_full_size(gpu, ops):
-    """BASELINE config 1: 2,048 rows, 16 query / 4 key heads of 128, fp16, from position 0."""
+    """benchmark configuration 1: 2,048 rows, 16 query / 4 key heads of 128, fp16, from position 0."""
     T, Hq, Hkv, D, p0 = 2048, 16, 4, 128, 0
     q, k, v, p0 = W.gqa_case(1, T, Hq, Hkv, D, T)
     dq, dk, dv = DevBuf.of(gpu, q), DevBuf.of(gpu, k), DevBuf.of(gpu, v)
@@ -191,7 +191,7 @@ def _repeat_on_device(gpu, blk, nbytes):
 
 
 def test_config_4_full_size_sampled(gpu, ops):
-    """BASELINE config 4 at full size: 4,096 bf16 rows over 32,768 cached tokens, 128 heads of 192 / 128 (3 GB of K and V,
+    """benchmark configuration 4 at full size: 4,096 bf16 rows over 32,768 cached tokens, 128 heads of 192 / 128 (3 GB of K and V,
     filled on the device from seeded 32 MiB blocks). (row, head) pairs sampled across the chunk, each against the oracle
     run for that row and head alone on the same values."""
     T, H, p0 = 4096, 128, 32768
