@@ -29,7 +29,8 @@ static const char* kEngines[] = {
     // qwen35 quantised caches
     "ns_q35_kv_store_q", "ns_q35_fwht32", "ns_q35_attn_probs",
     // deepseek41
-    "ns_ds41_attend", "ns_ds41_attend_xmx_supported", "ns_ds41_attend_xmx", "ns_ds41_ring_put", "ns_ds41_rows_f16", "ns_ds41_kv_post", "ns_ds41_att_post",
+    "ns_ds41_attend", "ns_ds41_attend_xmx_supported", "ns_ds41_attend_xmx", "ns_ds41_ring_put", "ns_ds41_rows_f16", "ns_ds41_kv_post", "ns_ds41_att_post", "ns_ds41_idx_score", "ns_ds41_block_max", "ns_ds41_idx_score_cand",
+    "ns_ds41_cand_pos", "ns_ds41_cand_mask",
     // native
     "ns_b200_gqa_decode_scratch", "ns_b200_gqa_decode", "ns_b200_gqa_prefill", "ns_b200_mla_prefill", "ns_b200_mla_decode_scratch", "ns_b200_mla_decode",
     "ns_b200_kvsplit_mailbox_bytes", "ns_b200_kvsplit_scratch", "ns_b200_kvsplit_decode", "ns_b200_kvsplit_combine", "ns_b200_ipc_export",

@@ -216,6 +216,21 @@ int ns_ds41_kv_post(ns_gpu* g, float* kv, const float* w, int64_t T, int64_t D, 
                     float ext_factor, float mscale, float corr0, float corr1, uint16_t* ring, int64_t R);
 int ns_ds41_att_post(ns_gpu* g, float* x, int64_t T, int64_t H, int64_t D, int64_t rd, int64_t pos0, float freq_base, float freq_scale, float ext_factor,
                      float mscale, float corr0, float corr1);
+/* kernels/llm/deepseek41/silo/ds41.h:57-71 (k41.cpp:96-250,352-483) - the indexer that produces `sel` for that attention.
+ * ns_ds41_idx_score: score [T][ld] = sum_h w[t][h] relu(q[t][h] . k_j) for j < min(n, (pos0+t+1)/ratio), -inf from there to
+ * ld; q [T][H][D] fp32, k fp16 [n][D]. With 32 heads of 128 and at least 8 keys the products run on the tensor cores in
+ * the numerics of the reference's XMX form (q rounded to fp16); otherwise the scalar form (fp32 q), as the reference picks.
+ * ns_ds41_block_max: bmax [T][ceil(n/bs)] = the best score of each bs positions; the block of a row's newest position +inf.
+ * ns_ds41_cand_mask: score to -inf outside the blocks cand [T][K] lists (mark: scratch of T x ceil(n/bs) bytes).
+ * ns_ds41_idx_score_cand: scores only over each row's candidate blocks (cand [T][K]: ids of blocks of 8 keys) into score
+ * [T][K*8], -inf where the row sees no key. ns_ds41_cand_pos: picks' compact indices selc [T][kp] back to positions. */
+int ns_ds41_idx_score(ns_gpu* g, const float* q, const float* w, const uint16_t* k, float* score, int64_t T, int64_t H, int64_t D, int64_t n, int64_t ld,
+                      int64_t pos0, int64_t ratio);
+int ns_ds41_block_max(ns_gpu* g, const float* score, float* bmax, int64_t T, int64_t n, int64_t ld, int64_t bs, int64_t pos0, int64_t ratio);
+int ns_ds41_idx_score_cand(ns_gpu* g, const float* q, const float* w, const uint16_t* k, const int32_t* cand, int64_t K, float* score, int64_t T, int64_t H,
+                           int64_t D, int64_t n, int64_t pos0, int64_t ratio);
+int ns_ds41_cand_pos(ns_gpu* g, const int32_t* selc, const int32_t* cand, int32_t* sel, int64_t T, int64_t K, int64_t kp, int64_t bs);
+int ns_ds41_cand_mask(ns_gpu* g, float* score, const int32_t* cand, uint8_t* mark, int64_t T, int64_t n, int64_t ld, int64_t K, int64_t bs);
 /* silo/ds41.cpp:116-133 - the writers of those caches: T fp32 rows [T][D] into ring slots (pos0 + t) % R as fp16; n fp32
  * rows into rows j0.. of an fp16 matrix */
 int ns_ds41_ring_put(ns_gpu* g, const float* kv, uint16_t* ring, int64_t T, int64_t pos0, int64_t R, int64_t D);

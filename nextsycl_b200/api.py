@@ -89,6 +89,11 @@ ATTN = {
     "ns_q35_qk_norm_rope_pos": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, i64, i64, vp, C.c_float, i64, C.c_float, vp, i64, i64, i64]),
     "ns_q35_rope": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, C.c_float, i64]),
     "ns_b200_qkv_prepare": (C.c_int, [vp, vp, i64, vp, i64, vp, i64, i64, i64, i64, i64, vp, vp, C.c_float, i64, C.c_float, i64, i64, vp, vp, vp]),
+    "ns_ds41_idx_score": (C.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64]),
+    "ns_ds41_block_max": (C.c_int, [vp, vp, vp, i64, i64, i64, i64, i64, i64]),
+    "ns_ds41_idx_score_cand": (C.c_int, [vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, i64, i64]),
+    "ns_ds41_cand_pos": (C.c_int, [vp, vp, vp, vp, i64, i64, i64, i64]),
+    "ns_ds41_cand_mask": (C.c_int, [vp, vp, vp, vp, i64, i64, i64, i64, i64]),
     "ns_ds41_kv_post": (C.c_int, [vp, vp, vp, i64, i64, C.c_float, i64, i64, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, vp, i64]),
     "ns_ds41_att_post": (C.c_int, [vp, vp, i64, i64, i64, i64, i64, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float]),
     "ns_ds2_rope": (C.c_int, [vp, vp, i64, i64, i64, i64, i64, i64, i64, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, vp, i64, i64]),

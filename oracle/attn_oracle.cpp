@@ -1080,6 +1080,80 @@ void orc_topk(const float* score, int32_t* sel, int64_t T, int64_t n, int64_t ld
     }
 }
 
+// ---- deepseek41's indexer (kernels/llm/deepseek41/silo/k41.cpp:96-250,352-483) ---------------------------------------
+// score of key j for row t: sum_h w[t][h] relu(q[t][h] . k_j); q fp32 [T][H][D] (half_q: rounded to fp16 first, as the XMX
+// form stages it, k41.cpp:125-128), k fp16 [n][D]
+static float ds41_key_score(const float* q, const float* w, const uint16_t* k, int64_t t, int64_t j, int64_t H, int64_t D, bool half_q) {
+    float s = 0.f;
+    for (int64_t h = 0; h < H; ++h) {
+        float acc = 0.f;
+        for (int64_t c = 0; c < D; ++c) {
+            const float qv = q[(t * H + h) * D + c];
+            acc += (half_q ? round_h(qv) : qv) * h2f(k[j * D + c]);
+        }
+        s += std::fmax(acc, 0.f) * w[t * H + h];
+    }
+    return s;
+}
+// ns_ds41_idx_score: score [T][ld], -inf from min(n, (pos0+t+1)/ratio) to ld
+void orc_ds41_idx_score(const float* q, const float* w, const uint16_t* k, float* score, int64_t T, int64_t H, int64_t D, int64_t n, int64_t ld,
+                        int64_t pos0, int64_t ratio, int half_q) {
+#pragma omp parallel for collapse(2)
+    for (int64_t t = 0; t < T; ++t)
+        for (int64_t j = 0; j < ld; ++j) {
+            const int64_t nv = std::min<int64_t>(n, (pos0 + t + 1) / ratio);
+            score[t * ld + j] = j < nv ? ds41_key_score(q, w, k, t, j, H, D, half_q != 0) : NEG_INF;
+        }
+}
+// ns_ds41_idx_score_cand: only over each row's candidate blocks of 8 keys (cand [T][K] block ids): score [T][K*8] compact
+void orc_ds41_idx_score_cand(const float* q, const float* w, const uint16_t* k, const int32_t* cand, int64_t K, float* score, int64_t T, int64_t H,
+                             int64_t D, int64_t n, int64_t pos0, int64_t ratio) {
+    const int64_t nb = (n + 7) / 8;
+    for (int64_t t = 0; t < T; ++t) {
+        const int64_t nv = std::min<int64_t>(n, (pos0 + t + 1) / ratio);
+        for (int64_t c = 0; c < K; ++c) {
+            const int64_t b = cand[t * K + c];
+            for (int e = 0; e < 8; ++e) {
+                const int64_t j = b * 8 + e;
+                score[t * K * 8 + c * 8 + e] = (b >= 0 && b < nb && j < nv) ? ds41_key_score(q, w, k, t, j, H, D, true) : NEG_INF;
+            }
+        }
+    }
+}
+// ns_ds41_block_max: bmax [T][nb] = the best score of each bs positions; the block of the row's newest position +inf
+void orc_ds41_block_max(const float* score, float* bmax, int64_t T, int64_t n, int64_t ld, int64_t bs, int64_t pos0, int64_t ratio) {
+    const int64_t nb = (n + bs - 1) / bs;
+    for (int64_t t = 0; t < T; ++t)
+        for (int64_t b = 0; b < nb; ++b) {
+            const int64_t lens = std::min<int64_t>(n, (pos0 + t + 1) / ratio);
+            float m = NEG_INF;
+            for (int64_t j = b * bs; j < std::min<int64_t>(n, (b + 1) * bs); ++j) m = std::fmax(m, score[t * ld + j]);
+            if (lens > 0 && b == (lens - 1) / bs) m = INFINITY;
+            bmax[t * nb + b] = m;
+        }
+}
+// ns_ds41_cand_mask: score to -inf outside the blocks cand [T][K] lists
+void orc_ds41_cand_mask(float* score, const int32_t* cand, int64_t T, int64_t n, int64_t ld, int64_t K, int64_t bs) {
+    const int64_t nb = (n + bs - 1) / bs;
+    for (int64_t t = 0; t < T; ++t) {
+        std::vector<uint8_t> mark((size_t) nb, 0);
+        for (int64_t c = 0; c < K; ++c) {
+            const int32_t b = cand[t * K + c];
+            if (b >= 0 && b < nb) mark[b] = 1;
+        }
+        for (int64_t j = 0; j < n; ++j)
+            if (!mark[j / bs]) score[t * ld + j] = NEG_INF;
+    }
+}
+// ns_ds41_cand_pos: the picks' compact indices (selc [T][kp], into the K*bs candidate keys) back to positions
+void orc_ds41_cand_pos(const int32_t* selc, const int32_t* cand, int32_t* sel, int64_t T, int64_t K, int64_t kp, int64_t bs) {
+    for (int64_t t = 0; t < T; ++t)
+        for (int64_t i = 0; i < kp; ++i) {
+            const int32_t c = selc[t * kp + i];
+            sel[t * kp + i] = cand[t * K + c / bs] * (int32_t) bs + c % bs;
+        }
+}
+
 // ---- cache writers -----------------------------------------------------------------------------------------------
 
 // ns_q35_kv_store (kernels/llm/qwen35/q35.cpp:573-588): fp32 rows k [T][ks], v [T][vs] -> fp16 caches [Hkv][cap][D]

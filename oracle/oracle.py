@@ -263,3 +263,35 @@ def topk(score, n, K):
     sel = np.full((T, K), -1, np.int32)
     lib().orc_topk(_f(score), sel.ctypes.data_as(_pi), i64(T), i64(n), i64(score.shape[1]), i64(K))
     return sel
+
+
+def ds41_idx_score(q, w, k, T, H, D, n, ld, pos0, ratio, half_q=True):
+    score = np.empty((T, ld), np.float32)
+    lib().orc_ds41_idx_score(_f(q), _f(w), _h(k), _f(score), i64(T), i64(H), i64(D), i64(n), i64(ld), i64(pos0), i64(ratio), C.c_int(1 if half_q else 0))
+    return score
+
+
+def ds41_idx_score_cand(q, w, k, cand, K, T, H, D, n, pos0, ratio):
+    score = np.empty((T, K * 8), np.float32)
+    lib().orc_ds41_idx_score_cand(_f(q), _f(w), _h(k), cand.ctypes.data_as(_pi), i64(K), _f(score), i64(T), i64(H), i64(D), i64(n), i64(pos0), i64(ratio))
+    return score
+
+
+def ds41_block_max(score, n, bs, pos0, ratio):
+    T, ld = score.shape
+    bmax = np.empty((T, -(-n // bs)), np.float32)
+    lib().orc_ds41_block_max(_f(score), _f(bmax), i64(T), i64(n), i64(ld), i64(bs), i64(pos0), i64(ratio))
+    return bmax
+
+
+def ds41_cand_mask(score, cand, n, bs):
+    T, ld = score.shape
+    lib().orc_ds41_cand_mask(_f(score), cand.ctypes.data_as(_pi), i64(T), i64(n), i64(ld), i64(cand.shape[1]), i64(bs))
+    return score
+
+
+def ds41_cand_pos(selc, cand, bs):
+    T, kp = selc.shape
+    sel = np.empty((T, kp), np.int32)
+    lib().orc_ds41_cand_pos(selc.ctypes.data_as(_pi), cand.ctypes.data_as(_pi), sel.ctypes.data_as(_pi), i64(T), i64(cand.shape[1]), i64(kp), i64(bs))
+    return sel

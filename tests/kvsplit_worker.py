@@ -1,0 +1,67 @@
+"""One rank of the multi-GPU KV-split parity check (launched by tests/test_kvsplit_multigpu.py under torch.distributed.run,
+one process a GPU). Every rank draws the same seeded context, keeps its own key range on its own GPU, runs a few steps
+of split decode + push + combine, and checks the combined rows against the CPU oracle's decode of the whole context and
+against every other rank's result (bit for bit: all ranks merge the same partials in the same order). Exits non-zero on a
+mismatch."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from nextsycl_b200 import DevBuf, Gpu  # noqa: E402
+from nextsycl_b200 import workloads as W  # noqa: E402
+from nextsycl_b200.dist import KvSplit, key_ranges  # noqa: E402
+from oracle import oracle as O  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", os.environ["RANK"]))
+    dist.init_process_group("gloo")
+    torch.cuda.set_device(local)
+    gpu = Gpu(local)
+    T, Hq, Hkv, D, kv = 4, 32, 4, 128, 20000 + 64 * 7          # ragged: the last rank's range is shorter
+    q, k, v, p0 = W.gqa_case(5, T, Hq, Hkv, D, kv)
+    base, count = key_ranges(kv, world)[rank]
+    kl = np.ascontiguousarray(k[:, base:base + count]) if count else np.zeros((Hkv, 1, D), np.float16)
+    vl = np.ascontiguousarray(v[:, base:base + count]) if count else np.zeros((Hkv, 1, D), np.float16)
+    dk, dv, dq = DevBuf.of(gpu, kl), DevBuf.of(gpu, vl), DevBuf.of(gpu, q)
+
+    def exchange(h):
+        out = [None] * world
+        dist.all_gather_object(out, h)
+        return out
+    grp = KvSplit(gpu, rank, world, T, Hq, D, exchange=exchange)
+    scratch = DevBuf(gpu, max(4, 4 * grp.scratch_floats(Hkv, count)))
+    out = DevBuf(gpu, T * Hq * D * 2)
+    want = O.gqa_flash_decode(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, kv, p0)
+    ok = True
+    for step in range(3):
+        out.fill(0xFF)
+        grp.decode(dq, Hq * D, dk, dv, Hkv, count, base, p0, scratch)
+        grp.combine(out)
+        gpu.sync()
+        got = out.read(np.float16).reshape(T, Hq * D)
+        d = np.abs(got.astype(np.float64) - want)
+        if not (np.isfinite(got).all() and np.all(d <= 2e-3 + 1e-2 * np.abs(want))):
+            print(f"rank {rank} step {step}: max abs {d.max():.3e} outside |d| <= 2e-3 + 1e-2 |want|", flush=True)
+            ok = False
+        every = [None] * world
+        dist.all_gather_object(every, got.view(np.uint16).tobytes())
+        if any(e != every[0] for e in every):
+            print(f"rank {rank} step {step}: the ranks' results differ", flush=True)
+            ok = False
+        dist.barrier()
+    grp.close()
+    flags = [None] * world
+    dist.all_gather_object(flags, ok)
+    dist.destroy_process_group()
+    if rank == 0:
+        print("kvsplit multi-gpu:", "ok" if all(flags) else "MISMATCH", f"({world} ranks, {kv} keys)", flush=True)
+    sys.exit(0 if all(flags) else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -78,3 +78,70 @@ def test_idx_pool_and_its_ring(gpu, pos0, T):
     lo, hi = pos0 // 4, (pos0 + T) // 4
     assert np.array_equal(got[:lo], before[:lo]) and np.array_equal(got[hi:], before[hi:])     # only the completed pools
     assert np.array_equal(dring.read(np.float32).reshape(8, 2 * D), wring)
+
+
+def _ds41_case(T, H, D, n, seed):
+    rng = W.rng(seed, 0)
+    q = rng.standard_normal((T, H, D), dtype=np.float32)
+    w = rng.standard_normal((T, H), dtype=np.float32)
+    k = O.to_f16_bits(rng.standard_normal((n, D), dtype=np.float32))
+    return q, w, k
+
+
+@pytest.mark.parametrize("T,H,D,n,ld,pos0,ratio", [(1, 32, 128, 5000, 5008, 19999, 4), (5, 32, 128, 777, 800, 3000, 4), (3, 32, 128, 8, 16, 30, 4),
+                                                   (2, 16, 64, 300, 300, 1100, 4), (2, 32, 128, 5, 8, 100, 4)])
+def test_ds41_idx_score(gpu, T, H, D, n, ld, pos0, ratio):
+    """32 heads of 128 with at least 8 keys: the tensor-core form (q rounded to fp16); else the scalar form (fp32 q). fp32
+    sums of 128 x 32 products in another order: 1e-3 absolute on scores of size ~100, 1e-4 relative."""
+    q, w, k = _ds41_case(T, H, D, n, 1430 + n)
+    dq, dw, dk, ds = DevBuf.of(gpu, q), DevBuf.of(gpu, w), DevBuf.of(gpu, k), DevBuf(gpu, T * ld * 4)
+    ds.fill(0x55)
+    check(gpu.api, gpu.api.ns_ds41_idx_score(gpu.raw, dq.ptr, dw.ptr, dk.ptr, ds.ptr, T, H, D, n, ld, pos0, ratio), "ns_ds41_idx_score")
+    gpu.sync()
+    got = ds.read(np.float32).reshape(T, ld)
+    tensor = H == 32 and D == 128 and n >= 8
+    want = O.ds41_idx_score(q, w, k, T, H, D, n, ld, pos0, ratio, half_q=tensor)
+    assert np.array_equal(np.isneginf(got), np.isneginf(want))
+    fin = np.isfinite(want)
+    assert np.all(np.abs(got[fin] - want[fin]) <= 1e-3 + 1e-4 * np.abs(want[fin])), float(np.abs(got[fin] - want[fin]).max())
+
+
+def test_ds41_candidate_steps(gpu):
+    api = gpu.api
+    T, H, D, n, pos0, ratio, bs, K = 3, 32, 128, 1003, 4100, 4, 8, 20
+    ld = 1008
+    q, w, k = _ds41_case(T, H, D, n, 1440)
+    score = O.ds41_idx_score(q, w, k, T, H, D, n, ld, pos0, ratio)
+    nb = -(-n // bs)
+    # block maxima: exact
+    dsc, dbm = DevBuf.of(gpu, score), DevBuf(gpu, T * nb * 4)
+    check(api, api.ns_ds41_block_max(gpu.raw, dsc.ptr, dbm.ptr, T, n, ld, bs, pos0, ratio), "ns_ds41_block_max")
+    gpu.sync()
+    assert np.array_equal(dbm.read(np.float32).reshape(T, nb), O.ds41_block_max(score, n, bs, pos0, ratio))
+    # the candidate blocks: the best K by block maximum (ns_topk), ascending - then the mask, exact
+    rng = W.rng(1441, 0)
+    cand = np.stack([np.sort(rng.choice(nb, size=K, replace=False)) for _ in range(T)]).astype(np.int32)
+    cand[1, 0] = -1                                   # an empty slot
+    cand[2, -1] = nb - 1                              # the last, partly filled block
+    dcand, dmark = DevBuf.of(gpu, cand), DevBuf(gpu, T * nb)
+    check(api, api.ns_ds41_cand_mask(gpu.raw, dsc.ptr, dcand.ptr, dmark.ptr, T, n, ld, K, bs), "ns_ds41_cand_mask")
+    gpu.sync()
+    assert np.array_equal(dsc.read(np.float32).reshape(T, ld), O.ds41_cand_mask(score.copy(), cand, n, bs))
+    # scores over the candidate blocks only
+    dq, dw, dk, dcs = DevBuf.of(gpu, q), DevBuf.of(gpu, w), DevBuf.of(gpu, k), DevBuf(gpu, T * K * 8 * 4)
+    check(api, api.ns_ds41_idx_score_cand(gpu.raw, dq.ptr, dw.ptr, dk.ptr, dcand.ptr, K, dcs.ptr, T, H, D, n, pos0, ratio), "ns_ds41_idx_score_cand")
+    gpu.sync()
+    got = dcs.read(np.float32).reshape(T, K * 8)
+    want = O.ds41_idx_score_cand(q, w, k, cand, K, T, H, D, n, pos0, ratio)
+    assert np.array_equal(np.isneginf(got), np.isneginf(want))
+    fin = np.isfinite(want)
+    assert np.all(np.abs(got[fin] - want[fin]) <= 1e-3 + 1e-4 * np.abs(want[fin]))
+    # compact picks back to positions: exact
+    kp = 33
+    selc = np.stack([np.sort(rng.choice(K * 8, size=kp, replace=False)) for _ in range(T)]).astype(np.int32)
+    cand_ok = np.where(cand < 0, 0, cand).astype(np.int32)
+    dselc, dc2, dsel = DevBuf.of(gpu, selc), DevBuf.of(gpu, cand_ok), DevBuf(gpu, T * kp * 4)
+    check(api, api.ns_ds41_cand_pos(gpu.raw, dselc.ptr, dc2.ptr, dsel.ptr, T, K, kp, bs), "ns_ds41_cand_pos")
+    gpu.sync()
+    assert np.array_equal(dsel.read(np.int32).reshape(T, kp), O.ds41_cand_pos(selc, cand_ok, bs))
+    assert api.ns_ds41_idx_score_cand(gpu.raw, dq.ptr, dw.ptr, dk.ptr, dcand.ptr, K, dcs.ptr, T, 16, D, n, pos0, ratio) == -1

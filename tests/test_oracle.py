@@ -303,3 +303,33 @@ def test_topk_selection_rule():
         order = np.lexsort((np.arange(n), -score[r, :n].astype(np.float64)))           # value descending, then position ascending
         assert np.array_equal(sel[r], np.sort(order[:K]))
     assert np.array_equal(O.topk(score, 20, 30)[0, :20], np.arange(20)) and np.all(O.topk(score, 20, 30)[0, 20:] == -1)
+
+
+def test_ds41_indexer_steps():
+    """kernels/llm/deepseek41/silo/k41.cpp:352-483 against numpy: scores, block maxima, candidate mask, compact picks."""
+    T, H, D, n, pos0, ratio = 3, 32, 128, 100, 390, 4          # rows see (391, 392, 393) // 4 = 97, 98, 98 keys
+    ld = 104
+    rng = W.rng(979, 0)
+    q = rng.standard_normal((T, H, D), dtype=np.float32)
+    w = rng.standard_normal((T, H), dtype=np.float32)
+    k = O.to_f16_bits(rng.standard_normal((n, D), dtype=np.float32))
+    kf = k.view(np.float16).astype(np.float64)
+    for half_q in (False, True):
+        qq = (q.astype(np.float16) if half_q else q).astype(np.float64)
+        want = np.einsum("th,thj->tj", w.astype(np.float64), np.maximum(np.einsum("thd,jd->thj", qq, kf), 0.0))
+        got = O.ds41_idx_score(q, w, k, T, H, D, n, ld, pos0, ratio, half_q)
+        for t in range(T):
+            nv = min(n, (pos0 + t + 1) // ratio)
+            assert np.allclose(got[t, :nv], want[t, :nv], rtol=1e-4, atol=1e-3) and np.all(np.isneginf(got[t, nv:]))
+    score = O.ds41_idx_score(q, w, k, T, H, D, n, ld, pos0, ratio)
+    bmax = O.ds41_block_max(score, n, 8, pos0, ratio)
+    assert bmax.shape == (T, 13) and np.isposinf(bmax[0, 96 // 8]) and np.isposinf(bmax[1, 97 // 8])
+    assert bmax[0, 3] == score[0, 24:32].max()
+    cand = np.array([[0, 5, 12, -1], [1, 2, 3, 40], [12, 11, 10, 9]], np.int32)
+    masked = O.ds41_cand_mask(score.copy(), cand, n, 8)
+    assert np.array_equal(masked[0, 40:48], score[0, 40:48]) and np.all(np.isneginf(masked[0, 8:40]))
+    sc = O.ds41_idx_score_cand(q, w, k, cand, 4, T, H, D, n, pos0, ratio)
+    assert np.array_equal(sc[0, 8:16], score[0, 40:48]) and np.all(np.isneginf(sc[0, 24:32])) and np.all(np.isneginf(sc[1, 24:32]))
+    selc = np.array([[0, 9, 17], [8, 1, 2], [31, 0, 7]], np.int32)
+    sel = O.ds41_cand_pos(selc, cand, 8)
+    assert np.array_equal(sel[0], [0, 41, 97]) and np.array_equal(sel[2], [9 * 8 + 7, 96, 103])
