@@ -12,6 +12,10 @@
 // operand. Warps 0-3 are the softmax: thread r owns row r (= tensor-memory lane r), so row max and sum need no
 // shuffles; it reads its S row, writes P back as packed 16-bit pairs, and rescales its O row only when the running
 // maximum grew by more than 2^8 (the final 1/l uses the same reference maximum, so the result is unchanged).
+// With NG = 2 there are two softmax groups (warps 0-3 and 4-7): group g owns keys [g BN/2, (g+1) BN/2) of every tile
+// with its own running maximum, sum and O accumulator in tensor memory (O_g += P_g V_g), so the groups never exchange
+// anything inside the loop and two warps a scheduler share the exponentials; the epilogue adds the two accumulators
+// under a common maximum. (The 256-wide instance keeps one group: two accumulators of 256 columns do not fit.)
 // Every mbarrier wait is bounded; on a timeout the CTA records a status code and runs to its teardown.
 #include "kernels.cuh"
 #include "tc05.cuh"
@@ -24,8 +28,7 @@ namespace {
 using namespace tc05;
 
 constexpr int BM = 128;           // query rows a CTA
-constexpr int SOFTMAX_THREADS = 128;
-constexpr int THREADS = 192;      // 4 softmax warps, 1 TMA warp, 1 MMA warp
+constexpr int SOFTMAX_THREADS = 128;   // a softmax group: thread r owns query row r
 constexpr float RESCALE_LOG2 = 8.0f;
 
 struct Params {
@@ -43,20 +46,28 @@ struct Smem {
     static constexpr int K_BYTES = BN * DQK * 2;
     static constexpr int V_BYTES = BN * DV * 2;
     static constexpr int STAGE = K_BYTES + V_BYTES;
-    static constexpr int BARS = 1024;   // mbarriers, the tensor-memory base slot, the abort flag
+    static constexpr int BARS = 256;    // mbarriers, the tensor-memory base slot, the flags
     static constexpr int TOTAL = 1024 /* alignment slack */ + Q_BYTES + NSTAGE * STAGE + BARS;
 };
 
-template <int DQK, int DV, int BN, int NSTAGE, int BF16>
-__global__ void __launch_bounds__(THREADS, 1)
+__device__ __forceinline__ void named_bar_sync(int id, int threads) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory"); }
+
+template <int DQK, int DV, int BN, int NSTAGE, int BF16, int NG>
+__global__ void __launch_bounds__(SOFTMAX_THREADS * (NG + 1), 1)
 flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                      const Params p) {
     using L = Smem<DQK, DV, BN, NSTAGE>;
     constexpr int S_COLS = BN;                   // fp32 columns of one S buffer
-    constexpr int O_COL = 2 * S_COLS;            // O after the two S buffers
-    constexpr int TMEM_COLS = (O_COL + DV) <= 256 ? 256 : 512;
-    static_assert(O_COL + DV <= 512, "tensor memory holds 512 columns");
-    static_assert(DQK % 64 == 0 && DV % 64 == 0 && BN % 32 == 0, "tiles in 64-element swizzle chunks");
+    constexpr int HC = BN / NG;                  // keys of a tile a softmax thread owns
+    constexpr int O_COL = 2 * S_COLS;            // the groups' O accumulators after the two S buffers
+    constexpr int TMEM_COLS = (O_COL + NG * DV) <= 256 ? 256 : 512;
+    // The MMA warp shares its scheduler with softmax warps and must not starve behind them: it is warp 0, the TMA
+    // warp is warp 1, warps 2 and 3 only wait for the teardown, and the softmax warps follow (a warp reads the
+    // tensor-memory lanes 32 (warp % 4) .. + 31, so a group is four consecutive warps starting at a multiple of four).
+    constexpr int MMA_WARP = 0, TMA_WARP = 1, SOFTMAX_WARP0 = 4;
+    static_assert(NG == 1 || NG == 2, "one or two softmax groups");
+    static_assert(O_COL + NG * DV <= 512, "tensor memory holds 512 columns");
+    static_assert(DQK % 64 == 0 && DV % 64 == 0 && HC % 32 == 0, "tiles in 64-element swizzle chunks");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);   // 128-byte swizzle wants 1024-byte tile bases
@@ -70,11 +81,13 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     uint64_t* k_empty = v_full + NSTAGE;         // [NSTAGE]
     uint64_t* v_empty = k_empty + NSTAGE;        // [NSTAGE]
     uint64_t* s_full = v_empty + NSTAGE;         // [2]
-    uint64_t* p_full = s_full + 2;               // [2]
+    uint64_t* p_full = s_full + 2;               // [2] every softmax thread of every group arrives
     uint64_t* pv_done = p_full + 2;              // [1]
-    uint64_t* o_final = pv_done + 1;              // [1] the last P V done
+    uint64_t* o_final = pv_done + 1;             // [1] the last P V done
     uint32_t* tmem_slot = (uint32_t*) (o_final + 1);
     volatile int* abort_flag = (volatile int*) (tmem_slot + 1);
+    volatile int* gave_up = abort_flag + 1;                   // a softmax thread left its loop early
+    float2* ml_s = (float2*) q_s;   // [NG][128] the groups' (maximum, sum) in the epilogue, when no product reads Q any more
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // the heaviest row blocks (most keys) first
@@ -87,6 +100,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
     if (tid == 0) {
         *abort_flag = 0;
+        *gave_up = 0;
         mbar_init(smem_u32(q_full), 1);
         for (int s = 0; s < NSTAGE; ++s) {
             mbar_init(smem_u32(k_full + s), 1);
@@ -96,13 +110,13 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(smem_u32(s_full + s), 1);
-            mbar_init(smem_u32(p_full + s), SOFTMAX_THREADS);
+            mbar_init(smem_u32(p_full + s), SOFTMAX_THREADS * NG);
         }
         mbar_init(smem_u32(pv_done), 1);
         mbar_init(smem_u32(o_final), 1);
         mbar_fence_init();
     }
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
         tmem_relinquish();
     }
@@ -111,8 +125,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 4) {
-        // ================= TMA producer =================
+    if (warp == TMA_WARP) {
+        // ================= TMA producer: keys two tiles ahead of the values (S(j+2) is issued with P(j) V(j)) ==========
         if (elect_one()) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
@@ -120,27 +134,38 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             mbar_expect_tx(smem_u32(q_full), L::Q_BYTES);
             for (int c = 0; c < DQK / 64; ++c) tma_load_3d(smem_u32(q_s + c * (BM * 128)), &tm_q, c * 64, h, r0, smem_u32(q_full));
             bool ok = true;
-            for (int j = 0; j < ntiles && ok; ++j) {
+            auto load_k = [&](int j) {
                 const int s = j % NSTAGE;
-                const uint32_t ph = (uint32_t) (j / NSTAGE) & 1;
                 uint8_t* ks = kv_s + s * L::STAGE;
-                uint8_t* vs = ks + L::K_BYTES;
-                if (j >= NSTAGE) ok = mbar_wait(smem_u32(k_empty + s), ph ^ 1, abort_flag, p.status, 101);
-                if (!ok) break;
+                if (j >= NSTAGE) ok = mbar_wait(smem_u32(k_empty + s), ((uint32_t) (j / NSTAGE) & 1) ^ 1, abort_flag, p.status, 101);
+                if (!ok) return;
                 mbar_expect_tx(smem_u32(k_full + s), L::K_BYTES);
                 for (int c = 0; c < DQK / 64; ++c) tma_load_3d(smem_u32(ks + c * (BN * 128)), &tm_k, c * 64, j * BN, hk, smem_u32(k_full + s));
-                if (j >= NSTAGE) ok = mbar_wait(smem_u32(v_empty + s), ph ^ 1, abort_flag, p.status, 102);
-                if (!ok) break;
+            };
+            auto load_v = [&](int j) {
+                const int s = j % NSTAGE;
+                uint8_t* vs = kv_s + s * L::STAGE + L::K_BYTES;
+                if (j >= NSTAGE) ok = mbar_wait(smem_u32(v_empty + s), ((uint32_t) (j / NSTAGE) & 1) ^ 1, abort_flag, p.status, 102);
+                if (!ok) return;
                 mbar_expect_tx(smem_u32(v_full + s), L::V_BYTES);
                 for (int c = 0; c < DV / 64; ++c) tma_load_3d(smem_u32(vs + c * (BN * 128)), &tm_v, c * 64, j * BN, hk, smem_u32(v_full + s));
+            };
+            load_k(0);
+            if (ntiles > 1) load_k(1);
+            for (int j = 0; j < ntiles && ok; ++j) {
+                if (j + 2 < ntiles) load_k(j + 2);
+                if (ok) load_v(j);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == MMA_WARP) {
         // ================= MMA issuer =================
+        // Order on the tensor pipe: S(0) S(1) PV(0) S(2) PV(1) S(3) ... - S(j+2) goes into the buffer P(j) lived in, behind
+        // P(j) V(j) of the same thread, and runs while the softmax works on S(j+1). A wait on a barrier that is already
+        // complete still costs this thread over a hundred clocks, so between P(j) becoming ready and S(j+2) being in the
+        // pipe there is one wait only: the loads a pass needs were waited for at the end of the pass before.
         if (elect_one()) {
             constexpr uint32_t idesc_qk = idesc_f16(BM, BN, BF16, 0, 0);
             constexpr uint32_t idesc_pv = idesc_f16(BM, DV, BF16, 0, 1);
-            bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, p.status, 201);
             auto issue_qk = [&](int j) {
                 const int s = j % NSTAGE;
                 const uint32_t kb = smem_u32(kv_s + s * L::STAGE), qb = smem_u32(q_s);
@@ -154,44 +179,55 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 mma_commit(smem_u32(k_empty + s));       // the K stage is free once these MMAs have read it
                 mma_commit(smem_u32(s_full + (j & 1)));  // and S is ready for the softmax
             };
-            if (ok) ok = mbar_wait(smem_u32(k_full + 0), 0, abort_flag, p.status, 202);
+            auto wait_k = [&](int j) { return mbar_wait(smem_u32(k_full + j % NSTAGE), (uint32_t) (j / NSTAGE) & 1, abort_flag, p.status, 202); };
+            auto wait_v = [&](int j) { return mbar_wait(smem_u32(v_full + j % NSTAGE), (uint32_t) (j / NSTAGE) & 1, abort_flag, p.status, 204); };
+            bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, p.status, 201);
+            if (ok) ok = wait_k(0);
             if (ok) {
                 fence_after_sync();
                 issue_qk(0);
             }
+            if (ok && ntiles > 1) {
+                ok = wait_k(1);
+                if (ok) issue_qk(1);
+            }
+            if (ok) ok = wait_v(0);
+            if (ok && ntiles > 2) ok = wait_k(2);
             for (int j = 0; j < ntiles && ok; ++j) {
                 const int s = j % NSTAGE;
-                const uint32_t ph = (uint32_t) (j / NSTAGE) & 1;
-                if (j + 1 < ntiles) {
-                    // S(j+1) goes into the buffer P(j-1) lived in: the tensor pipe runs this thread's MMAs in order,
-                    // so it starts after P(j-1) V(j-1); the softmax's reads of S(j-1) ended before it published P(j-1)
-                    ok = mbar_wait(smem_u32(k_full + (j + 1) % NSTAGE), (uint32_t) ((j + 1) / NSTAGE) & 1, abort_flag, p.status, 203);
-                    if (!ok) break;
-                    fence_after_sync();
-                    issue_qk(j + 1);
-                }
-                ok = mbar_wait(smem_u32(v_full + s), ph, abort_flag, p.status, 204);
-                if (ok) ok = mbar_wait(smem_u32(p_full + (j & 1)), (uint32_t) (j >> 1) & 1, abort_flag, p.status, 205);
+                ok = mbar_wait(smem_u32(p_full + (j & 1)), (uint32_t) (j >> 1) & 1, abort_flag, p.status, 205);
                 if (!ok) break;
                 fence_after_sync();
                 const uint32_t vb = smem_u32(kv_s + s * L::STAGE + L::K_BYTES);
-                const uint32_t pa = tmem + (uint32_t) ((j & 1) * S_COLS);
-                const uint32_t od = tmem + (uint32_t) O_COL;
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k) {
-                    // V tile: DV/64 chunks of [BN keys][64] 128 bytes a key; 16 keys a step
-                    const uint64_t bd = smem_desc_sw128(vb + k * (16 * 128), BN * 128, 1024);
-                    mma_ts(od, pa + (uint32_t) (k * 8), bd, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                for (int g = 0; g < NG; ++g) {
+                    // group g's keys of the tile: its P (over its own part of the S buffer) into its own accumulator
+                    const uint32_t pa = tmem + (uint32_t) ((j & 1) * S_COLS + g * HC);
+                    const uint32_t od = tmem + (uint32_t) (O_COL + g * DV);
+#pragma unroll
+                    for (int k = 0; k < HC / 16; ++k) {
+                        // V tile: DV/64 chunks of [BN keys][64] 128 bytes a key; 16 keys a step
+                        const uint64_t bd = smem_desc_sw128(vb + (g * (HC / 16) + k) * (16 * 128), BN * 128, 1024);
+                        mma_ts(od, pa + (uint32_t) (k * 8), bd, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                    }
                 }
-                mma_commit(smem_u32(v_empty + s));
                 mma_commit(smem_u32(pv_done));
+                // the V stage is free after these products: with two stages its reload is the next thing the ring needs,
+                // with three it can wait until S(j+2) is out
+                if (NSTAGE < 3) mma_commit(smem_u32(v_empty + s));
+                if (j + 2 < ntiles) issue_qk(j + 2);
+                if (NSTAGE >= 3) mma_commit(smem_u32(v_empty + s));
                 if (j == ntiles - 1) mma_commit(smem_u32(o_final));
+                // off the critical path: what the next pass reads
+                if (j + 1 < ntiles) ok = wait_v(j + 1);
+                if (ok && j + 3 < ntiles) ok = wait_k(j + 3);
             }
         }
-    } else {
-        // ================= softmax: thread r owns query row r0 + r =================
-        const int r = tid;                                  // 0..127 = tensor-memory lane
-        const uint32_t lane_base = (uint32_t) (warp * 32) << 16;
+    } else if (warp >= SOFTMAX_WARP0) {
+        // ================= softmax: thread r of group grp owns query row r0 + r and HC keys of every tile ==========
+        const int grp = (warp - SOFTMAX_WARP0) >> 2;
+        const int r = tid & (SOFTMAX_THREADS - 1);          // 0..127 = tensor-memory lane
+        const uint32_t lane_base = (uint32_t) ((warp & 3) * 32) << 16;
         const int64_t row_pos = p.p0 + r0 + r;              // last key this row sees
         const bool row_live = r0 + r < p.T;
         float m_ref = -INFINITY, l = 0.f;                   // m_ref in units of S * scale_log2
@@ -200,32 +236,32 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(s_full + (j & 1)), (uint32_t) (j >> 1) & 1, abort_flag, p.status, 301));
             if (!ok) break;
             fence_after_sync();
-            const uint32_t s_addr = tmem + lane_base + (uint32_t) ((j & 1) * S_COLS);
-            float s[BN];
+            const uint32_t s_addr = tmem + lane_base + (uint32_t) ((j & 1) * S_COLS + grp * HC);
+            float s[HC];
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = 0; c < HC / 32; ++c) {
                 uint32_t v[32];
                 tmem_ld32(s_addr + c * 32, v);
                 tmem_wait_ld();
 #pragma unroll
                 for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(v[e]);
             }
-            const int64_t k0 = (int64_t) j * BN;
+            const int64_t k0 = (int64_t) j * BN + grp * HC;
             // mask: keys past the row's position (the causal edge; it also covers keys past kv_len)
-            if (k0 + BN - 1 > row_pos) {
+            if (k0 + HC - 1 > row_pos) {
 #pragma unroll
-                for (int e = 0; e < BN; ++e)
+                for (int e = 0; e < HC; ++e)
                     if (k0 + e > row_pos) s[e] = -INFINITY;
             }
             float mx = -INFINITY;
 #pragma unroll
-            for (int e = 0; e < BN; ++e) mx = fmaxf(mx, s[e]);
+            for (int e = 0; e < HC; ++e) mx = fmaxf(mx, s[e]);
             mx *= p.scale_log2;
             // lazy rescale: move the reference maximum only when it would grow by more than 2^8
             float corr = 1.0f;
             bool need = false;
-            if (j == 0) {
-                m_ref = mx;
+            if (j == 0 || m_ref == -INFINITY) {
+                m_ref = mx;   // nothing weighed yet: O and l are zero, whatever the reference was
             } else if (mx > m_ref + RESCALE_LOG2) {
                 corr = ex2(m_ref - mx);
                 m_ref = mx;
@@ -236,7 +272,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(pv_done), (uint32_t) (j - 1) & 1, abort_flag, p.status, 302));
                 if (!ok) break;
                 fence_after_sync();
-                const uint32_t o_addr = tmem + lane_base + (uint32_t) O_COL;
+                const uint32_t o_addr = tmem + lane_base + (uint32_t) (O_COL + grp * DV);
 #pragma unroll
                 for (int c = 0; c < DV / 32; ++c) {
                     uint32_t v[32];
@@ -252,9 +288,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             // P = exp2(S * scale - m_ref), the sum from the unrounded weights, P rounded to the operand type
             const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
             float sum = 0.f;
-            const uint32_t p_addr = s_addr;   // P overlays the first BN/2 columns of its S buffer
+            const uint32_t p_addr = s_addr;   // P overlays the first half of the S columns it came from
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = 0; c < HC / 32; ++c) {
                 uint32_t w[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
@@ -281,16 +317,48 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // has not followed its phases; o_final completes exactly once, after the last product)
         if (ok) ok = mbar_wait(smem_u32(o_final), 0, abort_flag, p.status, 303);
         ok = __all_sync(0xffffffffu, ok);
+        // two groups: each writes half of the row's columns from both accumulators under the common maximum
+        float wgt[NG];
+        wgt[0] = 1.0f;
+        if (NG > 1) {
+            ml_s[grp * SOFTMAX_THREADS + r] = make_float2(m_ref, l);
+            if (!ok) *gave_up = 1;
+            named_bar_sync(1, SOFTMAX_THREADS * NG);   // every softmax thread gets here: its waits are bounded
+            ok = *gave_up == 0;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int g = 0; g < NG; ++g) mx = fmaxf(mx, ml_s[g * SOFTMAX_THREADS + r].x);
+            l = 0.f;
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                const float2 ml = ml_s[g * SOFTMAX_THREADS + r];
+                wgt[g] = ml.x == -INFINITY ? 0.f : ex2(ml.x - mx);
+                l += ml.y * wgt[g];
+            }
+        }
         if (ok) {
             fence_after_sync();
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             const uint32_t o_addr = tmem + lane_base + (uint32_t) O_COL;
             const int64_t row = (int64_t) (r0 + r) * p.Hq + h;
 #pragma unroll
-            for (int c = 0; c < DV / 32; ++c) {
+            for (int cc = 0; cc < DV / 32 / NG; ++cc) {
+                const int c = grp * (DV / 32 / NG) + cc;
                 uint32_t v[32];
                 tmem_ld32(o_addr + c * 32, v);
                 tmem_wait_ld();
+                if (NG > 1) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * wgt[0]);
+#pragma unroll
+                    for (int g = 1; g < NG; ++g) {
+                        uint32_t u[32];
+                        tmem_ld32(o_addr + g * DV + c * 32, u);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(fmaf(__uint_as_float(u[e]), wgt[g], __uint_as_float(v[e])));
+                    }
+                }
                 if (row_live) {
                     if (p.out_kind == 0) {
                         float4* dst = reinterpret_cast<float4*>((float*) p.out + row * DV + c * 32);
@@ -322,7 +390,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     // ---- teardown: every role is out of its loops (all waits are bounded); tensor memory goes back
     fence_before_sync();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         fence_after_sync();
         tmem_dealloc(tmem, TMEM_COLS);
     }
@@ -359,7 +427,7 @@ int make_map(CUtensorMap* m, const void* base, int bf16, uint64_t d0, uint64_t d
     return 0;
 }
 
-template <int DQK, int DV, int BN, int NSTAGE, int BF16>
+template <int DQK, int DV, int BN, int NSTAGE, int BF16, int NG>
 int launch(ns_gpu* g, const FlashPrefillArgs& a, const char* where) {
     using L = Smem<DQK, DV, BN, NSTAGE>;
     static_assert(L::TOTAL <= 232448, "shared memory of one CTA");
@@ -379,14 +447,14 @@ int launch(ns_gpu* g, const FlashPrefillArgs& a, const char* where) {
     p.p0 = a.p0;
     p.kv_len = a.kv_len;
     p.scale_log2 = a.scale_log2;
-    auto kern = flash_prefill_kernel<DQK, DV, BN, NSTAGE, BF16>;
+    auto kern = flash_prefill_kernel<DQK, DV, BN, NSTAGE, BF16, NG>;
     static bool set[64] = {};
     if (!set[g->dev & 63]) {
         NS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL), where);
         set[g->dev & 63] = true;
     }
     dim3 grid((unsigned) ((a.T + BM - 1) / BM), (unsigned) a.Hq, 1);
-    kern<<<grid, THREADS, L::TOTAL, g->compute>>>(tq, tk, tv, p);
+    kern<<<grid, SOFTMAX_THREADS * (NG + 1), L::TOTAL, g->compute>>>(tq, tk, tv, p);
     return ns_launched(where);
 }
 
@@ -399,10 +467,17 @@ int ns_launch_flash_prefill(ns_gpu* g, const FlashPrefillArgs& a, const char* wh
     // two softmax warpgroups share, not by latency.
     static const bool two_block = getenv("NS_B200_PREFILL_2BLOCK") != nullptr;
     if (a.Dqk == 128 && a.Dv == 128 && a.T > 128 && two_block) return ns_launch_flash_prefill2(g, a, where);
-    if (a.Dqk == 128 && a.Dv == 128 && !a.bf16) return launch<128, 128, 128, 2, 0>(g, a, where);
-    if (a.Dqk == 128 && a.Dv == 128 && a.bf16) return launch<128, 128, 128, 2, 1>(g, a, where);
-    if (a.Dqk == 192 && a.Dv == 128 && a.bf16) return launch<192, 128, 128, 2, 1>(g, a, where);
-    if (a.Dqk == 192 && a.Dv == 128 && !a.bf16) return launch<192, 128, 128, 2, 0>(g, a, where);
-    if (a.Dqk == 256 && a.Dv == 256 && !a.bf16) return launch<256, 256, 64, 2, 0>(g, a, where);
+    static const bool one_group = getenv("NS_B200_PREFILL_1GROUP") != nullptr;   // the single softmax group, for comparison
+    static const bool two_stage = getenv("NS_B200_PREFILL_2STAGE") != nullptr;   // the two-stage ring, for comparison
+    if (one_group) {
+        if (a.Dqk == 128 && a.Dv == 128 && !a.bf16) return launch<128, 128, 128, 2, 0, 1>(g, a, where);
+        if (a.Dqk == 192 && a.Dv == 128 && a.bf16) return launch<192, 128, 128, 2, 1, 1>(g, a, where);
+    }
+    if (two_stage && a.Dqk == 128 && a.Dv == 128 && !a.bf16) return launch<128, 128, 128, 2, 0, 2>(g, a, where);
+    if (a.Dqk == 128 && a.Dv == 128 && !a.bf16) return launch<128, 128, 128, 3, 0, 2>(g, a, where);
+    if (a.Dqk == 128 && a.Dv == 128 && a.bf16) return launch<128, 128, 128, 3, 1, 2>(g, a, where);
+    if (a.Dqk == 192 && a.Dv == 128 && a.bf16) return launch<192, 128, 128, 2, 1, 2>(g, a, where);
+    if (a.Dqk == 192 && a.Dv == 128 && !a.bf16) return launch<192, 128, 128, 2, 0, 2>(g, a, where);
+    if (a.Dqk == 256 && a.Dv == 256 && !a.bf16) return launch<256, 256, 64, 2, 0, 1>(g, a, where);
     return ns_fail(std::string(where) + ": head widths 128/128, 192/128 or 256/256");
 }
