@@ -6,13 +6,14 @@
 // weights rounded to the operand type before they meet V, fp32 sums. Also instantiated for the shape the reference has
 // no kernel for: bf16 with 192-wide keys and 128-wide values (non-absorbed MLA prefill).
 //
-// How: a CTA takes 128 query rows of one head. Warp 4 issues TMA loads (Q once; K and V tiles of BN keys through a
-// ring of stages, 128-byte swizzle). Warp 5 issues the MMAs: S = Q K^T into one of two S buffers in tensor memory, then
-// O += P V with P read from tensor memory (it overlays the S buffer it came from) and V as an MN-major shared-memory
-// operand. Warps 0-3 are the softmax: thread r owns row r (= tensor-memory lane r), so row max and sum need no
-// shuffles; it reads its S row, writes P back as packed 16-bit pairs, and rescales its O row only when the running
-// maximum grew by more than 2^8 (the final 1/l uses the same reference maximum, so the result is unchanged).
-// With NG = 2 there are two softmax groups (warps 0-3 and 4-7): group g owns keys [g BN/2, (g+1) BN/2) of every tile
+// How: a CTA takes 128 query rows of one head. Warp 0 issues the MMAs, warp 1 the TMA loads (Q once; K and V tiles of
+// BN keys through a ring of stages, 128-byte swizzle), warps 4 and up are the softmax. The MMAs: S = Q K^T into one of
+// two S buffers in tensor memory, then O += P V with P read from tensor memory (it overlays the S buffer it came from)
+// and V as an MN-major shared-memory operand; the order on the pipe is S(0) S(1) PV(0) S(2) PV(1) S(3) ... A softmax
+// thread owns row r (= tensor-memory lane r), so row max and sum need no shuffles; it reads its S row, writes P back as
+// packed 16-bit pairs, and rescales its O row only when the running maximum grew by more than 2^8 (the final 1/l uses
+// the same reference maximum, so the result is unchanged).
+// With NG = 2 there are two softmax groups (warps 4-7 and 8-11): group g owns keys [g BN/2, (g+1) BN/2) of every tile
 // with its own running maximum, sum and O accumulator in tensor memory (O_g += P_g V_g), so the groups never exchange
 // anything inside the loop and two warps a scheduler share the exponentials; the epilogue adds the two accumulators
 // under a common maximum. (The 256-wide instance keeps one group: two accumulators of 256 columns do not fit.)
@@ -76,9 +77,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     uint64_t* bars = (uint64_t*) (kv_s + NSTAGE * L::STAGE);
     // barrier map
     uint64_t* q_full = bars + 0;
-    uint64_t* k_full = bars + 1;                 // [NSTAGE]
-    uint64_t* v_full = k_full + NSTAGE;          // [NSTAGE]
-    uint64_t* k_empty = v_full + NSTAGE;         // [NSTAGE]
+    uint64_t* k_full = bars + 1;                 // [2] the first two key tiles, one use each
+    uint64_t* f_full = k_full + 2;               // [NSTAGE] what pass j of the MMA warp reads: V(j) and K(j+2)
+    uint64_t* k_empty = f_full + NSTAGE;         // [NSTAGE]
     uint64_t* v_empty = k_empty + NSTAGE;        // [NSTAGE]
     uint64_t* s_full = v_empty + NSTAGE;         // [2]
     uint64_t* p_full = s_full + 2;               // [2] every softmax thread of every group arrives
@@ -103,12 +104,12 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         *gave_up = 0;
         mbar_init(smem_u32(q_full), 1);
         for (int s = 0; s < NSTAGE; ++s) {
-            mbar_init(smem_u32(k_full + s), 1);
-            mbar_init(smem_u32(v_full + s), 1);
+            mbar_init(smem_u32(f_full + s), 1);
             mbar_init(smem_u32(k_empty + s), 1);
             mbar_init(smem_u32(v_empty + s), 1);
         }
         for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(k_full + s), 1);
             mbar_init(smem_u32(s_full + s), 1);
             mbar_init(smem_u32(p_full + s), SOFTMAX_THREADS * NG);
         }
@@ -126,7 +127,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint32_t tmem = *tmem_slot;
 
     if (warp == TMA_WARP) {
-        // ================= TMA producer: keys two tiles ahead of the values (S(j+2) is issued with P(j) V(j)) ==========
+        // ================= TMA producer: keys two tiles ahead of the values (S(j+2) is issued with P(j) V(j)); what one
+        // pass of the MMA warp reads, V(j) and K(j+2), lands on one barrier =================
         if (elect_one()) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
@@ -134,28 +136,23 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             mbar_expect_tx(smem_u32(q_full), L::Q_BYTES);
             for (int c = 0; c < DQK / 64; ++c) tma_load_3d(smem_u32(q_s + c * (BM * 128)), &tm_q, c * 64, h, r0, smem_u32(q_full));
             bool ok = true;
-            auto load_k = [&](int j) {
-                const int s = j % NSTAGE;
-                uint8_t* ks = kv_s + s * L::STAGE;
-                if (j >= NSTAGE) ok = mbar_wait(smem_u32(k_empty + s), ((uint32_t) (j / NSTAGE) & 1) ^ 1, abort_flag, p.status, 101);
+            // a key tile and a value tile that signal `bar`, after their stages are free (either may be absent: j < 0)
+            auto load = [&](int jk, int jv, uint64_t* bar) {
+                if (jk >= NSTAGE) ok = mbar_wait(smem_u32(k_empty + jk % NSTAGE), ((uint32_t) (jk / NSTAGE) & 1) ^ 1, abort_flag, p.status, 101);
+                if (ok && jv >= NSTAGE) ok = mbar_wait(smem_u32(v_empty + jv % NSTAGE), ((uint32_t) (jv / NSTAGE) & 1) ^ 1, abort_flag, p.status, 102);
                 if (!ok) return;
-                mbar_expect_tx(smem_u32(k_full + s), L::K_BYTES);
-                for (int c = 0; c < DQK / 64; ++c) tma_load_3d(smem_u32(ks + c * (BN * 128)), &tm_k, c * 64, j * BN, hk, smem_u32(k_full + s));
+                mbar_expect_tx(smem_u32(bar), (jk >= 0 ? L::K_BYTES : 0) + (jv >= 0 ? L::V_BYTES : 0));
+                if (jk >= 0) {
+                    uint8_t* ks = kv_s + (jk % NSTAGE) * L::STAGE;
+                    for (int c = 0; c < DQK / 64; ++c) tma_load_3d(smem_u32(ks + c * (BN * 128)), &tm_k, c * 64, jk * BN, hk, smem_u32(bar));
+                }
+                if (jv >= 0) {
+                    uint8_t* vs = kv_s + (jv % NSTAGE) * L::STAGE + L::K_BYTES;
+                    for (int c = 0; c < DV / 64; ++c) tma_load_3d(smem_u32(vs + c * (BN * 128)), &tm_v, c * 64, jv * BN, hk, smem_u32(bar));
+                }
             };
-            auto load_v = [&](int j) {
-                const int s = j % NSTAGE;
-                uint8_t* vs = kv_s + s * L::STAGE + L::K_BYTES;
-                if (j >= NSTAGE) ok = mbar_wait(smem_u32(v_empty + s), ((uint32_t) (j / NSTAGE) & 1) ^ 1, abort_flag, p.status, 102);
-                if (!ok) return;
-                mbar_expect_tx(smem_u32(v_full + s), L::V_BYTES);
-                for (int c = 0; c < DV / 64; ++c) tma_load_3d(smem_u32(vs + c * (BN * 128)), &tm_v, c * 64, j * BN, hk, smem_u32(v_full + s));
-            };
-            load_k(0);
-            if (ntiles > 1) load_k(1);
-            for (int j = 0; j < ntiles && ok; ++j) {
-                if (j + 2 < ntiles) load_k(j + 2);
-                if (ok) load_v(j);
-            }
+            for (int j = 0; j < 2 && j < ntiles && ok; ++j) load(j, -1, k_full + j);
+            for (int j = 0; j < ntiles && ok; ++j) load(j + 2 < ntiles ? j + 2 : -1, j, f_full + j % NSTAGE);
         }
     } else if (warp == MMA_WARP) {
         // ================= MMA issuer =================
@@ -179,20 +176,16 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 mma_commit(smem_u32(k_empty + s));       // the K stage is free once these MMAs have read it
                 mma_commit(smem_u32(s_full + (j & 1)));  // and S is ready for the softmax
             };
-            auto wait_k = [&](int j) { return mbar_wait(smem_u32(k_full + j % NSTAGE), (uint32_t) (j / NSTAGE) & 1, abort_flag, p.status, 202); };
-            auto wait_v = [&](int j) { return mbar_wait(smem_u32(v_full + j % NSTAGE), (uint32_t) (j / NSTAGE) & 1, abort_flag, p.status, 204); };
+            auto wait_f = [&](int j) { return mbar_wait(smem_u32(f_full + j % NSTAGE), (uint32_t) (j / NSTAGE) & 1, abort_flag, p.status, 204); };
             bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, p.status, 201);
-            if (ok) ok = wait_k(0);
-            if (ok) {
-                fence_after_sync();
-                issue_qk(0);
+            for (int j = 0; j < 2 && j < ntiles && ok; ++j) {
+                ok = mbar_wait(smem_u32(k_full + j), 0, abort_flag, p.status, 202);
+                if (ok) {
+                    fence_after_sync();
+                    issue_qk(j);
+                }
             }
-            if (ok && ntiles > 1) {
-                ok = wait_k(1);
-                if (ok) issue_qk(1);
-            }
-            if (ok) ok = wait_v(0);
-            if (ok && ntiles > 2) ok = wait_k(2);
+            if (ok) ok = wait_f(0);
             for (int j = 0; j < ntiles && ok; ++j) {
                 const int s = j % NSTAGE;
                 ok = mbar_wait(smem_u32(p_full + (j & 1)), (uint32_t) (j >> 1) & 1, abort_flag, p.status, 205);
@@ -219,8 +212,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 if (NSTAGE >= 3) mma_commit(smem_u32(v_empty + s));
                 if (j == ntiles - 1) mma_commit(smem_u32(o_final));
                 // off the critical path: what the next pass reads
-                if (j + 1 < ntiles) ok = wait_v(j + 1);
-                if (ok && j + 3 < ntiles) ok = wait_k(j + 3);
+                if (j + 1 < ntiles) ok = wait_f(j + 1);
             }
         }
     } else if (warp >= SOFTMAX_WARP0) {
@@ -238,13 +230,15 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             fence_after_sync();
             const uint32_t s_addr = tmem + lane_base + (uint32_t) ((j & 1) * S_COLS + grp * HC);
             float s[HC];
+            {
+                uint32_t v[HC / 32][32];
 #pragma unroll
-            for (int c = 0; c < HC / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(s_addr + c * 32, v);
+                for (int c = 0; c < HC / 32; ++c) tmem_ld32(s_addr + c * 32, v[c]);
                 tmem_wait_ld();
 #pragma unroll
-                for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(v[e]);
+                for (int c = 0; c < HC / 32; ++c)
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(v[c][e]);
             }
             const int64_t k0 = (int64_t) j * BN + grp * HC;
             // mask: keys past the row's position (the causal edge; it also covers keys past kv_len)
