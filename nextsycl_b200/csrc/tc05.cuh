@@ -46,20 +46,6 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// One look at the barrier, never suspending the thread (try_wait may park it for a while when the phase is not complete).
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred P;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, P;\n\t"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
 // Waits for the phase of `parity` to complete, at most `limit` polls. On giving up it raises *abort (shared memory:
 // every later wait of the CTA returns at once) and records `code` in *status (global or mapped host memory), so the
 // kernel runs to its teardown instead of hanging. Returns false when the wait did not complete.
@@ -118,14 +104,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
           "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
           "=r"(r[31])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -200,18 +178,6 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
 
-// 2^x on the FMA pipes for x <= 8 or so (weights of a softmax): x = n + f with n the nearest integer, a cubic for 2^f on
-// [-0.5, 0.5] (relative error 7.5e-5, under half an ulp of a 16-bit operand), n added into the exponent. Below -126 the
-// result is some value under 2^-125. Takes the load off the special-function unit, 16 results a clock an SM.
-__device__ __forceinline__ float ex2_fma(float x) {
-    x = fmaxf(x, -126.0f);
-    const float t = x + 12582912.0f;   // 1.5 * 2^23: the low mantissa bits of t hold n
-    const float f = x - (t - 12582912.0f);
-    float p = fmaf(0.0551715679f, f, 0.2426111102f);
-    p = fmaf(p, f, 0.6932610273f);
-    p = fmaf(p, f, 0.9999280572f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
