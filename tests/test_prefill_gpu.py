@@ -175,6 +175,28 @@ def test_16k_rows_sampled(gpu, ops):
         assert_close(got[r:r + 1], want, f"row {r}")
 
 
+def test_head_chunks_with_a_ragged_last_one(gpu, ops):
+    """The CTAs start longest first across a chunk of heads sized to L2: 24,576 keys of 128 + 128 wide make a key head
+    12 MB, so a chunk is 2 of the 3 key heads (4 of the 6 query heads) and the last chunk holds the other 2 query heads.
+    Every (row block, head) must still be computed exactly once: rows sampled across the length for every head, the
+    untouched rest of the output checked through a sentinel."""
+    T, Hq, Hkv, D = 24576, 6, 3, 128
+    q = W.normal_f16(1, 710, (T, Hq * D))
+    k = W.normal_f16(1, 711, (Hkv, T, D))
+    v = W.normal_f16(1, 712, (Hkv, T, D))
+    dq, dk, dv = DevBuf.of(gpu, q), DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+    out = DevBuf(gpu, T * Hq * D * 2)
+    out.fill(0xFF)   # fp16 NaN: a (row block, head) nobody wrote stays non-finite
+    ops.gqa_prefill(0, dq, Hq * D, dk, dv, T, Hq, Hkv, D, T, 0, out)
+    gpu.sync()
+    got = out.read(np.float16).reshape(T, Hq * D).astype(np.float32)
+    assert np.isfinite(got).all()
+    kb, vb = k.view(np.uint16), v.view(np.uint16)
+    for r in (0, 127, 128, 5000, 12287, 12288, 24575):
+        want = O.attn_tc(q[r:r + 1].astype(np.float32), kb, vb, 1, Hq, Hkv, D, D, T, r, np.float32(1 / np.sqrt(D)), kind=0)
+        assert_close(got[r:r + 1], want, f"row {r}")
+
+
 def _repeat_on_device(gpu, blk, nbytes):
     """A device buffer of nbytes holding the host block end to end (element i = blk[i mod len])."""
     from nextsycl_b200.core import check
