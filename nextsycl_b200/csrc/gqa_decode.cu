@@ -125,6 +125,22 @@ __device__ __forceinline__ uint4 dequant8(const uint8_t* row, int c) {
     }
 }
 
+// S = Q K^T over a quantised cache takes its key fragments straight from the raw rows: lane (g, t) of a warp reads
+// 16-byte chunks of key g's row and expands them in registers, so the keys never pass through an fp16 tile. A 16-byte
+// chunk is 16 (q8_0) or 32 (q4_0) consecutive features, not the (2t, 2t+1, 2t+8, 2t+9) a k-step's fragment holds, so the
+// contraction index is permuted: k-step ks, fragment pair `half` of lane t stands for the features frag_feature() names,
+// and the queries are staged in shared memory in the same order (a sum does not care about the order of its terms).
+// Chunk order: lane t takes chunks 2t + (i & 1) + 8 (i >> 1), i = 0..3 (q8_0, row stride 17 chunks) or 2t + i, i = 0..1
+// (q4_0, 9 chunks): the eight lanes of a quarter warp then touch eight different 16-byte bank groups.
+template <int QF>
+__host__ __device__ constexpr int frag_chunk(int t, int i) { return QF == 1 ? 2 * t + (i & 1) + 8 * (i >> 1) : 2 * t + i; }
+// first of the two consecutive features in pair `half` (0: fragment k 2t, 2t+1; 1: k 2t+8, 2t+9) of lane t in k-step ks
+template <int QF>
+__host__ __device__ constexpr int frag_feature(int ks, int t, int half) {
+    return QF == 1 ? 16 * frag_chunk<1>(t, ks / 4) + 4 * (ks % 4) + 2 * half
+                   : 32 * frag_chunk<2>(t, ks / 8) + 16 * (ks % 2) + 4 * ((ks % 8) / 2) + 2 * half;
+}
+
 // QF: the caches' form, 0 fp16, 1 q8_0, 2 q4_0. A quantised tile travels as it lies (cp.async of the raw rows into a ring
 // of raw stages) and is expanded by its warp into one fp16 tile just before each product reads it: the keys for S, then
 // the values, into the same 8 KB, for P V. The expansion is some 700 dependent instructions a tile and a warp, so these
@@ -166,7 +182,21 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
             const int t = rho / G, gq = rho % G;
             const int64_t at = (int64_t) b * p.q_seq + (int64_t) t * p.qs + (int64_t) (hk * G + gq) * D + c * 8;
             float f[8];
-            if (p.q_f32) {
+            if (QF != 0) {
+                // column 16 ks + pos of the staged row holds the feature that fragment position stands for
+                const int64_t base = at - c * 8;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int d = frag_feature<QF>(c / 2, e, c % 2);
+                    if (p.q_f32) {
+                        const float2 x = *reinterpret_cast<const float2*>((const float*) p.q + base + d);
+                        f[2 * e] = x.x, f[2 * e + 1] = x.y;
+                    } else {
+                        const float2 x = __half22float2(*reinterpret_cast<const __half2*>((const __half*) p.q + base + d));
+                        f[2 * e] = x.x, f[2 * e + 1] = x.y;
+                    }
+                }
+            } else if (p.q_f32) {
                 const float4 a = *reinterpret_cast<const float4*>((const float*) p.q + at);
                 const float4 bb = *reinterpret_cast<const float4*>((const float*) p.q + at + 4);
                 f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = bb.x, f[5] = bb.y, f[6] = bb.z, f[7] = bb.w;
@@ -276,13 +306,6 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
             __syncwarp();
             const uint8_t* ks = QF == 0 ? w_s + stage * (2 * TILE) : w_s;
             const uint8_t* vs = QF == 0 ? ks + TILE : w_s;
-            if (QF != 0) {
-                // the raw keys expanded into the warp's fp16 tile: row i, a lane one 16-byte chunk of it
-                const uint8_t* kr = w_s + TILE + stage * (2 * RAW_TILE);
-#pragma unroll 8
-                for (int i = 0; i < KT; ++i) *reinterpret_cast<uint4*>(w_s + swz<ROWB>(i, lane)) = dequant8<QF>(kr + i * RAWB, lane);
-                __syncwarp();
-            }
             const int64_t j0 = jbeg + (int64_t) tile * KT;
 
             // ---- S = Q K^T: MT x (16 rows x 16 keys)
@@ -293,16 +316,66 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
                 for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) s[mt][nt][e] = 0.f;
+            if (QF == 0) {
 #pragma unroll
-            for (int k = 0; k < KS; ++k) {
-                uint32_t kf[4];
-                ldsm_x4(smem_u32(ks + swz<ROWB>((lane & 7) + (lane >> 4) * 8, 2 * k + ((lane >> 3) & 1))), kf);
+                for (int k = 0; k < KS; ++k) {
+                    uint32_t kf[4];
+                    ldsm_x4(smem_u32(ks + swz<ROWB>((lane & 7) + (lane >> 4) * 8, 2 * k + ((lane >> 3) & 1))), kf);
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    uint32_t qf[4];
-                    ldsm_x4(smem_u32(q_s + swz<ROWB>(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * k + (lane >> 4))), qf);
-                    mma16816(s[mt][0], qf, kf[0], kf[1]);
-                    mma16816(s[mt][1], qf, kf[2], kf[3]);
+                    for (int mt = 0; mt < MT; ++mt) {
+                        uint32_t qf[4];
+                        ldsm_x4(smem_u32(q_s + swz<ROWB>(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * k + (lane >> 4))), qf);
+                        mma16816(s[mt][0], qf, kf[0], kf[1]);
+                        mma16816(s[mt][1], qf, kf[2], kf[3]);
+                    }
+                }
+            } else {
+                // key fragments from the raw rows (see frag_feature): keys g and g + 8 of the tile, this lane's chunks
+                const uint8_t* kr = w_s + TILE + stage * (2 * RAW_TILE);
+                const int g = lane >> 2, t = lane & 3;
+                const uint8_t* row0p = kr + g * RAWB;
+                const uint8_t* row1p = row0p + 8 * RAWB;
+                constexpr int NI = QF == 1 ? 4 : 2;           // chunks a lane reads of a row
+                constexpr int KPC = KS / NI;                   // k-steps a chunk feeds
+                const __half2 bias = QF == 1 ? __floats2half2_rn(1152.f, 1152.f) : __floats2half2_rn(1032.f, 1032.f);
+                // the blocks' scales: q8_0 chunks 2t + (i & 1) + 8 (i >> 1) lie in blocks t and t + 4, q4_0 chunk = block
+                __half2 d0[2], d1[2];
+                if (QF == 1) {
+                    d0[0] = __half2half2(*reinterpret_cast<const __half*>(row0p + 256 + 2 * t));
+                    d0[1] = __half2half2(*reinterpret_cast<const __half*>(row0p + 256 + 2 * (t + 4)));
+                    d1[0] = __half2half2(*reinterpret_cast<const __half*>(row1p + 256 + 2 * t));
+                    d1[1] = __half2half2(*reinterpret_cast<const __half*>(row1p + 256 + 2 * (t + 4)));
+                } else {
+                    const __half2 a = *reinterpret_cast<const __half2*>(row0p + 128 + 4 * t);
+                    const __half2 c = *reinterpret_cast<const __half2*>(row1p + 128 + 4 * t);
+                    d0[0] = __half2half2(__low2half(a)), d0[1] = __half2half2(__high2half(a));
+                    d1[0] = __half2half2(__low2half(c)), d1[1] = __half2half2(__high2half(c));
+                }
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    const int ch = frag_chunk<QF>(t, i);
+                    const uint4 c0 = *reinterpret_cast<const uint4*>(row0p + 16 * ch);
+                    const uint4 c1 = *reinterpret_cast<const uint4*>(row1p + 16 * ch);
+                    const uint32_t w0[4] = {c0.x, c0.y, c0.z, c0.w}, w1[4] = {c1.x, c1.y, c1.z, c1.w};
+                    const __half2 s0 = QF == 1 ? d0[i >> 1] : d0[i], s1 = QF == 1 ? d1[i >> 1] : d1[i];
+#pragma unroll
+                    for (int kk = 0; kk < KPC; ++kk) {
+                        const int k = i * KPC + kk;
+                        uint32_t x0, x1;
+                        if (QF == 1) {
+                            x0 = w0[kk] ^ 0x80808080u, x1 = w1[kk] ^ 0x80808080u;
+                        } else {
+                            const int sh = (kk & 1) * 4;   // k-steps in turn: the low nibbles (values j), the high ones (j + 16)
+                            x0 = (w0[kk >> 1] >> sh) & 0x0F0F0F0Fu, x1 = (w1[kk >> 1] >> sh) & 0x0F0F0F0Fu;
+                        }
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            uint32_t qf[4];
+                            ldsm_x4(smem_u32(q_s + swz<ROWB>(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * k + (lane >> 4))), qf);
+                            mma16816(s[mt][0], qf, scaled_pair(x0, 0x4140, bias, s0), scaled_pair(x0, 0x4342, bias, s0));
+                            mma16816(s[mt][1], qf, scaled_pair(x1, 0x4140, bias, s1), scaled_pair(x1, 0x4342, bias, s1));
+                        }
+                    }
                 }
             }
             // ---- mask, online softmax (a row's 16 scores sit in its quad: 4 a lane)
