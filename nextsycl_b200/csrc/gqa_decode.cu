@@ -39,6 +39,11 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t (&r)[4]) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                  : "r"(addr));
 }
+// 16 rows of 16 bytes, transposed: lane (g, t) gets the bytes of rows 4t .. 4t+3 in column g (r0) and in column g + 8 (r1).
+// Lanes 0-15 give the rows' addresses (16-byte aligned).
+__device__ __forceinline__ void ldsm_b8_t(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+    asm volatile("ldmatrix.sync.aligned.m16n16.x1.trans.shared.b8 {%0, %1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
 // D (fp32 16x8) += A (fp16 16x16, row) x B (fp16 16x8, col)
 __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -93,9 +98,9 @@ __device__ __forceinline__ uint32_t swz(int r, int c) {
 
 // ---- quantised caches (heads of 256; kernels/llm/qwen35/silo/attn.cpp:44-78): a head's row is q8_0 - 256 int8 then 8
 // fp16 scales, 272 bytes - or q4_0 - 8 blocks of 16 bytes (byte j: value j low nibble, value j + 16 high) then 8 fp16
-// scales, 144 bytes. Features 8c .. 8c+7 of a row as the 8 halves the reference's reader produces, half(float(q) *
-// float(d)): q becomes an exact half by placing its (biased) byte in the mantissa of 1024 and subtracting the bias, and
-// the half product of two halves is the exact product rounded once, as the reference's float product rounded to half is.
+// scales, 144 bytes. A key's features enter S as the halves the reference's reader produces, half(float(q) * float(d)):
+// q becomes an exact half by placing its (biased) byte in the mantissa of 1024 and subtracting the bias, and the half
+// product of two halves is the exact product rounded once, as the reference's float product rounded to half is.
 template <int QF>
 __host__ __device__ constexpr int raw_row_bytes(int D) { return QF == 0 ? D * 2 : QF == 1 ? D + D / 16 : D / 2 + D / 16; }
 
@@ -104,27 +109,12 @@ __device__ __forceinline__ uint32_t scaled_pair(uint32_t biased, uint32_t sel, _
     __half2 h = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&w), bias), d2);
     return *reinterpret_cast<uint32_t*>(&h);
 }
-template <int QF>
-__device__ __forceinline__ uint4 dequant8(const uint8_t* row, int c) {
-    if (QF == 1) {
-        const uint2 w = *reinterpret_cast<const uint2*>(row + 8 * c);
-        const __half2 d2 = __half2half2(*reinterpret_cast<const __half*>(row + 256 + 2 * (c >> 2)));
-        const __half2 bias = __floats2half2_rn(1152.f, 1152.f);   // 1024 + 128: the byte holds q + 128
-        const uint32_t x = w.x ^ 0x80808080u, y = w.y ^ 0x80808080u;
-        return make_uint4(scaled_pair(x, 0x4140, bias, d2), scaled_pair(x, 0x4342, bias, d2), scaled_pair(y, 0x4140, bias, d2),
-                          scaled_pair(y, 0x4342, bias, d2));
-    } else {
-        const int blk = c >> 2, sub = c & 3;
-        const uint2 w = *reinterpret_cast<const uint2*>(row + blk * 16 + (sub & 1) * 8);
-        const __half2 d2 = __half2half2(*reinterpret_cast<const __half*>(row + 128 + 2 * blk));
-        const __half2 bias = __floats2half2_rn(1032.f, 1032.f);   // 1024 + 8: the nibble holds q + 8
-        const int sh = sub >= 2 ? 4 : 0;
-        const uint32_t x = (w.x >> sh) & 0x0F0F0F0Fu, y = (w.y >> sh) & 0x0F0F0F0Fu;
-        return make_uint4(scaled_pair(x, 0x4140, bias, d2), scaled_pair(x, 0x4342, bias, d2), scaled_pair(y, 0x4140, bias, d2),
-                          scaled_pair(y, 0x4342, bias, d2));
-    }
+// the two halves (b_lo - bias', b_hi - bias') of the bytes `sel` picks: the quantised values themselves, exact
+__device__ __forceinline__ uint32_t value_pair(uint32_t biased, uint32_t sel, __half2 bias) {
+    const uint32_t w = __byte_perm(biased, 0x64646464u, sel);
+    __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&w), bias);
+    return *reinterpret_cast<uint32_t*>(&h);
 }
-
 // S = Q K^T over a quantised cache takes its key fragments straight from the raw rows: lane (g, t) of a warp reads
 // 16-byte chunks of key g's row and expands them in registers, so the keys never pass through an fp16 tile. A 16-byte
 // chunk is 16 (q8_0) or 32 (q4_0) consecutive features, not the (2t, 2t+1, 2t+8, 2t+9) a k-step's fragment holds, so the
@@ -132,6 +122,13 @@ __device__ __forceinline__ uint4 dequant8(const uint8_t* row, int c) {
 // and the queries are staged in shared memory in the same order (a sum does not care about the order of its terms).
 // Chunk order: lane t takes chunks 2t + (i & 1) + 8 (i >> 1), i = 0..3 (q8_0, row stride 17 chunks) or 2t + i, i = 0..1
 // (q4_0, 9 chunks): the eight lanes of a quarter warp then touch eight different 16-byte bank groups.
+// O += P V takes the value fragments from the raw rows too, through the transposing 8-bit ldmatrix: lane (g, t) gets the
+// bytes of four consecutive keys 4t .. 4t+3 in feature column g, so fragment positions (2t, 2t+1 | 2t+8, 2t+9) of the
+// contraction stand for keys (4t, 4t+1 | 4t+2, 4t+3) of the tile, and S is computed with its key columns in that order
+// (column n of n-tile nt is key 4 (n / 2) + 2 nt + n % 2). A value's scale depends on its key and its block of 32
+// features, so it goes onto the weights: per block, P' = half(P d[key][block]), and the values enter as the exact small
+// integers they are. The weights carry a factor 2^6 (so do the sums, it cancels in O / l) to keep P' out of the fp16
+// subnormals: P <= 64, d <= 65504 / 127, P' <= 33,024.
 template <int QF>
 __host__ __device__ constexpr int frag_chunk(int t, int i) { return QF == 1 ? 2 * t + (i & 1) + 8 * (i >> 1) : 2 * t + i; }
 // first of the two consecutive features in pair `half` (0: fragment k 2t, 2t+1; 1: k 2t+8, 2t+9) of lane t in k-step ks
@@ -142,9 +139,9 @@ __host__ __device__ constexpr int frag_feature(int ks, int t, int half) {
 }
 
 // QF: the caches' form, 0 fp16, 1 q8_0, 2 q4_0. A quantised tile travels as it lies (cp.async of the raw rows into a ring
-// of raw stages) and is expanded by its warp into one fp16 tile just before each product reads it: the keys for S, then
-// the values, into the same 8 KB, for P V. The expansion is some 700 dependent instructions a tile and a warp, so these
-// instances are sized for two CTAs an SM (two warps a scheduler to hide each other's latencies).
+// of raw stages) and both products take their fragments from the raw rows, expanding them in registers (above). The
+// expansion is several hundred dependent instructions a tile and a warp, so these instances are sized for two CTAs an SM
+// (two warps a scheduler to hide each other's latencies).
 template <int D, int MT, int NSTAGE, int QF>
 __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(const Params p) {
     constexpr int RG = 16 * MT;          // query rows a CTA
@@ -156,13 +153,13 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
     constexpr int RAWB = raw_row_bytes<QF>(D);      // bytes a key row as the cache holds it
     constexpr int RAW_CPR = RAWB / 16;
     constexpr int RAW_TILE = KT * RAWB;
-    constexpr int WARP_BYTES = QF == 0 ? NSTAGE * 2 * TILE : TILE + NSTAGE * 2 * RAW_TILE;
+    constexpr int WARP_BYTES = QF == 0 ? NSTAGE * 2 * TILE : NSTAGE * 2 * RAW_TILE;
     static_assert(QF == 0 || D == 256, "quantised caches have heads of 256: a row's 32 chunks are a warp's lanes");
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int row_flag[8];
     uint8_t* q_s = smem;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    uint8_t* w_s = smem + RG * ROWB + warp * WARP_BYTES;   // fp16: NSTAGE (K, V) tile pairs; quantised: one fp16 tile, then NSTAGE raw pairs
+    uint8_t* w_s = smem + RG * ROWB + warp * WARP_BYTES;   // NSTAGE (K, V) tile pairs, fp16 or raw
 
     // the row groups of one (split, key head) are neighbours in the grid: they run at the same time, and the second
     // to read a key tile finds it in L2
@@ -274,7 +271,7 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
                         cp_async16(smem_u32(vs + swz<ROWB>(r, c)), vbase + off, ok);
                     }
                 } else {
-                    uint8_t* kr = w_s + TILE + stage * (2 * RAW_TILE);
+                    uint8_t* kr = w_s + stage * (2 * RAW_TILE);
                     uint8_t* vr = kr + RAW_TILE;
 #pragma unroll
                     for (int i = 0; i < (KT * RAW_CPR + 31) / 32; ++i) {
@@ -331,10 +328,10 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
                 }
             } else {
                 // key fragments from the raw rows (see frag_feature): keys g and g + 8 of the tile, this lane's chunks
-                const uint8_t* kr = w_s + TILE + stage * (2 * RAW_TILE);
+                const uint8_t* kr = w_s + stage * (2 * RAW_TILE);
                 const int g = lane >> 2, t = lane & 3;
-                const uint8_t* row0p = kr + g * RAWB;
-                const uint8_t* row1p = row0p + 8 * RAWB;
+                const uint8_t* row0p = kr + (4 * (g >> 1) + (g & 1)) * RAWB;   // n-tile 0: key 4 (g / 2) + g % 2
+                const uint8_t* row1p = row0p + 2 * RAWB;                        // n-tile 1: two keys on
                 constexpr int NI = QF == 1 ? 4 : 2;           // chunks a lane reads of a row
                 constexpr int KPC = KS / NI;                   // k-steps a chunk feeds
                 const __half2 bias = QF == 1 ? __floats2half2_rn(1152.f, 1152.f) : __floats2half2_rn(1032.f, 1032.f);
@@ -393,7 +390,7 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int nt = e >> 1;
-                        const int key = rel0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+                        const int key = QF == 0 ? rel0 + nt * 8 + 2 * (lane & 3) + (e & 1) : rel0 + 4 * (lane & 3) + 2 * nt + (e & 1);
                         x[e] = key <= last ? s[mt][nt][hh * 2 + (e & 1)] : -INFINITY;
                         mx = fmaxf(mx, x[e]);
                     }
@@ -405,7 +402,7 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
                     float pv[4], sum = 0.f;
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        pv[e] = ex2_approx(x[e] - ref);
+                        pv[e] = ex2_approx(x[e] - (QF == 0 ? ref : ref - 6.0f));   // quantised values: weights and sums times 2^6
                         sum += pv[e];
                     }
                     l[mt][hh] = l[mt][hh] * c + sum;   // this lane's share; the quad's shares are added at the end
@@ -428,23 +425,64 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
                             o[mt][nt][hh * 2 + 1] *= cs[mt][hh];
                         }
             }
-            if (QF != 0) {
-                // the keys are consumed: the values take their place
-                __syncwarp();
-                const uint8_t* vr = w_s + TILE + stage * (2 * RAW_TILE) + RAW_TILE;
-#pragma unroll 8
-                for (int i = 0; i < KT; ++i) *reinterpret_cast<uint4*>(w_s + swz<ROWB>(i, lane)) = dequant8<QF>(vr + i * RAWB, lane);
-                __syncwarp();
-            }
             // ---- O += P V
+            if (QF == 0) {
 #pragma unroll
-            for (int jj = 0; jj < NT / 2; ++jj) {
-                uint32_t vf[4];
-                ldsm_x4_t(smem_u32(vs + swz<ROWB>((lane & 7) + ((lane >> 3) & 1) * 8, 2 * jj + (lane >> 4))), vf);
+                for (int jj = 0; jj < NT / 2; ++jj) {
+                    uint32_t vf[4];
+                    ldsm_x4_t(smem_u32(vs + swz<ROWB>((lane & 7) + ((lane >> 3) & 1) * 8, 2 * jj + (lane >> 4))), vf);
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    mma16816(o[mt][2 * jj], pf[mt], vf[0], vf[1]);
-                    mma16816(o[mt][2 * jj + 1], pf[mt], vf[2], vf[3]);
+                    for (int mt = 0; mt < MT; ++mt) {
+                        mma16816(o[mt][2 * jj], pf[mt], vf[0], vf[1]);
+                        mma16816(o[mt][2 * jj + 1], pf[mt], vf[2], vf[3]);
+                    }
+                }
+            } else {
+                const uint8_t* vr = w_s + stage * (2 * RAW_TILE) + RAW_TILE;
+                const int t = lane & 3;
+                constexpr int SC_OFF = QF == 1 ? 256 : 128;   // the 8 fp16 scales behind the values
+                const __half2 bias = QF == 1 ? __floats2half2_rn(1152.f, 1152.f) : __floats2half2_rn(1032.f, 1032.f);
+                uint4 sk[4];   // the scales of this lane's keys 4t .. 4t+3
+#pragma unroll
+                for (int q = 0; q < 4; ++q) sk[q] = *reinterpret_cast<const uint4*>(vr + (4 * t + q) * RAWB + SC_OFF);
+                const uint32_t ld_addr = smem_u32(vr + (lane & 15) * RAWB);
+#pragma unroll
+                for (int blk = 0; blk < 8; ++blk) {
+                    const uint32_t sel = (blk & 1) ? 0x7632u : 0x5410u;
+                    const uint32_t w0 = (&sk[0].x)[blk >> 1], w1 = (&sk[1].x)[blk >> 1], w2 = (&sk[2].x)[blk >> 1], w3 = (&sk[3].x)[blk >> 1];
+                    const uint32_t s01 = __byte_perm(w0, w1, sel), s23 = __byte_perm(w2, w3, sel);   // (d[4t], d[4t+1]), (d[4t+2], d[4t+3])
+                    uint32_t pa[MT][4];
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __half2 h = __hmul2(*reinterpret_cast<const __half2*>(&pf[mt][e]), *reinterpret_cast<const __half2*>(e < 2 ? &s01 : &s23));
+                            pa[mt][e] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                    if (QF == 1) {
+#pragma unroll
+                        for (int c2 = 0; c2 < 2; ++c2) {
+                            const int ch = 2 * blk + c2;   // 16 features: n-tiles 2 ch and 2 ch + 1
+                            uint32_t r0, r1;
+                            ldsm_b8_t(ld_addr + 16 * ch, r0, r1);
+                            const uint32_t x0 = r0 ^ 0x80808080u, x1 = r1 ^ 0x80808080u;
+#pragma unroll
+                            for (int mt = 0; mt < MT; ++mt) {
+                                mma16816(o[mt][2 * ch], pa[mt], value_pair(x0, 0x4140, bias), value_pair(x0, 0x4342, bias));
+                                mma16816(o[mt][2 * ch + 1], pa[mt], value_pair(x1, 0x4140, bias), value_pair(x1, 0x4342, bias));
+                            }
+                        }
+                    } else {
+                        // a block's 16 bytes: byte j holds value j (low nibble) and value j + 16 (high)
+                        uint32_t r0, r1;
+                        ldsm_b8_t(ld_addr + 16 * blk, r0, r1);
+                        const uint32_t x[4] = {r0 & 0x0F0F0F0Fu, r1 & 0x0F0F0F0Fu, (r0 >> 4) & 0x0F0F0F0Fu, (r1 >> 4) & 0x0F0F0F0Fu};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+#pragma unroll
+                            for (int mt = 0; mt < MT; ++mt)
+                                mma16816(o[mt][4 * blk + q], pa[mt], value_pair(x[q], 0x4140, bias), value_pair(x[q], 0x4342, bias));
+                    }
                 }
             }
             __syncwarp();
@@ -738,7 +776,7 @@ template <int D, int MT, int NSTAGE, int QF = 0>
 int launch(ns_gpu* g, const Params& p, int64_t B, const char* where) {
     constexpr int RG = 16 * MT;
     constexpr size_t tile = (size_t) KT * D * 2, raw_tile = (size_t) KT * raw_row_bytes<QF>(D);
-    constexpr size_t smem = (size_t) RG * D * 2 + (size_t) WARPS * (QF == 0 ? NSTAGE * 2 * tile : tile + NSTAGE * 2 * raw_tile);
+    constexpr size_t smem = (size_t) RG * D * 2 + (size_t) WARPS * (QF == 0 ? NSTAGE * 2 * tile : NSTAGE * 2 * raw_tile);
     static_assert(QF == 0 || 2 * (smem + 1024) <= 227 * 1024, "two CTAs of a quantised instance share an SM");
     static_assert(smem >= (size_t) RG * D * 2 + (size_t) WARPS * RG * (D + 2) * 4, "the merge buffer fits the stage memory");
     auto kern = gqa_decode_kernel<D, MT, NSTAGE, QF>;
@@ -792,7 +830,7 @@ int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where) {
     if (a.kt != 0) {
         if (a.D != 256 || (a.kt != 1 && a.kt != 2)) return ns_fail(std::string(where) + ": quantised caches are q8_0 (1) or q4_0 (2) with heads of 256");
         p.groups = (R + 15) / 16;
-        return a.kt == 1 ? launch<256, 1, 2, 1>(g, p, a.B, where) : launch<256, 1, 3, 2>(g, p, a.B, where);
+        return a.kt == 1 ? launch<256, 1, 3, 1>(g, p, a.B, where) : launch<256, 1, 4, 2>(g, p, a.B, where);
     }
     if (a.D == 128) {
         if (R <= 16) {
