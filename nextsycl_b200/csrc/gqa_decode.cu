@@ -271,17 +271,18 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
                         cp_async16(smem_u32(vs + swz<ROWB>(r, c)), vbase + off, ok);
                     }
                 } else {
+                    // a tile's raw rows are one run of KT * RAWB bytes in the cache and in the stage alike
                     uint8_t* kr = w_s + stage * (2 * RAW_TILE);
                     uint8_t* vr = kr + RAW_TILE;
+                    const int64_t at = j0 * RAWB;
+                    const int valid = (int) min((int64_t) RAW_TILE, (jend - j0) * RAWB);   // rows past the split: zeros (scale 0)
 #pragma unroll
                     for (int i = 0; i < (KT * RAW_CPR + 31) / 32; ++i) {
-                        const int idx = i * 32 + lane;
-                        if (idx < KT * RAW_CPR) {
-                            const int r = idx / RAW_CPR, c = idx % RAW_CPR;
-                            const bool ok = j0 + r < jend;   // a row past the split: zeros (scale 0)
-                            const int64_t off = ok ? (j0 + r) * RAWB + c * 16 : 0;
-                            cp_async16(smem_u32(kr + r * RAWB + c * 16), kbase + off, ok);
-                            cp_async16(smem_u32(vr + r * RAWB + c * 16), vbase + off, ok);
+                        const int off = (i * 32 + lane) * 16;
+                        if (off < RAW_TILE) {
+                            const bool ok = off < valid;
+                            cp_async16(smem_u32(kr + off), kbase + at + (ok ? off : 0), ok);
+                            cp_async16(smem_u32(vr + off), vbase + at + (ok ? off : 0), ok);
                         }
                     }
                 }
