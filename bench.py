@@ -429,6 +429,8 @@ def measure(env, name, steps, warmup):
         step, info = wl_prefill(env, 16384, 16, 4, 128)
     elif name == "prefill_c1":
         step, info = wl_prefill(env, 2048, 16, 4, 128)
+    elif name == "prefill_q35_16k":
+        step, info = wl_prefill(env, 16384, 24, 4, 256)
     elif name == "ds2_decode_32k":
         step, info = wl_ds2_decode(env, 32768)
     elif name.startswith("mla_decode_"):
@@ -460,7 +462,7 @@ def measure(env, name, steps, warmup):
 # profiles/ (a profiler's figure, constant for a workload; not measured by this script)
 NCU_TRAFFIC = {"decode_c2": 1.073912e9 + 12.0e6, "mla_decode_32k": 37.96e6 + 0.07e6, "decode_q35_q8": 285.29e6 + 3.9e6}
 
-OTHERS_1GPU = [("prefill_16k", 10), ("prefill_c1", 50), ("decode_c2_b1", 50), ("decode_128k", 30), ("decode_c5", 30), ("decode_q35_f16", 30),
+OTHERS_1GPU = [("prefill_16k", 10), ("prefill_c1", 50), ("prefill_q35_16k", 5), ("decode_c2_b1", 50), ("decode_128k", 30), ("decode_c5", 30), ("decode_q35_f16", 30),
                ("decode_q35_q8", 30), ("decode_q35_q4", 30), ("mla_decode_4k", 50),
                ("mla_decode_32k", 50), ("mla_decode_131k", 30), ("ds2_decode_32k", 50), ("mla_prefill_c4", 3)]
 OTHERS_NGPU = [("decode_c5_split", 50), ("prefill_16k", 10), ("mla_prefill_c4", 3)]
@@ -471,6 +473,7 @@ def config_of(name, n):
         "decode_c2": "config 2: GQA decode, 1 new token, 64 query / 8 key heads, head 128, 32,768 cached fp16 tokens, batch 8 per GPU",
         "prefill_16k": "16K causal GQA prefill, 16 query / 4 key heads of 128, fp16 (config 1's geometry at the target length)",
         "prefill_c1": "config 1: causal GQA prefill, 2,048 rows, 16 query / 4 key heads of 128, fp16",
+        "prefill_q35_16k": "16K causal GQA prefill of the qwen35 geometry, 24 query / 4 key heads of 256, fp16",
         "decode_c2_b1": "config 2, one sequence",
         "decode_128k": "128K GQA decode, 64 query / 8 key heads of 128, one sequence (512 MiB of K+V)",
         "decode_c5": "config 5 on one GPU: 4 verify rows, 32 query / 4 key heads of 128, 262,144 cached tokens (512 MiB of K+V)",
