@@ -127,8 +127,9 @@ __device__ __forceinline__ uint32_t value_pair(uint32_t biased, uint32_t sel, __
 // contraction stand for keys (4t, 4t+1 | 4t+2, 4t+3) of the tile, and S is computed with its key columns in that order
 // (column n of n-tile nt is key 4 (n / 2) + 2 nt + n % 2). A value's scale depends on its key and its block of 32
 // features, so it goes onto the weights: per block, P' = half(P d[key][block]), and the values enter as the exact small
-// integers they are. The weights carry a factor 2^6 (so do the sums, it cancels in O / l) to keep P' out of the fp16
-// subnormals: P <= 64, d <= 65504 / 127, P' <= 33,024.
+// integers they are. The weights carry a factor (so do the sums, it cancels in O / l) to keep P' out of the fp16
+// subnormals without leaving its range: 2^6 for q8_0 (d <= 65504 / 127: P' <= 33,024), 2^2 for q4_0 (d <= 65504 / 8:
+// P' <= 32,752).
 template <int QF>
 __host__ __device__ constexpr int frag_chunk(int t, int i) { return QF == 1 ? 2 * t + (i & 1) + 8 * (i >> 1) : 2 * t + i; }
 // first of the two consecutive features in pair `half` (0: fragment k 2t, 2t+1; 1: k 2t+8, 2t+9) of lane t in k-step ks
@@ -403,7 +404,8 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
                     float pv[4], sum = 0.f;
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        pv[e] = ex2_approx(x[e] - (QF == 0 ? ref : ref - 6.0f));   // quantised values: weights and sums times 2^6
+                        // quantised values: weights and sums times 2^6 (q8_0) or 2^2 (q4_0), see frag_feature
+                        pv[e] = ex2_approx(x[e] - (QF == 0 ? ref : QF == 1 ? ref - 6.0f : ref - 2.0f));
                         sum += pv[e];
                     }
                     l[mt][hh] = l[mt][hh] * c + sum;   // this lane's share; the quad's shares are added at the end

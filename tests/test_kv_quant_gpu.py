@@ -92,6 +92,31 @@ def test_decode_over_a_quantised_cache(gpu, kt, T, kv):
 
 
 @pytest.mark.parametrize("kt", [1, 2])
+@pytest.mark.parametrize("amp", [5000.0, 0.05])
+def test_decode_with_large_and_small_values(gpu, kt, amp):
+    """The decode kernel puts a value's scale onto the softmax weight (times 2^6) as a half: values near the top of the
+    fp16 range must not overflow that product, small ones must not lose it to subnormals. Relative tolerance only."""
+    T, Hq, Hkv, D, kv = 1, 24, 4, 256, 2100
+    cap, p0 = kv, kv - T
+    k, v = rows(1290 + kt, kv, Hkv)
+    v *= np.float32(amp)
+    dkc, dvc = store(gpu, kt, k, v, kv, Hkv, cap, 0)
+    q = W.rng(1291, kt).standard_normal((T, Hq * D), dtype=np.float32)
+    dq, out = DevBuf.of(gpu, q), DevBuf(gpu, T * Hq * D * 4)
+    sc = DevBuf(gpu, max(int(gpu.api.ns_q35_attn_decode_scratch(T, Hq, Hkv, D, p0)), 1) * 4)
+    check(gpu.api, gpu.api.ns_q35_attn_decode_kv(gpu.raw, kt, dq.ptr, Hq * D, dkc.ptr, dvc.ptr, T, Hq, Hkv, D, cap, p0, out.ptr, sc.ptr), "decode_kv")
+    gpu.sync()
+    got = out.read(np.float32).reshape(T, Hq * D).astype(np.float64)
+    rb = O.q_row_bytes(kt)
+    kq = O.kv_dequant(kt, dkc.read(np.uint8).reshape(Hkv, cap, rb), Hkv, cap, kv)
+    vq = O.kv_dequant(kt, dvc.read(np.uint8).reshape(Hkv, cap, rb), Hkv, cap, kv)
+    want = np.asarray(O.gqa_flash_decode(q, kq, vq, T, Hq, Hkv, D, kv, p0), np.float64)
+    assert np.isfinite(got).all()
+    d = np.abs(got - want)
+    assert (d <= ABS * amp + REL * np.abs(want)).all(), f"amp {amp}: max abs {d.max():.3e} against values of {np.abs(want).max():.3e}"
+
+
+@pytest.mark.parametrize("kt", [1, 2])
 def test_prompt_over_a_quantised_cache(gpu, kt):
     T, Hq, Hkv, D, p0 = 70, 12, 2, 256, 130
     kv, cap = p0 + T, p0 + T + 9
