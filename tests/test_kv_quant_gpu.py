@@ -92,6 +92,28 @@ def test_decode_over_a_quantised_cache(gpu, kt, T, kv):
 
 
 @pytest.mark.parametrize("kt", [1, 2])
+@pytest.mark.parametrize("kv", [1, 2, 3, 15, 16, 17, 31, 33, 64, 65, 130])
+def test_decode_short_contexts_and_tile_edges(gpu, kt, kv):
+    """The quantised decode takes a tile's keys in a permuted order (four consecutive keys a lane): contexts that end
+    anywhere inside a 16-key tile, and verify rows whose last visible key differs, must mask exactly the right ones."""
+    T = min(kv, 3)
+    Hq, Hkv, D = 12, 2, 256
+    cap, p0 = kv + 2, kv - T
+    k, v = rows(1300 + kt + kv, kv, Hkv)
+    dkc, dvc = store(gpu, kt, k, v, kv, Hkv, cap, 0)
+    q = W.rng(1301, kv).standard_normal((T, Hq * D), dtype=np.float32)
+    dq, out = DevBuf.of(gpu, q), DevBuf(gpu, T * Hq * D * 4)
+    sc = DevBuf(gpu, max(int(gpu.api.ns_q35_attn_decode_scratch(T, Hq, Hkv, D, p0)), 1) * 4)
+    check(gpu.api, gpu.api.ns_q35_attn_decode_kv(gpu.raw, kt, dq.ptr, Hq * D, dkc.ptr, dvc.ptr, T, Hq, Hkv, D, cap, p0, out.ptr, sc.ptr), "decode_kv")
+    gpu.sync()
+    got = out.read(np.float32).reshape(T, Hq * D)
+    rb = O.q_row_bytes(kt)
+    kq = O.kv_dequant(kt, dkc.read(np.uint8).reshape(Hkv, cap, rb), Hkv, cap, kv)
+    vq = O.kv_dequant(kt, dvc.read(np.uint8).reshape(Hkv, cap, rb), Hkv, cap, kv)
+    assert_close(got, O.gqa_flash_decode(q, kq, vq, T, Hq, Hkv, D, kv, p0), f"kt {kt} kv {kv}")
+
+
+@pytest.mark.parametrize("kt", [1, 2])
 @pytest.mark.parametrize("amp", [5000.0, 0.05])
 def test_decode_with_large_and_small_values(gpu, kt, amp):
     """The decode kernel puts a value's scale onto the softmax weight (times 2^6) as a half: values near the top of the
