@@ -87,9 +87,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     uint64_t* bars = (uint64_t*) (c_s + NSTAGE * TILE_BYTES);
     uint64_t* q_full = bars + 0;               // Q's shared-memory part landed
     uint64_t* qt_full = bars + 1;              // Q's tensor-memory part written (128 arrivals)
-    uint64_t* c_full = bars + 2;               // [NSTAGE]
-    uint64_t* c_empty = c_full + NSTAGE;       // [NSTAGE] (both products of the tile done)
-    uint64_t* s_full = c_empty + NSTAGE;       // [2]
+    uint64_t* c_full = bars + 2;               // [NSTAGE] the tile's late chunks landed: the four this CTA's P V reads
+    uint64_t* c_empty = c_full + NSTAGE;       // [NSTAGE] (both products of the tile done: the late chunks are free)
+    uint64_t* e_full = c_empty + NSTAGE;       // [NSTAGE] the tile's early chunks landed: the ones only S reads
+    uint64_t* k_free = e_full + NSTAGE;        // [NSTAGE] S is through with the early chunks
+    uint64_t* s_full = k_free + NSTAGE;        // [2]
     uint64_t* p_full = s_full + 2;             // [2]
     uint64_t* pv_done = p_full + 2;            // [1]
     uint64_t* o_final = pv_done + 1;              // [1] the last P V done
@@ -112,6 +114,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (int s = 0; s < NSTAGE; ++s) {
             mbar_init(smem_u32(c_full + s), 1);
             mbar_init(smem_u32(c_empty + s), 1);
+            mbar_init(smem_u32(e_full + s), 1);
+            mbar_init(smem_u32(k_free + s), 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(smem_u32(s_full + s), 1);
@@ -144,13 +148,32 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tma_load_3d(smem_u32(q_s + c * (BM * 128)), &tm_q, QT + c * 64, h0, t, smem_u32(q_full));
             }
             bool ok = true;
-            for (int j = 0; j < ntiles && ok; ++j) {
+            // A stage is refilled in two parts. The chunks only S reads (the other half's four and, with 576-wide rows,
+            // the ninth) are free as soon as S(j-2) is done, long before P(j-2) V(j-2) frees the four this CTA's P V
+            // reads; S(j) starts on them while the late four are still on their way.
+            constexpr int NCH = CR / 64, NLATE = DVH / 64, NEARLY = NCH - NLATE;
+            auto chunk_load = [&](int j, int c, uint64_t* bar) {
+                tma_load_3d(smem_u32(c_s + (j % NSTAGE) * TILE_BYTES + c * (BN * 128)), &tm_c, c * 64, (int) (jbeg + (int64_t) j * BN), t * p.zmul, smem_u32(bar));
+            };
+            auto load_early = [&](int j) {
+                const int s = j % NSTAGE;
+                if (j >= NSTAGE) ok = mbar_wait(smem_u32(k_free + s), ((uint32_t) (j / NSTAGE) & 1) ^ 1, abort_flag, p.status, 402);
+                if (!ok) return;
+                mbar_expect_tx(smem_u32(e_full + s), NEARLY * BN * 128);
+                for (int c = 0; c < NCH; ++c)
+                    if (c / NLATE != hv) chunk_load(j, c, e_full + s);
+            };
+            auto load_late = [&](int j) {
                 const int s = j % NSTAGE;
                 if (j >= NSTAGE) ok = mbar_wait(smem_u32(c_empty + s), ((uint32_t) (j / NSTAGE) & 1) ^ 1, abort_flag, p.status, 401);
-                if (!ok) break;
-                mbar_expect_tx(smem_u32(c_full + s), TILE_BYTES);
-                uint8_t* dst = c_s + s * TILE_BYTES;
-                for (int c = 0; c < CR / 64; ++c) tma_load_3d(smem_u32(dst + c * (BN * 128)), &tm_c, c * 64, (int) (jbeg + (int64_t) j * BN), t * p.zmul, smem_u32(c_full + s));
+                if (!ok) return;
+                mbar_expect_tx(smem_u32(c_full + s), NLATE * BN * 128);
+                for (int c = hv * NLATE; c < (hv + 1) * NLATE; ++c) chunk_load(j, c, c_full + s);
+            };
+            load_early(0);
+            for (int j = 0; j < ntiles && ok; ++j) {
+                if (j + 1 < ntiles) load_early(j + 1);   // S(j-1) is done before P(j-2) V(j-2) is
+                if (ok) load_late(j);
             }
         }
     } else if (warp == 5) {
@@ -163,18 +186,39 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // descriptors: everything but the start address is fixed, and the address field (bits 0..13, in 16-byte units)
             // cannot carry into the next field for any shared-memory address, so a step is one 32-bit add
             const uint64_t q_desc0 = smem_desc_sw128(smem_u32(q_s), 16, 1024);
-            auto issue_qk = [&](int j) {
+            // S(j) in two parts: over the early chunks when they have landed, over the late four when those have
+            auto qk_step = [&](uint64_t c_desc0, uint32_t d, int k, uint32_t acc) {
+                const uint64_t bd = c_desc0 + (uint64_t) (((k / 4) * (BN * 128) + (k % 4) * 32) >> 4);
+                if (k < QT / 16) {
+                    mma_ts(d, tmem + (uint32_t) (Q_COL + k * 8), bd, idesc_qk, acc);
+                } else {
+                    const int ks = k - QT / 16;
+                    mma_ss(d, q_desc0 + (uint64_t) (((ks / 4) * (BM * 128) + (ks % 4) * 32) >> 4), bd, idesc_qk, acc);
+                }
+            };
+            constexpr int KLATE = DVH / 16;   // k-steps over the late chunks: 16
+            auto issue_qk_early = [&](int j) {
                 const uint64_t c_desc0 = smem_desc_sw128(smem_u32(c_s + (j % NSTAGE) * TILE_BYTES), 16, 1024);
                 const uint32_t d = tmem + (uint32_t) (S_COL + (j & 1) * BN);
+                if (hv == 0) {
 #pragma unroll
-                for (int k = 0; k < CR / 16; ++k) {
-                    const uint64_t bd = c_desc0 + (uint64_t) (((k / 4) * (BN * 128) + (k % 4) * 32) >> 4);
-                    if (k < QT / 16) {
-                        mma_ts(d, tmem + (uint32_t) (Q_COL + k * 8), bd, idesc_qk, k > 0);
-                    } else {
-                        const int ks = k - QT / 16;
-                        mma_ss(d, q_desc0 + (uint64_t) (((ks / 4) * (BM * 128) + (ks % 4) * 32) >> 4), bd, idesc_qk, 1);
-                    }
+                    for (int k = KLATE; k < CR / 16; ++k) qk_step(c_desc0, d, k, k > KLATE);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < CR / 16; ++k)
+                        if (k < KLATE || k >= 2 * KLATE) qk_step(c_desc0, d, k, k > 0);
+                }
+                mma_commit(smem_u32(k_free + j % NSTAGE));
+            };
+            auto issue_qk_late = [&](int j) {
+                const uint64_t c_desc0 = smem_desc_sw128(smem_u32(c_s + (j % NSTAGE) * TILE_BYTES), 16, 1024);
+                const uint32_t d = tmem + (uint32_t) (S_COL + (j & 1) * BN);
+                if (hv == 0) {
+#pragma unroll
+                    for (int k = 0; k < KLATE; ++k) qk_step(c_desc0, d, k, 1);
+                } else {
+#pragma unroll
+                    for (int k = KLATE; k < 2 * KLATE; ++k) qk_step(c_desc0, d, k, 1);
                 }
                 mma_commit(smem_u32(s_full + (j & 1)));
             };
@@ -194,7 +238,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // (and the S buffer it overwrites has been consumed: P(qk-2) V(qk-2) issued), P(pv) V(pv) as soon as the
             // softmax published P(pv). A fixed order would queue P(j) V(j) - which frees tile j's stage for the next
             // load - behind S(j+1), which waits for a load that was itself waiting for a stage.
-            int qk = 0, pv = 0;
+            int qk = 0, qe = 0, pv = 0;   // next tile for S's late part, for S's early part, for P V
             uint32_t idle = 0;
             while (ok && pv < ntiles) {
                 bool did = false;
@@ -205,9 +249,15 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     ++pv;
                     did = true;
                 }
-                if (qk < ntiles && qk - pv < 2 && mbar_try(smem_u32(c_full + qk % NSTAGE), (uint32_t) (qk / NSTAGE) & 1)) {
+                if (qe < ntiles && qe - pv < 2 && mbar_try(smem_u32(e_full + qe % NSTAGE), (uint32_t) (qe / NSTAGE) & 1)) {
                     fence_after_sync();
-                    issue_qk(qk);
+                    issue_qk_early(qe);
+                    ++qe;
+                    did = true;
+                }
+                if (qk < qe && mbar_try(smem_u32(c_full + qk % NSTAGE), (uint32_t) (qk / NSTAGE) & 1)) {
+                    fence_after_sync();
+                    issue_qk_late(qk);
                     ++qk;
                     did = true;
                 }
