@@ -143,9 +143,12 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_expect_tx(smem_u32(q_full), QS_BYTES);
             // every CTA of the grid reads the same Q: each starts at another chunk, so that at any instant the requests spread
             // over more L2 lines than one chunk's
+            // Q's shared-memory part: the chunks that meet the tile's early chunks (slot e: chunk 4 + e for the CTA of output
+            // half 0, chunks 0..3 and then the ninth for half 1); the four that meet the late chunks go to tensor memory
             for (int cc = 0; cc < QS / 64; ++cc) {
-                const int c = (cc + split) % (QS / 64);
-                tma_load_3d(smem_u32(q_s + c * (BM * 128)), &tm_q, QT + c * 64, h0, t, smem_u32(q_full));
+                const int e = (cc + split) % (QS / 64);
+                const int chunk = hv == 0 ? 4 + e : (e < 4 ? e : 8);
+                tma_load_3d(smem_u32(q_s + e * (BM * 128)), &tm_q, chunk * 64, h0, t, smem_u32(q_full));
             }
             bool ok = true;
             // A stage is refilled in two parts. The chunks only S reads (the other half's four and, with 576-wide rows,
@@ -187,13 +190,16 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // cannot carry into the next field for any shared-memory address, so a step is one 32-bit add
             const uint64_t q_desc0 = smem_desc_sw128(smem_u32(q_s), 16, 1024);
             // S(j) in two parts: over the early chunks when they have landed, over the late four when those have
-            auto qk_step = [&](uint64_t c_desc0, uint32_t d, int k, uint32_t acc) {
-                const uint64_t bd = c_desc0 + (uint64_t) (((k / 4) * (BN * 128) + (k % 4) * 32) >> 4);
-                if (k < QT / 16) {
-                    mma_ts(d, tmem + (uint32_t) (Q_COL + k * 8), bd, idesc_qk, acc);
+            // k-step k = 4 chunk + step. Q's operand: tensor memory for the four late chunks (the part of S that the
+            // softmax waits for runs at the faster rate), shared memory for the early ones
+            auto qk_step = [&](uint64_t c_desc0, uint32_t d, int k, uint32_t acc, int half) {
+                const int chunk = k / 4, step = k % 4;
+                const uint64_t bd = c_desc0 + (uint64_t) ((chunk * (BN * 128) + step * 32) >> 4);
+                if (chunk < 8 && chunk / 4 == half) {
+                    mma_ts(d, tmem + (uint32_t) (Q_COL + ((chunk - 4 * half) * 4 + step) * 8), bd, idesc_qk, acc);
                 } else {
-                    const int ks = k - QT / 16;
-                    mma_ss(d, q_desc0 + (uint64_t) (((ks / 4) * (BM * 128) + (ks % 4) * 32) >> 4), bd, idesc_qk, acc);
+                    const int e = half == 0 ? chunk - 4 : (chunk < 4 ? chunk : 4);
+                    mma_ss(d, q_desc0 + (uint64_t) ((e * (BM * 128) + step * 32) >> 4), bd, idesc_qk, acc);
                 }
             };
             constexpr int KLATE = DVH / 16;   // k-steps over the late chunks: 16
@@ -202,11 +208,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const uint32_t d = tmem + (uint32_t) (S_COL + (j & 1) * BN);
                 if (hv == 0) {
 #pragma unroll
-                    for (int k = KLATE; k < CR / 16; ++k) qk_step(c_desc0, d, k, k > KLATE);
+                    for (int k = KLATE; k < CR / 16; ++k) qk_step(c_desc0, d, k, k > KLATE, 0);
                 } else {
 #pragma unroll
                     for (int k = 0; k < CR / 16; ++k)
-                        if (k < KLATE || k >= 2 * KLATE) qk_step(c_desc0, d, k, k > 0);
+                        if (k < KLATE || k >= 2 * KLATE) qk_step(c_desc0, d, k, k > 0, 1);
                 }
                 mma_commit(smem_u32(k_free + j % NSTAGE));
             };
@@ -215,10 +221,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const uint32_t d = tmem + (uint32_t) (S_COL + (j & 1) * BN);
                 if (hv == 0) {
 #pragma unroll
-                    for (int k = 0; k < KLATE; ++k) qk_step(c_desc0, d, k, 1);
+                    for (int k = 0; k < KLATE; ++k) qk_step(c_desc0, d, k, 1, 0);
                 } else {
 #pragma unroll
-                    for (int k = KLATE; k < 2 * KLATE; ++k) qk_step(c_desc0, d, k, 1);
+                    for (int k = KLATE; k < 2 * KLATE; ++k) qk_step(c_desc0, d, k, 1, 1);
                 }
                 mma_commit(smem_u32(s_full + (j & 1)));
             };
@@ -283,7 +289,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int r = tid;
         const uint32_t lane_base = (uint32_t) (warp * 32) << 16;
         const bool head_live = h0 + r < p.H;
-        // ---- the first 256 features of this head's query into tensor memory: column i = features (2i, 2i+1)
+        // ---- the 256 features of this head's query that meet the tile's late chunks (features 256 hv .. 256 hv + 255) into
+        // tensor memory: column i = features (256 hv + 2i, + 1)
         {
             const uint4* src = reinterpret_cast<const uint4*>(p.q + ((int64_t) t * p.H + (head_live ? h0 + r : 0)) * CR);
 #pragma unroll
@@ -292,7 +299,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 uint32_t w[32];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    const uint4 x = head_live ? src[c * 8 + e] : make_uint4(0, 0, 0, 0);
+                    const uint4 x = head_live ? src[(hv * (QT / 64) + c) * 8 + e] : make_uint4(0, 0, 0, 0);
                     w[4 * e] = x.x, w[4 * e + 1] = x.y, w[4 * e + 2] = x.z, w[4 * e + 3] = x.w;
                 }
                 tmem_st32(tmem + lane_base + (uint32_t) (Q_COL + c * 32), w);
