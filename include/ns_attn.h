@@ -267,6 +267,9 @@ int ns_b200_mla_decode(ns_gpu* g, const void* q, const void* cache, int64_t T, i
  * Epochs count from 1 and must increase by one per step on every rank (two buffers alternate by epoch parity, so a rank
  * may run one step ahead of its peers, never two). With epoch 0 in both calls the step number is kept in the rank's own
  * mailbox and advanced by the combine, so the pair can be recorded once (ns_q35_graph_begin/end) and replayed.
+ * A rank whose range is empty (kv_local 0: a context shorter than the ranks' share) still calls ns_b200_kvsplit_decode -
+ * caches and scratch may be null - so that its (empty) partial and its flag reach the others. After a combine gave up
+ * (code 701) the ranks' step numbers no longer agree: zero every mailbox and restart the epochs before the next step.
  * A mailbox is ns_b200_kvsplit_mailbox_bytes bytes, zeroed once. */
 int64_t ns_b200_kvsplit_mailbox_bytes(int64_t nranks, int64_t T, int64_t Hq, int64_t D);
 int64_t ns_b200_kvsplit_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t kv_local);
@@ -286,7 +289,8 @@ int ns_b200_ipc_close(ns_gpu* g, void* ptr);
  * not hit the device-wide synchronisation a cudaMalloc brings. The split partials go to an array built into the
  * library (NS_B200_STATIC_SCRATCH_FLOATS floats = 16 MiB, resident on every GPU the library is used on until the
  * process exits). The call allocates nothing, on the device or through any library. Arguments as ns_b200_gqa_decode;
- * -1 with a message when B*T*Hq*splits(max_kv)*(D+2) floats exceed the array.
+ * -1 with a message when B*T*Hq*S*(D+2) floats exceed the array, S = min(ceil(max_kv/64), ceil(296/Hkv)): the most key
+ * splits any sequence of up to max_kv keys has.
  * The first call on each device looks up the array's device address and queues a one-thread set-up kernel: make that
  * first call before starting any stream capture. All calls share the one array, which keeps whatever the last call
  * left in it (nothing in it needs to start at zero: each call writes every partial before reading it); two calls

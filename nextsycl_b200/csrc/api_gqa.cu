@@ -134,7 +134,7 @@ int ns_nhs_attn_decode(ns_gpu* g, const float* q, int64_t qs, const void* kc, co
 
 int64_t ns_b200_gqa_decode_scratch(int64_t B, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t max_kv) {
     if (B < 1 || T < 1 || Hkv < 1 || max_kv < 1) return 0;
-    const int64_t ns = ns_dec_splits(max_kv, Hkv);
+    const int64_t ns = ns_dec_splits_bound(max_kv, Hkv);   // shorter sequences of the batch may need more splits than the longest
     return ns > 1 ? B * T * Hq * ns * (D + 2) : 0;
 }
 
@@ -148,7 +148,7 @@ int ns_b200_gqa_decode(ns_gpu* g, const void* q, int64_t qs, int64_t q_seq, cons
     if (max_kv < T || max_kv >= ((int64_t) 1 << 31)) return ns_fail(std::string(name) + ": max_kv between T and 2^31");
     if (qs % 8 != 0 || q_seq % 8 != 0 || ((uintptr_t) q & 15) != 0) return ns_fail(std::string(name) + ": query rows 16-byte aligned");
     if (!q || !seqs || !out) return ns_fail(std::string(name) + ": a null buffer");
-    const int64_t ns = ns_dec_splits(max_kv, Hkv);
+    const int64_t ns = ns_dec_splits_bound(max_kv, Hkv);
     if (ns > 1 && !scratch) return ns_fail(std::string(name) + ": no scratch");
     GqaDecodeArgs a{};
     a.q = q;
@@ -172,8 +172,10 @@ int64_t ns_b200_kvsplit_mailbox_bytes(int64_t nranks, int64_t T, int64_t Hq, int
 }
 
 int64_t ns_b200_kvsplit_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t kv_local) {
-    if (T < 1 || Hkv < 1 || kv_local < 1) return 0;
-    return T * Hq * ns_dec_splits(kv_local, Hkv) * (D + 2);   // every row keeps its partial, also with one split
+    if (T < 1 || Hkv < 1 || kv_local < 1) return 0;   // a rank without keys needs none
+    // every row keeps its partial, also with one split; rows below the last see fewer keys of the last rank's slice and
+    // may need more splits than kv_local itself does, hence the bound
+    return T * Hq * ns_dec_splits_bound(kv_local, Hkv) * (D + 2);
 }
 
 int ns_b200_kvsplit_decode(ns_gpu* g, const void* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
@@ -184,11 +186,13 @@ int ns_b200_kvsplit_decode(ns_gpu* g, const void* q, int64_t qs, const void* kc,
     if (ns_enter(g, name)) return -1;
     if (T < 1 || T > 8 || !shape_ok(Hq, Hkv, D)) return ns_fail(std::string(name) + ": 1..8 rows, heads of 128 or 256, 1..16 query heads a key head");
     if (nranks < 1 || nranks > 64 || rank < 0 || rank >= nranks) return ns_fail(std::string(name) + ": rank within 1..64 ranks");
-    if (kv_local < 1 || kv_local >= ((int64_t) 1 << 31) || key_base < 0 || p0 < 0 || p0 + T >= ((int64_t) 1 << 40))
-        return ns_fail(std::string(name) + ": a key range of 1 .. 2^31 keys");
+    if (kv_local < 0 || kv_local >= ((int64_t) 1 << 31) || key_base < 0 || p0 < 0 || p0 + T >= ((int64_t) 1 << 40))
+        return ns_fail(std::string(name) + ": a key range of 0 .. 2^31 keys");
     if (epoch < 0) return ns_fail(std::string(name) + ": epochs count from 1 (0: the mailbox's own counter)");
     if (qs % 8 != 0 || ((uintptr_t) q & 15) != 0) return ns_fail(std::string(name) + ": query rows 16-byte aligned");
-    if (!q || !kc || !vc || !scratch || !mailboxes) return ns_fail(std::string(name) + ": a null buffer");
+    // a rank past the end of a short context (kv_local 0) streams nothing and still publishes its empty partials, so the
+    // others' combines do not wait for it; it needs no caches and no scratch
+    if (!q || !mailboxes || (kv_local > 0 && (!kc || !vc || !scratch))) return ns_fail(std::string(name) + ": a null buffer");
     GqaDecodeArgs a{};
     a.q = q;
     a.qs = qs;
@@ -198,7 +202,7 @@ int ns_b200_kvsplit_decode(ns_gpu* g, const void* q, int64_t qs, const void* kc,
     a.out = nullptr;
     a.part = scratch;
     a.B = 1, a.T = T, a.Hq = Hq, a.Hkv = Hkv, a.D = D;
-    a.ns_max = ns_dec_splits(kv_local, Hkv);
+    a.ns_max = std::max<int64_t>(1, ns_dec_splits_bound(kv_local, Hkv));
     a.q_f32 = 0, a.out_f32 = 0;
     a.mailboxes = (float* const*) mailboxes;
     a.rank = (int) rank;

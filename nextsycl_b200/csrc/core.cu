@@ -10,6 +10,10 @@
 namespace {
 thread_local std::string g_err;
 
+// A ticket names one of the last NS_RING events; an older one's slot has been reused by a newer mark, so it is refused
+// rather than silently standing for that newer event.
+bool ticket_live(const ns_gpu* g, int64_t ticket) { return ticket >= 0 && ticket < g->next_ticket && ticket >= g->next_ticket - NS_RING; }
+
 cudaEvent_t ticket_event(ns_gpu* g, int64_t ticket) {
     // caller holds g->mu
     if (g->ring.empty()) g->ring.assign((size_t) NS_RING, nullptr);
@@ -263,7 +267,7 @@ int ns_stream_copy(ns_gpu* g, void* dst, const void* src, size_t bytes, const in
     std::lock_guard<std::mutex> lk(g->mu);
     cudaStream_t s = g->lane[lane];
     for (int i = 0; i < ndeps; ++i) {
-        if (after[i] < 0 || after[i] >= g->next_ticket) return ns_fail("ns_stream_copy: no such ticket");
+        if (!ticket_live(g, after[i])) return ns_fail("ns_stream_copy: no such ticket (or older than the last 65,536 marks)");
         NS_CUDA(cudaStreamWaitEvent(s, ticket_event(g, after[i]), 0), "ns_stream_copy");
     }
     if (bytes) NS_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, s), "ns_stream_copy");
@@ -277,7 +281,7 @@ int ns_stream_copy(ns_gpu* g, void* dst, const void* src, size_t bytes, const in
 int ns_await(ns_gpu* g, int64_t ticket) {
     if (ns_enter(g, "ns_await")) return -1;
     std::lock_guard<std::mutex> lk(g->mu);
-    if (ticket < 0 || ticket >= g->next_ticket) return ns_fail("ns_await: no such ticket");
+    if (!ticket_live(g, ticket)) return ns_fail("ns_await: no such ticket (or older than the last 65,536 marks)");
     NS_CUDA(cudaStreamWaitEvent(g->compute, ticket_event(g, ticket), 0), "ns_await");
     return 0;
 }
@@ -291,7 +295,7 @@ int ns_elapsed(ns_gpu* g, int64_t t0, int64_t t1, double* ns) {
     cudaEvent_t a, b;
     {
         std::lock_guard<std::mutex> lk(g->mu);
-        if (t0 < 0 || t1 < 0 || t0 >= g->next_ticket || t1 >= g->next_ticket) return ns_fail("ns_elapsed: no such ticket");
+        if (!ticket_live(g, t0) || !ticket_live(g, t1)) return ns_fail("ns_elapsed: no such ticket (or older than the last 65,536 marks)");
         a = ticket_event(g, t0);
         b = ticket_event(g, t1);
     }
@@ -318,6 +322,9 @@ int ns_sync(ns_gpu* g) {
         const int code = *(volatile int*) g->status_host;
         *(volatile int*) g->status_host = 0;
         if (g->dec_sync) cudaMemset(g->dec_sync, 0, 2 * NS_DEC_SYNC_SLOTS * sizeof(unsigned int));   // counters a failed step may have left set
+        if (code == 802)
+            return ns_fail("ns_sync: a decode row needed more key splits than its call's max_kv laid out (code 802): a sequence is longer than "
+                           "max_kv; its output is not valid");
         return ns_fail("ns_sync: a kernel gave up a bounded wait (code " + std::to_string(code) + "); its output is not valid");
     }
     return 0;

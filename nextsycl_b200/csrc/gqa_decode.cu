@@ -615,6 +615,18 @@ __device__ __forceinline__ void merge_leave(const Params& p, int b, int hk) {
     }
 }
 
+// A row's split count as the merge may use it: never more than the partial buffer was laid out for. A row that needs
+// more (a sequence longer than the max_kv the caller promised) raises status 802 - its keys past the layout were never
+// streamed - instead of reading its neighbours' partials.
+__device__ __forceinline__ int clamp_splits(const Params& p, int64_t nsr) {
+    if (nsr <= p.ns_max) return (int) nsr;
+    if (threadIdx.x == 0 && p.status) {
+        *(volatile int*) p.status = 802;
+        __threadfence_system();
+    }
+    return p.ns_max;
+}
+
 // the splits of each (sequence, row, head) merged: attn.cpp:352-368's formula; rows with one split were written by
 // the first kernel
 constexpr int MERGE_THREADS = 256;
@@ -628,7 +640,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) gqa_merge_kernel(const Params p
     if (p.sync) merge_enter(p, b, hk);
     else pdl_wait();   // the split kernel's partials
     const ns_b200_seq seq = p.seqs ? p.seqs[b] : p.one;
-    const int nsr = (int) ns_dec_splits(row_keys(seq, t), p.Hkv);
+    const int nsr = clamp_splits(p, ns_dec_splits(row_keys(seq, t), p.Hkv));
     if (nsr == 1) {
         if (p.sync) merge_leave(p, b, hk);
         return;
@@ -655,7 +667,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) gqa_merge_push_kernel(const Par
     const int t = (int) (rh / p.Hq);
     const ns_b200_seq seq = p.seqs ? p.seqs[0] : p.one;
     const int64_t kv = row_keys(seq, t);
-    const int nsr = kv > 0 ? (int) ns_dec_splits(kv, p.Hkv) : 0;
+    const int nsr = kv > 0 ? clamp_splits(p, ns_dec_splits(kv, p.Hkv)) : 0;
     float mx, L;
     const float2 a = lse::merge_row<D, MERGE_THREADS>(p.part + rh * p.ns_max * (D + 2), D + 2, nsr, mx, L, sm);
     const int64_t rows = (int64_t) p.T * p.Hq;
@@ -894,7 +906,7 @@ extern "C" int ns_b200_gqa_decode_static(ns_gpu* g, const void* q, int64_t qs, i
     if (max_kv < T || max_kv >= ((int64_t) 1 << 31)) return ns_fail(std::string(name) + ": max_kv between T and 2^31");
     if (qs % 8 != 0 || q_seq % 8 != 0 || ((uintptr_t) q & 15) != 0) return ns_fail(std::string(name) + ": query rows 16-byte aligned");
     if (!q || !seqs || !out) return ns_fail(std::string(name) + ": a null buffer");
-    const int64_t ns = ns_dec_splits(max_kv, Hkv);
+    const int64_t ns = ns_dec_splits_bound(max_kv, Hkv);   // as ns_b200_gqa_decode lays its partials out
     const int64_t need = ns > 1 ? B * T * Hq * ns * (D + 2) : 0;
     if (need > (int64_t) NS_B200_STATIC_SCRATCH_FLOATS)
         return ns_fail(std::string(name) + ": this batch needs " + std::to_string(need) + " floats of split partials, the built-in scratch holds " +

@@ -18,6 +18,13 @@ __host__ __device__ inline int64_t ns_dec_splits(int64_t kv, int64_t Hkv) {
     const int64_t kb = ns_dec_split(kv, Hkv);
     return (kv + kb - 1) / kb;
 }
+// The most splits any row of 1 .. max_kv keys can have. ns_dec_splits is not monotone in kv (each 64-key step of the
+// split size lowers the count), so a partial buffer shared by rows of several lengths is laid out for this bound, never
+// for the longest row's own count: kb >= 64 gives ceil(max_kv / 64), kb >= kv Hkv / 296 gives ceil(296 / Hkv).
+__host__ __device__ inline int64_t ns_dec_splits_bound(int64_t max_kv, int64_t Hkv) {
+    const int64_t a = (max_kv + 63) / 64, b = (NS_DEC_TARGET_CTAS + Hkv - 1) / Hkv;
+    return a < b ? a : b;
+}
 
 struct GqaDecodeArgs {
     const void* q;             // [B][T] rows of Hq*D, fp32 or fp16

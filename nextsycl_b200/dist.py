@@ -75,8 +75,11 @@ class KvSplit:
         elif epoch == 0:
             self.device_epochs = True   # the mailbox counts the steps itself (a recorded step can be replayed)
         api = self.gpu.api
-        check(api, api.need("ns_b200_kvsplit_decode")(self.gpu.raw, q.ptr, qs, kc.ptr, vc.ptr, self.T, self.Hq, Hkv, self.D, kv_local, key_base, p0,
-                                                      scratch.ptr, self.rank, self.nranks, self.table.ptr, epoch), "ns_b200_kvsplit_decode")
+
+        def ptr(b):   # a rank without keys (kv_local 0) passes no caches and no scratch
+            return b.ptr if b is not None else None
+        check(api, api.need("ns_b200_kvsplit_decode")(self.gpu.raw, q.ptr, qs, ptr(kc), ptr(vc), self.T, self.Hq, Hkv, self.D, kv_local, key_base, p0,
+                                                      ptr(scratch), self.rank, self.nranks, self.table.ptr, epoch), "ns_b200_kvsplit_decode")
         return epoch
 
     def combine(self, out, epoch=None, wait_us=200000):

@@ -152,6 +152,51 @@ def test_native_batch_fp16(gpu, ops):
         assert_close(got[b], want[b], f"sequence {b}")
 
 
+def _batch(gpu, ops, seed, T, Hq, Hkv, D, kvs, cap):
+    qs, seqs, want, keep = [], [], [], []
+    for b, kv in enumerate(kvs):
+        q, k, v, p0 = W.gqa_case(seed, T, Hq, Hkv, D, kv, cap=cap, seq=b)
+        qs.append(q)
+        dk, dv = DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+        keep += [dk, dv]
+        seqs.append((dk, dv, cap, p0))
+        want.append(O.gqa_flash_decode(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, cap, p0))
+    return DevBuf.of(gpu, np.stack(qs)), ops.seq_table(seqs), want, keep
+
+
+@pytest.mark.parametrize("Hq,Hkv,kvs", [(64, 8, [9000, 4736]), (32, 4, [4737, 4736, 9472]), (16, 2, [20000, 9473, 64, 18944])])
+def test_ragged_batch_where_a_shorter_sequence_needs_more_splits(gpu, ops, Hq, Hkv, kvs):
+    """The split count is not monotone in the length (8 key heads: 4,736 keys make 37 splits, 9,000 make 36), so the
+    partials are laid out for the most any length up to max_kv can need; each sequence against the oracle."""
+    T, D = 1, 128
+    cap = max(kvs)
+    dq, table, want, keep = _batch(gpu, ops, 927, T, Hq, Hkv, D, kvs, cap)
+    B = len(kvs)
+    out = DevBuf(gpu, B * T * Hq * D * 2)
+    sc = DevBuf(gpu, 4 * ops.gqa_decode_scratch(B, T, Hq, Hkv, D, cap))
+    sc.fill(0xFF)
+    ops.gqa_decode(dq, Hq * D, T * Hq * D, table, B, T, Hq, Hkv, D, cap, out, sc)
+    got = out.read(np.float16).reshape(B, T, Hq * D).astype(np.float32)
+    for b in range(B):
+        assert_close(got[b], want[b], f"sequence {b} of {kvs}")
+
+
+def test_a_sequence_longer_than_max_kv_is_reported_not_misread(gpu, ops):
+    """max_kv sizes the partials; a longer sequence makes the merge stop at the layout and the next sync fail (code 802)."""
+    from nextsycl_b200 import Error
+    T, Hq, Hkv, D = 1, 16, 2, 128
+    dq, table, want, keep = _batch(gpu, ops, 928, T, Hq, Hkv, D, [1000], 1000)
+    out = DevBuf(gpu, T * Hq * D * 2)
+    sc = DevBuf(gpu, 4 * ops.gqa_decode_scratch(1, T, Hq, Hkv, D, 100))
+    ops.gqa_decode(dq, Hq * D, T * Hq * D, table, 1, T, Hq, Hkv, D, 100, out, sc)
+    with pytest.raises(Error, match="802"):
+        gpu.sync()
+    gpu.sync()   # the status is cleared; the GPU is usable
+    sc = DevBuf(gpu, 4 * ops.gqa_decode_scratch(1, T, Hq, Hkv, D, 1000))
+    ops.gqa_decode(dq, Hq * D, T * Hq * D, table, 1, T, Hq, Hkv, D, 1000, out, sc)
+    assert_close(out.read(np.float16).reshape(T, Hq * D).astype(np.float32), want[0], "after the report")
+
+
 @pytest.mark.parametrize("B", [1, 2])
 def test_full_size_config_2(gpu, ops, B):
     """benchmark configuration 2 at full size: 64 query heads, 8 key heads, 32,768 cached tokens, batch of sequences."""

@@ -58,7 +58,9 @@ def test_handle_exchange_over_gloo(tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("nranks,T,Hq,Hkv,kv", [(2, 1, 16, 2, 1000), (4, 4, 32, 4, 5000), (8, 4, 32, 4, 20000), (3, 2, 8, 2, 130)])
+@pytest.mark.parametrize("nranks,T,Hq,Hkv,kv", [(2, 1, 16, 2, 1000), (4, 4, 32, 4, 5000), (8, 4, 32, 4, 20000), (3, 2, 8, 2, 130),
+                                                  (8, 1, 8, 2, 100),      # six of the eight ranks hold no key at all
+                                                  (2, 4, 32, 4, 9537)])   # the last rank holds 4,737 keys: its rows 0..2 see <= 4,736 and need 74 splits, not 38
 def test_all_ranks_on_one_gpu_match_the_oracle(gpu, ops, nranks, T, Hq, Hkv, kv):
     from nextsycl_b200 import DevBuf
     from nextsycl_b200 import workloads as W
@@ -76,15 +78,15 @@ def test_all_ranks_on_one_gpu_match_the_oracle(gpu, ops, nranks, T, Hq, Hkv, kv)
     keep = []
     for step in range(2):   # two steps: both mailbox buffers, and the counter's return to zero
         for r, (base, count) in enumerate(key_ranges(kv, nranks)):
-            kl = max(count, 1)
-            ks = np.ascontiguousarray(k[:, base:base + kl]) if count else np.zeros((Hkv, 1, D), np.float16)
-            vs = np.ascontiguousarray(v[:, base:base + kl]) if count else np.zeros((Hkv, 1, D), np.float16)
-            dk, dv = DevBuf.of(gpu, ks), DevBuf.of(gpu, vs)
-            sc = DevBuf(gpu, 4 * groups[r].scratch_floats(Hkv, kl))
+            if count == 0:
+                # a rank past the end of a short context still publishes (an empty partial), with no caches and no scratch
+                groups[r].decode(dq, Hq * D, None, None, Hkv, 0, base, p0, None)
+                continue
+            dk, dv = DevBuf.of(gpu, np.ascontiguousarray(k[:, base:base + count])), DevBuf.of(gpu, np.ascontiguousarray(v[:, base:base + count]))
+            sc = DevBuf(gpu, 4 * groups[r].scratch_floats(Hkv, count))
             sc.fill(0xFF)
             keep += [dk, dv, sc]
-            # a rank without keys still publishes (an empty partial): its rows see nothing of a slice that starts past them
-            groups[r].decode(dq, Hq * D, dk, dv, Hkv, kl, base if count else kv + 8, p0, sc)
+            groups[r].decode(dq, Hq * D, dk, dv, Hkv, count, base, p0, sc)
         for r in range(nranks):
             out = DevBuf(gpu, T * Hq * D * 2)
             out.fill(0xFF)
