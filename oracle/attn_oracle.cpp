@@ -3,11 +3,16 @@
 // TEST INFRASTRUCTURE ONLY. Nothing in the shipped library calls into this file; it is the checker the GPU parity
 // tests, the smoke test and the benchmark's CPU-baseline leg compare against.
 //
-// PARITY UNPINNED: the reference tree holds no golden vector, known-answer test or fixture for any attention kernel,
-// and its SYCL kernels cannot be compiled without a oneAPI toolchain. Every function below restates the arithmetic
-// of the reference file and lines it cites (where values are rounded, in which order chunks are visited, which
-// exponential is used); the summation order inside one matrix tile is hardware-defined in the reference and is a
-// plain sequential fp32 sum here.
+// PARITY: PINNED FOR THE DEEPSEEK-V4.1 FUNCTIONS, UNPINNED FOR THE REST. The reference tree holds no golden vector,
+// known-answer test or fixture for any attention kernel, and its SYCL kernels cannot be compiled without a oneAPI
+// toolchain. It does hold one importable CPU implementation of arithmetic on this path, reference/deepseek41/ds41ref.py;
+// tests/golden/make_ref_fixtures.py runs that code (its fp8_sim, rms, freqs, rope and its Ref.attention, on seeded weights)
+// and tests/test_oracle.py holds to its output: orc_ds41_attend (both numerics), orc_ds41_kv_post and orc_ds41_att_post
+// (bit for bit), the E4M3 simulation (bit for bit), the YaRN rotation, orc_ds41_idx_score, orc_ds41_block_max and
+// orc_topk. The GQA, deepseek2 and glm5next functions remain UNPINNED: each restates the arithmetic of the reference
+// file and lines it cites (where values are rounded, in which order chunks are visited, which exponential is used) and
+// is checked only against an independent numpy statement of softmax attention and its own fp64 mode. The summation
+// order inside one matrix tile is hardware-defined in the reference and is a plain sequential fp32 sum here.
 //
 // Storage: fp16 / bf16 values travel as raw uint16_t bit patterns. All functions are pure (no global state) and
 // parallelise over (row, head) with OpenMP only, so a result does not depend on the thread count.

@@ -1,7 +1,9 @@
 """ctypes front of the CPU oracle (oracle/attn_oracle.cpp -> oracle/liboracle.so).
 
 TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke test and by the benchmark's CPU-baseline leg, never by the
-library. Parity unpinned: the reference holds no golden vectors for attention (see attn_oracle.cpp's header).
+library. Parity: the deepseek41 functions are pinned to fixtures produced by running the reference's own Python
+(tests/golden/make_ref_fixtures.py); the rest is unpinned - the reference holds no golden vectors for attention (see
+attn_oracle.cpp's header).
 
 Arrays are numpy: fp32 as float32, fp16 / bf16 storage as uint16 bit patterns (`np.float16.view(np.uint16)` for fp16;
 `to_bf16_bits` below for bf16).

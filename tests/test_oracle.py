@@ -333,3 +333,95 @@ def test_ds41_indexer_steps():
     selc = np.array([[0, 9, 17], [8, 1, 2], [31, 0, 7]], np.int32)
     sel = O.ds41_cand_pos(selc, cand, 8)
     assert np.array_equal(sel[0], [0, 41, 97]) and np.array_equal(sel[2], [9 * 8 + 7, 96, 103])
+
+
+# ---- the oracle pinned to values produced by the reference's own CPU code ------------------------------------------------
+# tests/golden/ds41ref_fixtures.npz was written by tests/golden/make_ref_fixtures.py, which imports
+# reference/deepseek41/ds41ref.py and runs its functions and its Ref.attention as written (seeded weights through a stub of
+# Ref.w). The oracle functions below are therefore held to reference output, not to a restatement.
+import ref_fixtures as RF  # noqa: E402
+
+
+def test_ref_pin_e4m3_simulation_bit_exact():
+    """ds41ref.fp8_sim (:42-52) == the simulation inside orc_ds41_att_post (no rotation: rd 0), bit for bit, ties included."""
+    g = RF.load()
+    x = g["fp8_in"].reshape(1, 1, 512).copy()
+    O.ds41_att_post(x, 1, 1, 512, 0, 0, (10000.0, 1.0, 0.0, 1.0, 0.0, 0.0))
+    assert np.array_equal(x.reshape(16, 32).view(np.uint32), g["fp8_out"].view(np.uint32))
+
+
+def test_ref_pin_rms_norm():
+    """ds41ref.rms (:88-90) against the oracle's per-head RMS norm (no rotation: n_rot 0)."""
+    g = RF.load()
+    y = O.qk_norm_rope(g["rms_in"], 5, 1, 96, g["rms_w"], 1e-6, 0, 10000.0)
+    assert np.allclose(y, g["rms_out"], rtol=2e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("name", ["plain", "yarn"])
+def test_ref_pin_rotation(name):
+    """ds41ref.freqs + rope (:93-113) against the oracle's YaRN rotation with the engine's parameter mapping. The reference
+    takes the angle in float64, the kernels in float32: a value may turn by one unit in the last place of the angle."""
+    g = RF.load()
+    y = RF.yarn_of(g[f"rope_{name}_cfg"])
+    for i, p in enumerate(g[f"rope_{name}_pos"]):
+        x = g[f"rope_{name}_in"][i].copy().reshape(-1)          # 3 heads of 64
+        O.ds2_rope(x, 1, 3, 192, 64, 0, 64, int(p), *y)
+        want = g[f"rope_{name}_out"][i]
+        tol = 2e-6 + float(p) * 2.0 ** -23 * float(np.abs(want).max()) * 1.5
+        assert np.abs(x.reshape(3, 64) - want).max() <= tol, (name, int(p))
+
+
+@pytest.mark.parametrize("L", [0, 1])
+def test_ref_pin_kv_post_and_att_post_bit_exact(L):
+    """Either side of the attention, as Ref.attention runs it (:187-191 norm, rotation, simulation of the window keys;
+    :251-253 the output's rotation undone and simulated): the oracle's results equal the reference's bit for bit."""
+    d = RF.layer(RF.load(), L)
+    kv = d["kv_in"].copy()
+    ring = np.zeros((64, d["HD"]), np.uint16)
+    O.ds41_kv_post(kv, d["kv_w"], d["T"], d["HD"], 1e-6, d["RD"], 0, d["yarn"], ring, 64)
+    assert np.array_equal(kv.astype(np.float16).view(np.uint16), d["kv_f16"])
+    assert np.array_equal(kv, d["kv_f16"].view(np.float16).astype(np.float32))
+    assert np.array_equal(ring[:d["T"]], d["kv_f16"])
+    for i, r in enumerate(d["qrows"]):
+        x = d["attn_out"][i:i + 1].copy()
+        O.ds41_att_post(x, 1, d["H"], d["HD"], d["RD"], int(r), d["yarn"])
+        assert np.array_equal(x[0], d["att_post_out"][i]), (L, int(r))
+
+
+@pytest.mark.parametrize("L", [0, 1])
+def test_ref_pin_attention_with_sinks(L):
+    """Ref.attention's scores, sink and weighted sum (:236-250) over the window and the compressed keys it picks: the
+    oracle's vector-kernel numerics (fp32 throughout) to 1e-5, its XMX numerics (fp16 q and weights) within the path's bar."""
+    d = RF.layer(RF.load(), L)
+    scale = np.float32(d["HD"] ** -0.5)
+    for i in range(len(d["qrows"])):
+        r, ring, comp, sel, K = RF.row_inputs(d, i)
+        want = d["attn_out"][i]
+        vec = O.ds41_attend(d["q"][i:i + 1].copy(), ring, 64, comp, max(d["ratio"], 1), sel, K, d["sinks"], 1, d["H"], r, d["WIN"], scale, mode=0)[0]
+        xmx = O.ds41_attend(d["q"][i:i + 1].copy(), ring, 64, comp, max(d["ratio"], 1), sel, K, d["sinks"], 1, d["H"], r, d["WIN"], scale, mode=1)[0]
+        assert np.abs(vec - want).max() < 1e-5, (L, r)
+        assert np.all(np.abs(xmx - want) <= RF.ABS + RF.REL * np.abs(want)), (L, r)
+
+
+def test_ref_pin_indexer_scores_candidates_and_picks():
+    """The indexer of Ref.attention (:212-231): scores sum_h w relu(q . k), -inf past what the row sees; block maxima with
+    the newest block forced in; the top blocks kept; the K best keys in ascending position."""
+    d = RF.layer(RF.load(), 1)
+    iq, w, k = d["idx_q"], d["idx_w"], d["idx_k_f16"]
+    n, (IH, ID) = k.shape[0], iq.shape[1:]
+    for i, r in enumerate(d["qrows"]):
+        r = int(r)
+        vis = (r + 1) // d["ratio"]
+        sc = O.ds41_idx_score(iq[i:i + 1].copy(), w[i:i + 1].copy(), k, 1, IH, ID, n, n, r, d["ratio"], half_q=False)
+        assert np.allclose(sc[0, :vis], d["idx_score"][i, :vis], rtol=1e-6, atol=1e-6) and np.all(np.isneginf(sc[0, vis:]))
+        if vis == 0:
+            continue      # nothing to pick; (the reference's kernel leaves such a row's blocks at -inf, its Python keeps block 0: k41.cpp:412)
+        bm = O.ds41_block_max(sc, n, d["cand_bs"], r, d["ratio"])
+        nb = bm.shape[1]
+        keep = np.zeros(nb, bool)
+        for b in O.topk(bm, nb, min(d["cand_top"], nb))[0]:
+            keep[b] = b >= 0 and bm[0, b] > -np.inf
+        assert np.array_equal(np.repeat(keep, d["cand_bs"])[:n], d["cand"][i].astype(bool)), r
+        sel = O.topk(sc, n, min(d["ITOP"], n))[0]
+        want = d["topk"][i]
+        assert np.array_equal(sel[:min(vis, d["ITOP"])], want[want >= 0]), r
