@@ -82,7 +82,7 @@ class ClockSampler:
         self._once()
 
         def loop():
-            while not self._stop.wait(0.02):
+            while not self._stop.wait(0.005):
                 self._once()
         self._t = threading.Thread(target=loop, daemon=True)
         self._t.start()
@@ -130,20 +130,34 @@ class Env:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t.item())
 
-    def timed(self, fn, steps, warmup):
+    def timed(self, fn, steps, warmup, sampler=None, min_ms=0.0):
         """W warm-up steps, then K steps between two stamps on the library's compute stream; barrier + sync on both
-        sides; the maximum over ranks. Returns milliseconds a step."""
+        sides; the maximum over ranks. `sampler` (a ClockSampler) runs over the timed region only. With `min_ms`, K grows
+        (the same on every rank) until the timed region lasts about that long, so that the clock samples are samples under
+        this load. Returns (milliseconds a step, K)."""
         for _ in range(warmup):
             fn()
+        if min_ms > 0:
+            self.barrier()
+            a = self.gpu.stamp()
+            for _ in range(3):
+                fn()
+            b = self.gpu.stamp()
+            self.gpu.sync()
+            est = self.max_over_ranks(self.gpu.elapsed_ns(a, b) / 3e6)
+            steps = int(max(steps, min(20000, -(-min_ms // max(est, 1e-4)))))
         self.barrier()
+        if sampler:
+            sampler.start()
         a = self.gpu.stamp()
         for _ in range(steps):
             fn()
         b = self.gpu.stamp()
         self.gpu.sync()
+        self.clocks = sampler.stop() if sampler else None
         ms = self.gpu.elapsed_ns(a, b) / 1e6
         self.barrier()
-        return self.max_over_ranks(ms) / steps
+        return self.max_over_ranks(ms) / steps, steps
 
     def close(self):
         if self.dist:
@@ -272,7 +286,7 @@ def wl_prefill(env, T, Hq, Hkv, D):
         hkv_r, hq_r = 1, Hq // w
     # input sets used in turn so that together they hold 300 MB (q, k, v and the output of a set are touched once a step)
     set_bytes = 2 * T * hq_r * D * 2 + 2 * hkv_r * T * D * 2
-    rotate = int(os.environ.get("NS_BENCH_PREFILL_SETS", 0)) or max(2, -(-300_000_000 // set_bytes))
+    rotate = max(2, -(-300_000_000 // set_bytes))
     sets = [(device_random_f16(env, T * hq_r * D * 2, 1 + 3 * r), device_random_f16(env, hkv_r * T * D * 2, 2 + 3 * r),
              device_random_f16(env, hkv_r * T * D * 2, 3 + 3 * r), DevBuf(env.gpu, T * hq_r * D * 2)) for r in range(rotate)]
     i = [0]
@@ -370,6 +384,7 @@ def wl_kvsplit_decode(env, T=4, Hq=32, Hkv=4, D=128, kv=262144):
     from nextsycl_b200 import workloads as W
     from nextsycl_b200.dist import KvSplit, key_ranges
     base, count = key_ranges(kv, env.world)[env.rank]
+    assert count > 0, "a context shorter than the ranks' shares is not a benchmark case"
 
     def exchange(h):
         got = [None] * env.world
@@ -403,13 +418,44 @@ def wl_kvsplit_decode(env, T=4, Hq=32, Hkv=4, D=128, kv=262144):
     def step():
         graphs[i[0] % rotate].launch()
         i[0] += 1
+    def check():
+        """After the timed region: one more step on cache set 0; every rank's rows must be the same bits, and rank 0 holds
+        them to the CPU checker's decode of the WHOLE context, rebuilt on the host from the ranks' seeds (a combine that
+        merged the wrong buffer, or a rank that pushed stale partials, shows here, not in the timing)."""
+        one(0)
+        env.gpu.sync()
+        mine = out.read(np.float16).reshape(T, Hq * D)
+        rows = [mine.tobytes()]
+        if env.dist:
+            rows = [None] * env.world
+            env.dist.all_gather_object(rows, mine.tobytes())
+        same = all(r == rows[0] for r in rows)
+        res = {"ranks_bit_equal": bool(same)}
+        if env.rank == 0:
+            from oracle import oracle as O
+            O.use_all_cores()
+            K = np.empty((Hkv, kv, D), np.float16)
+            V = np.empty((Hkv, kv, D), np.float16)
+            for r, (b, c) in enumerate(key_ranges(kv, env.world)):
+                if c == 0:
+                    continue
+                n = Hkv * c * D
+                for dst, seed in ((K, 200 + 16 * r), (V, 201 + 16 * r)):
+                    blk = W.normal_f16(90, seed, (min(n, 16 << 20),))
+                    dst[:, b:b + c] = np.resize(blk, n).reshape(Hkv, c, D)    # the device buffer is that block end to end
+            qh = W.normal_f16(5, 0, (T, Hq * D))
+            want = O.gqa_flash_decode(qh.astype(np.float32), K.view(np.uint16), V.view(np.uint16), T, Hq, Hkv, D, kv, kv - T)
+            d = np.abs(mine.astype(np.float32) - want)
+            res.update({"max_abs": float(d.max()), "ok": bool(same and np.all(d <= 2e-3 + 1e-2 * np.abs(want))),
+                        "against": "CPU checker (flash numerics) over all %d keys; tolerance 2e-3 + 1e-2 |want|" % kv})
+        return res
     info = {"bytes": 2 * count * Hkv * D * 2, "bytes_total": 2 * kv * Hkv * D * 2, "flops": 0, "bound": "hbm", "launches": 3,
-            "keep": (grp, q, caches, sc, out, graphs)}
+            "keep": (grp, q, caches, sc, out, graphs), "check": check}
     return step, info
 
 
-def measure(env, name, steps, warmup):
-    """Builds the workload, times it, returns a result dict (per GPU figures plus the whole-job rate)."""
+def measure(env, name, steps, warmup, min_ms=0.0):
+    """Builds the workload, times it under a clock sampler, returns a result dict (per GPU figures plus the whole-job rate)."""
     pk = peaks()
     if name == "decode_c2":
         step, info = wl_gqa_decode(env, 1, 64, 8, 128, 32768, 8)
@@ -439,8 +485,10 @@ def measure(env, name, steps, warmup):
         step, info = wl_mla_prefill(env)
     else:
         raise SystemExit(f"unknown workload {name}")
-    ms = env.timed(step, steps, max(3, warmup))
-    res = {"workload": name, "ms_per_step": ms, "steps": steps}
+    ms, steps = env.timed(step, steps, max(3, warmup), sampler=ClockSampler(env.local), min_ms=min_ms)
+    res = {"workload": name, "ms_per_step": ms, "steps": steps, "clocks": env.clocks}
+    if env.clocks and env.clocks.get("sm_mhz"):
+        res["ms_x_mhz"] = ms * env.clocks["sm_mhz"]
     if "tensor" in info["bound"]:
         tf = info["flops"] / (ms * 1e-3) / 1e12
         res.update({"tflops_per_gpu": tf, "frac_of_bf16_peak": tf / float(pk["bf16_tflops"]),
@@ -462,10 +510,10 @@ def measure(env, name, steps, warmup):
 # profiles/ (a profiler's figure, constant for a workload; not measured by this script)
 NCU_TRAFFIC = {"decode_c2": 1.073912e9 + 12.0e6, "mla_decode_32k": 37.96e6 + 0.07e6, "decode_q35_q8": 285.29e6 + 3.9e6}
 
-OTHERS_1GPU = [("prefill_16k", 10), ("prefill_c1", 50), ("prefill_q35_16k", 5), ("decode_c2_b1", 50), ("decode_128k", 30), ("decode_c5", 30), ("decode_q35_f16", 30),
+OTHERS_1GPU = [("prefill_16k", 10), ("prefill_c1", 50), ("prefill_q35_16k", 10), ("decode_c2_b1", 50), ("decode_128k", 30), ("decode_c5", 30), ("decode_q35_f16", 30),
                ("decode_q35_q8", 30), ("decode_q35_q4", 30), ("mla_decode_4k", 50),
-               ("mla_decode_32k", 50), ("mla_decode_131k", 30), ("ds2_decode_32k", 50), ("mla_prefill_c4", 3)]
-OTHERS_NGPU = [("decode_c5_split", 50), ("prefill_16k", 10), ("mla_prefill_c4", 3)]
+               ("mla_decode_32k", 50), ("mla_decode_131k", 30), ("ds2_decode_32k", 50), ("mla_prefill_c4", 10)]
+OTHERS_NGPU = [("decode_c5_split", 50), ("prefill_16k", 10), ("mla_prefill_c4", 10)]
 
 
 def config_of(name, n):
@@ -497,6 +545,7 @@ def cpu_decode_rate(seconds, steps=None, warmup=1):
     """The oracle's flash-numerics decode of ONE sequence of config 2 on all host threads; (bytes/s, threads, repeats, s each)."""
     from nextsycl_b200 import workloads as W
     from oracle import oracle as O
+    O.use_all_cores()   # a process launcher may have exported OMP_NUM_THREADS=1: the CPU arm is an all-core figure at every N
     T, Hq, Hkv, D, kv = 1, 64, 8, 128, 32768
     q, k, v, p0 = W.gqa_case(2, T, Hq, Hkv, D, kv, seq=0)
     qf, kb, vb = q.astype(np.float32), k.view(np.uint16), v.view(np.uint16)
@@ -522,7 +571,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": config_of("decode_c2", args.gpus),
+        "config": dict(config_of("decode_c2", args.gpus), sample="one sequence of the batch a step (a rate: the sample size does not scale it)"),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": "one sequence of the batch (134,217,728 KV bytes) a step; CPU restatement of the decode numerics of "
                                    "kernels/llm/qwen35/silo/attn.cpp, OpenMP over (row, head); the SYCL reference cannot be built without oneAPI"},
@@ -616,10 +665,8 @@ def run_ours(args):
     env = Env()
     pk = peaks()
     name = args.workload
-    sampler = ClockSampler(env.local)
-    sampler.start()
     res = measure(env, name, args.steps, args.warmup)
-    clocks = sampler.stop()
+    clocks = res.pop("clocks")
     info = res.pop("_info")
     ms = res["ms_per_step"]
     world = env.world
@@ -675,9 +722,14 @@ def run_ours(args):
             if oname == name:
                 continue
             try:
-                r = measure(env, oname, osteps, 3)
-                r.pop("_info")
+                # every workload under its own clock record (a tensor-bound figure means little without the SM clock it ran
+                # at), its timed region at least 100 ms long so that the record holds samples taken under its load
+                r = measure(env, oname, osteps, 3, min_ms=100.0)
+                oinfo = r.pop("_info")
                 others[oname] = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in r.items() if k != "workload"}
+                if "check" in oinfo:
+                    others[oname]["parity"] = oinfo["check"]()
+                del oinfo
             except Exception as e:   # a failed extra must not take the headline with it
                 others[oname] = {"error": str(e)[:200]}
         line["others"] = others

@@ -50,9 +50,10 @@ int ns_q35_attn_prompt_kv(ns_gpu* g, int kt, const float* q, int64_t qs, const v
 /* kernels/llm/qwen35/silo/silo.h:49-59 - decode rows (1..8), each at its own position p0+t; a row's result is the same
  * whatever rows share its pass. `_supported` is widened from the reference's (D 256, 6 heads a key head) to D 128 / 256
  * with 1..16 query heads a key head. kt (both _kv entry points): the cache's form, 0 fp16, 1 q8_0, 2 q4_0 (heads of 256;
- * rows as ns_q35_kv_store_q writes them). Decode streams a quantised cache as it lies and expands each tile in shared
- * memory to exactly the fp16 values the reference's reader kv_load8 produces (silo/attn.cpp:49-78); a prompt pass, bound
- * by its products, first expands the rows it reads into a buffer the library keeps and runs the fp16 kernel on that. */
+ * rows as ns_q35_kv_store_q writes them). Decode streams a quantised cache as it lies and expands the raw rows in
+ * registers, on their way into the tensor-core fragments, to exactly the fp16 values the reference's reader kv_load8
+ * produces (silo/attn.cpp:49-78); a prompt pass, bound by its products, first expands the rows it reads into a buffer
+ * the library keeps and runs the fp16 kernel on that. */
 int ns_q35_attn_decode_supported(int64_t T, int64_t Hq, int64_t Hkv, int64_t D);
 int64_t ns_q35_attn_decode_scratch(int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t p0);
 int ns_q35_attn_decode(ns_gpu* g, const float* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,

@@ -1,8 +1,9 @@
 """Builds dist/libnextsycl-llm.so from nextsycl_b200/csrc/*.cu with nvcc for sm_100a.
 
 The library keeps the reference's output name (kernels/build.sh:70-106 produces dist/libnextsycl-llm.so), so an engine
-switches to it by pointing NEXTSYCL_LIB at this file. Objects go to build/ (not tracked); the shared library is
-in-tree so it travels with the repository snapshot to machines that have no compiler run.
+switches to it by pointing NEXTSYCL_LIB at this file. Objects go to build/ and the library to dist/; both are built
+artefacts, kept out of version control, and the library file travels with a copy of the working tree to machines where no
+compiler runs.
 """
 import concurrent.futures
 import glob

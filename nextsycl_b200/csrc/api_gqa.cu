@@ -102,8 +102,8 @@ int ns_q35_attn_decode_kv(ns_gpu* g, int kt, const float* q, int64_t qs, const v
                           int64_t D, int64_t cap, int64_t p0, float* out, float* scratch) {
     NS_TRY
     if (kt == 0) return decode_f32(g, "ns_q35_attn_decode_kv", q, qs, kc, vc, T, Hq, Hkv, D, cap, p0, out, scratch);
-    // q8_0 / q4_0 caches (heads of 256): the decode kernel streams the rows as they lie and expands each tile in shared
-    // memory to the fp16 values the reference's reader hands its tensor cores (silo/attn.cpp:49-78)
+    // q8_0 / q4_0 caches (heads of 256): the decode kernel streams the rows as they lie and expands them in registers to
+    // the fp16 values the reference's reader hands its tensor cores (silo/attn.cpp:49-78)
     const char* name = "ns_q35_attn_decode_kv";
     if (kt != 1 && kt != 2) return ns_fail(std::string(name) + ": a cache form 0 (half), 1 (q8_0) or 2 (q4_0)");
     if (D != 256) return ns_fail(std::string(name) + ": quantised caches have heads of 256");

@@ -472,18 +472,6 @@ int launch(ns_gpu* g, const FlashPrefillArgs& a, const char* where) {
 
 int ns_launch_flash_prefill(ns_gpu* g, const FlashPrefillArgs& a, const char* where) {
     if (a.T <= 0) return 0;
-    // NS_B200_PREFILL_2BLOCK=1 selects the variant with two row blocks a CTA (flash_prefill2.cu). It is correct but was
-    // measured slower at 16K (769 against 1,007 TFLOP/s): the softmax is bound by the SM's instruction issue rate, which
-    // two softmax warpgroups share, not by latency.
-    static const bool two_block = getenv("NS_B200_PREFILL_2BLOCK") != nullptr;
-    if (a.Dqk == 128 && a.Dv == 128 && a.T > 128 && two_block) return ns_launch_flash_prefill2(g, a, where);
-    static const bool one_group = getenv("NS_B200_PREFILL_1GROUP") != nullptr;   // the single softmax group, for comparison
-    static const bool two_stage = getenv("NS_B200_PREFILL_2STAGE") != nullptr;   // the two-stage ring, for comparison
-    if (one_group) {
-        if (a.Dqk == 128 && a.Dv == 128 && !a.bf16) return launch<128, 128, 128, 2, 0, 1>(g, a, where);
-        if (a.Dqk == 192 && a.Dv == 128 && a.bf16) return launch<192, 128, 128, 2, 1, 1>(g, a, where);
-    }
-    if (two_stage && a.Dqk == 128 && a.Dv == 128 && !a.bf16) return launch<128, 128, 128, 2, 0, 2>(g, a, where);
     if (a.Dqk == 128 && a.Dv == 128 && !a.bf16) return launch<128, 128, 128, 3, 0, 2>(g, a, where);
     if (a.Dqk == 128 && a.Dv == 128 && a.bf16) return launch<128, 128, 128, 3, 1, 2>(g, a, where);
     if (a.Dqk == 192 && a.Dv == 128 && a.bf16) return launch<192, 128, 128, 2, 1, 2>(g, a, where);

@@ -89,8 +89,6 @@ struct FlashPrefillArgs {
     int bf16, out_f32;
 };
 int ns_launch_flash_prefill(ns_gpu* g, const FlashPrefillArgs& a, const char* where);
-// the 128/128 shape with two row blocks a CTA (flash_prefill2.cu)
-int ns_launch_flash_prefill2(ns_gpu* g, const FlashPrefillArgs& a, const char* where);
 
 // ---- absorbed MLA decode on tcgen05 (mla_decode.cu) --------------------------------------------------------------------
 struct MlaDecodeArgs {

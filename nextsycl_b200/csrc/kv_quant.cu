@@ -10,69 +10,57 @@ namespace {
 
 __host__ __device__ constexpr int64_t q_row_bytes(int kt) { return kt == 1 ? 272 : 144; }
 
-// a thread a block of 32 values, keys then values (q35.cpp:289-322). Products and sums are single roundings (no fused
-// multiply-add), as the CPU statement of the same arithmetic computes them.
-__global__ void kv_store_q_kernel(int kt, const float* __restrict__ k, int64_t ks, const float* __restrict__ v, int64_t vs, int64_t T, int64_t Hkv,
-                                  int64_t cap, int64_t p0, uint8_t* __restrict__ kd, uint8_t* __restrict__ vd) {
-    const int64_t total = 2 * T * Hkv * 8;
+// A warp a head row (256 values = 8 blocks of 32), keys then values; lane j holds value j of each of the 8 blocks, so every
+// load is one coalesced 128 bytes and a block's scale is a butterfly of shuffles. The arithmetic is llama.cpp's q8_0 /
+// q4_0 as the reference writes it (q35.cpp:289-322), every product and quotient a single rounding: q8_0 d = amax / 127,
+// q = round-half-away(x / d ... as x * (1 / d)); q4_0 d = m / -8 with m the FIRST value of largest magnitude, code =
+// min(15, trunc(x * (1 / d) + 8.5)), value j in the low nibble of byte j and value j + 16 in the high one.
+constexpr int QWARPS = 8;
+
+__global__ void __launch_bounds__(QWARPS * 32) kv_store_q_kernel(int kt, const float* __restrict__ k, int64_t ks, const float* __restrict__ v, int64_t vs,
+                                                                 int64_t T, int64_t Hkv, int64_t cap, int64_t p0, uint8_t* __restrict__ kd,
+                                                                 uint8_t* __restrict__ vd) {
+    const unsigned FULL = 0xffffffffu;
+    const int lane = threadIdx.x & 31;
+    const int64_t rows = 2 * T * Hkv;   // (k | v, token, key head)
     const int64_t rb = q_row_bytes(kt);
-    for (int64_t id = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; id < total; id += (int64_t) gridDim.x * blockDim.x) {
-        int64_t i = id;
-        const int b = (int) (i % 8);
-        i /= 8;
-        const int64_t h = i % Hkv;
-        i /= Hkv;
-        const int64_t t = i % T;
-        const bool isv = i / T == 1;
-        const float* x = (isv ? v + t * vs : k + t * ks) + h * 256 + b * 32;
+    for (int64_t r = (int64_t) blockIdx.x * QWARPS + (threadIdx.x >> 5); r < rows; r += (int64_t) gridDim.x * QWARPS) {
+        const bool isv = r >= T * Hkv;
+        const int64_t th = isv ? r - T * Hkv : r, t = th / Hkv, h = th % Hkv;
+        const float* x = (isv ? v + t * vs : k + t * ks) + h * 256;
         uint8_t* row = (isv ? vd : kd) + (h * cap + p0 + t) * rb;
-        float xv[32];
+        float xv[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float4 a = *reinterpret_cast<const float4*>(x + 4 * j);
-            xv[4 * j] = a.x, xv[4 * j + 1] = a.y, xv[4 * j + 2] = a.z, xv[4 * j + 3] = a.w;
-        }
-        if (kt == 1) {
-            float amax = 0.0f;
+        for (int b = 0; b < 8; ++b) xv[b] = x[b * 32 + lane];
+        float mine = 0.0f;   // lane b < 8 ends up holding block b's scale
 #pragma unroll
-            for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(xv[j]));
-            const float d = __fdiv_rn(amax, 127.0f), inv = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-            uint32_t w[8];
+        for (int b = 0; b < 8; ++b) {
+            // the block's largest magnitude and the lowest lane that holds it
+            float am = fabsf(xv[b]);
+            int at = lane;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                uint32_t word = 0;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) word |= ((uint32_t) (uint8_t) (int8_t) roundf(__fmul_rn(xv[4 * j + e], inv))) << (8 * e);
-                w[j] = word;
+            for (int o = 16; o > 0; o >>= 1) {
+                const float oa = __shfl_xor_sync(FULL, am, o);
+                const int oi = __shfl_xor_sync(FULL, at, o);
+                if (oa > am || (oa == am && oi < at)) am = oa, at = oi;
             }
-            uint4* dst = reinterpret_cast<uint4*>(row + b * 32);
-            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-            reinterpret_cast<__half*>(row + 256)[b] = __float2half_rn(d);
-        } else {
-            float m = 0.0f, am = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-                if (fabsf(xv[j]) > am) {
-                    am = fabsf(xv[j]);
-                    m = xv[j];
-                }
-            const float d = __fdiv_rn(m, -8.0f), inv = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-            uint32_t w[4];
-#pragma unroll
-            for (int j4 = 0; j4 < 4; ++j4) {
-                uint32_t word = 0;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int j = 4 * j4 + e;
-                    const int lo = min(15, (int) __fadd_rn(__fmul_rn(xv[j], inv), 8.5f)), hi = min(15, (int) __fadd_rn(__fmul_rn(xv[j + 16], inv), 8.5f));
-                    word |= (uint32_t) (lo | (hi << 4)) << (8 * e);
-                }
-                w[j4] = word;
+            float d;
+            if (kt == 1) {
+                d = __fdiv_rn(am, 127.0f);
+                const float inv = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+                row[b * 32 + lane] = (uint8_t) (int8_t) roundf(__fmul_rn(xv[b], inv));
+            } else {
+                const float first = __shfl_sync(FULL, xv[b], at);
+                const float m = am > 0.0f ? first : 0.0f;   // a block of zeros keeps the reference's initial m = +0, so d = -0
+                d = __fdiv_rn(m, -8.0f);
+                const float inv = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+                const int code = min(15, (int) __fadd_rn(__fmul_rn(xv[b], inv), 8.5f));
+                const int hi = __shfl_down_sync(FULL, code, 16);
+                if (lane < 16) row[b * 16 + lane] = (uint8_t) (code | (hi << 4));
             }
-            *reinterpret_cast<uint4*>(row + b * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-            reinterpret_cast<__half*>(row + 128)[b] = __float2half_rn(d);
+            if (lane == b) mine = d;
         }
+        if (lane < 8) reinterpret_cast<__half*>(row + (kt == 1 ? 256 : 128))[lane] = __float2half_rn(mine);
     }
 }
 
@@ -108,29 +96,26 @@ __global__ void kv_dequant_kernel(int kt, const uint8_t* __restrict__ c, int64_t
     }
 }
 
-// q35.cpp:328-348: a thread a block of 32, the butterflies in the reference's order
-__global__ void fwht32_kernel(float* __restrict__ x, int64_t rows, int64_t nb, int64_t stride) {
+// The normalised 32-point Walsh-Hadamard transform of every block of 32 (q35.cpp:328-348), a warp a block: lane i holds
+// element i and stage o (1, 2, 4, 8, 16) is one exchange with lane i ^ o - the lower lane of a pair keeps a + b, the upper
+// a - b, the pairs and their order the reference's, every sum a single rounding - then the factor 1 / sqrt(32).
+__global__ void __launch_bounds__(QWARPS * 32) fwht32_kernel(float* __restrict__ x, int64_t rows, int64_t nb, int64_t stride) {
+    const int lane = threadIdx.x & 31;
     const int64_t total = rows * nb;
-    for (int64_t id = (int64_t) blockIdx.x * blockDim.x + threadIdx.x; id < total; id += (int64_t) gridDim.x * blockDim.x) {
+    for (int64_t id = (int64_t) blockIdx.x * QWARPS + (threadIdx.x >> 5); id < total; id += (int64_t) gridDim.x * QWARPS) {
         float* p = x + (id / nb) * stride + (id % nb) * 32;
-        float v[32];
+        float val = p[lane];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = p[i];
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1)
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-                if (!(i & o)) {
-                    const float a = v[i], b = v[i + o];
-                    v[i] = __fadd_rn(a, b);
-                    v[i + o] = __fsub_rn(a, b);
-                }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) p[i] = __fmul_rn(v[i], 0.17677669529663687f);
+        for (int o = 1; o < 32; o <<= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, val, o);
+            val = (lane & o) ? __fsub_rn(other, val) : __fadd_rn(val, other);
+        }
+        p[lane] = __fmul_rn(val, 0.17677669529663687f);
     }
 }
 
 unsigned blocks_for(int64_t n) { return (unsigned) std::min<int64_t>(8192, (n + 255) / 256); }
+unsigned warp_blocks(int64_t warps) { return (unsigned) std::min<int64_t>(8192, (warps + QWARPS - 1) / QWARPS); }
 
 }  // namespace
 
@@ -151,7 +136,7 @@ int ns_q35_kv_store_q(ns_gpu* g, int kt, const float* k, int64_t ks, const float
     if (!k || !v || !kc || !vc || Hkv < 1) return ns_fail("ns_q35_kv_store_q: a null buffer");
     if (ks % 4 != 0 || vs % 4 != 0 || ((uintptr_t) k & 15) != 0 || ((uintptr_t) v & 15) != 0 || ((uintptr_t) kc & 15) != 0 || ((uintptr_t) vc & 15) != 0)
         return ns_fail("ns_q35_kv_store_q: rows 16-byte aligned");
-    kv_store_q_kernel<<<blocks_for(2 * T * Hkv * 8), 256, 0, g->compute>>>(kt, k, ks, v, vs, T, Hkv, cap, p0, (uint8_t*) kc, (uint8_t*) vc);
+    kv_store_q_kernel<<<warp_blocks(2 * T * Hkv), QWARPS * 32, 0, g->compute>>>(kt, k, ks, v, vs, T, Hkv, cap, p0, (uint8_t*) kc, (uint8_t*) vc);
     return ns_launched("ns_q35_kv_store_q");
     NS_CATCH("ns_q35_kv_store_q")
 }
@@ -162,7 +147,7 @@ int ns_q35_fwht32(ns_gpu* g, float* x, int64_t rows, int64_t n, int64_t stride) 
     if (rows <= 0) return 0;
     if (n % 32) return ns_fail("ns_q35_fwht32: rows of a multiple of 32");
     if (!x || stride < n) return ns_fail("ns_q35_fwht32: rows at least n floats apart");
-    fwht32_kernel<<<blocks_for(rows * (n / 32)), 256, 0, g->compute>>>(x, rows, n / 32, stride);
+    fwht32_kernel<<<warp_blocks(rows * (n / 32)), QWARPS * 32, 0, g->compute>>>(x, rows, n / 32, stride);
     return ns_launched("ns_q35_fwht32");
     NS_CATCH("ns_q35_fwht32")
 }

@@ -141,6 +141,18 @@ int orc_threads(void) {
 #endif
 }
 
+// sets the number of OpenMP threads later calls use (an inherited OMP_NUM_THREADS=1, as process launchers export it,
+// would otherwise make every timing a one-core figure); returns what is in force
+int orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void) n;
+    return 1;
+#endif
+}
+
 int64_t orc_flash_split(int64_t kv, int64_t Hkv) { return flash_split(kv, Hkv); }
 int64_t orc_flash_splits(int64_t kv, int64_t Hkv) { return flash_splits(kv, Hkv); }
 int64_t orc_plain_split(int64_t S, int64_t kv, int64_t groups) { return plain_split(S, kv, groups); }

@@ -52,6 +52,13 @@ def threads():
     return int(lib().orc_threads())
 
 
+def use_all_cores():
+    """Makes later calls use every core this process may run on, whatever OMP_NUM_THREADS said; returns the count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_threads.restype = C.c_int
+    return int(lib().orc_set_threads(C.c_int(n)))
+
+
 def _f(a):
     assert a.dtype == np.float32 and a.flags.c_contiguous
     return a.ctypes.data_as(_pf)

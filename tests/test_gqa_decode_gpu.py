@@ -218,6 +218,17 @@ def test_full_size_config_2(gpu, ops, B):
         assert_close(got[b], want[b], f"sequence {b}")
 
 
+@pytest.mark.parametrize("T,Hq,Hkv,kv", [(1, 64, 8, 32768), (4, 32, 4, 262144)])
+def test_nh_attn_against_the_plain_numerics_at_full_size(gpu, ops, T, Hq, Hkv, kv):
+    """Configurations 2 and 5 through ns_nh_attn, held to the numerics of the ONLY reference kernel that exists for heads of
+    128 - the vector-unit attn<8,8> (kernels/llm/nemotronh/nh.cpp:575-585: fp32 query times scale, natural exp, fp32
+    weights; the oracle's plain mode) - within the path's bar."""
+    D = 128
+    q, k, v, p0 = W.gqa_case(2 if T == 1 else 5, T, Hq, Hkv, D, kv)
+    got = run_compat(gpu, ops, q, k, v, T, Hq, Hkv, D, kv, p0, name="ns_nh_attn")
+    assert_close(got, O.gqa_plain(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, kv, p0), "vs plain numerics")
+
+
 def test_full_size_config_5(gpu, ops):
     """benchmark configuration 5 on one GPU at full size: 4 verify rows, 32 query / 4 key heads of 128, 262,144 cached tokens
     (512 MiB of K and V). Each row against the oracle's flash numerics, and row t against the one-row pass at its position

@@ -70,13 +70,15 @@ def test_ds2_whole_decode(gpu, ops):
 @pytest.mark.parametrize("n", [32768, 131072])
 def test_config_3_full_size(gpu, ops, n):
     """benchmark configuration 3: 128 heads, latent cache ~N(0, 0.5), query ~N(0, 1), scale 1/sqrt(192). All 128 heads run on the
-    GPU; the oracle checks the first 8 (the heads are independent rows of the same tile)."""
+    GPU; the oracle checks 16 of them: the first and last head of each of the four softmax warps of the tile (a warp owns 32
+    tensor-memory lanes = 32 heads) and 8 more in between; each checked row spans both output halves (two CTAs)."""
     T, H = 1, 128
     q = W.normal_f16(3, 0, (T, H, 576))
     cache = W.normal_f16(3, 1, (n, 576), 0.5)
     got = run(gpu, ops, q, cache, T, H, n - 1)
-    qs = np.ascontiguousarray(q[:, :8].astype(np.float32))
-    assert_close(got[:, :8], O.mla_gemm(qs, cache.view(np.uint16), T, 8, 512, 64, n - 1, np.float32(SCALE)), "config 3, heads 0..7")
+    heads = [0, 31, 32, 63, 64, 95, 96, 127, 7, 16, 45, 50, 77, 88, 101, 120]
+    qs = np.ascontiguousarray(q[:, heads].astype(np.float32))
+    assert_close(got[:, heads], O.mla_gemm(qs, cache.view(np.uint16), T, len(heads), 512, 64, n - 1, np.float32(SCALE)), f"config 3, heads {heads}")
     assert np.isfinite(got).all()
 
 

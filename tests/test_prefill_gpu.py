@@ -229,7 +229,12 @@ def test_config_4_full_size_sampled(gpu, ops):
     gpu.sync()
     got = O.from_bf16_bits(out.read(np.uint16).reshape(T, H, 128))
     j = np.arange(n, dtype=np.int64)[:, None]
-    for r, h in ((0, 0), (1, 77), (2047, 127), (2048, 5), (4095, 64)):
+    # 34 (row, head) pairs: the chunk's first rows, both sides of every kind of boundary (row blocks of 128 at 127 | 128,
+    # the middle, the last block 3968 .. 4095), heads across the whole range
+    pairs = [(0, 0), (1, 77), (127, 3), (128, 3), (127, 126), (128, 126), (129, 40), (255, 9), (256, 9), (1000, 31), (1023, 100), (1024, 100),
+             (2047, 127), (2048, 5), (2049, 64), (2500, 17), (3000, 90), (3071, 55), (3072, 55), (3500, 1), (3839, 70), (3840, 70), (3967, 12),
+             (3968, 12), (3969, 127), (4000, 33), (4031, 64), (4032, 64), (4064, 99), (4090, 0), (4093, 111), (4094, 127), (4095, 64), (4095, 0)]
+    for r, h in pairs:
         kh = kblk[(j * H * 192 + h * 192 + np.arange(192)[None, :]) % L][None]     # [1][n][192]
         vh = vblk[(j * H * 128 + h * 128 + np.arange(128)[None, :]) % L][None]
         qh = O.from_bf16_bits(qblk[(r * H * 192 + h * 192 + np.arange(192)) % L])[None]
