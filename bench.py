@@ -623,30 +623,28 @@ def e2e_decode(env, info, steps):
 
 
 def e2e_decode_native(env, info, steps):
-    """Config 2 from pinned host buffers through the native batched call: the step's queries (fp16) and new K, V rows
-    (fp32) up, one ns_q35_kv_store a sequence, ONE ns_b200_gqa_decode for the batch, the outputs (fp16) down, one sync."""
+    """Config 2 from pinned host buffers through the native batched calls: ONE copy up (the step's queries as fp16 and the new
+    K and V rows as fp32, packed in one pinned buffer), ONE ns_b200_kv_store_batch, ONE ns_b200_gqa_decode, ONE copy down (the
+    outputs, fp16), one sync."""
     from nextsycl_b200 import DevBuf, HostBuf
     from nextsycl_b200 import workloads as W
     gpu, ops = env.gpu, env.ops
     T, Hq, Hkv, D, kv, B = 1, 64, 8, 128, 32768, 8
     seqs, qs = info["seqs"], info["qs"]
-    hq, hk, hv, ho = HostBuf(gpu, B * Hq * D * 2), HostBuf(gpu, B * Hkv * D * 4), HostBuf(gpu, B * Hkv * D * 4), HostBuf(gpu, B * Hq * D * 2)
-    hq.array(np.float16)[:] = np.stack(qs).ravel()
-    hk.array(np.float32)[:] = W.rng(2, 9001 + env.rank).standard_normal(B * Hkv * D, dtype=np.float32)
-    hv.array(np.float32)[:] = W.rng(2, 9002 + env.rank).standard_normal(B * Hkv * D, dtype=np.float32)
-    dq, dkf, dvf, do = DevBuf(gpu, hq.len), DevBuf(gpu, hk.len), DevBuf(gpu, hv.len), DevBuf(gpu, ho.len)
+    qb, kb = B * Hq * D * 2, B * Hkv * D * 4
+    hin, ho = HostBuf(gpu, qb + 2 * kb), HostBuf(gpu, B * Hq * D * 2)
+    hin.array(np.float16, at=0, shape=(B * Hq * D,))[:] = np.stack(qs).ravel()
+    hin.array(np.float32, at=qb, shape=(B * Hkv * D,))[:] = W.rng(2, 9001 + env.rank).standard_normal(B * Hkv * D, dtype=np.float32)
+    hin.array(np.float32, at=qb + kb, shape=(B * Hkv * D,))[:] = W.rng(2, 9002 + env.rank).standard_normal(B * Hkv * D, dtype=np.float32)
+    din, do = DevBuf(gpu, hin.len), DevBuf(gpu, ho.len)
+    dq, dkf, dvf = din.view(0, qb), din.view(qb, kb), din.view(qb + kb, kb)
     table = ops.seq_table(seqs)
     sc = DevBuf(gpu, max(4, 4 * ops.gqa_decode_scratch(B, T, Hq, Hkv, D, kv)))
     api, raw = gpu.api, gpu.raw
-    views = [(dkf.view(b * Hkv * D * 4, Hkv * D * 4), dvf.view(b * Hkv * D * 4, Hkv * D * 4)) for b in range(B)]
 
     def step():
-        api.ns_copy_to(raw, dq.ptr, hq.ptr, hq.len)
-        api.ns_copy_to(raw, dkf.ptr, hk.ptr, hk.len)
-        api.ns_copy_to(raw, dvf.ptr, hv.ptr, hv.len)
-        for b in range(B):
-            dk, dv, cap, p0 = seqs[b]
-            ops.kv_store(views[b][0], Hkv * D, views[b][1], Hkv * D, 1, Hkv, D, cap, p0, dk, dv)
+        api.ns_copy_to(raw, din.ptr, hin.ptr, hin.len)
+        ops.kv_store_batch(dkf, Hkv * D, T * Hkv * D, dvf, Hkv * D, T * Hkv * D, table, B, T, Hkv, D)
         ops.gqa_decode(dq, Hq * D, T * Hq * D, table, B, T, Hq, Hkv, D, kv, do, sc)
         api.ns_copy_from(raw, ho.ptr, do.ptr, ho.len)
         gpu.sync()
@@ -658,7 +656,7 @@ def e2e_decode_native(env, info, steps):
     for _ in range(steps):
         step()
     s = (time.perf_counter() - t0) / steps
-    return env.max_over_ranks(s), int(hq.len + hk.len + hv.len), int(ho.len)
+    return env.max_over_ranks(s), int(hin.len), int(ho.len)
 
 
 def run_ours(args):
@@ -712,8 +710,8 @@ def run_ours(args):
         s2, h2d2, d2h2 = e2e_decode_native(env, info, e2e_steps)
         line["e2e_native"] = {"value": world * info["bytes"] / s2 / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d2, "d2h_bytes_per_step": d2h2,
                               "ms_per_step": s2 * 1e3,
-                              "path": "ns_copy_to q (fp16), k, v rows (pinned) -> ns_q35_kv_store per sequence -> one ns_b200_gqa_decode for the "
-                                      "batch -> ns_copy_from out (fp16); ns_sync a step"}
+                              "path": "one ns_copy_to of q (fp16) | k | v rows (one pinned buffer) -> one ns_b200_kv_store_batch -> one "
+                                      "ns_b200_gqa_decode for the batch -> one ns_copy_from out (fp16); ns_sync a step"}
     del info, res
 
     if not args.no_others:

@@ -34,7 +34,7 @@ static const char* kEngines[] = {
     // native
     "ns_b200_gqa_decode_scratch", "ns_b200_gqa_decode", "ns_b200_gqa_prefill", "ns_b200_mla_prefill", "ns_b200_mla_decode_scratch", "ns_b200_mla_decode",
     "ns_b200_kvsplit_mailbox_bytes", "ns_b200_kvsplit_scratch", "ns_b200_kvsplit_decode", "ns_b200_kvsplit_combine", "ns_b200_ipc_export",
-    "ns_b200_ipc_open", "ns_b200_ipc_close"};
+    "ns_b200_ipc_open", "ns_b200_ipc_close", "ns_b200_kv_store_batch", "ns_b200_gqa_decode_static"};
 
 int main(int argc, char** argv) {
     try {

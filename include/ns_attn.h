@@ -140,6 +140,14 @@ int ns_b200_qkv_prepare(ns_gpu* g, const float* q, int64_t qs, const float* k, i
                         int64_t D, const float* wq, const float* wk, float eps, int64_t n_rot, float theta, int64_t p0, int64_t cap, void* q_out, void* kc,
                         void* vc);
 
+/* The cache writer for a batch in one launch (replaces one ns_q35_kv_store call per sequence, kernels/llm/qwen35/q35.h:55-57,
+ * llm/qwen35/src/engine.rs:1577-1585): fp32 rows k, v [B][T][Hkv*D] (ks / vs floats between rows, k_seq / v_seq between
+ * sequences) go to positions p0 .. p0+T-1 of each sequence's own fp16 caches, both taken from the DEVICE table seqs [B] that
+ * ns_b200_gqa_decode reads, so a recorded step stays valid as the positions advance. One rounding to fp16, as ns_q35_kv_store.
+ * A row past its cache's capacity is skipped and the next ns_sync returns -1 (code 803). */
+int ns_b200_kv_store_batch(ns_gpu* g, const float* k, int64_t ks, int64_t k_seq, const float* v, int64_t vs, int64_t v_seq, const ns_b200_seq* seqs,
+                           int64_t B, int64_t T, int64_t Hkv, int64_t D);
+
 /* Split-KV GQA decode of a batch (replaces one ns_q35_attn_decode call per sequence, llm/qwen35/src/engine.rs:1535,
  * 1596-1600). q [B][T][Hq*D] fp16 (qs elements between rows, q_seq between sequences), seqs a DEVICE array [B],
  * out [B][T][Hq*D] fp16 dense. max_kv bounds every p0+T (it sizes the grid and the scratch; the lengths themselves

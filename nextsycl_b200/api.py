@@ -111,6 +111,7 @@ ATTN = {
     "ns_ds41_rows_f16": (C.c_int, [vp, vp, vp, i64, i64, i64]),
     "ns_b200_mla_decode_scratch": (i64, [vp, i64, i64, i64]),
     "ns_b200_mla_decode": (C.c_int, [vp, vp, vp, i64, i64, i64, C.c_float, vp, vp]),
+    "ns_b200_kv_store_batch": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, vp, i64, i64, i64, i64]),
     "ns_b200_gqa_decode_scratch": (i64, [i64, i64, i64, i64, i64, i64]),
     "ns_b200_gqa_decode": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, i64, vp, vp]),
     "ns_q35_graph_begin": (C.c_int, [vp, C.POINTER(vp)]),

@@ -132,6 +132,19 @@ int ns_nhs_attn_decode(ns_gpu* g, const float* q, int64_t qs, const void* kc, co
     NS_CATCH("ns_nhs_attn_decode")
 }
 
+int ns_b200_kv_store_batch(ns_gpu* g, const float* k, int64_t ks, int64_t k_seq, const float* v, int64_t vs, int64_t v_seq, const ns_b200_seq* seqs,
+                           int64_t B, int64_t T, int64_t Hkv, int64_t D) {
+    NS_TRY
+    const char* name = "ns_b200_kv_store_batch";
+    if (ns_enter(g, name)) return -1;
+    if (B < 1 || T < 1) return 0;
+    if (!k || !v || !seqs || Hkv < 1) return ns_fail(std::string(name) + ": a null buffer");
+    if (D % 8 != 0 || ks % 4 != 0 || vs % 4 != 0 || k_seq % 4 != 0 || v_seq % 4 != 0 || ((uintptr_t) k & 15) != 0 || ((uintptr_t) v & 15) != 0)
+        return ns_fail(std::string(name) + ": head width a multiple of 8, rows 16-byte aligned");
+    return ns_launch_kv_store_batch(g, k, ks, k_seq, v, vs, v_seq, seqs, B, T, Hkv, D);
+    NS_CATCH("ns_b200_kv_store_batch")
+}
+
 int64_t ns_b200_gqa_decode_scratch(int64_t B, int64_t T, int64_t Hq, int64_t Hkv, int64_t D, int64_t max_kv) {
     if (B < 1 || T < 1 || Hkv < 1 || max_kv < 1) return 0;
     const int64_t ns = ns_dec_splits_bound(max_kv, Hkv);   // shorter sequences of the batch may need more splits than the longest

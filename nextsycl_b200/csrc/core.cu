@@ -325,6 +325,7 @@ int ns_sync(ns_gpu* g) {
         if (code == 802)
             return ns_fail("ns_sync: a decode row needed more key splits than its call's max_kv laid out (code 802): a sequence is longer than "
                            "max_kv; its output is not valid");
+        if (code == 803) return ns_fail("ns_sync: a batched cache write would have passed a cache's capacity (code 803); those rows were not written");
         return ns_fail("ns_sync: a kernel gave up a bounded wait (code " + std::to_string(code) + "); its output is not valid");
     }
     return 0;

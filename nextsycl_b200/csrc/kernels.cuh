@@ -67,6 +67,9 @@ int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where);
 int ns_launch_kv_store(ns_gpu* g, const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hkv, int64_t D, int64_t cap, int64_t p0,
                        void* kc, void* vc);
 
+int ns_launch_kv_store_batch(ns_gpu* g, const float* k, int64_t ks, int64_t k_seq, const float* v, int64_t vs, int64_t v_seq, const ns_b200_seq* seqs,
+                             int64_t B, int64_t T, int64_t Hkv, int64_t D);
+
 // rows [0, n) of each head of a quantised cache (kt 1: q8_0, 2: q4_0; heads of 256) as fp16 [Hkv][n][256] (kv_quant.cu)
 int ns_launch_kv_dequant(ns_gpu* g, int kt, const void* c, int64_t Hkv, int64_t cap, int64_t n, void* out, const char* where);
 

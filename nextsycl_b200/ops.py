@@ -71,6 +71,14 @@ class Ops:
         host = np.frombuffer(bytes(arr), dtype=np.uint8)
         return DevBuf.of(self.gpu, host)
 
+    def kv_store_batch(self, k, ks, k_seq, v, vs, v_seq, table, B, T, Hkv, D):
+        """fp32 rows k, v [B][T][Hkv*D] into each sequence's caches at its own p0.. in one launch (ns_b200_kv_store_batch)."""
+        _need(k, ((B - 1) * k_seq + (T - 1) * ks + Hkv * D) * 4, "kv_store_batch k")
+        _need(v, ((B - 1) * v_seq + (T - 1) * vs + Hkv * D) * 4, "kv_store_batch v")
+        _need(table, B * C.sizeof(_api.Seq), "kv_store_batch sequence table")
+        check(self.api, self.api.need("ns_b200_kv_store_batch")(self.gpu.raw, k.ptr, ks, k_seq, v.ptr, vs, v_seq, table.ptr, B, T, Hkv, D),
+              "ns_b200_kv_store_batch")
+
     def gqa_decode_scratch(self, B, T, Hq, Hkv, D, max_kv):
         return int(self.api.need("ns_b200_gqa_decode_scratch")(B, T, Hq, Hkv, D, max_kv))
 

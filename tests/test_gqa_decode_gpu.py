@@ -247,3 +247,33 @@ def test_full_size_config_5(gpu, ops):
         dq1 = DevBuf.of(gpu, q[t:t + 1].copy())
         ops.gqa_decode(dq1, Hq * D, Hq * D, ops.seq_table([(dk, dv, kv, p0 + t)]), 1, 1, Hq, Hkv, D, kv, one, sc)
         assert np.array_equal(one.read(np.float16).reshape(Hq * D).view(np.uint16), got[t].view(np.uint16)), f"row {t}"
+
+
+def test_batched_cache_writer_equals_the_per_sequence_one(gpu, ops):
+    """ns_b200_kv_store_batch: one launch writes every sequence's new rows at its own position, bit for bit what one
+    ns_q35_kv_store a sequence writes; a row past a cache's capacity is skipped and reported."""
+    from nextsycl_b200 import Error
+    B, T, Hkv, D, cap = 3, 2, 4, 128, 40
+    p0s = [0, 17, 38]
+    k = W.rng(929, 0).standard_normal((B, T, Hkv * D), dtype=np.float32)
+    v = W.rng(929, 1).standard_normal((B, T, Hkv * D), dtype=np.float32)
+    dk, dv = DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+    one, batch = [], []
+    for b in range(B):
+        for dst in (one, batch):
+            kc, vc = DevBuf(gpu, Hkv * cap * D * 2), DevBuf(gpu, Hkv * cap * D * 2)
+            kc.fill(0x11), vc.fill(0x22)
+            dst.append((kc, vc))
+        ops.kv_store(dk.view(b * T * Hkv * D * 4, T * Hkv * D * 4), Hkv * D, dv.view(b * T * Hkv * D * 4, T * Hkv * D * 4), Hkv * D, T, Hkv, D, cap, p0s[b],
+                     one[b][0], one[b][1])
+    table = ops.seq_table([(batch[b][0], batch[b][1], cap, p0s[b]) for b in range(B)])
+    ops.kv_store_batch(dk, Hkv * D, T * Hkv * D, dv, Hkv * D, T * Hkv * D, table, B, T, Hkv, D)
+    gpu.sync()
+    for b in range(B):
+        assert np.array_equal(batch[b][0].read(np.uint16), one[b][0].read(np.uint16)), b
+        assert np.array_equal(batch[b][1].read(np.uint16), one[b][1].read(np.uint16)), b
+    table = ops.seq_table([(batch[0][0], batch[0][1], cap, cap - 1)])      # two rows at the last position: the second does not fit
+    ops.kv_store_batch(dk, Hkv * D, T * Hkv * D, dv, Hkv * D, T * Hkv * D, table, 1, T, Hkv, D)
+    with pytest.raises(Error, match="803"):
+        gpu.sync()
+    gpu.sync()
