@@ -21,9 +21,9 @@ static const char* kEngines[] = {
     "ns_nhs_attn_decode_scratch", "ns_nhs_attn_decode",
     // glm5next
     "ns_mla_attend", "ns_mla_attend_sel", "ns_mla_attend_sel_q8", "ns_mla_cells", "ns_softmax_masked", "ns_to_f16", "ns_to_q8row", "ns_gather_q8_h",
-    "ns_gather_h", "ns_idx_pool", "ns_idx_score", "ns_topk",
+    "ns_gather_h", "ns_gemm_batch_h", "ns_idx_pool", "ns_idx_score", "ns_topk",
     // deepseek2
-    "ns_ds2_mla_decode", "ns_ds2_rope", "ns_ds2_kv_store",
+    "ns_ds2_mla_decode", "ns_ds2_mla_decode_q6k", "ns_ds2_rope", "ns_ds2_kv_store",
     // qwen35: the step before attention
     "ns_q35_qk_norm_rope", "ns_q35_qk_norm_rope_pos", "ns_q35_rope", "ns_b200_qkv_prepare",
     // qwen35 quantised caches

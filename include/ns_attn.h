@@ -178,6 +178,12 @@ int ns_b200_mla_prefill(ns_gpu* g, const void* q, int64_t q_tok, const void* k, 
 int ns_ds2_mla_decode(ns_gpu* g, const float* q, const uint16_t* kb, const uint16_t* vb, const uint16_t* cache, float* out, int64_t T, int64_t H,
                       int64_t pos0, float scale);
 
+/* kernels/llm/deepseek2/ds2.h:38-41 - the same with kv_b as the model file stores it (Q6_K: 210-byte blocks of 256 values;
+ * [H x (128 + 128)] rows of 512: per head its 128 k rows - row i holds k_i[0..511], q~ = sum_i q_nope[i] k_i - then its 128 v
+ * rows), decoded where it is read; no fp16 k_b / v_b is kept. The engine takes this form whenever the model keeps kv_b
+ * quantised (llm/deepseek2/src/engine.rs:1155). */
+int ns_ds2_mla_decode_q6k(ns_gpu* g, const float* q, const void* kvb, const uint16_t* cache, float* out, int64_t T, int64_t H, int64_t pos0, float scale);
+
 /* kernels/llm/glm5next/glm.h:47 - dense causal absorbed MLA over fp32 latents: qa [T][H][L], c [n][L], u [T][H][L] =
  * sum_s softmax(qa . c_s * scale) c_s over s <= pos0+t; exact two-pass softmax in fp32 (L up to 512). */
 int ns_mla_attend(ns_gpu* g, const float* qa, const float* c, float* u, int64_t T, int64_t H, int64_t L, int64_t pos0, float scale);
@@ -193,14 +199,23 @@ int ns_mla_attend_sel_q8(ns_gpu* g, const float* qa, const void* c, float* u, in
                          const int32_t* sel, const int32_t* sel_cnt, int64_t K);
 /* kernels/llm/glm5next/glm.h:58-62,70,72,76-78 - the helper steps of the reference's GEMM-form prompt MLA, under their own
  * names: each row's cell indices and count; the masked row softmax; fp32 -> fp16; fp32 rows -> q8 latent rows; rows
- * gathered by index from an fp16 matrix or from q8 rows. (The GEMMs between them are oneMKL calls in the reference,
- * ns_gemm_batch_h; this library does not export a GEMM - ns_mla_attend_sel replaces the whole sequence.) */
+ * gathered by index from an fp16 matrix or from q8 rows. Together with ns_gemm_batch_h below they are the whole call
+ * sequence of llm/glm5next/src/engine.rs:1908-1938; ns_mla_attend_sel does the same in one call for any number of rows. */
 int ns_mla_cells(ns_gpu* g, const int32_t* sel, const int32_t* sel_cnt, int64_t T, int64_t K, int64_t pos0, int32_t* idx, int32_t* n, int64_t NC);
 int ns_softmax_masked(ns_gpu* g, float* S, int64_t R, int64_t H, int64_t NC, const int32_t* n, float scale);
 int ns_to_f16(ns_gpu* g, const float* x, uint16_t* y, int64_t n);
 int ns_to_q8row(ns_gpu* g, const float* x, void* y, int64_t n, int64_t L);
 int ns_gather_q8_h(ns_gpu* g, const void* src, const int32_t* idx, uint16_t* out, int64_t n, int64_t L);
 int ns_gather_h(ns_gpu* g, const uint16_t* src, const int32_t* idx, uint16_t* out, int64_t n, int64_t C);
+
+/* kernels/llm/glm5next/glm.h:63-64 (glm.cpp:264-277, a oneMKL gemm_batch there) - `batch` independent products in fp16 with
+ * fp32 results: y_b [T, N] (+)= x_b [T, K] . op(w_b), op(w) = w^T (w [N, K], rows ldw apart) with trans_w, else w ([K, N]);
+ * x_b = x + b*sx (rows ldx apart), w_b = w + b*sw, y_b = y + b*sy (rows ldy apart), strides in elements; accumulate 0
+ * overwrites y. Here a tcgen05 kernel (operands staged by TMA, the accumulator in tensor memory) whenever x and w are
+ * 16-byte aligned with ldx, ldw, sx, sw multiples of 8 - the engine's shapes are - and a plain kernel otherwise. The order
+ * of the fp32 sums is the tensor cores' (oneMKL's is unspecified as well). */
+int ns_gemm_batch_h(ns_gpu* g, int64_t batch, int trans_w, int64_t T, int64_t N, int64_t K, const uint16_t* x, int64_t ldx, int64_t sx,
+                    const uint16_t* w, int64_t ldw, int64_t sw, float* y, int64_t ldy, int64_t sy, int accumulate);
 
 /* kernels/llm/deepseek41/silo/ds41.h:28-36 - deepseek41's MQA with heads of 512 where a key is its own value. A row at
  * position p = pos0 + t reads its last min(window, p+1) raw keys from the ring (fp16 [R][512], slot pos % R) and then the

@@ -76,6 +76,7 @@ ATTN = {
     "ns_b200_gqa_prefill": (C.c_int, [vp, C.c_int, vp, i64, vp, vp, i64, i64, i64, i64, i64, i64, vp]),
     "ns_b200_mla_prefill": (C.c_int, [vp, vp, i64, vp, i64, vp, i64, i64, i64, i64, C.c_float, vp]),
     "ns_ds2_mla_decode": (C.c_int, [vp, vp, vp, vp, vp, vp, i64, i64, i64, C.c_float]),
+    "ns_ds2_mla_decode_q6k": (C.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, C.c_float]),
     "ns_mla_attend": (C.c_int, [vp, vp, vp, vp, i64, i64, i64, i64, C.c_float]),
     "ns_mla_attend_sel": (C.c_int, [vp, vp, vp, vp, i64, i64, i64, i64, C.c_float, vp, vp, i64]),
     "ns_mla_attend_sel_q8": (C.c_int, [vp, vp, vp, vp, i64, i64, i64, i64, C.c_float, vp, vp, i64]),
@@ -85,6 +86,7 @@ ATTN = {
     "ns_to_q8row": (C.c_int, [vp, vp, vp, i64, i64]),
     "ns_gather_q8_h": (C.c_int, [vp, vp, vp, vp, i64, i64]),
     "ns_gather_h": (C.c_int, [vp, vp, vp, vp, i64, i64]),
+    "ns_gemm_batch_h": (C.c_int, [vp, i64, C.c_int, i64, i64, i64, vp, i64, i64, vp, i64, i64, vp, i64, i64, C.c_int]),
     "ns_q35_qk_norm_rope": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, i64, i64, vp, C.c_float, i64, C.c_float, i64]),
     "ns_q35_qk_norm_rope_pos": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, i64, i64, vp, C.c_float, i64, C.c_float, vp, i64, i64, i64]),
     "ns_q35_rope": (C.c_int, [vp, vp, i64, i64, vp, i64, i64, i64, i64, i64, C.c_float, i64]),

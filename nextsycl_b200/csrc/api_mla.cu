@@ -89,6 +89,99 @@ __global__ void __launch_bounds__(256) mla_unabsorb_kernel(const float* __restri
     }
 }
 
+// ---- kv_b as the model file stores it: Q6_K rows of 512 values (two 210-byte blocks: ql [128], qh [64], scales [16] int8,
+// d half; kernels/llm/deepseek2/ds2.cpp:117-137), per head its 128 k rows then its 128 v rows. A warp decodes one row at a
+// time: lane = (block, half n, group l4 of four l) takes the 16 values (quarter g 0..3) x (l = 4 l4 .. 4 l4 + 3), i.e.
+// columns 256 block + 128 n + 32 g + 4 l4 + e, from four bytes of ql's low part, four of its high part, four of qh and
+// the four scales of its half - read as 16-bit words, the blocks being only 2-byte aligned. Value = d * scale * (q - 32)
+// in fp32, the reference's order.
+constexpr int Q6_ROW_BYTES = 2 * 210;
+__device__ __forceinline__ uint32_t ld_u32_2(const uint8_t* p) {
+    const uint16_t* h = reinterpret_cast<const uint16_t*>(p);
+    return (uint32_t) h[0] | ((uint32_t) h[1] << 16);
+}
+__device__ __forceinline__ int q6_col(int lane, int g, int e) { return 256 * (lane >> 4) + 128 * ((lane >> 3) & 1) + 32 * g + 4 * (lane & 7) + e; }
+__device__ __forceinline__ void q6_decode16(const uint8_t* row, int lane, float (&v)[16]) {
+    const uint8_t* blk = row + (lane >> 4) * 210;
+    const int n = (lane >> 3) & 1, l4 = lane & 7;
+    const uint32_t qa = ld_u32_2(blk + 64 * n + 4 * l4), qb = ld_u32_2(blk + 64 * n + 32 + 4 * l4), qh = ld_u32_2(blk + 128 + 32 * n + 4 * l4);
+    const float d = __half2float(*reinterpret_cast<const __half*>(blk + 208));
+    const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192) + 8 * n + (l4 >> 2);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const float ds = __fmul_rn(d, (float) sc[2 * g]);
+        const uint32_t ql = (g & 1) ? qb : qa;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t lb = (ql >> (8 * e)) & 0xFF, hb = (qh >> (8 * e)) & 0xFF;
+            const int lo = g < 2 ? (int) (lb & 0xF) : (int) (lb >> 4);
+            const int q = (lo | (int) (((hb >> (2 * g)) & 3) << 4)) - 32;
+            v[4 * g + e] = __fmul_rn(ds, (float) q);
+        }
+    }
+}
+
+// q~[t,h,c] = sum_i q_nope[i] k_i[c] over the head's 128 Q6_K k rows (ds2.cpp:172-183), the rotated 64 copied behind it,
+// as fp16 [T][H][576]. A block a (row, head): its 8 warps each take every 8th k row, the sums meet in shared memory.
+__global__ void __launch_bounds__(256) mla_absorb_q6k_kernel(const float* __restrict__ q, const uint8_t* __restrict__ kvb, __half* __restrict__ qa, int H) {
+    __shared__ float qn[NOPE];
+    __shared__ float part[8][L];
+    const int th = blockIdx.x, h = th % H;
+    const float* qr = q + (int64_t) th * KL;
+    if (threadIdx.x < NOPE) qn[threadIdx.x] = qr[threadIdx.x];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint8_t* rows = kvb + (int64_t) h * (NOPE + V) * Q6_ROW_BYTES;
+    float acc[16];
+#pragma unroll
+    for (int f = 0; f < 16; ++f) acc[f] = 0.f;
+    for (int i = warp; i < NOPE; i += 8) {
+        float v[16];
+        q6_decode16(rows + (int64_t) i * Q6_ROW_BYTES, lane, v);
+        const float qi = qn[i];
+#pragma unroll
+        for (int f = 0; f < 16; ++f) acc[f] = fmaf(qi, v[f], acc[f]);
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) part[warp][q6_col(lane, g, e)] = acc[4 * g + e];
+    __syncthreads();
+    __half* dst = qa + (int64_t) th * CR;
+    for (int c = threadIdx.x; c < L; c += 256) {
+        float a = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) a += part[w][c];
+        dst[c] = __float2half_rn(a);
+    }
+    if (threadIdx.x < R) dst[L + threadIdx.x] = __float2half_rn(qr[NOPE + threadIdx.x]);
+}
+
+// out[t,h,r] = sum_c v_r[c] u[c] over the head's 128 Q6_K v rows (ds2.cpp:237-255). A block a (row, head), a warp a v row at a time.
+__global__ void __launch_bounds__(256) mla_unabsorb_q6k_kernel(const float* __restrict__ u, const uint8_t* __restrict__ kvb, float* __restrict__ out, int H) {
+    __shared__ float us[L];
+    const int th = blockIdx.x, h = th % H;
+    for (int i = threadIdx.x; i < L; i += 256) us[i] = u[(int64_t) th * L + i];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint8_t* rows = kvb + ((int64_t) h * (NOPE + V) + NOPE) * Q6_ROW_BYTES;
+    float mine[16];
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mine[4 * g + e] = us[q6_col(lane, g, e)];
+    for (int r = warp; r < V; r += 8) {
+        float v[16];
+        q6_decode16(rows + (int64_t) r * Q6_ROW_BYTES, lane, v);
+        float a = 0.f;
+#pragma unroll
+        for (int f = 0; f < 16; ++f) a = fmaf(v[f], mine[f], a);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane == 0) out[(int64_t) th * V + r] = a;
+    }
+}
+
 int check_rows(const char* name, int64_t T, int64_t H, int64_t pos0) {
     if (T < 1 || T > 64) return ns_fail(std::string(name) + ": 1..64 rows");
     if (H < 1 || H > 1024) return ns_fail(std::string(name) + ": 1..1024 heads");
@@ -144,6 +237,31 @@ int ns_ds2_mla_decode(ns_gpu* g, const float* q, const uint16_t* kb, const uint1
     mla_unabsorb_kernel<<<(unsigned) (T * H * UNABSORB_SPLIT), 256, 0, g->compute>>>(u, (const __half*) vb, out, (int) T, (int) H);
     return ns_launched(name);
     NS_CATCH("ns_ds2_mla_decode")
+}
+
+// kernels/llm/deepseek2/ds2.h:38-41: the same with kv_b as the model file stores it - Q6_K, [H x (128 + 128)] rows of 512: per
+// head its 128 k rows (row i = k_i[0..511], so q~ = sum_i q_nope[i] k_i), then its 128 v rows - decoded where it is read.
+int ns_ds2_mla_decode_q6k(ns_gpu* g, const float* q, const void* kvb, const uint16_t* cache, float* out, int64_t T, int64_t H, int64_t pos0, float scale) {
+    NS_TRY
+    const char* name = "ns_ds2_mla_decode_q6k";
+    if (ns_enter(g, name)) return -1;
+    if (check_rows(name, T, H, pos0)) return -1;
+    if (!q || !kvb || !cache || !out) return ns_fail(std::string(name) + ": a null buffer");
+    if (((uintptr_t) kvb & 1) != 0 || ((uintptr_t) cache & 15) != 0) return ns_fail(std::string(name) + ": kv_b 2-byte aligned, the cache 16-byte aligned");
+    const int64_t qa_bytes = (T * H * CR * 2 + 255) / 256 * 256, u_bytes = (T * H * L * 4 + 255) / 256 * 256;
+    const int64_t part_floats = ns_mla_partial_floats(pos0 + T, T, H, g->sms);
+    void* kept = nullptr;
+    if (ns_kept(g, (size_t) (qa_bytes + u_bytes + part_floats * 4), &kept)) return -1;
+    __half* qa = (__half*) kept;
+    float* u = (float*) ((uint8_t*) kept + qa_bytes);
+    float* part = part_floats ? (float*) ((uint8_t*) kept + qa_bytes + u_bytes) : nullptr;
+    mla_absorb_q6k_kernel<<<(unsigned) (T * H), 256, 0, g->compute>>>(q, (const uint8_t*) kvb, qa, (int) H);
+    if (ns_launched(name)) return -1;
+    MlaDecodeArgs a{qa, cache, u, part, T, H, pos0, scale, 64, pos0 + T, nullptr, 0, nullptr};
+    if (ns_launch_mla_decode(g, a, name)) return -1;
+    mla_unabsorb_q6k_kernel<<<(unsigned) (T * H), 256, 0, g->compute>>>(u, (const uint8_t*) kvb, out, (int) H);
+    return ns_launched(name);
+    NS_CATCH("ns_ds2_mla_decode_q6k")
 }
 
 }  // extern "C"

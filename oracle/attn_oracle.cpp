@@ -475,6 +475,33 @@ void orc_mla_gemm(const float* q, const uint16_t* cache, int64_t T, int64_t H, i
     }
 }
 
+// Q6_K rows as deepseek2's decode reads kv_b (kernels/llm/deepseek2/ds2.cpp:117-137; ggml's block_q6_K, kernels/ns/ns_gguf.h:
+// 210 bytes a 256 values: ql [128], qh [64], scales [16] int8, d half). Value l (0..31) of quarter g (0..3) of half n (0..1)
+// of a block: ((low or high nibble of ql[64 n + 32 (g & 1) + l]) | 2 bits of qh[32 n + l] at 2 g) << 4) - 32, times
+// d x scales[8 n + 2 g + l / 16] - the product taken as float(d) * float(scale) * float(q), left to right.
+// rows [nrows] of `cols` values (cols a multiple of 256) -> out fp32 [nrows][cols]
+void orc_q6k_rows(const uint8_t* blocks, int64_t nrows, int64_t cols, float* out) {
+    const int64_t nb = cols / 256;
+    for (int64_t r = 0; r < nrows; ++r)
+        for (int64_t b = 0; b < nb; ++b) {
+            const uint8_t* blk = blocks + (r * nb + b) * 210;
+            const uint8_t* ql = blk;
+            const uint8_t* qh = blk + 128;
+            const int8_t* sc = (const int8_t*) (blk + 192);
+            uint16_t dbits;
+            std::memcpy(&dbits, blk + 208, 2);
+            const float d = h2f(dbits);
+            for (int n = 0; n < 2; ++n)
+                for (int g = 0; g < 4; ++g)
+                    for (int l = 0; l < 32; ++l) {
+                        const uint8_t lb = ql[64 * n + 32 * (g & 1) + l];
+                        const int lo = g < 2 ? (lb & 0xF) : (lb >> 4);
+                        const int q = (lo | (((qh[32 * n + l] >> (2 * g)) & 3) << 4)) - 32;
+                        out[r * cols + b * 256 + 128 * n + 32 * g + l] = d * (float) sc[8 * n + 2 * g + l / 16] * (float) q;
+                    }
+        }
+}
+
 // fp64 yardstick for absorbed MLA over the fp16 cache (q fp32 as given).
 void orc_mla_exact(const float* q, const uint16_t* cache, int64_t T, int64_t H, int64_t L, int64_t R, int64_t pos0, double scale, double* u) {
     const int64_t CR = L + R;

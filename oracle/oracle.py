@@ -304,3 +304,28 @@ def ds41_cand_pos(selc, cand, bs):
     sel = np.empty((T, kp), np.int32)
     lib().orc_ds41_cand_pos(selc.ctypes.data_as(_pi), cand.ctypes.data_as(_pi), sel.ctypes.data_as(_pi), i64(T), i64(cand.shape[1]), i64(kp), i64(bs))
     return sel
+
+
+def gemm_batch_h(batch, trans_w, T, N, K, x, ldx, sx, w, ldw, sw, y=None, ldy=None, sy=None):
+    """kernels/llm/glm5next/glm.cpp:264-277 (a oneMKL gemm_batch in the reference; its summation order is unspecified, so the
+    checker sums in float64): y_b [T, N] (+)= x_b [T, K] . op(w_b) over flat fp16 arrays x, w (uint16 bit patterns) with
+    the call's strides; y (flat float32, or None for zeros) supplies what is accumulated onto. -> float64 [batch, T, N]."""
+    xf, wf = x.view(np.float16).astype(np.float64), w.view(np.float16).astype(np.float64)
+    out = np.zeros((batch, T, N))
+    for b in range(batch):
+        xb = np.lib.stride_tricks.as_strided(xf[b * sx:], (T, K), (ldx * 8, 8))
+        if trans_w:
+            wb = np.lib.stride_tricks.as_strided(wf[b * sw:], (N, K), (ldw * 8, 8)).T
+        else:
+            wb = np.lib.stride_tricks.as_strided(wf[b * sw:], (K, N), (ldw * 8, 8))
+        out[b] = xb @ wb
+        if y is not None:
+            out[b] += np.lib.stride_tricks.as_strided(y[b * sy:], (T, N), (ldy * 4, 4))
+    return out
+
+
+def q6k_rows(blocks, nrows, cols):
+    """Q6_K rows (uint8 [nrows, cols/256 * 210]) -> fp32 [nrows, cols], as deepseek2's decode expands kv_b (ds2.cpp:117-137)."""
+    out = np.empty((nrows, cols), np.float32)
+    lib().orc_q6k_rows(blocks.ctypes.data_as(C.POINTER(C.c_uint8)), i64(nrows), i64(cols), _f(out))
+    return out

@@ -126,3 +126,79 @@ def test_helper_kernels(gpu):
         e = np.exp(z - z.max(-1, keepdims=True))
         assert np.allclose(got[t, :, :m], e / e.sum(-1, keepdims=True), atol=1e-6)
         assert not got[t, :, m:].any()
+
+
+def _gemm(gpu, batch, trans_w, T, N, K, x, ldx, sx, w, ldw, sw, y, ldy, sy, accumulate):
+    dx, dw, dy = DevBuf.of(gpu, x), DevBuf.of(gpu, w), DevBuf.of(gpu, y)
+    check(gpu.api, gpu.api.ns_gemm_batch_h(gpu.raw, batch, trans_w, T, N, K, dx.ptr, ldx, sx, dw.ptr, ldw, sw, dy.ptr, ldy, sy, accumulate), "ns_gemm_batch_h")
+    gpu.sync()
+    return dy.read(np.float32)
+
+
+@pytest.mark.parametrize("batch,trans_w,T,N,K,pad,acc", [
+    (32, 1, 64, 2112, 512, 0, 0),     # the engine's score product at its largest cell count (llm/glm5next/src/engine.rs:1925)
+    (32, 0, 64, 512, 2112, 0, 0),     # and its value product (:1930)
+    (3, 1, 64, 64, 512, 0, 0),        # the smallest padded cell count
+    (3, 0, 64, 512, 64, 0, 1),        # accumulating
+    (2, 1, 200, 300, 136, 8, 1),      # ragged tiles in every dimension, padded rows, accumulating
+    (2, 0, 130, 72, 200, 16, 0),
+    (1, 1, 1, 8, 8, 0, 0),            # one row
+    (2, 1, 33, 50, 70, 3, 0),         # odd strides: the plain kernel
+    (2, 0, 33, 50, 70, 5, 1),
+])
+def test_gemm_batch_h(gpu, batch, trans_w, T, N, K, pad, acc):
+    """ns_gemm_batch_h against float64 products of the same fp16 values. Tolerance: fp32 accumulation of K products of
+    magnitude ~1: |got - want| <= 1e-3 + 1e-4 |want| sqrt(K) is generous; the sums are exact to ~1e-5 in practice."""
+    rng = W.rng(963, batch * 1000 + T + N + K + trans_w)
+    ldx, ldy = K + pad, N + pad
+    wr, wc = (N, K) if trans_w else (K, N)
+    ldw = wc + pad
+    sx, sw, sy = T * ldx + pad, wr * ldw + pad, T * ldy + pad
+    x = (rng.standard_normal(batch * sx, dtype=np.float32)).astype(np.float16).view(np.uint16)
+    w = (rng.standard_normal(batch * sw, dtype=np.float32)).astype(np.float16).view(np.uint16)
+    y0 = rng.standard_normal(batch * sy, dtype=np.float32)
+    got = _gemm(gpu, batch, trans_w, T, N, K, x, ldx, sx, w, ldw, sw, y0.copy(), ldy, sy, acc)
+    want = O.gemm_batch_h(batch, trans_w, T, N, K, x, ldx, sx, w, ldw, sw, y0 if acc else None, ldy, sy)
+    keep = np.ones(batch * sy, bool)      # everything outside the [T, N] blocks must be untouched
+    for b in range(batch):
+        g = np.lib.stride_tricks.as_strided(got[b * sy:], (T, N), (ldy * 4, 4))
+        d = np.abs(g - want[b])
+        assert np.all(d <= 1e-3 + 1e-4 * np.abs(want[b]) * np.sqrt(K)), (b, float(d.max()))
+        for t in range(T):
+            keep[b * sy + t * ldy: b * sy + t * ldy + N] = False
+    assert np.array_equal(got[keep], y0[keep])
+
+
+def test_prompt_block_as_the_engine_calls_it(gpu):
+    """The reference engine's prompt path for one block of rows, call for call (llm/glm5next/src/engine.rs:1908-1938):
+    ns_mla_cells, ns_gather_h, ns_to_f16, ns_gemm_batch_h (scores), ns_softmax_masked, ns_to_f16, ns_gemm_batch_h (values) -
+    against the oracle's statement of the same attention (glm.cpp's mla_dec<512> numerics restated) and against
+    ns_mla_attend_sel, the one-call form."""
+    api = gpu.api
+    tr, H, L, pos0, K = 5, 64, 512, 300, 16
+    NC = -(-(4 * K + 3) // 64) * 64
+    rng = W.rng(964, 0)
+    qa = rng.standard_normal((tr, H, L), dtype=np.float32)
+    c16 = (0.5 * rng.standard_normal((pos0 + tr, L), dtype=np.float32)).astype(np.float16)
+    sel = np.stack([np.sort(rng.choice((pos0 + t + 1) // 4, size=K, replace=False)) for t in range(tr)]).astype(np.int32)
+    cnt = np.full(tr, K, np.int32)
+    scale = np.float32(1 / 16.0)
+    dq, dc, dsel, dcnt = DevBuf.of(gpu, qa), DevBuf.of(gpu, c16), DevBuf.of(gpu, sel), DevBuf.of(gpu, cnt)
+    didx, dn = DevBuf(gpu, tr * NC * 4), DevBuf(gpu, tr * 4)
+    gh, qh = DevBuf(gpu, tr * NC * L * 2), DevBuf(gpu, tr * H * L * 2)
+    sb, ph, u = DevBuf(gpu, tr * H * NC * 4), DevBuf(gpu, tr * H * NC * 2), DevBuf(gpu, tr * H * L * 4)
+    check(api, api.ns_mla_cells(gpu.raw, dsel.ptr, dcnt.ptr, tr, K, pos0, didx.ptr, dn.ptr, NC), "cells")
+    check(api, api.ns_gather_h(gpu.raw, dc.ptr, didx.ptr, gh.ptr, tr * NC, L), "gather")
+    check(api, api.ns_to_f16(gpu.raw, dq.ptr, qh.ptr, tr * H * L), "to_f16")
+    check(api, api.ns_gemm_batch_h(gpu.raw, tr, 1, H, NC, L, qh.ptr, L, H * L, gh.ptr, L, NC * L, sb.ptr, NC, H * NC, 0), "scores")
+    check(api, api.ns_softmax_masked(gpu.raw, sb.ptr, tr, H, NC, dn.ptr, scale), "softmax")
+    check(api, api.ns_to_f16(gpu.raw, sb.ptr, ph.ptr, tr * H * NC), "to_f16")
+    check(api, api.ns_gemm_batch_h(gpu.raw, tr, 0, H, L, NC, ph.ptr, NC, H * NC, gh.ptr, L, NC * L, u.ptr, L, H * L, 0), "values")
+    gpu.sync()
+    got = u.read(np.float32).reshape(tr, H, L)
+    want = O.mla_dec512(qa, c16.view(np.uint16), tr, H, pos0, scale, sel=sel, sel_cnt=cnt, K=K)
+    close(got, want)
+    one = DevBuf(gpu, tr * H * L * 4)
+    check(api, api.ns_mla_attend_sel(gpu.raw, dq.ptr, dc.ptr, one.ptr, tr, H, L, pos0, scale, dsel.ptr, dcnt.ptr, K), "attend_sel")
+    gpu.sync()
+    close(one.read(np.float32).reshape(tr, H, L), got)

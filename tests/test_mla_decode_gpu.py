@@ -97,3 +97,57 @@ def test_a_verify_row_equals_the_one_row_pass(gpu, ops):
     q = W.normal_f16(941, 2, (T, H, 576))
     got = run(gpu, ops, q, cache, T, H, n - T)
     assert_close(got, O.mla_gemm(q.astype(np.float32), cache.view(np.uint16), T, H, 512, 64, n - T, np.float32(SCALE)), "12 rows")
+
+
+def _q6k_blocks(rng, nrows, cols=512):
+    """Random Q6_K rows: any bytes are a valid block; d a small half so the values are O(0.1)."""
+    nb = cols // 256
+    blk = rng.integers(0, 256, size=(nrows, nb, 210), dtype=np.uint8)
+    blk[:, :, 192:208] = rng.integers(-32, 32, size=(nrows, nb, 16)).astype(np.int8).view(np.uint8)
+    d = (rng.uniform(2e-4, 6e-4, size=(nrows, nb)).astype(np.float32) * rng.choice([-1.0, 1.0], size=(nrows, nb)).astype(np.float32)).astype(np.float16)
+    blk[:, :, 208:210] = d.view(np.uint8).reshape(nrows, nb, 2)
+    return np.ascontiguousarray(blk.reshape(nrows, nb * 210))
+
+
+def _run_q6k(gpu, q, kvb, cache, T, H, pos0):
+    from nextsycl_b200.core import check
+    dq, dk, dc = DevBuf.of(gpu, q), DevBuf.of(gpu, kvb), DevBuf.of(gpu, cache)
+    out = DevBuf(gpu, T * H * 128 * 4)
+    out.fill(0xFF)
+    check(gpu.api, gpu.api.need("ns_ds2_mla_decode_q6k")(gpu.raw, dq.ptr, dk.ptr, dc.ptr, out.ptr, T, H, pos0, np.float32(SCALE)), "ns_ds2_mla_decode_q6k")
+    gpu.sync()
+    return out.read(np.float32).reshape(T, H, 128)
+
+
+def test_ds2_q6k_decoder_bit_exact(gpu):
+    """The Q6_K reader of ns_ds2_mla_decode_q6k, read out exactly: one cell whose latent is a one-hot column c makes the
+    attention's u that one-hot, so out[h][r] = v_r[c] as the decoder produced it - equal to the oracle's decode of the same
+    blocks (kernels/llm/deepseek2/ds2.cpp:123-137) bit for bit, for columns in every (block, half, quarter, scale half)."""
+    H = 4
+    rng = W.rng(945, 0)
+    kvb = _q6k_blocks(rng, H * 256)
+    vals = O.q6k_rows(kvb, H * 256, 512).reshape(H, 256, 512)
+    q = rng.standard_normal((1, H, 192), dtype=np.float32)
+    cols = [256 * b + 128 * n + 32 * g + l for b in (0, 1) for n in (0, 1) for g in (0, 1, 2, 3) for l in (0, 15, 16, 31)][::3] + [0, 511]
+    for c in cols:
+        cache = np.zeros((1, 576), np.float16)
+        cache[0, c] = 1.0
+        got = _run_q6k(gpu, q, kvb, cache, 1, H, 0)
+        assert np.array_equal(got[0].view(np.uint32), vals[:, 128:, c].view(np.uint32)), c
+
+
+@pytest.mark.parametrize("T,H,n", [(1, 128, 700), (3, 16, 2500)])
+def test_ds2_q6k_whole_decode(gpu, T, H, n):
+    """ns_ds2_mla_decode_q6k against the same three stages on the CPU: kv_b expanded by the oracle's Q6_K reader, q~ = sum_i
+    q_nope[i] k_i, the oracle's latent attention (GEMM-form numerics), out = v . u."""
+    rng = W.rng(946, T)
+    kvb = _q6k_blocks(rng, H * 256)
+    vals = O.q6k_rows(kvb, H * 256, 512).reshape(H, 256, 512).astype(np.float64)
+    q = rng.standard_normal((T, H, 192), dtype=np.float32)
+    cache = W.normal_f16(946, 3, (n, 576), 0.5)
+    got = _run_q6k(gpu, q, kvb, cache, T, H, n - T)
+    qa = np.einsum("thi,hic->thc", q[:, :, :128].astype(np.float64), vals[:, :128]).astype(np.float32)
+    qfull = np.ascontiguousarray(np.concatenate([qa, q[:, :, 128:]], axis=2))
+    u = O.mla_gemm(qfull, cache.view(np.uint16), T, H, 512, 64, n - T, np.float32(SCALE))
+    want = np.einsum("hrc,thc->thr", vals[:, 128:], u.astype(np.float64))
+    assert_close(got, want, "q6k whole decode")

@@ -425,3 +425,26 @@ def test_ref_pin_indexer_scores_candidates_and_picks():
         sel = O.topk(sc, n, min(d["ITOP"], n))[0]
         want = d["topk"][i]
         assert np.array_equal(sel[:min(vis, d["ITOP"])], want[want >= 0]), r
+
+
+def test_q6k_reader_is_ggml_block_layout():
+    """orc_q6k_rows (kernels/llm/deepseek2/ds2.cpp:117-137) against ggml's published block_q6_K layout written out in numpy."""
+    rng = np.random.default_rng(7)
+    blk = rng.integers(0, 256, size=(3, 420), dtype=np.uint8)
+    d = np.array([1e-3, -2e-3], np.float16)
+    for b in range(2):
+        blk[:, b * 210 + 208:b * 210 + 210] = d[b:b + 1].view(np.uint8)
+    got = O.q6k_rows(blk, 3, 512)
+    want = np.zeros((3, 512), np.float32)
+    for r in range(3):
+        for b in range(2):
+            x = blk[r, b * 210:(b + 1) * 210]
+            ql, qh, sc, dd = x[:128].astype(np.int32), x[128:192].astype(np.int32), x[192:208].view(np.int8), np.float32(x[208:210].view(np.float16)[0])
+            for n in range(2):
+                for l in range(32):
+                    h = qh[32 * n + l]
+                    qs = [(ql[64 * n + l] & 0xF) | ((h & 3) << 4), (ql[64 * n + l + 32] & 0xF) | (((h >> 2) & 3) << 4),
+                          (ql[64 * n + l] >> 4) | (((h >> 4) & 3) << 4), (ql[64 * n + l + 32] >> 4) | (((h >> 6) & 3) << 4)]
+                    for g in range(4):
+                        want[r, b * 256 + 128 * n + 32 * g + l] = dd * np.float32(sc[8 * n + l // 16 + 2 * g]) * np.float32(qs[g] - 32)
+    assert np.array_equal(got, want)
