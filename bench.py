@@ -376,10 +376,13 @@ def wl_mla_prefill(env, T=4096, p0=32768, H=128):
     return step, info
 
 
-def wl_kvsplit_decode(env, T=4, Hq=32, Hkv=4, D=128, kv=262144):
+def wl_kvsplit_decode(env, T=4, Hq=32, Hkv=4, D=128, kv=262144, mode="fused"):
     """benchmark configuration 5 over the ranks: each rank holds kv/N keys of every key head; a step is this rank's split-KV
     decode, the push of its partial into every rank's mailbox over NVLink, and the combine of what arrived in its own
-    (strong scaling: the context is fixed, the ranks share it)."""
+    (strong scaling: the context is fixed, the ranks share it). mode "fused": the step as ONE kernel (ns_b200_kvsplit_step);
+    "launches": the same protocol as three dependent launches (ns_b200_kvsplit_decode + _combine); "nccl": the exchange as a
+    library all-gather (ns_b200_kvsplit_partial -> torch.distributed.all_gather_into_tensor over NCCL on the library's stream ->
+    ns_b200_kvsplit_merge), launched from the host every step - the baseline the other two are measured against."""
     from nextsycl_b200 import DevBuf
     from nextsycl_b200 import workloads as W
     from nextsycl_b200.dist import KvSplit, key_ranges
@@ -404,20 +407,51 @@ def wl_kvsplit_decode(env, T=4, Hq=32, Hkv=4, D=128, kv=262144):
     out = DevBuf(env.gpu, T * Hq * D * 2)
     env.barrier()
 
+    nccl = None
+    if mode == "nccl":
+        import torch
+        api, raw = env.gpu.api, env.gpu.raw
+        rows = T * Hq
+        if env.dist:
+            stream = torch.cuda.ExternalStream(env.gpu.stream(), device=torch.device("cuda", env.local))
+            t_part = torch.empty(rows * (D + 2), dtype=torch.float32, device="cuda")
+            t_all = torch.empty(env.world * rows * (D + 2), dtype=torch.float32, device="cuda")
+            part_ptr, all_ptr = t_part.data_ptr(), t_all.data_ptr()
+            nccl = (torch, stream, t_part, t_all)
+        else:
+            both = DevBuf(env.gpu, rows * (D + 2) * 4)
+            part_ptr = all_ptr = both.ptr
+            nccl = (None, None, both, both)
+
     def one(r):
         kc, vc = caches[r]
-        grp.decode(q, Hq * D, kc, vc, Hkv, count, base, kv - T, sc, epoch=0)   # step numbers kept on the device
-        grp.combine(out, epoch=0, wait_us=500000)
-    # a step is recorded once per cache set and replayed: one submission instead of three launches from Python, so the
-    # ranks' hosts do not set the pace
+        if mode == "fused":
+            grp.step(q, Hq * D, kc, vc, Hkv, count, base, kv - T, sc, out, epoch=0, wait_us=500000)   # step numbers kept on the device
+        elif mode == "launches":
+            grp.decode(q, Hq * D, kc, vc, Hkv, count, base, kv - T, sc, epoch=0)
+            grp.combine(out, epoch=0, wait_us=500000)
+        else:
+            from nextsycl_b200.core import check
+            check(api, api.ns_b200_kvsplit_partial(raw, q.ptr, Hq * D, kc.ptr, vc.ptr, T, Hq, Hkv, D, count, base, kv - T, sc.ptr, part_ptr), "partial")
+            if nccl[0] is not None:
+                with nccl[0].cuda.stream(nccl[1]):
+                    env.dist.all_gather_into_tensor(nccl[3], nccl[2])
+            check(api, api.ns_b200_kvsplit_merge(raw, all_ptr, env.world, T, Hq, D, out.ptr), "merge")
     one(0)
     env.barrier()
-    graphs = [env.gpu.record(lambda r=r: one(r)) for r in range(rotate)]
     i = [0]
+    if mode == "nccl":
+        def step():
+            one(i[0] % rotate)
+            i[0] += 1
+        graphs = None
+    else:
+        # a step is recorded once per cache set and replayed: one submission, so the ranks' hosts do not set the pace
+        graphs = [env.gpu.record(lambda r=r: one(r)) for r in range(rotate)]
 
-    def step():
-        graphs[i[0] % rotate].launch()
-        i[0] += 1
+        def step():
+            graphs[i[0] % rotate].launch()
+            i[0] += 1
     def check():
         """After the timed region: one more step on cache set 0; every rank's rows must be the same bits, and rank 0 holds
         them to the CPU checker's decode of the WHOLE context, rebuilt on the host from the ranks' seeds (a combine that
@@ -449,8 +483,8 @@ def wl_kvsplit_decode(env, T=4, Hq=32, Hkv=4, D=128, kv=262144):
             res.update({"max_abs": float(d.max()), "ok": bool(same and np.all(d <= 2e-3 + 1e-2 * np.abs(want))),
                         "against": "CPU checker (flash numerics) over all %d keys; tolerance 2e-3 + 1e-2 |want|" % kv})
         return res
-    info = {"bytes": 2 * count * Hkv * D * 2, "bytes_total": 2 * kv * Hkv * D * 2, "flops": 0, "bound": "hbm", "launches": 3,
-            "keep": (grp, q, caches, sc, out, graphs), "check": check}
+    info = {"bytes": 2 * count * Hkv * D * 2, "bytes_total": 2 * kv * Hkv * D * 2, "flops": 0, "bound": "hbm", "launches": 1 if mode == "fused" else 3,
+            "keep": (grp, q, caches, sc, out, graphs, nccl), "check": check}
     return step, info
 
 
@@ -467,6 +501,10 @@ def measure(env, name, steps, warmup, min_ms=0.0):
         step, info = wl_gqa_decode(env, 4, 32, 4, 128, 262144, 1, rotate=2, real_data=False, graph=True)
     elif name == "decode_c5_split":
         step, info = wl_kvsplit_decode(env)
+    elif name == "decode_c5_split_3launch":
+        step, info = wl_kvsplit_decode(env, mode="launches")
+    elif name == "decode_c5_split_nccl":
+        step, info = wl_kvsplit_decode(env, mode="nccl")
     elif name.startswith("decode_split_kv"):      # decode_split_kv<tokens>: the same with another context length
         step, info = wl_kvsplit_decode(env, kv=int(name[len("decode_split_kv"):]))
     elif name.startswith("decode_q35_"):
@@ -513,7 +551,7 @@ NCU_TRAFFIC = {"decode_c2": 1.073912e9 + 12.0e6, "mla_decode_32k": 37.96e6 + 0.0
 OTHERS_1GPU = [("prefill_16k", 10), ("prefill_c1", 50), ("prefill_q35_16k", 10), ("decode_c2_b1", 50), ("decode_128k", 30), ("decode_c5", 30), ("decode_q35_f16", 30),
                ("decode_q35_q8", 30), ("decode_q35_q4", 30), ("mla_decode_4k", 50),
                ("mla_decode_32k", 50), ("mla_decode_131k", 30), ("ds2_decode_32k", 50), ("mla_prefill_c4", 10)]
-OTHERS_NGPU = [("decode_c5_split", 50), ("prefill_16k", 10), ("mla_prefill_c4", 10)]
+OTHERS_NGPU = [("decode_c5_split", 50), ("decode_c5_split_3launch", 50), ("decode_c5_split_nccl", 50), ("prefill_16k", 10), ("mla_prefill_c4", 10)]
 
 
 def config_of(name, n):
@@ -528,7 +566,9 @@ def config_of(name, n):
         "decode_q35_f16": "qwen35 geometry: 1 decode row, 24 query / 4 key heads of 256, 131,072 cached tokens, fp16 caches (ns_q35_attn_decode_kv)",
         "decode_q35_q8": "the same over q8_0 caches (272-byte rows)",
         "decode_q35_q4": "the same over q4_0 caches (144-byte rows)",
-        "decode_c5_split": "config 5 over the ranks: 262,144 cached tokens split by key ranges, partials pushed over NVLink and combined (strong scaling)",
+        "decode_c5_split": "config 5 over the ranks: 262,144 cached tokens split by key ranges, partials pushed over NVLink and combined, the step one kernel (strong scaling)",
+        "decode_c5_split_3launch": "the same protocol as three dependent launches (split decode, merge + push, combine)",
+        "decode_c5_split_nccl": "the same split with the partials exchanged by an NCCL all-gather launched from the host every step (baseline)",
         "ds2_decode_32k": "ns_ds2_mla_decode, the reference's whole decode op around config 3's attention: fp32 q [128 x 192] absorbed through k_b, 32,768 cells, out through v_b",
         "mla_decode_4k": "config 3: absorbed MLA decode, 128 heads, 576-wide latent cache, 4,096 cells",
         "mla_decode_32k": "config 3, 32,768 cells",

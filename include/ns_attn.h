@@ -302,6 +302,22 @@ int ns_b200_kvsplit_decode(ns_gpu* g, const void* q, int64_t qs, const void* kc,
                            int64_t epoch);
 int ns_b200_kvsplit_combine(ns_gpu* g, void* mailbox, int64_t nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t wait_us,
                             void* out);
+/* The same step as ONE kernel launch: this rank's split-KV decode, the push of its partials into every mailbox and the
+ * combine of what arrives in its own (own_mailbox: this rank's mailbox as the host addresses it, also entry `rank` of
+ * mailboxes), rows written to out [T][Hq*D] fp16. The kernel's CTAs hand work to one another, so it is launched
+ * cooperatively (every CTA resident) - which the benchmark's long-context shape and anything up to two CTAs an SM allows;
+ * larger grids run the three launches of the two calls above instead, with the same result. Arguments and epochs as above;
+ * a wait that runs out raises code 701 (peers) or 801 (this GPU's own CTAs) at the next ns_sync. */
+int ns_b200_kvsplit_step(ns_gpu* g, const void* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                         int64_t kv_local, int64_t key_base, int64_t p0, float* scratch, int64_t rank, int64_t nranks, void* const* mailboxes,
+                         void* own_mailbox, int64_t epoch, int64_t wait_us, void* out);
+/* The exchange left to the caller (the baseline the mailbox forms are measured against): ns_b200_kvsplit_partial runs this
+ * rank's split-KV decode and leaves its merged partial - (O [D], m in log2 units, l) per (row, head), [T*Hq][D+2] floats -
+ * in `part`; the caller gathers the ranks' partials side by side (a library all-gather such as ncclAllGather) into
+ * [nranks][T*Hq][D+2]; ns_b200_kvsplit_merge merges them into out [T][Hq*D] fp16. */
+int ns_b200_kvsplit_partial(ns_gpu* g, const void* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                            int64_t kv_local, int64_t key_base, int64_t p0, float* scratch, float* part);
+int ns_b200_kvsplit_merge(ns_gpu* g, const float* parts, int64_t nranks, int64_t T, int64_t Hq, int64_t D, void* out);
 /* Device memory shared between processes of one machine (CUDA IPC): a 64-byte handle for ptr (the start of an
  * ns_alloc allocation), opened in another process as a peer-mapped address, closed when done. */
 int ns_b200_ipc_export(ns_gpu* g, void* ptr, void* handle64);

@@ -225,6 +225,73 @@ int ns_b200_kvsplit_decode(ns_gpu* g, const void* q, int64_t qs, const void* kc,
     NS_CATCH("ns_b200_kvsplit_decode")
 }
 
+int ns_b200_kvsplit_partial(ns_gpu* g, const void* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                            int64_t kv_local, int64_t key_base, int64_t p0, float* scratch, float* part) {
+    NS_TRY
+    const char* name = "ns_b200_kvsplit_partial";
+    if (ns_enter(g, name)) return -1;
+    if (T < 1 || T > 8 || !shape_ok(Hq, Hkv, D)) return ns_fail(std::string(name) + ": 1..8 rows, heads of 128 or 256, 1..16 query heads a key head");
+    if (kv_local < 0 || kv_local >= ((int64_t) 1 << 31) || key_base < 0 || p0 < 0 || p0 + T >= ((int64_t) 1 << 40))
+        return ns_fail(std::string(name) + ": a key range of 0 .. 2^31 keys");
+    if (qs % 8 != 0 || ((uintptr_t) q & 15) != 0 || ((uintptr_t) part & 7) != 0) return ns_fail(std::string(name) + ": query rows 16-byte aligned");
+    if (!q || !part || (kv_local > 0 && (!kc || !vc || !scratch))) return ns_fail(std::string(name) + ": a null buffer");
+    GqaDecodeArgs a{};
+    a.q = q;
+    a.qs = qs;
+    a.one = ns_b200_seq{kc, vc, kv_local, p0 - key_base};
+    a.part = scratch;
+    a.B = 1, a.T = T, a.Hq = Hq, a.Hkv = Hkv, a.D = D;
+    a.ns_max = std::max<int64_t>(1, ns_dec_splits_bound(kv_local, Hkv));
+    a.local_part = part;
+    return ns_launch_gqa_decode(g, a, name);
+    NS_CATCH("ns_b200_kvsplit_partial")
+}
+
+int ns_b200_kvsplit_merge(ns_gpu* g, const float* parts, int64_t nranks, int64_t T, int64_t Hq, int64_t D, void* out) {
+    NS_TRY
+    const char* name = "ns_b200_kvsplit_merge";
+    if (ns_enter(g, name)) return -1;
+    if (!parts || !out) return ns_fail(std::string(name) + ": a null buffer");
+    if (nranks < 1 || nranks > 64 || T < 1 || T > 8 || Hq < 1) return ns_fail(std::string(name) + ": 1..64 ranks, 1..8 rows");
+    return ns_launch_gqa_merge_ranks(g, parts, (int) nranks, T, Hq, D, out, 0, name);
+    NS_CATCH("ns_b200_kvsplit_merge")
+}
+
+int ns_b200_kvsplit_step(ns_gpu* g, const void* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
+                         int64_t kv_local, int64_t key_base, int64_t p0, float* scratch, int64_t rank, int64_t nranks, void* const* mailboxes,
+                         void* own_mailbox, int64_t epoch, int64_t wait_us, void* out) {
+    NS_TRY
+    const char* name = "ns_b200_kvsplit_step";
+    if (ns_enter(g, name)) return -1;
+    if (T < 1 || T > 8 || !shape_ok(Hq, Hkv, D)) return ns_fail(std::string(name) + ": 1..8 rows, heads of 128 or 256, 1..16 query heads a key head");
+    if (nranks < 1 || nranks > 64 || rank < 0 || rank >= nranks) return ns_fail(std::string(name) + ": rank within 1..64 ranks");
+    if (kv_local < 0 || kv_local >= ((int64_t) 1 << 31) || key_base < 0 || p0 < 0 || p0 + T >= ((int64_t) 1 << 40))
+        return ns_fail(std::string(name) + ": a key range of 0 .. 2^31 keys");
+    if (epoch < 0) return ns_fail(std::string(name) + ": epochs count from 1 (0: the mailbox's own counter)");
+    if (wait_us < 1 || wait_us > 2000000) return ns_fail(std::string(name) + ": a wait of 1 us .. 2 s");
+    if (qs % 8 != 0 || ((uintptr_t) q & 15) != 0) return ns_fail(std::string(name) + ": query rows 16-byte aligned");
+    if (!q || !mailboxes || !own_mailbox || !out || (kv_local > 0 && (!kc || !vc || !scratch))) return ns_fail(std::string(name) + ": a null buffer");
+    GqaDecodeArgs a{};
+    a.q = q;
+    a.qs = qs;
+    a.q_seq = 0;
+    a.seqs = nullptr;
+    a.one = ns_b200_seq{kc, vc, kv_local, p0 - key_base};
+    a.out = out;
+    a.part = scratch;
+    a.B = 1, a.T = T, a.Hq = Hq, a.Hkv = Hkv, a.D = D;
+    a.ns_max = std::max<int64_t>(1, ns_dec_splits_bound(kv_local, Hkv));
+    a.q_f32 = 0, a.out_f32 = 0;
+    a.mailboxes = (float* const*) mailboxes;
+    a.rank = (int) rank;
+    a.nranks = (int) nranks;
+    a.epoch = epoch;
+    a.fused_spins = wait_us * 10;
+    a.own_mailbox = (float*) own_mailbox;
+    return ns_launch_gqa_decode(g, a, name);
+    NS_CATCH("ns_b200_kvsplit_step")
+}
+
 int ns_b200_kvsplit_combine(ns_gpu* g, void* mailbox, int64_t nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t wait_us,
                             void* out) {
     NS_TRY

@@ -85,6 +85,9 @@ struct Params {
     // kernel's CTAs of that pair that have written their partials, sync[NS_DEC_SYNC_SLOTS + ...] the merge blocks done with them
     unsigned int* sync;
     int* status;
+    long long spins;       // fused KV-split step: polls (100 ns apart) a wait on the peers' flags may take; 0: not that step
+    float* mailboxes_host_own;   // this rank's own mailbox as the host knows it (the step's fallback launches the combine on it)
+    float* local_part;     // [T*Hq][D+2]: the merge keeps the rank's partial here instead of pushing it (no mailboxes)
 };
 
 // keys row t of a sequence sees: its causal length, bounded by what the cache slice holds
@@ -139,11 +142,30 @@ __host__ __device__ constexpr int frag_feature(int ks, int t, int half) {
                    : 32 * frag_chunk<2>(t, ks / 8) + 16 * (ks % 2) + 4 * ((ks % 8) / 2) + 2 * half;
 }
 
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* ptr) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.u32 %0, [%1];\n" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+// A row's split count as the merge may use it: never more than the partial buffer was laid out for. A row that needs
+// more (a sequence longer than the max_kv the caller promised) raises status 802 - its keys past the layout were never
+// streamed - instead of reading its neighbours' partials.
+__device__ __forceinline__ int clamp_splits(const Params& p, int64_t nsr) {
+    if (nsr <= p.ns_max) return (int) nsr;
+    if (threadIdx.x == 0 && p.status) {
+        *(volatile int*) p.status = 802;
+        __threadfence_system();
+    }
+    return p.ns_max;
+}
+template <int D>
+__device__ void fused_split_tail(const Params& p, const ns_b200_seq& seq, int hk, float* sm);
+
 // QF: the caches' form, 0 fp16, 1 q8_0, 2 q4_0. A quantised tile travels as it lies (cp.async of the raw rows into a ring
 // of raw stages) and both products take their fragments from the raw rows, expanding them in registers (above). The
 // expansion is several hundred dependent instructions a tile and a warp, so these instances are sized for two CTAs an SM
 // (two warps a scheduler to hide each other's latencies).
-template <int D, int MT, int NSTAGE, int QF>
+template <int D, int MT, int NSTAGE, int QF, bool FUSED = false>
 __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(const Params p) {
     constexpr int RG = 16 * MT;          // query rows a CTA
     constexpr int ROWB = D * 2;          // bytes a key row
@@ -568,6 +590,10 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
         }
         __syncthreads();   // the merge buffer is stage memory again for the next pass
     }
+    if (FUSED) {
+        fused_split_tail<D>(p, seq, hk, reinterpret_cast<float*>(smem));   // the stage memory is free: the merge's scratch
+        return;
+    }
     if (p.sync) {
         // this CTA's partials are written: one more of its (sequence, key head)'s splits is ready for the merge
         __threadfence();
@@ -576,11 +602,139 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
     }
 }
 
-__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* ptr) {
-    unsigned int v;
-    asm volatile("ld.acquire.gpu.u32 %0, [%1];\n" : "=r"(v) : "l"(ptr) : "memory");
-    return v;
+// The KV-split step in ONE kernel (every CTA of the grid resident: a cooperative launch). After its own split's partials
+// are out a CTA counts itself in on its key head. The head's (row, head) pairs are dealt over the head's CTAs; a CTA
+// that holds pairs waits (bounded, code 801) until the head's count is full, merges each of its pairs' splits
+// (attn.cpp:352-368) and stores the pair's (O, m, l) into slot `rank` of EVERY rank's mailbox with plain stores over
+// NVLink. The CTA whose stores complete the rank's pairs publishes the step number in every mailbox (one system fence,
+// relaxed stores). Then the same CTAs poll their OWN mailbox (bounded, code 701) until every rank's flag shows the step,
+// merge their pairs across the ranks and write the rows; the last of them returns the counters to zero and, when the
+// step numbers live on the device (epoch 0), advances the mailbox's. No second or third launch, no gap between them.
+template <int D>
+__device__ void fused_split_tail(const Params& p, const ns_b200_seq& seq, int hk, float* sm) {
+    __shared__ int ready_s;
+    const int tid = threadIdx.x;
+    const int ctas_head = (int) gridDim.x, R = p.T * p.G;
+    const int64_t rows = (int64_t) p.T * p.Hq;
+    float* own = p.mailboxes[p.rank];
+    int* counters = reinterpret_cast<int*>(own + ns_mbox_flags_off(p.nranks, rows, D)) + 4 * p.nranks;   // [0] pairs pushed, [1] pairs combined
+    unsigned int* head_cnt = p.sync + hk;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) atomicAdd(head_cnt, 1u);
+    int mine = 0;
+    for (int pr = (int) blockIdx.x; pr < R; pr += ctas_head) ++mine;
+    if (mine == 0) return;
+
+    long long* epoch_slot = ns_mbox_epoch(own, p.nranks, rows, D);
+    const long long epoch = p.epoch ? p.epoch : *epoch_slot + 1;
+    const int buf = (int) (epoch & 1);
+    if (tid == 0) {
+        int ok = 1;
+        unsigned int i = 0;
+        while (ld_acquire_gpu(head_cnt) < (unsigned int) ctas_head) {
+            if (++i > (1u << 21)) {
+                ok = 0;
+                if (p.status) {
+                    *(volatile int*) p.status = 801;
+                    __threadfence_system();
+                }
+                break;
+            }
+            __nanosleep(100);
+        }
+        ready_s = ok;
+    }
+    __syncthreads();
+    if (!ready_s) return;   // the peers' combines give up in their turn (code 701)
+
+    // ---- this CTA's pairs: the splits merged, the result into every rank's mailbox
+    for (int pr = (int) blockIdx.x; pr < R; pr += ctas_head) {
+        const int t = pr / p.G, gq = pr - t * p.G;
+        const int64_t rh = (int64_t) t * p.Hq + hk * p.G + gq;
+        const int64_t kv = row_keys(seq, t);
+        const int nsr = kv > 0 ? clamp_splits(p, ns_dec_splits(kv, p.Hkv)) : 0;
+        float mx, L;
+        const float2 a = lse::merge_row<D, THREADS>(p.part + rh * p.ns_max * (D + 2), D + 2, nsr, mx, L, sm);
+        if (tid < D / 2) {
+            for (int r = 0; r < p.nranks; ++r) {
+                float* slot = p.mailboxes[r] + ns_mbox_slot(buf, p.rank, p.nranks, rows, D) + rh * (D + 2);
+                *reinterpret_cast<float2*>(slot + 2 * tid) = a;
+                if (tid == 0) *reinterpret_cast<float2*>(slot + D) = make_float2(mx, L);
+            }
+        }
+        __syncthreads();   // the merge's scratch is reused by the next pair
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+        if (atomicAdd(counters, mine) + mine == (int) rows) {
+            __threadfence_system();
+            for (int r = 0; r < p.nranks; ++r) {
+                long long* flag = reinterpret_cast<long long*>(p.mailboxes[r] + ns_mbox_flags_off(p.nranks, rows, D)) + buf * p.nranks + p.rank;
+                asm volatile("st.relaxed.sys.global.s64 [%0], %1;\n" ::"l"(flag), "l"(epoch) : "memory");
+            }
+        }
+        // ---- every rank's partials for this step: a bounded poll of this rank's own memory
+        const long long* flags = reinterpret_cast<const long long*>(own + ns_mbox_flags_off(p.nranks, rows, D)) + buf * p.nranks;
+        int ok = 1;
+        for (int r = 0; r < p.nranks && ok; ++r) {
+            long long v = 0, it = 0;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.s64 %0, [%1];\n" : "=l"(v) : "l"(flags + r) : "memory");
+                if (v >= epoch) break;
+                if (++it > p.spins) {
+                    ok = 0;
+                    break;
+                }
+                __nanosleep(100);
+            }
+        }
+        if (!ok && p.status) {
+            *(volatile int*) p.status = 701;
+            __threadfence_system();
+        }
+        ready_s = ok;
+    }
+    __syncthreads();
+    const int ready = ready_s;
+    if (ready) {
+        const int64_t stride = rows * (D + 2);
+        for (int pr = (int) blockIdx.x; pr < R; pr += ctas_head) {
+            const int t = pr / p.G, gq = pr - t * p.G;
+            const int64_t rh = (int64_t) t * p.Hq + hk * p.G + gq;
+            const float* base = own + ns_mbox_slot(buf, 0, p.nranks, rows, D) + rh * (D + 2);
+            float mx = -INFINITY;
+            for (int r = 0; r < p.nranks; ++r) mx = fmaxf(mx, __ldcg(base + r * stride + D));
+            for (int d = tid; d < D; d += THREADS) {
+                float L = 0.f, A = 0.f;
+                if (mx != -INFINITY) {
+                    for (int r = 0; r < p.nranks; ++r) {
+                        const float mk = __ldcg(base + r * stride + D);
+                        const float e = mk == -INFINITY ? 0.f : exp2f(mk - mx);
+                        L += __ldcg(base + r * stride + D + 1) * e;
+                        A += __ldcg(base + r * stride + d) * e;
+                    }
+                }
+                const float v = L > 0.f ? A / L : 0.f;
+                if (p.out_f32) ((float*) p.out)[rh * D + d] = v;
+                else ((__half*) p.out)[rh * D + d] = __float2half_rn(v);
+            }
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        if (atomicAdd(counters + 1, mine) + mine == (int) rows) {
+            // the step's last CTA: every count it returns to zero has been read by all who wait on it
+            for (int h = 0; h < p.Hkv; ++h) p.sync[h] = 0u;
+            counters[0] = 0;
+            counters[1] = 0;
+            if (p.epoch == 0 && ready) *epoch_slot = epoch;
+            __threadfence();
+        }
+    }
 }
+
 // A merge block's way in and out when the split kernel counts its CTAs. In: wait (bounded) until every split CTA of the
 // block's (sequence, key head) has written - the block was placed while the split kernel's last CTAs still ran, so pairs
 // that finished early are merged under that tail. Out: the last merge block of the pair returns both counters to zero.
@@ -613,18 +767,6 @@ __device__ __forceinline__ void merge_leave(const Params& p, int b, int hk) {
             __threadfence();
         }
     }
-}
-
-// A row's split count as the merge may use it: never more than the partial buffer was laid out for. A row that needs
-// more (a sequence longer than the max_kv the caller promised) raises status 802 - its keys past the layout were never
-// streamed - instead of reading its neighbours' partials.
-__device__ __forceinline__ int clamp_splits(const Params& p, int64_t nsr) {
-    if (nsr <= p.ns_max) return (int) nsr;
-    if (threadIdx.x == 0 && p.status) {
-        *(volatile int*) p.status = 802;
-        __threadfence_system();
-    }
-    return p.ns_max;
 }
 
 // the splits of each (sequence, row, head) merged: attn.cpp:352-368's formula; rows with one split were written by
@@ -671,6 +813,15 @@ __global__ void __launch_bounds__(MERGE_THREADS) gqa_merge_push_kernel(const Par
     float mx, L;
     const float2 a = lse::merge_row<D, MERGE_THREADS>(p.part + rh * p.ns_max * (D + 2), D + 2, nsr, mx, L, sm);
     const int64_t rows = (int64_t) p.T * p.Hq;
+    if (p.local_part) {
+        // no mailboxes: the rank's partial stays here, for an exchange the caller runs itself (a library all-gather)
+        if (threadIdx.x < D / 2) {
+            float* slot = p.local_part + rh * (D + 2);
+            *reinterpret_cast<float2*>(slot + 2 * threadIdx.x) = a;
+            if (threadIdx.x == 0) *reinterpret_cast<float2*>(slot + D) = make_float2(mx, L);
+        }
+        return;
+    }
     // epoch 0: the step number lives in this rank's own mailbox (the combine advances it), so a recorded graph of the
     // step can be replayed
     const long long epoch = p.epoch ? p.epoch : *ns_mbox_epoch(p.mailboxes[p.rank], p.nranks, rows, D) + 1;
@@ -772,6 +923,30 @@ __global__ void __launch_bounds__(D) gqa_combine_kernel(const CombineParams c) {
     else ((__half*) c.out)[rh * D + d] = __float2half_rn(v);
 }
 
+// The ranks' partials side by side in this GPU's memory ([nranks][rows][D+2], however they got there) merged into the rows:
+// the combine without mailbox or wait.
+template <int D>
+__global__ void __launch_bounds__(D) gqa_merge_ranks_kernel(const float* __restrict__ parts, int nranks, long long rows, void* out, int out_f32) {
+    const int64_t rh = blockIdx.x;
+    const int d = threadIdx.x;
+    const float* base = parts + rh * (D + 2);
+    const int64_t stride = rows * (D + 2);
+    float mx = -INFINITY;
+    for (int r = 0; r < nranks; ++r) mx = fmaxf(mx, base[r * stride + D]);
+    float L = 0.f, A = 0.f;
+    if (mx != -INFINITY) {
+        for (int r = 0; r < nranks; ++r) {
+            const float mk = base[r * stride + D];
+            const float e = mk == -INFINITY ? 0.f : exp2f(mk - mx);
+            L += base[r * stride + D + 1] * e;
+            A += base[r * stride + d] * e;
+        }
+    }
+    const float v = L > 0.f ? A / L : 0.f;
+    if (out_f32) ((float*) out)[rh * D + d] = v;
+    else ((__half*) out)[rh * D + d] = __float2half_rn(v);
+}
+
 template <class K, class P>
 cudaError_t launch_dependent(K kernel, unsigned blocks, unsigned threads, cudaStream_t stream, const P& params) {
     cudaLaunchConfig_t cfg = {};
@@ -801,9 +976,45 @@ int launch(ns_gpu* g, const Params& p, int64_t B, const char* where) {
         set[g->dev & 63] = true;
     }
     dim3 grid((unsigned) (p.ns_max * p.groups), (unsigned) p.Hkv, (unsigned) B);
+    if constexpr (QF == 0) {
+        if (p.spins > 0) {
+            // the whole KV-split step as one kernel, when every CTA of the grid can be resident at once (its CTAs wait on
+            // one another): a cooperative launch, which the driver refuses rather than run partly
+            auto fused = gqa_decode_kernel<D, MT, NSTAGE, QF, true>;
+            static bool fset[64] = {};
+            static int per_sm[64] = {};
+            if (!fset[g->dev & 63]) {
+                NS_CUDA(cudaFuncSetAttribute(fused, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem), where);
+                NS_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm[g->dev & 63], fused, THREADS, smem), where);
+                fset[g->dev & 63] = true;
+            }
+            if ((int64_t) grid.x * grid.y <= (int64_t) per_sm[g->dev & 63] * g->sms) {
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = grid;
+                cfg.blockDim = dim3(THREADS);
+                cfg.dynamicSmemBytes = smem;
+                cfg.stream = g->compute;
+                cudaLaunchAttribute attr[1];
+                attr[0].id = cudaLaunchAttributeCooperative;
+                attr[0].val.cooperative = 1;
+                cfg.attrs = attr;
+                cfg.numAttrs = 1;
+                NS_CUDA(cudaLaunchKernelEx(&cfg, fused, p), where);
+                return ns_launched(where);
+            }
+            // too many CTAs to be resident together: the three launches below
+            Params q = p;
+            q.sync = nullptr;
+            kern<<<grid, THREADS, smem, g->compute>>>(q);
+            if (ns_launched(where)) return -1;
+            NS_CUDA(launch_dependent(gqa_merge_push_kernel<D>, (unsigned) (p.T * p.Hq), MERGE_THREADS, g->compute, q), where);
+            if (ns_launched(where)) return -1;
+            return ns_launch_gqa_combine(g, p.mailboxes_host_own, p.nranks, p.T, p.Hq, D, p.epoch, p.spins, p.out, p.out_f32, where);
+        }
+    }
     kern<<<grid, THREADS, smem, g->compute>>>(p);
     if (ns_launched(where)) return -1;
-    if (p.mailboxes) {
+    if (p.mailboxes || p.local_part) {
         NS_CUDA(launch_dependent(gqa_merge_push_kernel<D>, (unsigned) (p.T * p.Hq), MERGE_THREADS, g->compute, p), where);
         if (ns_launched(where)) return -1;
     } else if (p.ns_max > 1) {
@@ -832,14 +1043,23 @@ int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where) {
     p.q_f32 = a.q_f32;
     p.out_f32 = a.out_f32;
     p.qscale = 1.0f / sqrtf((float) a.D) * 1.4426950408889634f;
-    p.force_part = a.mailboxes ? 1 : 0;
+    p.force_part = (a.mailboxes || a.local_part) ? 1 : 0;
+    p.local_part = a.local_part;
     p.rank = a.rank;
     p.nranks = a.nranks;
     p.mailboxes = a.mailboxes;
     p.epoch = a.epoch;
     // the counted hand-over to the merge: one sequence-and-key-head pair a counter; the KV-split path keeps the plain dependent
-    p.sync = (!a.mailboxes && a.ns_max > 1 && a.B * a.Hkv <= NS_DEC_SYNC_SLOTS) ? g->dec_sync : nullptr;
+    p.sync = (!a.mailboxes && !a.local_part && a.ns_max > 1 && a.B * a.Hkv <= NS_DEC_SYNC_SLOTS) ? g->dec_sync : nullptr;
     p.status = g->status_dev;
+    p.spins = 0;
+    p.mailboxes_host_own = nullptr;
+    if (a.mailboxes && a.fused_spins > 0) {
+        if (a.kt != 0 || a.Hkv > NS_DEC_SYNC_SLOTS) return ns_fail(std::string(where) + ": the one-kernel step takes fp16 caches");
+        p.sync = g->dec_sync;      // [Hkv] CTAs of a key head done; the step's last CTA returns them to zero
+        p.spins = a.fused_spins;
+        p.mailboxes_host_own = a.own_mailbox;
+    }
     const int R = p.T * p.G;
     if (a.B > 65535) return ns_fail(std::string(where) + ": too many sequences for one launch");
     if (a.kt != 0) {
@@ -925,6 +1145,13 @@ extern "C" int ns_b200_gqa_decode_static(ns_gpu* g, const void* q, int64_t qs, i
     a.q_f32 = 0, a.out_f32 = 0;
     return ns_launch_gqa_decode(g, a, name);
     NS_CATCH("ns_b200_gqa_decode_static")
+}
+
+int ns_launch_gqa_merge_ranks(ns_gpu* g, const float* parts, int nranks, int64_t T, int64_t Hq, int64_t D, void* out, int out_f32, const char* where) {
+    if (D == 128) gqa_merge_ranks_kernel<128><<<(unsigned) (T * Hq), 128, 0, g->compute>>>(parts, nranks, T * Hq, out, out_f32);
+    else if (D == 256) gqa_merge_ranks_kernel<256><<<(unsigned) (T * Hq), 256, 0, g->compute>>>(parts, nranks, T * Hq, out, out_f32);
+    else return ns_fail(std::string(where) + ": heads of 128 or 256");
+    return ns_launched(where);
 }
 
 int ns_launch_gqa_combine(ns_gpu* g, float* mailbox, int nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t spins, void* out,

@@ -42,6 +42,11 @@ struct GqaDecodeArgs {
     int rank, nranks;
     int64_t epoch;
     int kt = 0;                // the caches' form: 0 fp16, 1 q8_0, 2 q4_0 (heads of 256; rows of 272 / 144 bytes)
+    // the whole KV-split step (decode, push, combine) in one kernel: polls a wait on the peers may take (0: the decode and
+    // push only), and this rank's own mailbox as the host addresses it
+    int64_t fused_spins = 0;
+    float* own_mailbox = nullptr;
+    float* local_part = nullptr;   // [T*Hq][D+2]: keep the rank's merged partial here (no mailboxes, nothing pushed)
 };
 
 // A rank's mailbox for the KV-split combine, in floats from its base: partials [2 buffers][nranks][rows][D+2], then
@@ -62,6 +67,7 @@ __host__ __device__ inline long long* ns_mbox_epoch(float* mailbox, int nranks, 
 int ns_launch_gqa_combine(ns_gpu* g, float* mailbox, int nranks, int64_t T, int64_t Hq, int64_t D, int64_t epoch, int64_t spins, void* out,
                           int out_f32, const char* where);
 int ns_launch_gqa_decode(ns_gpu* g, const GqaDecodeArgs& a, const char* where);
+int ns_launch_gqa_merge_ranks(ns_gpu* g, const float* parts, int nranks, int64_t T, int64_t Hq, int64_t D, void* out, int out_f32, const char* where);
 
 // ---- cache writers (kv_store.cu) ------------------------------------------------------------------------------------
 int ns_launch_kv_store(ns_gpu* g, const float* k, int64_t ks, const float* v, int64_t vs, int64_t T, int64_t Hkv, int64_t D, int64_t cap, int64_t p0,

@@ -82,6 +82,22 @@ class KvSplit:
                                                       ptr(scratch), self.rank, self.nranks, self.table.ptr, epoch), "ns_b200_kvsplit_decode")
         return epoch
 
+    def step(self, q, qs, kc, vc, Hkv, kv_local, key_base, p0, scratch, out, epoch=None, wait_us=200000):
+        """decode + push + combine as one kernel launch (ns_b200_kvsplit_step); epochs as `decode`."""
+        if epoch is None:
+            self.epoch += 1
+            epoch = self.epoch
+        elif epoch == 0:
+            self.device_epochs = True
+        api = self.gpu.api
+
+        def ptr(b):
+            return b.ptr if b is not None else None
+        check(api, api.need("ns_b200_kvsplit_step")(self.gpu.raw, q.ptr, qs, ptr(kc), ptr(vc), self.T, self.Hq, Hkv, self.D, kv_local, key_base, p0,
+                                                    ptr(scratch), self.rank, self.nranks, self.table.ptr, self.mailbox.ptr, epoch, wait_us, out.ptr),
+              "ns_b200_kvsplit_step")
+        return epoch
+
     def combine(self, out, epoch=None, wait_us=200000):
         api = self.gpu.api
         if epoch is None:

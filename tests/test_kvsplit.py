@@ -145,3 +145,73 @@ def test_recorded_step_replays_with_device_epochs(gpu, ops):
         got = out.read(np.float16).reshape(T, Hq * D).astype(np.float32)
         assert np.all(np.abs(got - want) <= 2e-3 + 1e-2 * np.abs(want)), rep
     graph.free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,Hq,Hkv,D,kv", [(4, 32, 4, 128, 3000), (1, 64, 8, 128, 20000), (2, 24, 4, 256, 900), (8, 16, 1, 128, 5000)])
+def test_the_step_as_one_kernel(gpu, ops, T, Hq, Hkv, D, kv):
+    """ns_b200_kvsplit_step with one rank (its own mailbox is the only one): split decode, merge, push, flag, poll and combine
+    inside one cooperative launch, called twice and then replayed from a recording (step numbers on the device). The last
+    shape (128 rows of one key head: four row groups x 296 splits) does not fit the GPU at once and takes the three launches."""
+    from nextsycl_b200 import DevBuf
+    from nextsycl_b200 import workloads as W
+    from nextsycl_b200.dist import KvSplit
+    from oracle import oracle as O
+    q, k, v, p0 = W.gqa_case(952, T, Hq, Hkv, D, kv)
+    dq, dk, dv = DevBuf.of(gpu, q), DevBuf.of(gpu, k), DevBuf.of(gpu, v)
+    box = DevBuf(gpu, KvSplit.mailbox_bytes(gpu.api, 1, T, Hq, D))
+    box.fill(0)
+    grp = KvSplit(gpu, 0, 1, T, Hq, D, local_mailboxes=[box])
+    sc = DevBuf(gpu, 4 * grp.scratch_floats(Hkv, kv))
+    sc.fill(0xFF)
+    out = DevBuf(gpu, T * Hq * D * 2)
+    want = O.gqa_flash_decode(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, kv, p0)
+
+    def one():
+        grp.step(dq, Hq * D, dk, dv, Hkv, kv, 0, p0, sc, out, epoch=0, wait_us=100000)
+
+    def check(what):
+        gpu.sync()
+        got = out.read(np.float16).reshape(T, Hq * D).astype(np.float32)
+        assert np.isfinite(got).all(), what
+        assert np.all(np.abs(got - want) <= 2e-3 + 1e-2 * np.abs(want)), (what, float(np.abs(got - want).max()))
+    for i in range(2):
+        out.fill(0xFF)
+        one()
+        check(f"call {i}")
+    graph = gpu.record(one)
+    for rep in range(3):
+        out.fill(0xFF)
+        graph.launch()
+        check(f"replay {rep}")
+    graph.free()
+
+
+@pytest.mark.gpu
+def test_partials_gathered_by_the_caller(gpu, ops):
+    """ns_b200_kvsplit_partial per key range, the partials laid side by side as an all-gather would leave them,
+    ns_b200_kvsplit_merge: the library-exchange baseline's two ends."""
+    from nextsycl_b200 import DevBuf
+    from nextsycl_b200 import workloads as W
+    from nextsycl_b200.core import check
+    from oracle import oracle as O
+    api = gpu.api
+    nranks, T, Hq, Hkv, D, kv = 4, 4, 32, 4, 128, 7000
+    q, k, v, p0 = W.gqa_case(953, T, Hq, Hkv, D, kv)
+    dq = DevBuf.of(gpu, q)
+    rows = T * Hq
+    parts = DevBuf(gpu, nranks * rows * (D + 2) * 4)
+    parts.fill(0xFF)
+    keep = []
+    for r, (base, count) in enumerate(key_ranges(kv, nranks)):
+        dk, dv = DevBuf.of(gpu, np.ascontiguousarray(k[:, base:base + count])), DevBuf.of(gpu, np.ascontiguousarray(v[:, base:base + count]))
+        sc = DevBuf(gpu, 4 * int(api.ns_b200_kvsplit_scratch(T, Hq, Hkv, D, count)))
+        keep += [dk, dv, sc]
+        check(api, api.ns_b200_kvsplit_partial(gpu.raw, dq.ptr, Hq * D, dk.ptr, dv.ptr, T, Hq, Hkv, D, count, base, p0, sc.ptr,
+                                               parts.ptr + r * rows * (D + 2) * 4), "partial")
+    out = DevBuf(gpu, rows * D * 2)
+    check(api, api.ns_b200_kvsplit_merge(gpu.raw, parts.ptr, nranks, T, Hq, D, out.ptr), "merge")
+    gpu.sync()
+    got = out.read(np.float16).reshape(T, Hq * D).astype(np.float32)
+    want = O.gqa_flash_decode(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, kv, p0)
+    assert np.all(np.abs(got - want) <= 2e-3 + 1e-2 * np.abs(want)), float(np.abs(got - want).max())
