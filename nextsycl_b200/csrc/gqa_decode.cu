@@ -194,7 +194,9 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
     const int64_t p0 = seq.p0;
     const int t_lo = row0 / G, t_hi = min(T - 1, (row0 + RG - 1) / G);
 
-    // ---- the group's queries, scaled and rounded to fp16, swizzled like the key tiles (rows past R: zeros)
+    // ---- the group's queries, scaled and rounded to fp16, swizzled like the key tiles (rows past R: zeros). Run after the
+    // first key and value tiles have been requested (they do not depend on it), so its latency hides under theirs.
+    auto stage_q = [&]() {
     for (int i = tid; i < RG * CPR; i += THREADS) {
         const int r = i / CPR, c = i % CPR, rho = row0 + r;
         uint4 w = make_uint4(0, 0, 0, 0);
@@ -236,7 +238,8 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
         }
         *reinterpret_cast<uint4*>(q_s + swz<ROWB>(r, c)) = w;
     }
-    __syncthreads();
+    };
+    bool q_staged = false;
 
     // rows of one pass share a split size; where the rows' own sizes differ (a row's context crosses a step of the
     // split function) the rows go one at a time, each with its own - the same arithmetic either way
@@ -315,6 +318,11 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
 
 #pragma unroll
         for (int s = 0; s < NSTAGE - 1; ++s) issue(warp + s * WARPS, s);
+        if (!q_staged) {   // once, by the CTA's first pass that has keys (the condition is the same for all its threads)
+            stage_q();
+            __syncthreads();
+            q_staged = true;
+        }
 
         int stage = 0;
         for (int tile = warp; tile < ntiles; tile += WARPS) {
@@ -605,19 +613,37 @@ __global__ void __launch_bounds__(THREADS, QF == 0 ? 1 : 2) gqa_decode_kernel(co
 // The KV-split step in ONE kernel (every CTA of the grid resident: a cooperative launch). After its own split's partials
 // are out a CTA counts itself in on its key head. The head's (row, head) pairs are dealt over the head's CTAs; a CTA
 // that holds pairs waits (bounded, code 801) until the head's count is full, merges each of its pairs' splits
-// (attn.cpp:352-368) and stores the pair's (O, m, l) into slot `rank` of EVERY rank's mailbox with plain stores over
-// NVLink. The CTA whose stores complete the rank's pairs publishes the step number in every mailbox (one system fence,
-// relaxed stores). Then the same CTAs poll their OWN mailbox (bounded, code 701) until every rank's flag shows the step,
-// merge their pairs across the ranks and write the rows; the last of them returns the counters to zero and, when the
-// step numbers live on the device (epoch 0), advances the mailbox's. No second or third launch, no gap between them.
+// (attn.cpp:352-368) and stores the pair's (O, m, l) into slot `rank` of EVERY rank's mailbox over NVLink as 16-byte lines
+// (value, step tag, value, step tag): a line arrives whole, so the tag is the value's own flag - no fence, no counter, no
+// flag round trip. The same CTAs then read their pairs' lines of every rank from their OWN mailbox, polling (bounded, code
+// 701) until the tags show this step, merge across the ranks and write the rows. The last of them returns the counters
+// to zero and, when the step numbers live on the device (epoch 0), advances the mailbox's. One launch, no gaps.
+__device__ __forceinline__ void st_line(uint4* dst, float x, float y, uint32_t tag) {
+    asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"l"(dst), "r"(__float_as_uint(x)), "r"(tag), "r"(__float_as_uint(y)), "r"(tag) : "memory");
+}
+// polls a line until both halves carry `tag`; false when `spins` polls run out
+__device__ __forceinline__ bool ld_line(const uint4* src, uint32_t tag, long long spins, float& x, float& y) {
+    uint4 v;
+    for (long long it = 0;; ++it) {
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+        if (v.y == tag && v.w == tag) break;
+        if (it > spins) return false;
+        __nanosleep(100);
+    }
+    x = __uint_as_float(v.x), y = __uint_as_float(v.z);
+    return true;
+}
+
 template <int D>
 __device__ void fused_split_tail(const Params& p, const ns_b200_seq& seq, int hk, float* sm) {
+    constexpr int LPR = D / 2 + 1;   // lines a row: D values two a line, then (m, l)
     __shared__ int ready_s;
+    __shared__ float2 ml_s[64];      // the ranks' (m, l) of the pair being combined
     const int tid = threadIdx.x;
     const int ctas_head = (int) gridDim.x, R = p.T * p.G;
     const int64_t rows = (int64_t) p.T * p.Hq;
     float* own = p.mailboxes[p.rank];
-    int* counters = reinterpret_cast<int*>(own + ns_mbox_flags_off(p.nranks, rows, D)) + 4 * p.nranks;   // [0] pairs pushed, [1] pairs combined
+    int* counters = reinterpret_cast<int*>(own + ns_mbox_flags_off(p.nranks, rows, D)) + 4 * p.nranks;   // [1]: pairs combined
     unsigned int* head_cnt = p.sync + hk;
     __threadfence();
     __syncthreads();
@@ -629,6 +655,7 @@ __device__ void fused_split_tail(const Params& p, const ns_b200_seq& seq, int hk
     long long* epoch_slot = ns_mbox_epoch(own, p.nranks, rows, D);
     const long long epoch = p.epoch ? p.epoch : *epoch_slot + 1;
     const int buf = (int) (epoch & 1);
+    const uint32_t tag = (uint32_t) epoch;   // a mailbox starts zeroed and epochs count from 1: a line never written never matches
     if (tid == 0) {
         int ok = 1;
         unsigned int i = 0;
@@ -649,6 +676,7 @@ __device__ void fused_split_tail(const Params& p, const ns_b200_seq& seq, int hk
     if (!ready_s) return;   // the peers' combines give up in their turn (code 701)
 
     // ---- this CTA's pairs: the splits merged, the result into every rank's mailbox
+    const int64_t ll_off = ns_mbox_ll_off_bytes(p.nranks, rows, D);
     for (int pr = (int) blockIdx.x; pr < R; pr += ctas_head) {
         const int t = pr / p.G, gq = pr - t * p.G;
         const int64_t rh = (int64_t) t * p.Hq + hk * p.G + gq;
@@ -656,80 +684,61 @@ __device__ void fused_split_tail(const Params& p, const ns_b200_seq& seq, int hk
         const int nsr = kv > 0 ? clamp_splits(p, ns_dec_splits(kv, p.Hkv)) : 0;
         float mx, L;
         const float2 a = lse::merge_row<D, THREADS>(p.part + rh * p.ns_max * (D + 2), D + 2, nsr, mx, L, sm);
-        if (tid < D / 2) {
-            for (int r = 0; r < p.nranks; ++r) {
-                float* slot = p.mailboxes[r] + ns_mbox_slot(buf, p.rank, p.nranks, rows, D) + rh * (D + 2);
-                *reinterpret_cast<float2*>(slot + 2 * tid) = a;
-                if (tid == 0) *reinterpret_cast<float2*>(slot + D) = make_float2(mx, L);
-            }
+        const int64_t line0 = ns_mbox_ll_line(buf, p.rank, p.nranks, rows, D) + rh * LPR;
+        for (int r = 0; r < p.nranks; ++r) {
+            uint4* lines = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.mailboxes[r]) + ll_off) + line0;
+            if (tid < D / 2) st_line(lines + tid, a.x, a.y, tag);
+            if (tid == THREADS - 1) st_line(lines + D / 2, mx, L, tag);
         }
         __syncthreads();   // the merge's scratch is reused by the next pair
     }
-    __threadfence_system();
-    __syncthreads();
-    if (tid == 0) {
-        if (atomicAdd(counters, mine) + mine == (int) rows) {
-            __threadfence_system();
-            for (int r = 0; r < p.nranks; ++r) {
-                long long* flag = reinterpret_cast<long long*>(p.mailboxes[r] + ns_mbox_flags_off(p.nranks, rows, D)) + buf * p.nranks + p.rank;
-                asm volatile("st.relaxed.sys.global.s64 [%0], %1;\n" ::"l"(flag), "l"(epoch) : "memory");
-            }
+
+    // ---- the pairs again, now across the ranks: every rank's lines for this step, from this rank's own memory
+    bool ok = true;
+    const uint4* mine_ll = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(own) + ll_off);
+    for (int pr = (int) blockIdx.x; pr < R; pr += ctas_head) {
+        const int t = pr / p.G, gq = pr - t * p.G;
+        const int64_t rh = (int64_t) t * p.Hq + hk * p.G + gq;
+        if (tid < p.nranks) {
+            float m, l;
+            if (ld_line(mine_ll + ns_mbox_ll_line(buf, tid, p.nranks, rows, D) + rh * LPR + D / 2, tag, p.spins, m, l)) ml_s[tid] = make_float2(m, l);
+            else ok = false, ml_s[tid] = make_float2(-INFINITY, 0.f);
         }
-        // ---- every rank's partials for this step: a bounded poll of this rank's own memory
-        const long long* flags = reinterpret_cast<const long long*>(own + ns_mbox_flags_off(p.nranks, rows, D)) + buf * p.nranks;
-        int ok = 1;
-        for (int r = 0; r < p.nranks && ok; ++r) {
-            long long v = 0, it = 0;
-            for (;;) {
-                asm volatile("ld.acquire.sys.global.s64 %0, [%1];\n" : "=l"(v) : "l"(flags + r) : "memory");
-                if (v >= epoch) break;
-                if (++it > p.spins) {
-                    ok = 0;
+        __syncthreads();
+        float mx = -INFINITY;
+        for (int r = 0; r < p.nranks; ++r) mx = fmaxf(mx, ml_s[r].x);
+        for (int c = tid; c < D / 2; c += THREADS) {
+            float L = 0.f, ax = 0.f, ay = 0.f;
+            for (int r = 0; r < p.nranks; ++r) {
+                float x, y;
+                if (!ld_line(mine_ll + ns_mbox_ll_line(buf, r, p.nranks, rows, D) + rh * LPR + c, tag, p.spins, x, y)) {
+                    ok = false;
                     break;
                 }
-                __nanosleep(100);
+                const float mk = ml_s[r].x;
+                const float e = (mk == -INFINITY || mx == -INFINITY) ? 0.f : exp2f(mk - mx);
+                L += ml_s[r].y * e;
+                ax += x * e, ay += y * e;
+            }
+            if (ok) {
+                const float inv = L > 0.f ? 1.0f / L : 0.f;
+                if (p.out_f32) *reinterpret_cast<float2*>((float*) p.out + rh * D + 2 * c) = make_float2(ax * inv, ay * inv);
+                else *reinterpret_cast<__half2*>((__half*) p.out + rh * D + 2 * c) = __floats2half2_rn(ax * inv, ay * inv);
             }
         }
-        if (!ok && p.status) {
-            *(volatile int*) p.status = 701;
-            __threadfence_system();
-        }
-        ready_s = ok;
+        __syncthreads();   // ml_s is reused by the next pair
     }
-    __syncthreads();
-    const int ready = ready_s;
-    if (ready) {
-        const int64_t stride = rows * (D + 2);
-        for (int pr = (int) blockIdx.x; pr < R; pr += ctas_head) {
-            const int t = pr / p.G, gq = pr - t * p.G;
-            const int64_t rh = (int64_t) t * p.Hq + hk * p.G + gq;
-            const float* base = own + ns_mbox_slot(buf, 0, p.nranks, rows, D) + rh * (D + 2);
-            float mx = -INFINITY;
-            for (int r = 0; r < p.nranks; ++r) mx = fmaxf(mx, __ldcg(base + r * stride + D));
-            for (int d = tid; d < D; d += THREADS) {
-                float L = 0.f, A = 0.f;
-                if (mx != -INFINITY) {
-                    for (int r = 0; r < p.nranks; ++r) {
-                        const float mk = __ldcg(base + r * stride + D);
-                        const float e = mk == -INFINITY ? 0.f : exp2f(mk - mx);
-                        L += __ldcg(base + r * stride + D + 1) * e;
-                        A += __ldcg(base + r * stride + d) * e;
-                    }
-                }
-                const float v = L > 0.f ? A / L : 0.f;
-                if (p.out_f32) ((float*) p.out)[rh * D + d] = v;
-                else ((__half*) p.out)[rh * D + d] = __float2half_rn(v);
-            }
-        }
+    if (!ok && p.status) {
+        *(volatile int*) p.status = 701;
+        __threadfence_system();
     }
-    __syncthreads();
+    const int all_ok = __syncthreads_and(ok ? 1 : 0);
     if (tid == 0) {
         if (atomicAdd(counters + 1, mine) + mine == (int) rows) {
             // the step's last CTA: every count it returns to zero has been read by all who wait on it
             for (int h = 0; h < p.Hkv; ++h) p.sync[h] = 0u;
-            counters[0] = 0;
             counters[1] = 0;
-            if (p.epoch == 0 && ready) *epoch_slot = epoch;
+            if (p.epoch == 0 && all_ok) *epoch_slot = epoch;
             __threadfence();
         }
     }
@@ -979,7 +988,7 @@ int launch(ns_gpu* g, const Params& p, int64_t B, const char* where) {
     if constexpr (QF == 0) {
         if (p.spins > 0) {
             // the whole KV-split step as one kernel, when every CTA of the grid can be resident at once (its CTAs wait on
-            // one another): a cooperative launch, which the driver refuses rather than run partly
+            // one another)
             auto fused = gqa_decode_kernel<D, MT, NSTAGE, QF, true>;
             static bool fset[64] = {};
             static int per_sm[64] = {};
@@ -989,6 +998,8 @@ int launch(ns_gpu* g, const Params& p, int64_t B, const char* where) {
                 fset[g->dev & 63] = true;
             }
             if ((int64_t) grid.x * grid.y <= (int64_t) per_sm[g->dev & 63] * g->sms) {
+                // a cooperative launch: the driver guarantees what the kernel relies on. (Measured against a plain launch of
+                // the same grid: 37.7 against 45.7 us a step at 32,768 keys a rank, 70.7 against 104 at 131,072.)
                 cudaLaunchConfig_t cfg = {};
                 cfg.gridDim = grid;
                 cfg.blockDim = dim3(THREADS);

@@ -57,8 +57,19 @@ __host__ __device__ inline int64_t ns_mbox_slot(int buf, int rank, int nranks, i
 __host__ __device__ inline int64_t ns_mbox_flags_off(int nranks, int64_t rows, int64_t D) {
     return (2 * (int64_t) nranks * rows * (D + 2) + 15) / 16 * 16;
 }
+__host__ __device__ inline int64_t ns_mbox_bytes(int nranks, int64_t rows, int64_t D);
+// Behind all that, 16-byte aligned, the lines of the one-kernel step: [2 buffers][nranks][rows][D/2 + 1] lines of 16 bytes
+// = (value, step tag, value, step tag) - a row's D values two a line, then (m, l). A line is written by ONE 16-byte store,
+// and each of its 8-byte halves carries its own tag, so a reader that sees the tag has the value: data and flag in one
+// transfer, no fence and no second round trip over NVLink.
+__host__ __device__ inline int64_t ns_mbox_ll_off_bytes(int nranks, int64_t rows, int64_t D) {
+    return (ns_mbox_flags_off(nranks, rows, D) * 4 + 2 * (int64_t) nranks * 8 + 64 + 15) / 16 * 16;
+}
+__host__ __device__ inline int64_t ns_mbox_ll_line(int buf, int rank, int nranks, int64_t rows, int64_t D) {
+    return ((int64_t) (buf * nranks + rank) * rows) * (D / 2 + 1);
+}
 __host__ __device__ inline int64_t ns_mbox_bytes(int nranks, int64_t rows, int64_t D) {
-    return ns_mbox_flags_off(nranks, rows, D) * 4 + 2 * (int64_t) nranks * 8 + 64;
+    return ns_mbox_ll_off_bytes(nranks, rows, D) + 2 * (int64_t) nranks * rows * (D / 2 + 1) * 16;
 }
 // after the flags: two block counters (ints), then the rank's own step number (used when a call passes epoch 0)
 __host__ __device__ inline long long* ns_mbox_epoch(float* mailbox, int nranks, int64_t rows, int64_t D) {
