@@ -33,7 +33,7 @@ static const char* kEngines[] = {
     "ns_ds41_cand_pos", "ns_ds41_cand_mask",
     // native
     "ns_b200_gqa_decode_scratch", "ns_b200_gqa_decode", "ns_b200_gqa_prefill", "ns_b200_mla_prefill", "ns_b200_mla_decode_scratch", "ns_b200_mla_decode",
-    "ns_b200_kvsplit_mailbox_bytes", "ns_b200_kvsplit_scratch", "ns_b200_kvsplit_decode", "ns_b200_kvsplit_combine", "ns_b200_kvsplit_step", "ns_b200_kvsplit_partial", "ns_b200_kvsplit_merge", "ns_b200_ipc_export",
+    "ns_b200_kvsplit_mailbox_bytes", "ns_b200_kvsplit_scratch", "ns_b200_kvsplit_decode", "ns_b200_kvsplit_combine", "ns_b200_kvsplit_step", "ns_b200_mla_kvsplit_scratch", "ns_b200_mla_kvsplit_decode", "ns_b200_mla_kvsplit_combine", "ns_b200_kvsplit_partial", "ns_b200_kvsplit_merge", "ns_b200_ipc_export",
     "ns_b200_ipc_open", "ns_b200_ipc_close", "ns_b200_kv_store_batch", "ns_b200_gqa_decode_static"};
 
 int main(int argc, char** argv) {

@@ -318,6 +318,16 @@ int ns_b200_kvsplit_step(ns_gpu* g, const void* q, int64_t qs, const void* kc, c
 int ns_b200_kvsplit_partial(ns_gpu* g, const void* q, int64_t qs, const void* kc, const void* vc, int64_t T, int64_t Hq, int64_t Hkv, int64_t D,
                             int64_t kv_local, int64_t key_base, int64_t p0, float* scratch, float* part);
 int ns_b200_kvsplit_merge(ns_gpu* g, const float* parts, int64_t nranks, int64_t T, int64_t Hq, int64_t D, void* out);
+/* The same split for the absorbed-MLA latent cache (the middle stage, ns_b200_mla_decode's arguments): rank r holds the cells
+ * [cell_base, cell_base + cells_local) as cache [cells_local][576] fp16; q [T][H][576] fp16 is the same on all ranks; row t
+ * sees global cells 0 .. pos0+t. ns_b200_mla_kvsplit_decode runs this rank's cells on the tensor cores, merges its splits and
+ * pushes (O [512], m, l) per (row, head) into every rank's mailbox (ns_b200_kvsplit_mailbox_bytes(nranks, T, H, 512) bytes
+ * each, the same protocol, epochs and flags as above); ns_b200_mla_kvsplit_combine polls this rank's own mailbox (bounded,
+ * code 701) and writes u [T][H][512] fp32. No reference counterpart. */
+int64_t ns_b200_mla_kvsplit_scratch(ns_gpu* g, int64_t T, int64_t H, int64_t cells_local);
+int ns_b200_mla_kvsplit_decode(ns_gpu* g, const void* q, const void* cache, int64_t T, int64_t H, int64_t cells_local, int64_t cell_base, int64_t pos0,
+                               float scale, float* scratch, int64_t rank, int64_t nranks, void* const* mailboxes, int64_t epoch);
+int ns_b200_mla_kvsplit_combine(ns_gpu* g, void* mailbox, int64_t nranks, int64_t T, int64_t H, int64_t epoch, int64_t wait_us, float* out);
 /* Device memory shared between processes of one machine (CUDA IPC): a 64-byte handle for ptr (the start of an
  * ns_alloc allocation), opened in another process as a peer-mapped address, closed when done. */
 int ns_b200_ipc_export(ns_gpu* g, void* ptr, void* handle64);

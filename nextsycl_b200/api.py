@@ -127,6 +127,9 @@ ATTN = {
     "ns_b200_kvsplit_merge": (C.c_int, [vp, vp, i64, i64, i64, i64, vp]),
     "ns_b200_kvsplit_step": (C.c_int, [vp, vp, i64, vp, vp, i64, i64, i64, i64, i64, i64, i64, vp, i64, i64, vp, vp, i64, i64, vp]),
     "ns_b200_kvsplit_combine": (C.c_int, [vp, vp, i64, i64, i64, i64, i64, i64, vp]),
+    "ns_b200_mla_kvsplit_scratch": (i64, [vp, i64, i64, i64]),
+    "ns_b200_mla_kvsplit_decode": (C.c_int, [vp, vp, vp, i64, i64, i64, i64, i64, C.c_float, vp, i64, i64, vp, i64]),
+    "ns_b200_mla_kvsplit_combine": (C.c_int, [vp, vp, i64, i64, i64, i64, i64, vp]),
     "ns_b200_ipc_export": (C.c_int, [vp, vp, vp]),
     "ns_b200_ipc_open": (C.c_int, [vp, vp, C.POINTER(vp)]),
     "ns_b200_ipc_close": (C.c_int, [vp, vp]),

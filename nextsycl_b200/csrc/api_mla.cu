@@ -239,6 +239,43 @@ int ns_ds2_mla_decode(ns_gpu* g, const float* q, const uint16_t* kb, const uint1
     NS_CATCH("ns_ds2_mla_decode")
 }
 
+// ---- one context's latent cache split over several GPUs by cell ranges -------------------------------------------------
+int64_t ns_b200_mla_kvsplit_scratch(ns_gpu* g, int64_t T, int64_t H, int64_t cells_local) {
+    if (!g || T < 1 || H < 1 || cells_local < 1) return 0;
+    return ns_mla_partial_floats_split(cells_local, T, H, g->sms);
+}
+
+int ns_b200_mla_kvsplit_decode(ns_gpu* g, const void* q, const void* cache, int64_t T, int64_t H, int64_t cells_local, int64_t cell_base, int64_t pos0,
+                               float scale, float* scratch, int64_t rank, int64_t nranks, void* const* mailboxes, int64_t epoch) {
+    NS_TRY
+    const char* name = "ns_b200_mla_kvsplit_decode";
+    if (ns_enter(g, name)) return -1;
+    if (check_rows(name, T, H, pos0)) return -1;
+    if (T > 8) return ns_fail(std::string(name) + ": 1..8 rows");
+    if (nranks < 1 || nranks > 64 || rank < 0 || rank >= nranks) return ns_fail(std::string(name) + ": rank within 1..64 ranks");
+    if (cells_local < 0 || cells_local >= ((int64_t) 1 << 31) || cell_base < 0 || epoch < 0) return ns_fail(std::string(name) + ": a cell range of 0 .. 2^31 cells, epochs from 1");
+    if (!q || !mailboxes || (cells_local > 0 && (!cache || !scratch))) return ns_fail(std::string(name) + ": a null buffer");
+    if (((uintptr_t) q & 15) != 0 || ((uintptr_t) cache & 15) != 0 || ((uintptr_t) scratch & 15) != 0) return ns_fail(std::string(name) + ": buffers 16-byte aligned");
+    MlaDecodeArgs a{q, cache, nullptr, scratch, T, H, pos0 - cell_base, scale, 64, cells_local, nullptr, 0, nullptr};
+    a.mailboxes = (float* const*) mailboxes;
+    a.rank = (int) rank;
+    a.nranks = (int) nranks;
+    a.epoch = epoch;
+    return ns_launch_mla_decode(g, a, name);
+    NS_CATCH("ns_b200_mla_kvsplit_decode")
+}
+
+int ns_b200_mla_kvsplit_combine(ns_gpu* g, void* mailbox, int64_t nranks, int64_t T, int64_t H, int64_t epoch, int64_t wait_us, float* out) {
+    NS_TRY
+    const char* name = "ns_b200_mla_kvsplit_combine";
+    if (ns_enter(g, name)) return -1;
+    if (!mailbox || !out) return ns_fail(std::string(name) + ": a null buffer");
+    if (nranks < 1 || nranks > 64 || T < 1 || T > 8 || H < 1 || epoch < 0) return ns_fail(std::string(name) + ": 1..64 ranks, 1..8 rows, epochs from 1");
+    if (wait_us < 1 || wait_us > 2000000) return ns_fail(std::string(name) + ": a wait of 1 us .. 2 s");
+    return ns_launch_gqa_combine(g, (float*) mailbox, (int) nranks, T, H, L, epoch, wait_us * 10, out, 1, name);
+    NS_CATCH("ns_b200_mla_kvsplit_combine")
+}
+
 // kernels/llm/deepseek2/ds2.h:38-41: the same with kv_b as the model file stores it - Q6_K, [H x (128 + 128)] rows of 512: per
 // head its 128 k rows (row i = k_i[0..511], so q~ = sum_i q_nope[i] k_i), then its 128 v rows - decoded where it is read.
 int ns_ds2_mla_decode_q6k(ns_gpu* g, const float* q, const void* kvb, const uint16_t* cache, float* out, int64_t T, int64_t H, int64_t pos0, float scale) {

@@ -1179,6 +1179,7 @@ int ns_launch_gqa_combine(ns_gpu* g, float* mailbox, int nranks, int64_t T, int6
     c.spins = spins;
     if (D == 128) gqa_combine_kernel<128><<<(unsigned) (T * Hq), 128, 0, g->compute>>>(c);
     else if (D == 256) gqa_combine_kernel<256><<<(unsigned) (T * Hq), 256, 0, g->compute>>>(c);
-    else return ns_fail(std::string(where) + ": heads of 128 or 256");
+    else if (D == 512) gqa_combine_kernel<512><<<(unsigned) (T * Hq), 512, 0, g->compute>>>(c);   // absorbed MLA's latent rows
+    else return ns_fail(std::string(where) + ": rows of 128, 256 or 512");
     return ns_launched(where);
 }

@@ -123,7 +123,15 @@ struct MlaDecodeArgs {
     const int* counts;        // device [T]: cells each row attends to; null: pos0 + t + 1 (causal over one shared cache)
     int64_t cache_rows_apart; // elements between the rows' own cell matrices; 0: one shared cache
     const float* sinks;       // device [H] or null: a per-head sink (natural-log units) that joins the denominator only
+    // One context split over several GPUs by cell ranges (null mailboxes: the whole context on this GPU). `cache` then holds
+    // this rank's cells only, n_max of them, and pos0 is the first row's position RELATIVE to the rank's first cell (it may be
+    // negative or beyond the slice: a row sees min(pos0 + t + 1, n_max) of the rank's cells, none when that is <= 0). Every
+    // row's partial is kept, merged over the rank's splits and pushed into slot `rank` of every rank's mailbox.
+    float* const* mailboxes = nullptr;
+    int rank = 0, nranks = 0;
+    int64_t epoch = 0;
 };
 // floats of partials for a pass of T rows that see up to n cells, on a GPU of `sms` SMs
 int64_t ns_mla_partial_floats(int64_t n, int64_t T, int64_t H, int sms);
+int64_t ns_mla_partial_floats_split(int64_t n, int64_t T, int64_t H, int sms);
 int ns_launch_mla_decode(ns_gpu* g, const MlaDecodeArgs& a, const char* where);

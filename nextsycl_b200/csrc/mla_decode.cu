@@ -74,7 +74,19 @@ struct Params {
     int per_row, units, sms;   // per_row: each row's split size from its own cells (mla_split(n, units, sms)); else kb
     int64_t pos0, kb;      // cells a split
     float scale_log2;
+    // a context split over several GPUs: this rank's cells only (cap of them; pos0 relative to the first), partials always kept
+    int64_t cap;           // 0: no bound beyond the row's own position
+    float* const* mailboxes;
+    int rank, nranks;
+    long long epoch;
 };
+
+// cells of the (rank's) cache row t attends to
+__device__ __forceinline__ int64_t row_cells(const Params& p, int t) {
+    int64_t n = p.counts ? (int64_t) p.counts[t] : p.pos0 + t + 1;
+    if (p.cap > 0) n = min(n, p.cap);
+    return n > 0 ? n : 0;
+}
 
 template <int CR>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -101,7 +113,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int tid = threadIdx.x, warp = tid >> 5;
     const int hv = blockIdx.x & 1, split = blockIdx.x >> 1;
     const int h0 = blockIdx.y * BM, t = blockIdx.z;
-    const int64_t n = p.counts ? (int64_t) p.counts[t] : p.pos0 + t + 1;   // cells this row sees
+    const int64_t n = row_cells(p, t);                                      // cells this row sees
     const int64_t kb = p.per_row ? mla_split(n, p.units, p.sms) : p.kb;
     const int64_t jbeg = (int64_t) split * kb, jend = min(n, (int64_t) (split + 1) * kb);
     const int ntiles = jbeg < jend ? (int) ((jend - jbeg + BN - 1) / BN) : 0;
@@ -388,7 +400,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (ok) {
             fence_after_sync();
             const int64_t row = (int64_t) t * p.H + h0 + r;
-            const bool direct = n <= kb;   // the row's only split: normalised and written as the result
+            const bool direct = n <= kb && !p.mailboxes;   // the row's only split: normalised and written as the result
             float inv = 1.0f;
             if (direct) {
                 // with a sink s: out = O 2^(m - mx) / (l 2^(m - mx) + 2^(s - mx)), mx = max(m, s) (kernels/llm/deepseek41/silo/attn.cpp:266-285)
@@ -459,7 +471,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) mla_merge_kernel(const Params p
     const int t = (int) (row / p.H);
     const int tid = threadIdx.x, g = tid >> 6, lane = tid & 63;
     pdl_wait();   // the split kernel's partials
-    const int64_t n = p.counts ? (int64_t) p.counts[t] : p.pos0 + t + 1;
+    const int64_t n = row_cells(p, t);
     const int64_t kb = p.per_row ? mla_split(n, p.units, p.sms) : p.kb;
     const int nsr = (int) (((uint32_t) n + (uint32_t) kb - 1) / (uint32_t) kb);
     if (nsr <= 1) return;   // the whole block: the row's one split wrote the result itself
@@ -526,6 +538,43 @@ __global__ void __launch_bounds__(MERGE_THREADS) mla_merge_kernel(const Params p
 }
 
 
+// A context split over several GPUs by cell ranges, this rank's side: its splits merged into one partial (O [512], m in log2
+// units, l) per (row, head), stored - plain stores over NVLink - into slot `rank` of EVERY rank's mailbox (the GQA
+// KV-split's mailbox with rows of 512 + 2 floats); the last block publishes the step in every mailbox's flag for this rank
+// after one system fence. A rank that holds none of a row's cells pushes (0, -inf, 0).
+__global__ void __launch_bounds__(256) mla_merge_push_kernel(const Params p) {
+    __shared__ float sm[lse::smem_floats<L, 256>()];
+    pdl_wait();
+    const int64_t rh = blockIdx.x;   // (t, h)
+    const int t = (int) (rh / p.H);
+    const int64_t n = row_cells(p, t);
+    const int64_t kb = p.per_row ? mla_split(n, p.units, p.sms) : p.kb;
+    const int nsr = n > 0 ? (int) (((uint32_t) n + (uint32_t) kb - 1) / (uint32_t) kb) : 0;
+    float mx, den;
+    const float2 a = lse::merge_row<L, 256>(p.part + rh * p.ns * PS, PS, nsr < p.ns ? nsr : p.ns, mx, den, sm);
+    const int64_t rows = (int64_t) p.T * p.H;
+    const long long epoch = p.epoch ? p.epoch : *ns_mbox_epoch(p.mailboxes[p.rank], p.nranks, rows, L) + 1;
+    const int buf = (int) (epoch & 1);
+    for (int r = 0; r < p.nranks; ++r) {
+        float* slot = p.mailboxes[r] + ns_mbox_slot(buf, p.rank, p.nranks, rows, L) + rh * (L + 2);
+        *reinterpret_cast<float2*>(slot + 2 * threadIdx.x) = a;
+        if (threadIdx.x == 0) *reinterpret_cast<float2*>(slot + L) = make_float2(mx, den);
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* counter = reinterpret_cast<int*>(p.mailboxes[p.rank] + ns_mbox_flags_off(p.nranks, rows, L)) + 4 * p.nranks;
+        if (atomicAdd(counter, 1) + 1 == (int) gridDim.x) {
+            *counter = 0;
+            __threadfence_system();
+            for (int r = 0; r < p.nranks; ++r) {
+                long long* flag = reinterpret_cast<long long*>(p.mailboxes[r] + ns_mbox_flags_off(p.nranks, rows, L)) + buf * p.nranks + p.rank;
+                asm volatile("st.relaxed.sys.global.s64 [%0], %1;\n" ::"l"(flag), "l"(epoch) : "memory");
+            }
+        }
+    }
+}
+
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -568,6 +617,15 @@ static void mla_layout(int64_t n, int64_t T, int64_t H, int sms, int& per_row, i
     }
 }
 
+// the split form keeps every row's partial, also where a rank's cells make one split
+int64_t ns_mla_partial_floats_split(int64_t n, int64_t T, int64_t H, int sms) {
+    if (n < 1) return 0;
+    int per_row, units;
+    int64_t kb, ns;
+    mla_layout(n, T, H, sms, per_row, units, kb, ns);
+    return T * H * (ns > 1 ? ns : 1) * PS;
+}
+
 int64_t ns_mla_partial_floats(int64_t n, int64_t T, int64_t H, int sms) {
     int per_row, units;
     int64_t kb, ns;
@@ -591,18 +649,26 @@ int launch(ns_gpu* g, const MlaDecodeArgs& a, const char* where) {
     p.H = (int) a.H;
     p.pos0 = a.pos0;
     int64_t ns = 1;
-    mla_layout(n, a.T, a.H, g->sms, p.per_row, p.units, p.kb, ns);
-    p.ns = (int) ns;
+    mla_layout(n > 0 ? n : 1, a.T, a.H, g->sms, p.per_row, p.units, p.kb, ns);
+    p.ns = (int) (ns > 1 ? ns : 1);
     p.sms = g->sms;
     if (p.ns > 1 && !a.part) return ns_fail(std::string(where) + ": no scratch for the key splits");
     p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.cap = a.mailboxes ? n : 0;
+    p.mailboxes = a.mailboxes;
+    p.rank = a.rank;
+    p.nranks = a.nranks;
+    p.epoch = a.epoch;
+    if (a.mailboxes && ((n > 0 && !a.part) || a.sinks || a.counts || a.cache_rows_apart > 0)) return ns_fail(std::string(where) + ": the split form takes scratch, one shared cache and no sinks");
     if (p.ns > lse::MAX_SPLITS) return ns_fail(std::string(where) + ": more key splits than the merge holds");
     CUtensorMap tq, tc;
-    // Q [T][H][CR]: a box = 128 heads x 64 features of one row
-    if (make_map(&tq, a.q, CR, (uint64_t) a.H, (uint64_t) a.T, CR * 2, (uint64_t) a.H * CR * 2, BM, where)) return -1;
-    // cells [Z][n][CR]: a box = 64 cells x 64 features; cells past n read as zeros
-    const uint64_t z = p.zmul ? (uint64_t) a.T : 1, zs = p.zmul ? (uint64_t) a.cache_rows_apart * 2 : (uint64_t) n * CR * 2;
-    if (make_map(&tc, a.cache, CR, (uint64_t) n, z, CR * 2, zs, BN, where)) return -1;
+    if (n > 0) {
+        // Q [T][H][CR]: a box = 128 heads x 64 features of one row
+        if (make_map(&tq, a.q, CR, (uint64_t) a.H, (uint64_t) a.T, CR * 2, (uint64_t) a.H * CR * 2, BM, where)) return -1;
+        // cells [Z][n][CR]: a box = 64 cells x 64 features; cells past n read as zeros
+        const uint64_t z = p.zmul ? (uint64_t) a.T : 1, zs = p.zmul ? (uint64_t) a.cache_rows_apart * 2 : (uint64_t) n * CR * 2;
+        if (make_map(&tc, a.cache, CR, (uint64_t) n, z, CR * 2, zs, BN, where)) return -1;
+    }
     auto kern = mla_decode_kernel<CR>;
     static bool set[64] = {};
     if (!set[g->dev & 63]) {
@@ -610,8 +676,23 @@ int launch(ns_gpu* g, const MlaDecodeArgs& a, const char* where) {
         set[g->dev & 63] = true;
     }
     dim3 grid((unsigned) (2 * p.ns), (unsigned) ((a.H + BM - 1) / BM), (unsigned) a.T);
-    kern<<<grid, THREADS, Geo<CR>::SMEM_TOTAL, g->compute>>>(tq, tc, p);
-    if (ns_launched(where)) return -1;
+    if (n > 0) {
+        kern<<<grid, THREADS, Geo<CR>::SMEM_TOTAL, g->compute>>>(tq, tc, p);
+        if (ns_launched(where)) return -1;
+    }
+    if (a.mailboxes) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned) (a.T * a.H));
+        cfg.blockDim = dim3(256);
+        cfg.stream = g->compute;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        NS_CUDA(cudaLaunchKernelEx(&cfg, mla_merge_push_kernel, p), where);
+        return 0;
+    }
     if (p.ns > 1) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned) (a.T * a.H), 2);

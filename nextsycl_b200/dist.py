@@ -105,6 +105,30 @@ class KvSplit:
         check(api, api.need("ns_b200_kvsplit_combine")(self.gpu.raw, self.mailbox.ptr, self.nranks, self.T, self.Hq, self.D, epoch, wait_us, out.ptr),
               "ns_b200_kvsplit_combine")
 
+    # ---- the absorbed-MLA latent cache split the same way (a group made with D = 512 and Hq = the number of heads) -------
+    def mla_scratch_floats(self, cells_local):
+        return int(self.gpu.api.need("ns_b200_mla_kvsplit_scratch")(self.gpu.raw, self.T, self.Hq, max(0, cells_local)))
+
+    def mla_decode(self, q, cache, cells_local, cell_base, pos0, scale, scratch, epoch=None):
+        """This rank's cells (cache fp16 [cells_local][576]); pushes its partial to every mailbox under `epoch`."""
+        if epoch is None:
+            self.epoch += 1
+            epoch = self.epoch
+        elif epoch == 0:
+            self.device_epochs = True
+        api = self.gpu.api
+        check(api, api.need("ns_b200_mla_kvsplit_decode")(self.gpu.raw, q.ptr, cache.ptr if cache is not None else None, self.T, self.Hq, cells_local,
+                                                          cell_base, pos0, scale, scratch.ptr if scratch is not None else None, self.rank, self.nranks,
+                                                          self.table.ptr, epoch), "ns_b200_mla_kvsplit_decode")
+        return epoch
+
+    def mla_combine(self, out, epoch=None, wait_us=200000):
+        api = self.gpu.api
+        if epoch is None:
+            epoch = 0 if getattr(self, "device_epochs", False) else self.epoch
+        check(api, api.need("ns_b200_mla_kvsplit_combine")(self.gpu.raw, self.mailbox.ptr, self.nranks, self.T, self.Hq, epoch, wait_us, out.ptr),
+              "ns_b200_mla_kvsplit_combine")
+
     def close(self):
         api = self.gpu.api
         for p in self.opened:

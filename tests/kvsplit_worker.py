@@ -34,6 +34,7 @@ def main():
     # key and still publish), and the benchmark's long-context configuration at full size
     for kv in (20000 + 64 * 7, 70, 262144):
         ok = one_context(gpu, grp, rank, world, T, Hq, Hkv, D, kv) and ok
+    ok = mla_context(gpu, rank, world, exchange, 131072) and ok
     grp.close()
     flags = [None] * world
     dist.all_gather_object(flags, ok)
@@ -41,6 +42,48 @@ def main():
     if rank == 0:
         print("kvsplit multi-gpu:", "ok" if all(flags) else "MISMATCH", f"({world} ranks)", flush=True)
     sys.exit(0 if all(flags) else 1)
+
+
+def mla_context(gpu, rank, world, exchange, n):
+    """The absorbed-MLA latent cache (benchmark configuration 3 at 131,072 cells) split by cell ranges over the ranks: every
+    rank's combined rows against the oracle on 16 heads spread over the tile, and against the other ranks' bit for bit."""
+    T, H = 1, 128
+    scale = float(1.0 / np.sqrt(192.0))
+    q = W.normal_f16(3, 0, (T, H, 576))
+    cache = W.normal_f16(3, 1, (n, 576), 0.5)
+    grp = KvSplit(gpu, rank, world, T, H, 512, exchange=exchange)
+    base, count = key_ranges(n, world)[rank]
+    dq, dc = DevBuf.of(gpu, q), DevBuf.of(gpu, np.ascontiguousarray(cache[base:base + count]))
+    sc = DevBuf(gpu, 4 * grp.mla_scratch_floats(count))
+    out = DevBuf(gpu, T * H * 512 * 4)
+    heads = [0, 31, 32, 63, 64, 95, 96, 127, 7, 16, 45, 50, 77, 88, 101, 120]
+    box = [None]
+    if rank == 0:
+        O.use_all_cores()
+        box[0] = O.mla_gemm(np.ascontiguousarray(q[:, heads].astype(np.float32)), cache.view(np.uint16), T, len(heads), 512, 64, n - T, np.float32(scale))
+    dist.broadcast_object_list(box, src=0)
+    want = box[0]
+    ok = True
+    for step in range(3):
+        out.fill(0xFF)
+        grp.mla_decode(dq, dc, count, base, n - T, scale, sc)
+        grp.mla_combine(out)
+        gpu.sync()
+        got = out.read(np.float32).reshape(T, H, 512)
+        d = np.abs(got[:, heads].astype(np.float64) - want)
+        if not (np.isfinite(got).all() and np.all(d <= 2e-3 + 1e-2 * np.abs(want))):
+            print(f"rank {rank} step {step} (MLA, {n} cells): max abs {d.max():.3e} outside |d| <= 2e-3 + 1e-2 |want|", flush=True)
+            ok = False
+        every = [None] * world
+        dist.all_gather_object(every, got.tobytes())
+        if any(e != every[0] for e in every):
+            print(f"rank {rank} step {step} (MLA): the ranks' results differ", flush=True)
+            ok = False
+        dist.barrier()
+    grp.close()
+    if rank == 0:
+        print(f"  MLA {n} cells over {world} ranks: {'ok' if ok else 'MISMATCH'}", flush=True)
+    return ok
 
 
 def one_context(gpu, grp, rank, world, T, Hq, Hkv, D, kv):

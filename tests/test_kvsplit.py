@@ -215,3 +215,44 @@ def test_partials_gathered_by_the_caller(gpu, ops):
     got = out.read(np.float16).reshape(T, Hq * D).astype(np.float32)
     want = O.gqa_flash_decode(q.astype(np.float32), k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, kv, p0)
     assert np.all(np.abs(got - want) <= 2e-3 + 1e-2 * np.abs(want)), float(np.abs(got - want).max())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("nranks,T,H,n", [(2, 1, 128, 1000), (4, 3, 128, 5000), (8, 1, 128, 20000), (3, 2, 16, 130), (8, 1, 128, 100)])
+def test_mla_cell_ranges_on_one_gpu_match_the_oracle(gpu, ops, nranks, T, H, n):
+    """The absorbed-MLA latent cache split by cell ranges: every rank's slice run one after another on one GPU, each pushing
+    into every rank's mailbox, then each rank's combine (all flags set by then: nothing waits on another launch). Against the
+    oracle's decode of the whole cache; two steps (both mailbox buffers). (8 ranks over 100 cells: six hold none.)"""
+    from nextsycl_b200 import DevBuf
+    from nextsycl_b200 import workloads as W
+    from nextsycl_b200.dist import KvSplit
+    from oracle import oracle as O
+    scale = float(1.0 / np.sqrt(192.0))
+    q = W.normal_f16(955, 0, (T, H, 576))
+    cache = W.normal_f16(955, 1, (n, 576), 0.5)
+    pos0 = n - T
+    dq = DevBuf.of(gpu, q)
+    boxes = [DevBuf(gpu, KvSplit.mailbox_bytes(gpu.api, nranks, T, H, 512)) for _ in range(nranks)]
+    for b in boxes:
+        b.fill(0)
+    groups = [KvSplit(gpu, r, nranks, T, H, 512, local_mailboxes=boxes) for r in range(nranks)]
+    want = O.mla_gemm(q.astype(np.float32), cache.view(np.uint16), T, H, 512, 64, pos0, np.float32(scale))
+    keep = []
+    for step in range(2):
+        for r, (base, count) in enumerate(key_ranges(n, nranks)):
+            if count == 0:
+                groups[r].mla_decode(dq, None, 0, base, pos0, scale, None)
+                continue
+            dc = DevBuf.of(gpu, np.ascontiguousarray(cache[base:base + count]))
+            sc = DevBuf(gpu, 4 * groups[r].mla_scratch_floats(count))
+            sc.fill(0xFF)
+            keep += [dc, sc]
+            groups[r].mla_decode(dq, dc, count, base, pos0, scale, sc)
+        for r in range(nranks):
+            out = DevBuf(gpu, T * H * 512 * 4)
+            out.fill(0xFF)
+            groups[r].mla_combine(out, wait_us=1000)
+            gpu.sync()
+            got = out.read(np.float32).reshape(T, H, 512)
+            d = np.abs(got - want)
+            assert np.isfinite(got).all() and np.all(d <= 2e-3 + 1e-2 * np.abs(want)), (step, r, float(d.max()))

@@ -120,20 +120,21 @@ def _run_q6k(gpu, q, kvb, cache, T, H, pos0):
 
 
 def test_ds2_q6k_decoder_bit_exact(gpu):
-    """The Q6_K reader of ns_ds2_mla_decode_q6k, read out exactly: one cell whose latent is a one-hot column c makes the
-    attention's u that one-hot, so out[h][r] = v_r[c] as the decoder produced it - equal to the oracle's decode of the same
-    blocks (kernels/llm/deepseek2/ds2.cpp:123-137) bit for bit, for columns in every (block, half, quarter, scale half)."""
+    """The Q6_K reader of ns_ds2_mla_decode_q6k, read out exactly: one cell whose latent is a one-hot column c, under a zero
+    query (score 0, weight exactly 1, sum exactly 1), makes the attention's u that one-hot, so out[h][r] = v_r[c] as the
+    decoder produced it - equal to the oracle's decode of the same blocks (kernels/llm/deepseek2/ds2.cpp:123-137) bit for bit,
+    for columns in every (block, half, quarter, scale half)."""
     H = 4
     rng = W.rng(945, 0)
     kvb = _q6k_blocks(rng, H * 256)
     vals = O.q6k_rows(kvb, H * 256, 512).reshape(H, 256, 512)
-    q = rng.standard_normal((1, H, 192), dtype=np.float32)
+    q = np.zeros((1, H, 192), np.float32)
     cols = [256 * b + 128 * n + 32 * g + l for b in (0, 1) for n in (0, 1) for g in (0, 1, 2, 3) for l in (0, 15, 16, 31)][::3] + [0, 511]
     for c in cols:
         cache = np.zeros((1, 576), np.float16)
         cache[0, c] = 1.0
         got = _run_q6k(gpu, q, kvb, cache, 1, H, 0)
-        assert np.array_equal(got[0].view(np.uint32), vals[:, 128:, c].view(np.uint32)), c
+        assert np.array_equal(got[0].view(np.uint32), np.ascontiguousarray(vals[:, 128:, c]).view(np.uint32)), c
 
 
 @pytest.mark.parametrize("T,H,n", [(1, 128, 700), (3, 16, 2500)])
