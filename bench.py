@@ -357,6 +357,28 @@ def wl_ds2_decode(env, n):
     return step, info
 
 
+def wl_glm_prompt_gemms(env, tr=32, H=64, nc=2112, L=512):
+    """The two batched fp16 GEMMs of the glm5next engine's prompt path for one block of 32 rows at its largest cell count
+    (llm/glm5next/src/engine.rs:1925,1930): scores [64 x 2,112] = q~ . G^T and latents [64 x 512] = P . G per row, through
+    the reference's own symbol ns_gemm_batch_h. Input sets in turn as elsewhere."""
+    from nextsycl_b200 import DevBuf
+    from nextsycl_b200.core import check
+    api, raw = env.gpu.api, env.gpu.raw
+    set_bytes = tr * (nc * L * 2 + H * L * 2 + H * nc * 2 + H * nc * 4 + H * L * 4)
+    rotate = max(2, -(-300_000_000 // set_bytes))
+    sets = [(device_random_f16(env, tr * nc * L * 2, 400 + 3 * r, 0.5), device_random_f16(env, tr * H * L * 2, 401 + 3 * r),
+             device_random_f16(env, tr * H * nc * 2, 402 + 3 * r, 0.02), DevBuf(env.gpu, tr * H * nc * 4), DevBuf(env.gpu, tr * H * L * 4)) for r in range(rotate)]
+    i = [0]
+
+    def step():
+        gh, qh, ph, sb, u = sets[i[0] % rotate]
+        i[0] += 1
+        check(api, api.ns_gemm_batch_h(raw, tr, 1, H, nc, L, qh.ptr, L, H * L, gh.ptr, L, nc * L, sb.ptr, nc, H * nc, 0), "scores")
+        check(api, api.ns_gemm_batch_h(raw, tr, 0, H, L, nc, ph.ptr, nc, H * nc, gh.ptr, L, nc * L, u.ptr, L, H * L, 0), "values")
+    info = {"flops": 2 * 2 * tr * H * nc * L, "bytes": set_bytes, "bound": "tensor", "launches": 2, "keep": sets}
+    return step, info
+
+
 def wl_mla_prefill(env, T=4096, p0=32768, H=128):
     """benchmark configuration 4: 4,096 new rows over a 32,768-token cache, bf16, 192-wide keys / 128-wide values; the 128 heads
     sharded over the ranks (each rank its own heads' K and V; no exchange)."""
@@ -594,6 +616,8 @@ def measure(env, name, steps, warmup, min_ms=0.0):
         step, info = wl_mla_decode(env, {"4k": 4096, "32k": 32768, "131k": 131072}[name.split("_")[-1]])
     elif name == "mla_prefill_c4":
         step, info = wl_mla_prefill(env)
+    elif name == "glm_prompt_gemms":
+        step, info = wl_glm_prompt_gemms(env)
     else:
         raise SystemExit(f"unknown workload {name}")
     ms, steps = env.timed(step, steps, max(3, warmup), sampler=ClockSampler(env.local), min_ms=min_ms)
@@ -623,7 +647,7 @@ NCU_TRAFFIC = {"decode_c2": 1.073912e9 + 12.0e6, "mla_decode_32k": 37.96e6 + 0.0
 
 OTHERS_1GPU = [("prefill_16k", 10), ("prefill_c1", 50), ("prefill_q35_16k", 10), ("decode_c2_b1", 50), ("decode_128k", 30), ("decode_c5", 30), ("decode_q35_f16", 30),
                ("decode_q35_q8", 30), ("decode_q35_q4", 30), ("mla_decode_4k", 50),
-               ("mla_decode_32k", 50), ("mla_decode_131k", 30), ("ds2_decode_32k", 50), ("mla_prefill_c4", 10)]
+               ("mla_decode_32k", 50), ("mla_decode_131k", 30), ("ds2_decode_32k", 50), ("glm_prompt_gemms", 50), ("mla_prefill_c4", 10)]
 OTHERS_NGPU = [("decode_c5_split", 50), ("decode_c5_split_3launch", 50), ("decode_c5_split_nccl", 50), ("mla_decode_131k_split", 50), ("prefill_16k", 10), ("mla_prefill_c4", 10)]
 
 
@@ -647,6 +671,7 @@ def config_of(name, n):
         "mla_decode_4k": "config 3: absorbed MLA decode, 128 heads, 576-wide latent cache, 4,096 cells",
         "mla_decode_32k": "config 3, 32,768 cells",
         "mla_decode_131k": "config 3, 131,072 cells",
+        "glm_prompt_gemms": "ns_gemm_batch_h twice: the glm5next prompt path's scores and latents GEMMs for 32 rows x 64 heads over 2,112 gathered cells of 512",
         "mla_prefill_c4": "config 4: bf16 MLA prefill chunk, 4,096 rows over 32,768 cached, 128 heads (192/128), heads sharded over ranks",
     }
     return {"workload": texts.get(name, name), "name": name,
