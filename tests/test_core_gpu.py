@@ -95,3 +95,19 @@ def test_errors_are_per_call_and_null_gpu_is_rejected(api):
     out = C.c_void_p()
     assert api.ns_gpu_open(10_000, C.byref(out)) == -1
     assert "no GPU" in api.last_error()
+
+
+def test_a_ticket_older_than_the_ring_is_refused(gpu):
+    """Tickets index a ring of 65,536 events (kernels/ns/ns_internal.hpp:14): a ticket more than a ring older than the newest
+    names an event slot a newer mark has taken, so it is refused instead of standing for that newer event."""
+    api = gpu.api
+    first, t = C.c_int64(), C.c_int64()
+    assert api.ns_mark(gpu.raw, C.byref(first)) == 0
+    for _ in range(65536):
+        assert api.ns_mark(gpu.raw, C.byref(t)) == 0
+    gpu.sync()
+    assert api.ns_await(gpu.raw, t.value) == 0
+    assert api.ns_await(gpu.raw, first.value) == -1 and "older" in api.last_error()
+    ns = C.c_double()
+    assert api.ns_elapsed(gpu.raw, first.value, t.value, C.byref(ns)) == -1
+    assert api.ns_elapsed(gpu.raw, t.value - 5, t.value, C.byref(ns)) == 0 and ns.value >= 0
