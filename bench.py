@@ -9,8 +9,10 @@ GPU, so every step's reads miss L2. A step is one pass of the path over the batc
 
   value      KV bytes the step must read / device time, inputs resident in HBM, summed over ranks (weak scaling:
              every rank holds its own 8 sequences; independent sequences need no exchange)
-  e2e        the same metric through the reference's own calls with HOST buffers: per sequence ns_copy_to(q, k, v
-             rows) -> ns_q35_kv_store -> ns_q35_attn_decode -> ns_copy_from(out), one ns_sync a step
+  e2e        the same metric from HOST buffers through the library's C-ABI: the step's q | k | v rows up from one pinned
+             buffer, ns_b200_kv_store_batch, ns_b200_gqa_decode, the outputs down, one ns_sync a step
+  e2e_reference_symbols  the same through the reference's own per-sequence calls: ns_copy_to(q, k, v rows) ->
+             ns_q35_kv_store -> ns_q35_attn_decode -> ns_copy_from(out) a sequence, one ns_sync a step
   roofline   algorithmic bytes (or flops) a launch / CUDA-event time, against the measured peaks
   cpu_baseline, --impl reference: the CPU restatement of the reference kernel (oracle/) on the host cores; the
              reference's SYCL kernels themselves cannot be built without a oneAPI toolchain
@@ -616,6 +618,8 @@ def measure(env, name, steps, warmup, min_ms=0.0):
         step, info = wl_mla_decode(env, {"4k": 4096, "32k": 32768, "131k": 131072}[name.split("_")[-1]])
     elif name == "mla_prefill_c4":
         step, info = wl_mla_prefill(env)
+    elif name == "mla_prefill_c4_h16":      # one rank's share of config 4 at 8 GPUs (16 of the 128 heads): the profiler's case
+        step, info = wl_mla_prefill(env, H=16 * env.world)
     elif name == "glm_prompt_gemms":
         step, info = wl_glm_prompt_gemms(env)
     else:
@@ -842,15 +846,18 @@ def run_ours(args):
     }
     if name == "decode_c2":
         e2e_steps = max(5, min(args.steps, 200))
-        s, h2d, d2h = e2e_decode(env, info, e2e_steps)
-        line["e2e"] = {"value": world * info["bytes"] / s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                       "ms_per_step": s * 1e3,
-                       "path": "per sequence: ns_copy_to q,k,v rows (pinned) -> ns_q35_kv_store -> ns_q35_attn_decode -> ns_copy_from out; ns_sync a step"}
+        # e2e: the batch through the library's batched C-ABI calls from pinned host buffers; beside it the same batch through
+        # the reference's own per-sequence symbols (what an engine gets by swapping the library and changing nothing else)
         s2, h2d2, d2h2 = e2e_decode_native(env, info, e2e_steps)
-        line["e2e_native"] = {"value": world * info["bytes"] / s2 / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d2, "d2h_bytes_per_step": d2h2,
-                              "ms_per_step": s2 * 1e3,
-                              "path": "one ns_copy_to of q (fp16) | k | v rows (one pinned buffer) -> one ns_b200_kv_store_batch -> one "
-                                      "ns_b200_gqa_decode for the batch -> one ns_copy_from out (fp16); ns_sync a step"}
+        line["e2e"] = {"value": world * info["bytes"] / s2 / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d2, "d2h_bytes_per_step": d2h2,
+                       "ms_per_step": s2 * 1e3,
+                       "path": "one ns_copy_to of q (fp16) | k | v rows (one pinned buffer) -> one ns_b200_kv_store_batch -> one "
+                               "ns_b200_gqa_decode for the batch -> one ns_copy_from out (fp16); ns_sync a step"}
+        s, h2d, d2h = e2e_decode(env, info, e2e_steps)
+        line["e2e_reference_symbols"] = {"value": world * info["bytes"] / s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                                         "ms_per_step": s * 1e3,
+                                         "path": "per sequence: ns_copy_to q,k,v rows (pinned) -> ns_q35_kv_store -> ns_q35_attn_decode -> "
+                                                 "ns_copy_from out; ns_sync a step"}
     del info, res
 
     if not args.no_others:
