@@ -328,6 +328,42 @@ def wl_mla_decode(env, n):
     return step, info
 
 
+def wl_glm_sel_decode(env, n=131072, H=64, K=512):
+    """The one attention kernel the reference publishes a time for (TODO.md:546-551: GLM-5.3's absorbed-MLA decode attention at
+    128K context, 2,051 selected cells x 64 heads x 512-wide fp16 latents, 1,047 -> 444 us a layer on Arc Pro B70 / B65): one
+    decode row over the indexer's 512 selected pools of 4 tokens plus the 3 tokens of its incomplete pool, through the
+    reference's own symbol ns_mla_attend_sel. Cache sets in turn; the selection differs per set."""
+    from nextsycl_b200 import DevBuf
+    from nextsycl_b200 import workloads as W
+    from nextsycl_b200.core import check
+    api, gpu = env.gpu.api, env.gpu
+    pos0 = n + 2                                   # (pos0 + 1) % 4 == 3: three tokens in the row's incomplete pool
+    cells = pos0 + 1
+    q = DevBuf.of(gpu, W.normal_f32(3, 60, (1, H * 512)))
+    rotate = max(2, -(-300_000_000 // (cells * 1024)))
+    whole = device_random_f16(env, rotate * cells * 1024, 61, 0.5)
+    caches = [whole.view(r * cells * 1024, cells * 1024) for r in range(rotate)]
+    sels = [DevBuf.of(gpu, np.sort(W.rng(3, 62 + r).choice((pos0 + 1) // 4, size=K, replace=False)).astype(np.int32)) for r in range(rotate)]
+    cnt = DevBuf.of(gpu, np.array([K], np.int32))
+    out = DevBuf(gpu, H * 512 * 4)
+
+    def one(r):
+        check(api, api.ns_mla_attend_sel(gpu.raw, q.ptr, caches[r].ptr, out.ptr, 1, H, 512, pos0, np.float32(1 / 16.0), sels[r].ptr, cnt.ptr, K), "ns_mla_attend_sel")
+    one(0)
+    gpu.sync()
+    graphs = [gpu.record(lambda r=r: one(r)) for r in range(rotate)]
+    i = [0]
+
+    def step():
+        graphs[i[0] % rotate].launch()
+        i[0] += 1
+    info = {"bytes": (4 * K + 3) * 1024, "flops": (4 * K + 3) * H * 2 * (512 + 512), "bound": "hbm", "launches": 3,
+            "keep": (q, whole, caches, sels, cnt, out, graphs),
+            "published": {"reference_us": 444.0, "reference_us_before": 1047.0, "hardware": "Intel Arc Pro B70 / B65 (608 GB/s)",
+                          "source": "TODO.md:546-551 (per layer and pass, 2,051 cells x 64 heads, fp16 latents)"}}
+    return step, info
+
+
 def wl_ds2_decode(env, n):
     """The reference's whole deepseek2 decode op for one row (ns_ds2_mla_decode: absorb q through k_b, the latent attention of
     config 3, out through v_b), fp32 rows in and out, 128 heads; cache sets in turn as in wl_mla_decode."""
@@ -612,6 +648,8 @@ def measure(env, name, steps, warmup, min_ms=0.0):
         step, info = wl_prefill(env, 16384, 24, 4, 256)
     elif name == "ds2_decode_32k":
         step, info = wl_ds2_decode(env, 32768)
+    elif name == "glm_sel_decode_2051":
+        step, info = wl_glm_sel_decode(env)
     elif name == "mla_decode_131k_split":
         step, info = wl_mla_kvsplit(env)
     elif name.startswith("mla_decode_"):
@@ -641,6 +679,8 @@ def measure(env, name, steps, warmup, min_ms=0.0):
             res["gbs_job"] = info["bytes_total"] / (ms * 1e-3) / 1e9
         if "tokens_bytes_f16" in info:   # a quantised cache: the same tokens as so many fp16 bytes a second
             res["f16_equivalent_gbs"] = info["tokens_bytes_f16"] / (ms * 1e-3) / 1e9
+    if "published" in info:   # the reference's own published time for this kernel (other hardware): ours beside it
+        res["published"] = dict(info["published"], ours_us=ms * 1e3, ratio=info["published"]["reference_us"] / (ms * 1e3))
     res["_info"] = info
     return res
 
@@ -651,7 +691,7 @@ NCU_TRAFFIC = {"decode_c2": 1.073912e9 + 12.0e6, "mla_decode_32k": 37.96e6 + 0.0
 
 OTHERS_1GPU = [("prefill_16k", 10), ("prefill_c1", 50), ("prefill_q35_16k", 10), ("decode_c2_b1", 50), ("decode_128k", 30), ("decode_c5", 30), ("decode_q35_f16", 30),
                ("decode_q35_q8", 30), ("decode_q35_q4", 30), ("mla_decode_4k", 50),
-               ("mla_decode_32k", 50), ("mla_decode_131k", 30), ("ds2_decode_32k", 50), ("glm_prompt_gemms", 50), ("mla_prefill_c4", 10)]
+               ("mla_decode_32k", 50), ("mla_decode_131k", 30), ("ds2_decode_32k", 50), ("glm_sel_decode_2051", 50), ("glm_prompt_gemms", 50), ("mla_prefill_c4", 10)]
 OTHERS_NGPU = [("decode_c5_split", 50), ("decode_c5_split_3launch", 50), ("decode_c5_split_nccl", 50), ("mla_decode_131k_split", 50), ("prefill_16k", 10), ("mla_prefill_c4", 10)]
 
 
@@ -675,6 +715,7 @@ def config_of(name, n):
         "mla_decode_4k": "config 3: absorbed MLA decode, 128 heads, 576-wide latent cache, 4,096 cells",
         "mla_decode_32k": "config 3, 32,768 cells",
         "mla_decode_131k": "config 3, 131,072 cells",
+        "glm_sel_decode_2051": "ns_mla_attend_sel: glm5next decode attention at 128K context, 2,051 selected cells x 64 heads x 512 (the one attention kernel the reference publishes a time for)",
         "glm_prompt_gemms": "ns_gemm_batch_h twice: the glm5next prompt path's scores and latents GEMMs for 32 rows x 64 heads over 2,112 gathered cells of 512",
         "mla_prefill_c4": "config 4: bf16 MLA prefill chunk, 4,096 rows over 32,768 cached, 128 heads (192/128), heads sharded over ranks",
     }
@@ -819,7 +860,7 @@ def run_ours(args):
                 "note": "per GPU; algorithmic bytes = 2*kv*Hkv*D*2 B a sequence x sequences a launch; duration = CUDA-event time of a step "
                         "(the split kernel plus its merge kernel)"}
         scaling = "strong" if "bytes_total" in info else "weak"
-    elif name.startswith("mla_decode") or name.startswith("ds2_decode"):
+    elif name.startswith("mla_decode") or name.startswith("ds2_decode") or name.startswith("glm_sel"):
         value, unit = info.get("bytes_total", info["bytes"]) / (ms * 1e-3) / 1e9, "GB/s"
         roof = {"bound": "hbm", "achieved": res["gbs_per_gpu"], "peak": float(pk["hbm_gbs"]), "unit": "GB/s", "frac": res["frac_of_hbm_peak"],
                 "traffic": NCU_TRAFFIC.get(name), "peak_source": pk["_source"], "note": "algorithmic bytes = 1,152 B a cell; flops 278,528 a cell",
