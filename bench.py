@@ -885,6 +885,10 @@ def run_ours(args):
         "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "bf16" if name == "mla_prefill_c4" else "f16", "data": "synthetic",
         "config": config_of(name, world), "roofline": roof, "gpu_launches": int(args.steps * info["launches"]), "clocks": clocks,
     }
+    if "check" in info:      # a workload that can check its own output (the multi-GPU exchanges): after the timed region
+        line["parity"] = info["check"]()
+    if "published" in res:
+        line["published"] = res["published"]
     if name == "decode_c2":
         e2e_steps = max(5, min(args.steps, 200))
         # e2e: the batch through the library's batched C-ABI calls from pinned host buffers; beside it the same batch through
