@@ -145,6 +145,8 @@ def _gemm(gpu, batch, trans_w, T, N, K, x, ldx, sx, w, ldw, sw, y, ldy, sy, accu
     (1, 1, 1, 8, 8, 0, 0),            # one row
     (2, 1, 33, 50, 70, 3, 0),         # odd strides: the plain kernel
     (2, 0, 33, 50, 70, 5, 1),
+    (2, 1, 5, 7, 0, 0, 1),            # nothing to sum: y stays (accumulate) ...
+    (2, 0, 5, 7, 0, 0, 0),            # ... or becomes zero
 ])
 def test_gemm_batch_h(gpu, batch, trans_w, T, N, K, pad, acc):
     """ns_gemm_batch_h against float64 products of the same fp16 values. Tolerance: fp32 accumulation of K products of
