@@ -268,6 +268,9 @@ int ns_b200_kvsplit_step(ns_gpu* g, const void* q, int64_t qs, const void* kc, c
     if (kv_local < 0 || kv_local >= ((int64_t) 1 << 31) || key_base < 0 || p0 < 0 || p0 + T >= ((int64_t) 1 << 40))
         return ns_fail(std::string(name) + ": a key range of 0 .. 2^31 keys");
     if (epoch < 0) return ns_fail(std::string(name) + ": epochs count from 1 (0: the mailbox's own counter)");
+    // a line's tag is the step number's low 32 bits, and a mailbox starts zeroed: a step whose tag would be 0 could take a
+    // line nobody wrote for one that arrived
+    if (epoch != 0 && (uint32_t) epoch == 0) return ns_fail(std::string(name) + ": a step number whose low 32 bits are zero (restart the epochs from 1)");
     if (wait_us < 1 || wait_us > 2000000) return ns_fail(std::string(name) + ": a wait of 1 us .. 2 s");
     if (qs % 8 != 0 || ((uintptr_t) q & 15) != 0) return ns_fail(std::string(name) + ": query rows 16-byte aligned");
     if (!q || !mailboxes || !own_mailbox || !out || (kv_local > 0 && (!kc || !vc || !scratch))) return ns_fail(std::string(name) + ": a null buffer");
