@@ -3,10 +3,11 @@
 // its user: per block of 32 rows, scores [64 heads, cells] = q~ . G^T (op = transpose) and latents [64, 512] = P . G
 // (no transpose) over each row's own gathered cells (llm/glm5next/src/engine.rs:1925,1930).
 //
-// How: a CTA owns a 128 x 128 tile of one product's output. Warp 0 issues TMA loads of 64-wide K slices (x as a K-major
+// How: persistent CTAs, one an SM, walk the 128 x 128 output tiles of all the products. Warp 0 issues TMA loads of 64-wide K slices (x as a K-major
 // tile; w as a K-major tile when it is transposed, as an MN-major tile - rows of 64 contiguous n - when it is not) into
-// a 3-stage ring, warp 1 issues tcgen05.mma (fp32 accumulator in tensor memory), warps 2-5 read the accumulator back
-// (a warp the 32 lanes it may touch) and store, or add to, the rows of y. Rows past T, columns past N and K's tail are
+// a 6-stage ring and never stops between tiles, warp 1 issues tcgen05.mma into one of two fp32 accumulators in tensor
+// memory, warps 2-5 read the finished accumulator back (a warp the 32 lanes it may touch) and store, or add to, the rows of
+// y while the next tile's MMAs fill the other. Rows past T, columns past N and K's tail are
 // zeros from TMA's out-of-bounds fill, never read from memory. Every wait is bounded (status codes 6xx).
 // Operands TMA cannot address (a base or stride that is not a multiple of 16 bytes) take a plain shared-memory kernel.
 #include "kernels.cuh"
@@ -14,10 +15,12 @@
 
 #include <cuda.h>
 
+#include <algorithm>
+
 namespace {
 using namespace tc05;
 
-constexpr int BM = 128, BN = 128, BK = 64, NSTAGE = 3;   // 97 KB of stages: two CTAs an SM, one's epilogue under the other's loop
+constexpr int BM = 128, BN = 128, BK = 64, NSTAGE = 6;   // 192 KB of stages: one CTA an SM with a deep ring (see the launch)
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE = A_BYTES + B_BYTES;
 constexpr int SMEM_TOTAL = 1024 + NSTAGE * STAGE + 256;
 constexpr int THREADS = 192;
@@ -25,26 +28,36 @@ constexpr int THREADS = 192;
 struct GemmParams {
     float* y;
     int64_t ldy, sy;
-    int T, N, K;
+    int T, N, K, batch;
     int accumulate;
     int* status;
 };
 
 template <int TRANS_W>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(THREADS, 1)
 gemm_batch_h_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
     uint64_t* bars = (uint64_t*) (smem + NSTAGE * STAGE);
-    uint64_t* full = bars;                 // [NSTAGE]
-    uint64_t* empty = bars + NSTAGE;       // [NSTAGE]
-    uint64_t* acc_full = empty + NSTAGE;   // [1]
-    uint32_t* tmem_slot = (uint32_t*) (acc_full + 1);
+    uint64_t* full = bars;                   // [NSTAGE]
+    uint64_t* empty = bars + NSTAGE;         // [NSTAGE]
+    uint64_t* acc_full = empty + NSTAGE;     // [2] a tile's accumulator complete
+    uint64_t* acc_empty = acc_full + 2;      // [2] the epilogue has read it (4 arrivals: one a warp)
+    uint32_t* tmem_slot = (uint32_t*) (acc_empty + 2);
     volatile int* abort_flag = (volatile int*) (tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, b = blockIdx.z;
     const int nk = (p.K + BK - 1) / BK;
+    // The CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...: column tiles of one product fastest (they share its rows of
+    // x), then row tiles, then products. The loads never stop between tiles, and a tile's epilogue runs under the next
+    // tile's MMAs (two accumulators in tensor memory).
+    const int ntn = (p.N + BN - 1) / BN, ntm = (p.T + BM - 1) / BM;
+    const long long ntiles = (long long) ntn * ntm * p.batch;
+    auto tile_of = [&](long long t, int& n0, int& m0, int& b) {
+        n0 = (int) (t % ntn) * BN;
+        m0 = (int) ((t / ntn) % ntm) * BM;
+        b = (int) (t / ((long long) ntn * ntm));
+    };
 
     if (tid == 0) {
         *abort_flag = 0;
@@ -52,11 +65,14 @@ gemm_batch_h_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             mbar_init(smem_u32(full + s), 1);
             mbar_init(smem_u32(empty + s), 1);
         }
-        mbar_init(smem_u32(acc_full), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(acc_full + s), 1);
+            mbar_init(smem_u32(acc_empty + s), 4);
+        }
         mbar_fence_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), BN);
+        tmem_alloc(smem_u32(tmem_slot), 2 * BN);
         tmem_relinquish();
     }
     fence_before_sync();
@@ -69,20 +85,30 @@ gemm_batch_h_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             tma_prefetch_desc(&tm_x);
             tma_prefetch_desc(&tm_w);
             bool ok = true;
-            for (int kt = 0; kt < nk && ok; ++kt) {
-                const int s = kt % NSTAGE;
-                if (kt >= NSTAGE) ok = mbar_wait(smem_u32(empty + s), ((uint32_t) (kt / NSTAGE) & 1) ^ 1, abort_flag, p.status, 601);
-                if (!ok) break;
-                uint8_t* a_s = smem + s * STAGE;
-                uint8_t* b_s = a_s + A_BYTES;
-                mbar_expect_tx(smem_u32(full + s), STAGE);
-                tma_load_3d(smem_u32(a_s), &tm_x, kt * BK, m0, b, smem_u32(full + s));
-                if (TRANS_W) {
-                    tma_load_3d(smem_u32(b_s), &tm_w, kt * BK, n0, b, smem_u32(full + s));
-                } else {
-                    // two chunks of 64 columns, each [64 k][64 n]
-                    tma_load_3d(smem_u32(b_s), &tm_w, n0, kt * BK, b, smem_u32(full + s));
-                    tma_load_3d(smem_u32(b_s + BK * 128), &tm_w, n0 + 64, kt * BK, b, smem_u32(full + s));
+            uint32_t it = 0;   // k-steps issued so far, over all of this CTA's tiles
+            for (long long t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+                int n0, m0, b;
+                tile_of(t, n0, m0, b);
+                // Each tile starts its walk over K at another slice and wraps around: CTAs that run in step would otherwise all
+                // ask for the same 128-byte window of every 1 KB row at the same time, and such a stride lands on a few of the
+                // memory channels only. (The order of a tile's sum moves with it; it is the same every run.)
+                const int rot = (int) (t % nk);
+                for (int k0 = 0; k0 < nk && ok; ++k0, ++it) {
+                    const int kt = k0 + rot < nk ? k0 + rot : k0 + rot - nk;
+                    const int s = (int) (it % NSTAGE);
+                    if (it >= NSTAGE) ok = mbar_wait(smem_u32(empty + s), ((it / NSTAGE) & 1) ^ 1, abort_flag, p.status, 601);
+                    if (!ok) break;
+                    uint8_t* a_s = smem + s * STAGE;
+                    uint8_t* b_s = a_s + A_BYTES;
+                    mbar_expect_tx(smem_u32(full + s), STAGE);
+                    tma_load_3d(smem_u32(a_s), &tm_x, kt * BK, m0, b, smem_u32(full + s));
+                    if (TRANS_W) {
+                        tma_load_3d(smem_u32(b_s), &tm_w, kt * BK, n0, b, smem_u32(full + s));
+                    } else {
+                        // two chunks of 64 columns, each [64 k][64 n]
+                        tma_load_3d(smem_u32(b_s), &tm_w, n0, kt * BK, b, smem_u32(full + s));
+                        tma_load_3d(smem_u32(b_s + BK * 128), &tm_w, n0 + 64, kt * BK, b, smem_u32(full + s));
+                    }
                 }
             }
         }
@@ -90,43 +116,51 @@ gemm_batch_h_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         if (elect_one()) {
             constexpr uint32_t idesc = idesc_f16(BM, BN, 0, 0, TRANS_W ? 0 : 1);
             bool ok = true;
-            for (int kt = 0; kt < nk && ok; ++kt) {
-                const int s = kt % NSTAGE;
-                ok = mbar_wait(smem_u32(full + s), (uint32_t) (kt / NSTAGE) & 1, abort_flag, p.status, 602);
+            uint32_t it = 0, tc = 0;   // k-steps and tiles so far
+            for (long long t = blockIdx.x; t < ntiles && ok; t += gridDim.x, ++tc) {
+                const int ab = (int) (tc & 1);
+                const uint32_t use = tc >> 1;   // how often this accumulator was used before
+                if (use > 0) ok = mbar_wait(smem_u32(acc_empty + ab), (use & 1) ^ 1, abort_flag, p.status, 604);
                 if (!ok) break;
                 fence_after_sync();
-                const uint32_t ab = smem_u32(smem + s * STAGE), bb = ab + A_BYTES;
+                const uint32_t d = tmem + (uint32_t) (ab * BN);
+                for (int kt = 0; kt < nk && ok; ++kt, ++it) {
+                    const int s = (int) (it % NSTAGE);
+                    ok = mbar_wait(smem_u32(full + s), (it / NSTAGE) & 1, abort_flag, p.status, 602);
+                    if (!ok) break;
+                    fence_after_sync();
+                    const uint32_t ab_s = smem_u32(smem + s * STAGE), bb = ab_s + A_BYTES;
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k) {
-                    const uint64_t ad = smem_desc_sw128(ab + k * 32, 16, 1024);
-                    const uint64_t bd = TRANS_W ? smem_desc_sw128(bb + k * 32, 16, 1024) : smem_desc_sw128(bb + k * (16 * 128), BK * 128, 1024);
-                    mma_ss(tmem, ad, bd, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = smem_desc_sw128(ab_s + k * 32, 16, 1024);
+                        const uint64_t bd = TRANS_W ? smem_desc_sw128(bb + k * 32, 16, 1024) : smem_desc_sw128(bb + k * (16 * 128), BK * 128, 1024);
+                        mma_ss(d, ad, bd, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+                    }
+                    mma_commit(smem_u32(empty + s));
                 }
-                mma_commit(smem_u32(empty + s));
+                if (ok) mma_commit(smem_u32(acc_full + ab));
             }
-            if (ok) mma_commit(smem_u32(acc_full));
         }
     } else {
         // ---- epilogue: warp w may read tensor-memory lanes 32 (w % 4) ..; a thread owns one row of the tile
         const int quarter = warp & 3;
-        const int row = m0 + quarter * 32 + lane;
+        const bool vec = (p.ldy % 4 == 0) && (p.sy % 4 == 0) && (((uintptr_t) p.y & 15) == 0);
         bool ok = true;
-        if (nk > 0) ok = mbar_wait(smem_u32(acc_full), 0, abort_flag, p.status, 603);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
+        uint32_t tc = 0;
+        for (long long t = blockIdx.x; t < ntiles && ok; t += gridDim.x, ++tc) {
+            int n0, m0, b;
+            tile_of(t, n0, m0, b);
+            const int ab = (int) (tc & 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(acc_full + ab), (tc >> 1) & 1, abort_flag, p.status, 603));
+            if (!ok) break;
             fence_after_sync();
+            const int row = m0 + quarter * 32 + lane;
             float* yr = p.y + (int64_t) b * p.sy + (int64_t) row * p.ldy;
-            const bool vec = (p.ldy % 4 == 0) && (p.sy % 4 == 0) && (((uintptr_t) p.y & 15) == 0);
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t v[32];
-                if (nk > 0) {
-                    tmem_ld32(tmem + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (c * 32), v);
-                    tmem_wait_ld();
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) v[e] = 0u;
-                }
+                tmem_ld32(tmem + ((uint32_t) (quarter * 32) << 16) + (uint32_t) (ab * BN + c * 32), v);
+                tmem_wait_ld();
                 if (row >= p.T) continue;
                 const int col0 = n0 + c * 32;
                 if (vec && col0 + 32 <= p.N) {
@@ -146,13 +180,17 @@ gemm_batch_h_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                         if (col0 + e < p.N) yr[col0 + e] = (p.accumulate ? yr[col0 + e] : 0.f) + __uint_as_float(v[e]);
                 }
             }
+            // the accumulator is read: the MMA warp may start the tile after next in it
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(acc_empty + ab));
         }
     }
     fence_before_sync();
     __syncthreads();
     if (warp == 1) {
         fence_after_sync();
-        tmem_dealloc(tmem, BN);
+        tmem_dealloc(tmem, 2 * BN);
     }
 }
 
@@ -250,15 +288,18 @@ extern "C" int ns_gemm_batch_h(ns_gpu* g, int64_t batch, int trans_w, int64_t T,
             if (make_map(&tw, w, (uint64_t) N, (uint64_t) K, (uint64_t) batch, (uint64_t) ldw * 2, swb, BK, name)) return -1;
         }
         GemmParams p;
-        p.y = y, p.ldy = ldy, p.sy = sy, p.T = (int) T, p.N = (int) N, p.K = (int) K, p.accumulate = accumulate ? 1 : 0, p.status = g->status_dev;
+        p.y = y, p.ldy = ldy, p.sy = sy, p.T = (int) T, p.N = (int) N, p.K = (int) K, p.batch = (int) batch, p.accumulate = accumulate ? 1 : 0, p.status = g->status_dev;
         static bool set[64][2] = {};
         if (!set[g->dev & 63][trans_w ? 1 : 0]) {
             if (trans_w) NS_CUDA(cudaFuncSetAttribute(gemm_batch_h_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL), name);
             else NS_CUDA(cudaFuncSetAttribute(gemm_batch_h_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL), name);
             set[g->dev & 63][trans_w ? 1 : 0] = true;
         }
-        dim3 grid((unsigned) ((N + BN - 1) / BN), (unsigned) ((T + BM - 1) / BM), (unsigned) batch);
-        if (grid.y > 65535) return ns_fail(std::string(name) + ": too many rows for one launch");
+        // Persistent CTAs, one an SM, walking the tiles through a six-stage ring. Measured at the glm5next prompt shapes (the
+        // pair of products): a CTA a tile, two an SM, three stages 43.5 us; the same persistent 40.1; one an SM with six
+        // stages 35.1 (seven: 35.8) - what counts is how many K-steps ONE pipeline has in flight, not the bytes an SM has.
+        const int64_t ntiles = ((N + BN - 1) / BN) * ((T + BM - 1) / BM) * batch;
+        const unsigned grid = (unsigned) std::min<int64_t>(ntiles, (int64_t) g->sms);
         if (trans_w) gemm_batch_h_kernel<1><<<grid, THREADS, SMEM_TOTAL, g->compute>>>(tx, tw, p);
         else gemm_batch_h_kernel<0><<<grid, THREADS, SMEM_TOTAL, g->compute>>>(tx, tw, p);
         return ns_launched(name);
