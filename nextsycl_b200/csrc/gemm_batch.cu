@@ -297,7 +297,7 @@ extern "C" int ns_gemm_batch_h(ns_gpu* g, int64_t batch, int trans_w, int64_t T,
         }
         // Persistent CTAs, one an SM, walking the tiles through a six-stage ring. Measured at the glm5next prompt shapes (the
         // pair of products): a CTA a tile, two an SM, three stages 43.5 us; the same persistent 40.1; one an SM with six
-        // stages 35.1 (seven: 35.8) - what counts is how many K-steps ONE pipeline has in flight, not the bytes an SM has.
+        // stages 35.1 (seven: 35.8) - one deep pipeline an SM beats two shallow ones holding the same bytes in flight.
         const int64_t ntiles = ((N + BN - 1) / BN) * ((T + BM - 1) / BM) * batch;
         const unsigned grid = (unsigned) std::min<int64_t>(ntiles, (int64_t) g->sms);
         if (trans_w) gemm_batch_h_kernel<1><<<grid, THREADS, SMEM_TOTAL, g->compute>>>(tx, tw, p);
