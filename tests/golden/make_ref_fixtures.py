@@ -13,7 +13,7 @@ module-level functions it calls. Nothing is retyped: every expected value in the
 the reference's code. tests/test_oracle.py holds the oracle to these fixtures.
 
 Run where the reference checkout is available (not on the GPU machines):
-    python tests/golden/make_ref_fixtures.py [/path/to/reference]
+    python tests/golden/make_ref_fixtures.py /path/to/the/nextsycl/checkout
 """
 import os
 import sys
@@ -22,7 +22,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) != 2:
+    raise SystemExit("usage: python tests/golden/make_ref_fixtures.py /path/to/the/nextsycl/checkout")
+REF = sys.argv[1]
 sys.path.insert(0, os.path.join(REF, "reference", "deepseek41"))
 os.environ.setdefault("NS_REF_THREADS", "4")
 import ds41ref as R  # noqa: E402
