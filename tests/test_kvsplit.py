@@ -256,3 +256,13 @@ def test_mla_cell_ranges_on_one_gpu_match_the_oracle(gpu, ops, nranks, T, H, n):
             got = out.read(np.float32).reshape(T, H, 512)
             d = np.abs(got - want)
             assert np.isfinite(got).all() and np.all(d <= 2e-3 + 1e-2 * np.abs(want)), (step, r, float(d.max()))
+
+
+@pytest.mark.gpu
+def test_the_one_kernel_step_refuses_a_step_number_whose_tag_is_zero(gpu, ops):
+    from nextsycl_b200 import DevBuf
+    api = gpu.api
+    d = DevBuf(gpu, 1 << 20)
+    rc = api.ns_b200_kvsplit_step(gpu.raw, d.ptr, 128, d.ptr, d.ptr, 1, 1, 1, 128, 64, 0, 63, d.ptr, 0, 1, d.ptr, d.ptr, 1 << 32, 1000, d.ptr)
+    assert rc == -1 and "low 32 bits" in api.last_error()
+    gpu.sync()
