@@ -10,6 +10,12 @@
 // loads; 256 B a key row, XOR-swizzled in shared memory), compute S = Q K^T and O += P V on mma.sync m16n8k16 (the
 // rows are too few for a tcgen05 tile; the kernel is HBM-bound), keep their own online softmax (quad shuffles for
 // the row max and sum) and merge once at the end through shared memory. No block-wide barrier in the key loop.
+//
+// The same file holds what follows the split kernel: the merge of a row's splits (a programmatic dependent that starts on a
+// key head as soon as that head's split CTAs have counted themselves in), and, for one context split over several GPUs by
+// key ranges, the exchange of the ranks' partials over NVLink - as a merge-push kernel plus a combine kernel, as a
+// merge that leaves the partial for a caller-run all-gather, or (FUSED) as the split kernel's own tail, the whole step
+// one launch.
 #include "kernels.cuh"
 #include "lse_merge.cuh"
 
