@@ -96,6 +96,46 @@ def test_native_16bit_entry(gpu, ops, dtype):
         assert_close(got, ex, "vs fp64", abs_tol=2e-2)
 
 
+STREAMED = [
+    # T, Hq, Hkv, p0, dtype: more (row block, head) items than SMs and at most eight times as many, one chunk of heads -
+    # the shapes the streaming kernel takes (a CTA an SM, each working through several items)
+    (700, 40, 8, 0, 0),       # 240 items of 1..6 tiles, a ragged last row block
+    (300, 64, 64, 900, 0),    # 192 items of 8..10 tiles: a prompt continued far into the cache, no head sharing
+    (129, 96, 8, 0, 0),       # 192 items of one or two tiles, the second row block a single row
+    (520, 32, 4, 5, 1),       # bf16, 160 items
+    (1100, 24, 2, 0, 0),      # 216 items, 12 query heads a key head
+]
+
+
+@pytest.mark.parametrize("T,Hq,Hkv,p0,dtype", STREAMED)
+def test_streamed_items(gpu, ops, T, Hq, Hkv, p0, dtype):
+    D = 128
+    kv = p0 + T
+    if dtype == 0:
+        qb = W.normal_f16(934, 0, (T, Hq * D)).view(np.uint16)
+        kb = W.normal_f16(934, 1, (Hkv, kv, D)).view(np.uint16)
+        vb = W.normal_f16(934, 2, (Hkv, kv, D)).view(np.uint16)
+        qf = qb.view(np.float16).astype(np.float32)
+    else:
+        qb = W.normal_bf16_bits(934, 0, (T, Hq * D))
+        kb = W.normal_bf16_bits(934, 1, (Hkv, kv, D))
+        vb = W.normal_bf16_bits(934, 2, (Hkv, kv, D))
+        qf = O.from_bf16_bits(qb)
+    dq, dk, dv = DevBuf.of(gpu, qb), DevBuf.of(gpu, kb), DevBuf.of(gpu, vb)
+    out = DevBuf(gpu, T * Hq * D * 2)
+    out.fill(0xFF)
+    sc = 1 / np.sqrt(D)
+    tc = O.attn_tc(qf, kb, vb, T, Hq, Hkv, D, D, kv, p0, np.float32(sc), kind=dtype)
+    ex = O.attn_exact(qf, kb, vb, T, Hq, Hkv, D, D, kv, p0, sc, kind=dtype)
+    for again in range(2):   # twice: the second call finds the caches warm and the CTAs' pace different
+        ops.gqa_prefill(dtype, dq, Hq * D, dk, dv, T, Hq, Hkv, D, kv, p0, out)
+        gpu.sync()
+        raw = out.read(np.uint16).reshape(T, Hq * D)
+        got = raw.view(np.float16).astype(np.float32) if dtype == 0 else O.from_bf16_bits(raw)
+        assert_close(got, tc, "vs tensor-core numerics", abs_tol=ABS if dtype == 0 else 4e-3)
+        assert_close(got, ex, "vs fp64", abs_tol=ABS if dtype == 0 else 2e-2)
+
+
 def test_rows_entry_routes_long_passes_to_the_prompt_kernel(gpu, ops):
     T, Hq, Hkv, D, p0 = 40, 8, 2, 128, 10
     q, k, v, cap = prefill_case(932, T, Hq, Hkv, D, p0)
