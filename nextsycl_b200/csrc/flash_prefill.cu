@@ -18,6 +18,9 @@
 // anything inside the loop and two warps a scheduler share the exponentials; the epilogue adds the two accumulators
 // under a common maximum. (The 256-wide instance keeps one group: two accumulators of 256 columns do not fit.)
 // Every mbarrier wait is bounded; on a timeout the CTA records a status code and runs to its teardown.
+// The file holds two kernels of the same arithmetic: flash_prefill_kernel, a CTA a (row block, head) item, and, for the
+// 128-wide heads, flash_prefill_stream_kernel, a CTA an SM that works through several items as one stream of key tiles (taken
+// for prompts of a few rounds of items; see the launch function).
 #include "kernels.cuh"
 #include "tc05.cuh"
 
