@@ -58,8 +58,6 @@ struct Smem {
     static constexpr int TOTAL = 1024 /* alignment slack */ + Q_BYTES + NSTAGE * STAGE + BARS;
 };
 
-__device__ __forceinline__ void named_bar_sync(int id, int threads) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory"); }
-
 template <int DQK, int DV, int BN, int NSTAGE, int BF16, int NG>
 __global__ void __launch_bounds__(SOFTMAX_THREADS * (NG + 1), 1)
 flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,

@@ -179,6 +179,9 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
 
+// a barrier among `threads` threads of the CTA (whole warps); id 0 is __syncthreads's
+__device__ __forceinline__ void named_bar_sync(int id, int threads) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory"); }
+
 // ---- a pair of CTAs (a cluster of two) on one MMA: cta_group::2 ------------------------------------------------------
 // The CTA of even rank (the leader) issues the MMAs; an M = 128 product gives each CTA 64 rows of D, A comes from each
 // CTA's own shared memory (its 64 rows), B from both (each holds half of N), all at the same offsets in both CTAs.
@@ -199,7 +202,7 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
 }
 // one arrival on a barrier of any CTA of the cluster (address from cluster_map)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
 }
 // writes this thread made to shared memory become visible to the tensor core and TMA (the async proxy)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
