@@ -5,13 +5,13 @@
 // latent cache [n][576] fp16 (512 latent + 64 rotated), score = (q . c) * scale with q rounded to fp16, softmax over the
 // row's cells 0 .. pos0+t, u = sum_p p * c[:512] with p rounded to fp16, fp32 sums.
 //
-// How: the 128 heads of a row are the M = 128 rows of a tcgen05 tile, so every cell is read once for all heads. The
-// output tile [128 x 512] fp32 alone would fill tensor memory (512 columns), so a CTA owns one half of the 512 latent
-// output columns: grid = (2 x key splits, head tiles, rows). Tensor memory per CTA: O half (256 columns), two S
-// buffers of 64 columns (P overlays its S), and the first 256 features of Q as a tensor-memory A operand (128
-// columns); the other 320 features of Q sit in shared memory (80 KB) beside a two-stage ring of 64-cell tiles
-// (72 KB each). One TMA-staged cell tile serves both products: K-major for S = Q C^T (all 576 features) and MN-major
-// for O += P C[:, half] (its 256 columns). Splits are merged by a second kernel (log-sum-exp combine).
+// How: the 128 heads of a row are the M = 128 rows of a tcgen05 tile, so every cell is read once for all heads, and the
+// tile is worked on by a PAIR of SMs: the two CTAs of a key split are a cluster of two and share one MMA
+// (tcgen05.mma.cta_group::2), each holding 64 of the heads. Grid = (2 x key splits, head tiles, rows). Per CTA: its 64 heads
+// of Q in shared memory (72 KB), its heads' whole 512-wide output rows in tensor memory (256 columns in the pair's
+// accumulator layout) beside two S buffers, a ring of key slots (its 32 cells of a 64-cell tile, every feature, K-major:
+// the pair's halves are the columns of S = Q C^T) and a ring of value slots (every cell, its 256 of the 512 latent
+// features, MN-major, for O += P C), P through shared memory. Splits are merged by a second kernel (log-sum-exp combine).
 // Every mbarrier wait is bounded; a wait that gives up records a status code and the CTA runs to its teardown.
 #include "kernels.cuh"
 #include "tc05.cuh"
@@ -25,9 +25,7 @@ using namespace tc05;
 constexpr int L = 512;                         // latent width; a cache row is CR = 512 + rotated part (64 or 0)
 constexpr int BM = 128;                        // heads a tile
 constexpr int BN = 64;                         // cells a tile
-constexpr int NSTAGE = 2;
-constexpr int QT = 256;                        // features of Q kept in tensor memory
-constexpr int DVH = 256;                       // output columns a CTA
+constexpr int DVH = 256;                       // output columns a merge block takes
 constexpr int THREADS = 192;
 constexpr int PS = 516;                        // floats a partial row: O[512], m, l, 2 pad
 constexpr float RESCALE_LOG2 = 8.0f;
@@ -37,15 +35,6 @@ constexpr float RESCALE_LOG2 = 8.0f;
 // once this grid has completed and its partials are visible.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
-
-constexpr int O_COL = 0, Q_COL = 256, S_COL = 384;   // tensor-memory columns; S buffers at 384 and 448
-template <int CR>
-struct Geo {
-    static constexpr int QS = CR - QT;                       // features of Q kept in shared memory (320 or 256)
-    static constexpr int TILE_BYTES = BN * CR * 2;           // 73,728 or 65,536
-    static constexpr int QS_BYTES = BM * QS * 2;             // 81,920 or 65,536
-    static constexpr int SMEM_TOTAL = 1024 + QS_BYTES + NSTAGE * TILE_BYTES + 512;
-};
 
 // Cells a key split for a row that sees n cells, when `units` (head tiles x rows sharing the launch) such rows are to fill
 // `sms` SMs once with pairs of CTAs: whole tiles, at least two of them (a partial costs 2 KB a head).
@@ -88,381 +77,10 @@ __device__ __forceinline__ int64_t row_cells(const Params& p, int t) {
     return n > 0 ? n : 0;
 }
 
-template <int CR>
-__global__ void __launch_bounds__(THREADS, 1)
-mla_decode_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_c, const Params p) {
-    constexpr int QS = Geo<CR>::QS, TILE_BYTES = Geo<CR>::TILE_BYTES, QS_BYTES = Geo<CR>::QS_BYTES;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*) (((uintptr_t) smem_raw + 1023) & ~(uintptr_t) 1023);
-    uint8_t* q_s = smem;                       // 5 chunks of [128 heads][64 features]
-    uint8_t* c_s = smem + QS_BYTES;            // stages of 9 chunks of [64 cells][64 features]
-    uint64_t* bars = (uint64_t*) (c_s + NSTAGE * TILE_BYTES);
-    uint64_t* q_full = bars + 0;               // Q's shared-memory part landed
-    uint64_t* qt_full = bars + 1;              // Q's tensor-memory part written (128 arrivals)
-    uint64_t* c_full = bars + 2;               // [NSTAGE] the tile's late chunks landed: the four this CTA's P V reads
-    uint64_t* c_empty = c_full + NSTAGE;       // [NSTAGE] (both products of the tile done: the late chunks are free)
-    uint64_t* e_full = c_empty + NSTAGE;       // [NSTAGE] the tile's early chunks landed: the ones only S reads
-    uint64_t* k_free = e_full + NSTAGE;        // [NSTAGE] S is through with the early chunks
-    uint64_t* s_full = k_free + NSTAGE;        // [2]
-    uint64_t* p_full = s_full + 2;             // [2]
-    uint64_t* pv_done = p_full + 2;            // [1]
-    uint64_t* o_final = pv_done + 1;              // [1] the last P V done
-    uint32_t* tmem_slot = (uint32_t*) (o_final + 1);
-    volatile int* abort_flag = (volatile int*) (tmem_slot + 1);
-
-    const int tid = threadIdx.x, warp = tid >> 5;
-    const int hv = blockIdx.x & 1, split = blockIdx.x >> 1;
-    const int h0 = blockIdx.y * BM, t = blockIdx.z;
-    const int64_t n = row_cells(p, t);                                      // cells this row sees
-    const int64_t kb = p.per_row ? mla_split(n, p.units, p.sms) : p.kb;
-    const int64_t jbeg = (int64_t) split * kb, jend = min(n, (int64_t) (split + 1) * kb);
-    const int ntiles = jbeg < jend ? (int) ((jend - jbeg + BN - 1) / BN) : 0;
-    if (ntiles == 0) return;                                // the whole CTA: this split holds none of the row's cells
-
-    if (tid == 0) {
-        *abort_flag = 0;
-        mbar_init(smem_u32(q_full), 1);
-        mbar_init(smem_u32(qt_full), 128);
-        for (int s = 0; s < NSTAGE; ++s) {
-            mbar_init(smem_u32(c_full + s), 1);
-            mbar_init(smem_u32(c_empty + s), 1);
-            mbar_init(smem_u32(e_full + s), 1);
-            mbar_init(smem_u32(k_free + s), 1);
-        }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(smem_u32(s_full + s), 1);
-            mbar_init(smem_u32(p_full + s), 128);
-        }
-        mbar_init(smem_u32(pv_done), 1);
-        mbar_init(smem_u32(o_final), 1);
-        mbar_fence_init();
-    }
-    if (warp == 5) {
-        tmem_alloc(smem_u32(tmem_slot), 512);
-        tmem_relinquish();
-    }
-    fence_before_sync();
-    __syncthreads();
-    fence_after_sync();
-    const uint32_t tmem = *tmem_slot;
-    pdl_launch_dependents();
-
-    if (warp == 4) {
-        // ================= TMA producer =================
-        if (elect_one()) {
-            tma_prefetch_desc(&tm_q);
-            tma_prefetch_desc(&tm_c);
-            mbar_expect_tx(smem_u32(q_full), QS_BYTES);
-            // every CTA of the grid reads the same Q: each starts at another chunk, so that at any instant the requests spread
-            // over more L2 lines than one chunk's
-            // Q's shared-memory part: the chunks that meet the tile's early chunks (slot e: chunk 4 + e for the CTA of output
-            // half 0, chunks 0..3 and then the ninth for half 1); the four that meet the late chunks go to tensor memory
-            for (int cc = 0; cc < QS / 64; ++cc) {
-                const int e = (cc + split) % (QS / 64);
-                const int chunk = hv == 0 ? 4 + e : (e < 4 ? e : 8);
-                tma_load_3d(smem_u32(q_s + e * (BM * 128)), &tm_q, chunk * 64, h0, t, smem_u32(q_full));
-            }
-            bool ok = true;
-            // A stage is refilled in two parts. The chunks only S reads (the other half's four and, with 576-wide rows,
-            // the ninth) are free as soon as S(j-2) is done, long before P(j-2) V(j-2) frees the four this CTA's P V
-            // reads; S(j) starts on them while the late four are still on their way.
-            constexpr int NCH = CR / 64, NLATE = DVH / 64, NEARLY = NCH - NLATE;
-            auto chunk_load = [&](int j, int c, uint64_t* bar) {
-                tma_load_3d(smem_u32(c_s + (j % NSTAGE) * TILE_BYTES + c * (BN * 128)), &tm_c, c * 64, (int) (jbeg + (int64_t) j * BN), t * p.zmul, smem_u32(bar));
-            };
-            auto load_early = [&](int j) {
-                const int s = j % NSTAGE;
-                if (j >= NSTAGE) ok = mbar_wait(smem_u32(k_free + s), ((uint32_t) (j / NSTAGE) & 1) ^ 1, abort_flag, p.status, 402);
-                if (!ok) return;
-                mbar_expect_tx(smem_u32(e_full + s), NEARLY * BN * 128);
-                for (int c = 0; c < NCH; ++c)
-                    if (c / NLATE != hv) chunk_load(j, c, e_full + s);
-            };
-            auto load_late = [&](int j) {
-                const int s = j % NSTAGE;
-                if (j >= NSTAGE) ok = mbar_wait(smem_u32(c_empty + s), ((uint32_t) (j / NSTAGE) & 1) ^ 1, abort_flag, p.status, 401);
-                if (!ok) return;
-                mbar_expect_tx(smem_u32(c_full + s), NLATE * BN * 128);
-                for (int c = hv * NLATE; c < (hv + 1) * NLATE; ++c) chunk_load(j, c, c_full + s);
-            };
-            load_early(0);
-            for (int j = 0; j < ntiles && ok; ++j) {
-                if (j + 1 < ntiles) load_early(j + 1);   // S(j-1) is done before P(j-2) V(j-2) is
-                if (ok) load_late(j);
-            }
-        }
-    } else if (warp == 5) {
-        // ================= MMA issuer =================
-        if (elect_one()) {
-            constexpr uint32_t idesc_qk = idesc_f16(BM, BN, 0, 0, 0);
-            constexpr uint32_t idesc_pv = idesc_f16(BM, DVH, 0, 0, 1);
-            bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag, p.status, 501);
-            if (ok) ok = mbar_wait(smem_u32(qt_full), 0, abort_flag, p.status, 502);
-            // descriptors: everything but the start address is fixed, and the address field (bits 0..13, in 16-byte units)
-            // cannot carry into the next field for any shared-memory address, so a step is one 32-bit add
-            const uint64_t q_desc0 = smem_desc_sw128(smem_u32(q_s), 16, 1024);
-            // S(j) in two parts: over the early chunks when they have landed, over the late four when those have
-            // k-step k = 4 chunk + step. Q's operand: tensor memory for the four late chunks (the part of S that the
-            // softmax waits for runs at the faster rate), shared memory for the early ones
-            auto qk_step = [&](uint64_t c_desc0, uint32_t d, int k, uint32_t acc, int half) {
-                const int chunk = k / 4, step = k % 4;
-                const uint64_t bd = c_desc0 + (uint64_t) ((chunk * (BN * 128) + step * 32) >> 4);
-                if (chunk < 8 && chunk / 4 == half) {
-                    mma_ts(d, tmem + (uint32_t) (Q_COL + ((chunk - 4 * half) * 4 + step) * 8), bd, idesc_qk, acc);
-                } else {
-                    const int e = half == 0 ? chunk - 4 : (chunk < 4 ? chunk : 4);
-                    mma_ss(d, q_desc0 + (uint64_t) ((e * (BM * 128) + step * 32) >> 4), bd, idesc_qk, acc);
-                }
-            };
-            constexpr int KLATE = DVH / 16;   // k-steps over the late chunks: 16
-            auto issue_qk_early = [&](int j) {
-                const uint64_t c_desc0 = smem_desc_sw128(smem_u32(c_s + (j % NSTAGE) * TILE_BYTES), 16, 1024);
-                const uint32_t d = tmem + (uint32_t) (S_COL + (j & 1) * BN);
-                if (hv == 0) {
-#pragma unroll
-                    for (int k = KLATE; k < CR / 16; ++k) qk_step(c_desc0, d, k, k > KLATE, 0);
-                } else {
-#pragma unroll
-                    for (int k = 0; k < CR / 16; ++k)
-                        if (k < KLATE || k >= 2 * KLATE) qk_step(c_desc0, d, k, k > 0, 1);
-                }
-                mma_commit(smem_u32(k_free + j % NSTAGE));
-            };
-            auto issue_qk_late = [&](int j) {
-                const uint64_t c_desc0 = smem_desc_sw128(smem_u32(c_s + (j % NSTAGE) * TILE_BYTES), 16, 1024);
-                const uint32_t d = tmem + (uint32_t) (S_COL + (j & 1) * BN);
-                if (hv == 0) {
-#pragma unroll
-                    for (int k = 0; k < KLATE; ++k) qk_step(c_desc0, d, k, 1, 0);
-                } else {
-#pragma unroll
-                    for (int k = KLATE; k < 2 * KLATE; ++k) qk_step(c_desc0, d, k, 1, 1);
-                }
-                mma_commit(smem_u32(s_full + (j & 1)));
-            };
-            auto issue_pv = [&](int j) {
-                const int s = j % NSTAGE;
-                // the value operand: this CTA's 4 chunks of the same tile, MN-major; 16 cells a step
-                const uint64_t v_desc0 = smem_desc_sw128(smem_u32(c_s + s * TILE_BYTES) + (uint32_t) (hv * (DVH / 64) * (BN * 128)), BN * 128, 1024);
-                const uint32_t pa = tmem + (uint32_t) (S_COL + (j & 1) * BN);
-#pragma unroll
-                for (int k = 0; k < BN / 16; ++k)
-                    mma_ts(tmem + (uint32_t) O_COL, pa + (uint32_t) (k * 8), v_desc0 + (uint64_t) ((k * (16 * 128)) >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-                mma_commit(smem_u32(c_empty + s));
-                mma_commit(smem_u32(pv_done));
-                if (j == ntiles - 1) mma_commit(smem_u32(o_final));
-            };
-            // The two products are issued in whatever order their inputs arrive: S(qk) as soon as its tile has landed
-            // (and the S buffer it overwrites has been consumed: P(qk-2) V(qk-2) issued), P(pv) V(pv) as soon as the
-            // softmax published P(pv). A fixed order would queue P(j) V(j) - which frees tile j's stage for the next
-            // load - behind S(j+1), which waits for a load that was itself waiting for a stage.
-            int qk = 0, qe = 0, pv = 0;   // next tile for S's late part, for S's early part, for P V
-            uint32_t idle = 0;
-            while (ok && pv < ntiles) {
-                bool did = false;
-                // P V first: it is short, and it frees a tile stage for the next load
-                if (pv < qk && mbar_try(smem_u32(p_full + (pv & 1)), (uint32_t) (pv >> 1) & 1)) {
-                    fence_after_sync();
-                    issue_pv(pv);
-                    ++pv;
-                    did = true;
-                }
-                if (qe < ntiles && qe - pv < 2 && mbar_try(smem_u32(e_full + qe % NSTAGE), (uint32_t) (qe / NSTAGE) & 1)) {
-                    fence_after_sync();
-                    issue_qk_early(qe);
-                    ++qe;
-                    did = true;
-                }
-                if (qk < qe && mbar_try(smem_u32(c_full + qk % NSTAGE), (uint32_t) (qk / NSTAGE) & 1)) {
-                    fence_after_sync();
-                    issue_qk_late(qk);
-                    ++qk;
-                    did = true;
-                }
-                if (did) {
-                    idle = 0;
-                    continue;
-                }
-                __nanosleep(40);   // an idle poll must not take issue slots from the softmax warps on this scheduler
-                if (*abort_flag || ++idle > WAIT_LIMIT) {
-                    if (!*abort_flag) {
-                        *abort_flag = 1;
-                        if (p.status) {
-                            *(volatile int*) p.status = 504;
-                            __threadfence_system();
-                        }
-                    }
-                    ok = false;
-                }
-            }
-        }
-    } else {
-        // ================= softmax: thread r owns head h0 + r =================
-        const int r = tid;
-        const uint32_t lane_base = (uint32_t) (warp * 32) << 16;
-        const bool head_live = h0 + r < p.H;
-        // ---- the 256 features of this head's query that meet the tile's late chunks (features 256 hv .. 256 hv + 255) into
-        // tensor memory: column i = features (256 hv + 2i, + 1)
-        {
-            const uint4* src = reinterpret_cast<const uint4*>(p.q + ((int64_t) t * p.H + (head_live ? h0 + r : 0)) * CR);
-#pragma unroll
-            for (int cc = 0; cc < QT / 64; ++cc) {
-                const int c = (cc + split) & (QT / 64 - 1);   // as above: the CTAs start at different chunks
-                uint32_t w[32];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const uint4 x = head_live ? src[(hv * (QT / 64) + c) * 8 + e] : make_uint4(0, 0, 0, 0);
-                    w[4 * e] = x.x, w[4 * e + 1] = x.y, w[4 * e + 2] = x.z, w[4 * e + 3] = x.w;
-                }
-                tmem_st32(tmem + lane_base + (uint32_t) (Q_COL + c * 32), w);
-            }
-            tmem_wait_st();
-            fence_before_sync();
-            mbar_arrive(smem_u32(qt_full));
-        }
-        float m_ref = -INFINITY, l = 0.f;
-        bool ok = true;
-        for (int j = 0; j < ntiles; ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(s_full + (j & 1)), (uint32_t) (j >> 1) & 1, abort_flag, p.status, 601));
-            if (!ok) break;
-            fence_after_sync();
-            const uint32_t s_addr = tmem + lane_base + (uint32_t) (S_COL + (j & 1) * BN);
-            float s[BN];
-            {
-                // both halves of the row requested before the one wait
-                uint32_t v0[32], v1[32];
-                tmem_ld32(s_addr, v0);
-                tmem_ld32(s_addr + 32, v1);
-                tmem_wait_ld();
-#pragma unroll
-                for (int e = 0; e < 32; ++e) s[e] = __uint_as_float(v0[e]), s[32 + e] = __uint_as_float(v1[e]);
-            }
-            const int64_t c0 = jbeg + (int64_t) j * BN;
-            if (c0 + BN > jend) {
-#pragma unroll
-                for (int e = 0; e < BN; ++e)
-                    if (c0 + e >= jend) s[e] = -INFINITY;
-            }
-            float mx = -INFINITY;
-#pragma unroll
-            for (int e = 0; e < BN; ++e) mx = fmaxf(mx, s[e]);
-            mx *= p.scale_log2;
-            float corr = 1.0f;
-            bool need = false;
-            if (j == 0) {
-                m_ref = mx;
-            } else if (mx > m_ref + RESCALE_LOG2) {
-                corr = ex2(m_ref - mx);
-                m_ref = mx;
-                need = true;
-            }
-            if (__any_sync(0xffffffffu, need)) {
-                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(pv_done), (uint32_t) (j - 1) & 1, abort_flag, p.status, 602));
-                if (!ok) break;
-                fence_after_sync();
-#pragma unroll
-                for (int c = 0; c < DVH / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem + lane_base + (uint32_t) (O_COL + c * 32), v);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * corr);
-                    tmem_st32(tmem + lane_base + (uint32_t) (O_COL + c * 32), v);
-                }
-                tmem_wait_st();
-                l *= corr;
-            }
-            const float neg_m = -m_ref;   // finite: the first cell of the first tile is always inside the split
-            float sum = 0.f;
-#pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t w[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const float a = ex2(fmaf(s[c * 32 + 2 * e], p.scale_log2, neg_m));
-                    const float b = ex2(fmaf(s[c * 32 + 2 * e + 1], p.scale_log2, neg_m));
-                    sum += a + b;
-                    __half2 hh = __floats2half2_rn(a, b);
-                    w[e] = *reinterpret_cast<uint32_t*>(&hh);
-                }
-                tmem_st16(s_addr + c * 16, w);
-            }
-            l += sum;
-            tmem_wait_st();
-            fence_before_sync();
-            mbar_arrive(smem_u32(p_full + (j & 1)));
-        }
-        // ---- epilogue: this half of O, and (from the half-0 CTA) the row's m and l
-        // (pv_done cannot serve here: a parity wait only tells the current phase from the one before it, and this thread
-        // has not followed its phases; o_final completes exactly once, after the last product)
-        if (ok) ok = mbar_wait(smem_u32(o_final), 0, abort_flag, p.status, 603);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-            fence_after_sync();
-            const int64_t row = (int64_t) t * p.H + h0 + r;
-            const bool direct = n <= kb && !p.mailboxes;   // the row's only split: normalised and written as the result
-            float inv = 1.0f;
-            if (direct) {
-                // with a sink s: out = O 2^(m - mx) / (l 2^(m - mx) + 2^(s - mx)), mx = max(m, s) (kernels/llm/deepseek41/silo/attn.cpp:266-285)
-                float f = 1.0f, den = l;
-                if (p.sinks && head_live) {
-                    const float sk = p.sinks[h0 + r] * 1.4426950408889634f, mx = fmaxf(m_ref, sk);
-                    f = ex2(m_ref - mx);
-                    den = l * f + ex2(sk - mx);
-                }
-                inv = den > 0.f ? f / den : 0.f;
-            }
-            // A thread holds one row of O; written as it lies, a warp's store would touch 32 rows. Each block of 64
-            // columns goes through a padded [32][68] tile in shared memory (the tile stages are idle by now), so that a
-            // warp instruction writes 256 contiguous bytes of each of two rows, 16 bytes a lane.
-            float* tile = reinterpret_cast<float*>(c_s) + warp * (32 * 68);
-            const int lane = tid & 31, half = lane >> 4, l16 = lane & 15;
-            const int64_t row_w = (int64_t) t * p.H + h0 + warp * 32;   // the warp's first row
-            const int rows_w = max(0, min(32, p.H - (h0 + warp * 32)));
-            float* dst0 = direct ? p.out + row_w * L + hv * DVH : p.part + (row_w * p.ns + split) * PS + hv * DVH;
-            const int64_t dst_row = direct ? L : (int64_t) p.ns * PS;
-#pragma unroll 1
-            for (int c = 0; c < DVH / 64; ++c) {
-                uint32_t v0[32], v1[32];
-                tmem_ld32(tmem + lane_base + (uint32_t) (O_COL + c * 64), v0);
-                tmem_ld32(tmem + lane_base + (uint32_t) (O_COL + c * 64 + 32), v1);
-                tmem_wait_ld();
-                float4* trow = reinterpret_cast<float4*>(tile + lane * 68);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    trow[e] = make_float4(__uint_as_float(v0[4 * e]) * inv, __uint_as_float(v0[4 * e + 1]) * inv, __uint_as_float(v0[4 * e + 2]) * inv,
-                                          __uint_as_float(v0[4 * e + 3]) * inv);
-                    trow[8 + e] = make_float4(__uint_as_float(v1[4 * e]) * inv, __uint_as_float(v1[4 * e + 1]) * inv, __uint_as_float(v1[4 * e + 2]) * inv,
-                                              __uint_as_float(v1[4 * e + 3]) * inv);
-                }
-                __syncwarp();
-#pragma unroll
-                for (int rr = 0; rr < 32; rr += 2) {
-                    const int ri = rr + half;
-                    if (ri < rows_w)
-                        *reinterpret_cast<float4*>(dst0 + ri * dst_row + c * 64 + l16 * 4) = *reinterpret_cast<const float4*>(tile + ri * 68 + l16 * 4);
-                }
-                __syncwarp();
-            }
-            if (head_live && !direct && hv == 0) {
-                float* st = p.part + (row * p.ns + split) * PS + L;
-                st[0] = m_ref;
-                st[1] = l;
-            }
-        }
-    }
-    fence_before_sync();
-    __syncthreads();
-    if (warp == 5) {
-        fence_after_sync();
-        tmem_dealloc(tmem, 512);
-    }
-}
-
-// ---- the same on a pair of SMs ----------------------------------------------------------------------------------------
+// ---- the kernel ----------------------------------------------------------------------------------------------------------
 // mla_decode_pair_kernel: the two CTAs of a key split are a cluster and share ONE MMA (tcgen05.mma.cta_group::2, M = 128):
-// each CTA holds 64 of the tile's 128 heads, S is computed once for the pair (above, both CTAs compute all of it), each CTA
-// keeps its heads' whole 512-wide output row in tensor memory and reads only its own 64 rows of Q. What a CTA stages of a
+// each CTA holds 64 of the tile's 128 heads, S is computed once for the pair, each CTA keeps its heads' whole 512-wide
+// output row in tensor memory and reads only its own 64 rows of Q. What a CTA stages of a
 // 64-cell tile: for S its 32 cells with all features (K-major; the pair's two halves are the 64 columns of S), for O all 64
 // cells with its 256 of the 512 latent features (MN-major; rank 0 features 0-127 and 256-383, rank 1 the others: the two
 // N = 256 products take half of their columns from each CTA) - 68 KB against the 72 KB of a whole tile. A pair's accumulator
@@ -655,7 +273,8 @@ mla_decode_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 commit_both(p_free + (j & 1));
                 if (j == ntiles - 1) commit_both(o_final);
             };
-            // whichever product has its inputs goes next, P V first (it is what the softmax and the value ring wait for)
+            // The two products are issued in whatever order their inputs arrive, P V first (it is short, and it is what the
+            // softmax's next P buffer and the value ring wait for). A fixed order would queue it behind an S that waits for a load.
             int qk = 0, pv = 0;
             bool v_ready = false;      // value slot of tile pv seen full (a barrier's phase is tested once it can be the wanted one)
             uint32_t idle = 0;
@@ -701,6 +320,8 @@ mla_decode_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         volatile int* bad = abort_flag + 1;     // [3]: tiles of either parity, the epilogue
         bool ok = true, left = false;
         for (int j = 0; j < ntiles; ++j) {
+            // this tile's P buffer was last read by P(j-2) V(j-2): waited for here, where the thread waits for S anyway
+            if (j >= 2) ok = ok && mbar_wait(smem_u32(p_free + (j & 1)), ((uint32_t) (j >> 1) & 1) ^ 1, abort_flag, p.status, 604);
             ok = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(s_full + (j & 1)), (uint32_t) (j >> 1) & 1, abort_flag, p.status, 601));
             float s[32];
             float mx = -INFINITY;
@@ -764,8 +385,6 @@ mla_decode_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 }
                 l *= corr;
             }
-            // this tile's P buffer was last read by P(j-2) V(j-2)
-            if (j >= 2) ok = __all_sync(0xffffffffu, ok && mbar_wait(smem_u32(p_free + (j & 1)), ((uint32_t) (j >> 1) & 1) ^ 1, abort_flag, p.status, 604));
             const float neg_m = -m_ref;   // finite: the first cell of the first tile is always inside the split
             float sum = 0.f;
             // P as a K-major operand tile: head `row` is row `row` of 128 bytes, its 16-byte chunks swizzled by the row
@@ -810,8 +429,9 @@ mla_decode_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 }
                 inv = den > 0.f ? f / den : 0.f;
             }
-            // as above: 64 columns at a time through a padded [32][68] tile of the (idle) rings, so that a warp instruction
-            // writes 256 contiguous bytes of each of two rows
+            // A thread holds one row of O; written as it lies, a warp's store would touch 32 rows. Each block of 64 columns
+            // goes through a padded [32][68] tile in shared memory (the rings are idle by now), so that a warp instruction
+            // writes 256 contiguous bytes of each of two rows, 16 bytes a lane.
             float* tile = reinterpret_cast<float*>(k_s) + warp * (32 * 68);
             const int lane = tid & 31, half = lane >> 4, l16 = lane & 15;
             const int head_w = h0 + 64 * (int) rank + (warp & 1) * 32;     // the warp's first head

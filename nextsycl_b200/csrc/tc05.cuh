@@ -231,6 +231,18 @@ __device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, ui
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// the same with A in tensor memory: each CTA's 64 rows, K-major, 16-bit elements two a column, held twice - lanes 0..63 and
+// again lanes 64..127 (the pair's operand form)
+__device__ __forceinline__ void mma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // one arrival on the barrier at `cluster_addr` (a cluster_map address: either CTA's) when every MMA of the pair that this
 // thread issued before has completed
 __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
