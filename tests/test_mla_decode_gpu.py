@@ -70,8 +70,9 @@ def test_ds2_whole_decode(gpu, ops):
 @pytest.mark.parametrize("n", [32768, 131072])
 def test_config_3_full_size(gpu, ops, n):
     """benchmark configuration 3: 128 heads, latent cache ~N(0, 0.5), query ~N(0, 1), scale 1/sqrt(192). All 128 heads run on the
-    GPU; the oracle checks 16 of them: the first and last head of each of the four softmax warps of the tile (a warp owns 32
-    tensor-memory lanes = 32 heads) and 8 more in between; each checked row spans both output halves (two CTAs)."""
+    GPU; the oracle checks 16 of them: the first and last head of each run of 32 (a softmax warp's 32 tensor-memory lanes;
+    heads 0-63 are the pair's first CTA, 64-127 its second) and 8 more in between; every checked row spans all 512 output
+    columns, i.e. both lane halves of the accumulator and both threads of a head."""
     T, H = 1, 128
     q = W.normal_f16(3, 0, (T, H, 576))
     cache = W.normal_f16(3, 1, (n, 576), 0.5)
