@@ -3,13 +3,20 @@
 // TEST INFRASTRUCTURE ONLY. Nothing in the shipped library calls into this file; it is the checker the GPU parity
 // tests, the smoke test and the benchmark's CPU-baseline leg compare against.
 //
-// PARITY: PINNED FOR THE DEEPSEEK-V4.1 FUNCTIONS, UNPINNED FOR THE REST. The reference tree holds no golden vector,
+// PARITY: PINNED FOR THE DEEPSEEK-V4.1 FUNCTIONS AND FOR THE CACHE AND ROW FORMATS, UNPINNED FOR THE REST. The reference tree holds no golden vector,
 // known-answer test or fixture for any attention kernel, and its SYCL kernels cannot be compiled without a oneAPI
 // toolchain. It does hold one importable CPU implementation of arithmetic on this path, reference/deepseek41/ds41ref.py;
 // tests/golden/make_ref_fixtures.py runs that code (its fp8_sim, rms, freqs, rope and its Ref.attention, on seeded weights)
 // and tests/test_oracle.py holds to its output: orc_ds41_attend (both numerics), orc_ds41_kv_post and orc_ds41_att_post
 // (bit for bit), the E4M3 simulation (bit for bit), the YaRN rotation, orc_ds41_idx_score, orc_ds41_block_max and
-// orc_topk. The GQA, deepseek2 and glm5next functions remain UNPINNED: each restates the arithmetic of the reference
+// orc_topk. A second pin is the reference's own C++: its simplest kernels - loops over independent work-items - compile for
+// the CPU behind a host stand-in for the SYCL names they use (oracle/ref_build.py takes their lines out of a checkout at build
+// time; nothing of them is kept here), and tests/test_ref_compiled.py holds to them bit for bit: orc_kv_store (ns_q35_kv_store),
+// orc_kv_store_q (ns_q35_kv_store_q, q8_0 and q4_0), orc_kv_dequant (the attention kernel's row reader kv_load8),
+// orc_fwht32 (ns_q35_fwht32), orc_q6k_rows (deepseek2's q6k_cols32), orc_to_q8row (ns_to_q8row; and ns_gather_q8_h,
+// ns_to_f16, ns_ds41_rows_f16 against the roundings the tests state). The attention arithmetic of the GQA, deepseek2 and
+// glm5next functions remains UNPINNED (their kernels use work-group barriers, reductions and matrix units, which that
+// stand-in does not provide): each restates the arithmetic of the reference
 // file and lines it cites (where values are rounded, in which order chunks are visited, which exponential is used) and
 // is checked only against an independent numpy statement of softmax attention and its own fp64 mode. The summation
 // order inside one matrix tile is hardware-defined in the reference and is a plain sequential fp32 sum here.

@@ -2,8 +2,9 @@
 
 TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke test and by the benchmark's CPU-baseline leg, never by the
 library. Parity: the deepseek41 functions are pinned to fixtures produced by running the reference's own Python
-(tests/golden/make_ref_fixtures.py); the rest is unpinned - the reference holds no golden vectors for attention (see
-attn_oracle.cpp's header).
+(tests/golden/make_ref_fixtures.py), the cache and row formats to the reference's own kernels compiled for the CPU
+(`build_ref`, tests/test_ref_compiled.py); the attention arithmetic of the rest is unpinned - the reference holds no golden
+vectors for it (see attn_oracle.cpp's header).
 
 Arrays are numpy: fp32 as float32, fp16 / bf16 storage as uint16 bit patterns (`np.float16.view(np.uint16)` for fp16;
 `to_bf16_bits` below for bf16).
@@ -11,6 +12,7 @@ Arrays are numpy: fp32 as float32, fp16 / bf16 storage as uint16 bit patterns (`
 import ctypes as C
 import os
 import subprocess
+import sys
 
 import numpy as np
 
@@ -46,6 +48,32 @@ def lib():
             getattr(_lib, n).restype = i64
             getattr(_lib, n).argtypes = [i64, i64, i64]
     return _lib
+
+
+_REF_SO = os.path.join(_HERE, "_ref", "libref.so")
+_ref = None
+
+
+def build_ref(checkout):
+    """Compiles oracle/_ref/libref.so - a few of the reference's own kernels for the CPU - from a nextsycl checkout
+    (oracle/ref_build.py). Returns the path, or None when the checkout is not there."""
+    if not os.path.isdir(os.path.join(checkout, "kernels", "llm")):
+        return None
+    sys_path = os.path.join(_HERE, "ref_build.py")
+    subprocess.check_call([sys.executable, sys_path, checkout], stdout=subprocess.DEVNULL)
+    return _REF_SO
+
+
+def ref_lib():
+    """The reference's own kernels compiled for the CPU (see build_ref), or None when they were not built."""
+    global _ref
+    if _ref is None and os.path.exists(_REF_SO):
+        _ref = C.CDLL(_REF_SO)
+        _ref.ref_gpu.restype = C.c_void_p
+        _ref.ref_error.restype = C.c_char_p
+        _ref.ref_kv_row.restype = i64
+        _ref.ref_q8_row_bytes_512.restype = i64
+    return _ref
 
 
 def threads():
