@@ -155,3 +155,127 @@ def test_fp16_rows():
     cache = np.full((10, 512), 0x7E01, np.uint16)
     assert ref.ns_ds41_rows_f16(g(), x.ctypes.data_as(f32p), cache.ctypes.data_as(u16p), i64(6), i64(3), i64(512)) == 0
     assert np.array_equal(cache[3:9], want) and (cache[:3] == 0x7E01).all() and (cache[9:] == 0x7E01).all()
+
+
+# ---- kernels with work-groups: the reference's own attention and rotation kernels, run as cooperative fibers -------------
+
+def close(got, want, tol, what):
+    d = np.abs(np.asarray(got, np.float64) - np.asarray(want, np.float64))
+    lim = tol * (1.0 + np.abs(np.asarray(want, np.float64)))
+    assert (d <= lim).all(), f"{what}: max abs {d.max():.3e} against {tol:g} (1 + |want|)"
+
+
+@pytest.mark.parametrize("T,Hq,Hkv,D,kv", [(1, 12, 2, 256, 700), (1, 12, 2, 256, 5000), (1, 8, 2, 256, 40), (3, 8, 2, 256, 300), (2, 4, 4, 128, 200),
+                                            (1, 16, 2, 256, 1), (8, 4, 2, 256, 64)])
+def test_decode_attention_kernel(T, Hq, Hkv, D, kv):
+    """ns_q35_attn (kernels/llm/qwen35/q35.cpp: the kernel `attn`, its key splits and its merge kernel) - the reference's
+    lines, sub-groups of 16 - against orc_gqa_plain. Equal to the bit: the oracle sums a sub-group's partial dot products
+    in lane order and its sub-groups' and splits' shares in their order, as this runs them."""
+    q, k, v, p0 = W.gqa_case(950, T, Hq, Hkv, D, kv)
+    qf = q.astype(np.float32)
+    ref.ns_q35_attn_scratch.restype = i64
+    n = ref.ns_q35_attn_scratch(i64(T), i64(Hq), i64(Hkv), i64(D), i64(p0))
+    assert n == (O.lib().orc_plain_splits(i64(T), i64(p0 + T), i64(Hkv)) > 1) * T * Hq * O.lib().orc_plain_splits(i64(T), i64(p0 + T), i64(Hkv)) * (D + 2)
+    sc = np.zeros(max(1, n), np.float32)
+    got = np.zeros((T, Hq * D), np.float32)
+    rc = ref.ns_q35_attn(g(), qf.ctypes.data_as(f32p), i64(Hq * D), k.view(np.uint16).ctypes.data_as(u16p), v.view(np.uint16).ctypes.data_as(u16p), i64(T),
+                         i64(Hq), i64(Hkv), i64(D), i64(kv), i64(p0), got.ctypes.data_as(f32p), sc.ctypes.data_as(f32p))
+    assert rc == 0, ref.ref_error()
+    want = O.gqa_plain(qf, k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, kv, p0)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("D,n_rot,p0", [(256, 64, 0), (256, 64, 4097), (128, 128, 33)])
+def test_norm_and_rotary_kernels(D, n_rot, p0):
+    """ns_q35_qk_norm_rope, ns_q35_rope and ns_q35_qk_norm_rope_pos (q35.cpp) against orc_qk_norm_rope."""
+    T, H = 3, 5
+    x = W.rng(951, D).standard_normal((T, H * D)).astype(np.float32)
+    w = (1.0 + 0.1 * W.rng(951, 1).standard_normal(D)).astype(np.float32)
+    theta, eps = np.float32(1.0e6), np.float32(1e-6)
+    got = np.zeros((T, H * D), np.float32)
+    assert ref.ns_q35_qk_norm_rope(g(), x.ctypes.data_as(f32p), i64(H * D), i64(D), got.ctypes.data_as(f32p), i64(H * D), i64(T), i64(H), i64(D),
+                                   w.ctypes.data_as(f32p), C.c_float(eps), i64(n_rot), C.c_float(theta), i64(p0)) == 0, ref.ref_error()
+    close(got, O.qk_norm_rope(x, T, H, D, w, eps, n_rot, theta, p0), 2e-6, "norm + rotation")
+    got2 = np.zeros((T, H * D), np.float32)
+    assert ref.ns_q35_rope(g(), x.ctypes.data_as(f32p), i64(H * D), i64(D), got2.ctypes.data_as(f32p), i64(H * D), i64(T), i64(H), i64(D), i64(n_rot),
+                           C.c_float(theta), i64(p0)) == 0, ref.ref_error()
+    close(got2, O.qk_norm_rope(x, T, H, D, None, eps, n_rot, theta, p0), 2e-6, "rotation alone")
+    pos3 = np.stack([np.arange(T) + p0, np.arange(T) * 2 + 7, np.arange(T) * 3 + 1]).astype(np.int32)      # [3, T]
+    sections = (n_rot // 4 - 3, 2, 1)
+    got3 = np.zeros((T, H * D), np.float32)
+    assert ref.ns_q35_qk_norm_rope_pos(g(), x.ctypes.data_as(f32p), i64(H * D), i64(D), got3.ctypes.data_as(f32p), i64(H * D), i64(T), i64(H), i64(D),
+                                       w.ctypes.data_as(f32p), C.c_float(eps), i64(n_rot), C.c_float(theta), pos3.ctypes.data_as(C.POINTER(C.c_int32)),
+                                       i64(sections[0]), i64(sections[1]), i64(sections[2])) == 0, ref.ref_error()
+    close(got3, O.qk_norm_rope(x, T, H, D, w, eps, n_rot, theta, 0, pos3=np.ascontiguousarray(pos3), sections=sections), 2e-6, "sectioned positions")
+
+
+YARN = dict(freq_base=np.float32(10000.0), freq_scale=np.float32(0.025), ext_factor=np.float32(1.0), mscale=np.float32(1.0 + 0.1 * np.log(40.0)),
+            corr0=np.float32(10.0), corr1=np.float32(23.0))
+YK = ("freq_base", "freq_scale", "ext_factor", "mscale", "corr0", "corr1")
+
+
+@pytest.mark.parametrize("ext", [0.0, 1.0])
+def test_ds2_rotation_and_cache_writer(ext):
+    """ns_ds2_rope and ns_ds2_kv_store (kernels/llm/deepseek2/ds2.cpp: YaRN, the latent cache's writer) against orc_ds2_rope
+    and orc_ds2_kv_store."""
+    f = C.c_float
+    T, H, head, off, n_dims, pos0 = 4, 6, 192, 128, 64, 3000
+    y = dict(YARN, ext_factor=np.float32(ext))
+    x = W.rng(952, 0).standard_normal((T, H * head)).astype(np.float32)
+    got, gout = x.copy().ravel(), np.zeros(T * H * n_dims, np.float32)
+    assert ref.ns_ds2_rope(g(), got.ctypes.data_as(f32p), i64(T), i64(H), i64(H * head), i64(head), i64(off), i64(n_dims), i64(pos0), *[f(y[k]) for k in YK],
+                           gout.ctypes.data_as(f32p), i64(H * n_dims), i64(n_dims)) == 0, ref.ref_error()
+    want, wout = x.copy().ravel(), np.zeros(T * H * n_dims, np.float32)
+    O.ds2_rope(want, T, H, H * head, head, off, n_dims, pos0, *[float(y[k]) for k in YK], out=wout, out_row=H * n_dims, out_head=n_dims)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)) and np.array_equal(gout.view(np.uint32), wout.view(np.uint32))
+    L, R = 512, 64
+    kv = W.rng(952, 1).standard_normal((T, L + R)).astype(np.float32)
+    w = (1.0 + 0.1 * W.rng(952, 2).standard_normal(L)).astype(np.float32)
+    gc, wc = (np.full((pos0 % 7 + T + 2, L + R), 0x7E01, np.uint16) for _ in range(2))
+    p = pos0 % 7
+    assert ref.ns_ds2_kv_store(g(), kv.ctypes.data_as(f32p), w.ctypes.data_as(f32p), f(1e-6), gc.ctypes.data_as(u16p), i64(T), i64(L), i64(R), i64(p),
+                               *[f(y[k]) for k in YK]) == 0, ref.ref_error()
+    O.ds2_kv_store(kv, w, np.float32(1e-6), wc, T, L, R, p, *[float(y[k]) for k in YK])
+    # the 256 work-items' shares of a row's sum of squares meet in another order than the oracle's: the normed values may
+    # differ in the last place before they are rounded to fp16
+    a, b = gc[p:p + T].view(np.float16).astype(np.float32), wc[p:p + T].view(np.float16).astype(np.float32)
+    close(a, b, 1.0e-3, "latent rows")
+    assert (gc[p:p + T] != wc[p:p + T]).mean() < 0.01
+    assert np.array_equal(gc[:p], wc[:p]) and np.array_equal(gc[p + T:], wc[p + T:])
+
+
+def _q6k_blocks(rng, nrows):
+    blocks = rng.integers(0, 256, size=(nrows, 2, 210), dtype=np.uint8)
+    blocks[:, :, 192:208] = rng.integers(-40, 41, size=(nrows, 2, 16)).astype(np.int8).view(np.uint8)
+    blocks[:, :, 208:210] = (np.abs(rng.standard_normal((nrows, 2, 1))) * 2.0e-4 + 1.0e-4).astype(np.float16).view(np.uint8).reshape(nrows, 2, 2)
+    return np.ascontiguousarray(blocks.reshape(nrows, 420))
+
+
+@pytest.mark.parametrize("T,H,n", [(1, 3, 300), (2, 2, 77), (1, 2, 1)])
+def test_ds2_fused_decode_kernel(T, H, n):
+    """ns_ds2_mla_decode and ns_ds2_mla_decode_q6k (ds2.cpp: mla_decode_t, one work-group of 256 a (row, head): absorb, online
+    softmax over the cache, un-absorb) against the same three stages stated with the oracle: q~ = k_b q_nope, orc_mla_fused over
+    the latent cache, out = v_b u. The stages' fp32 sums meet in other orders: 2e-5 (1 + |want|)."""
+    pos0 = n - T
+    scale = np.float32(1.0 / np.sqrt(192.0))
+    q = W.rng(953, T).standard_normal((T, H, 192)).astype(np.float32)
+    cache = W.normal_f16(953, 3, (n, 576), 0.5)
+    kb = W.normal_f16(953, 1, (H, 512, 128), 0.1)
+    vb = W.normal_f16(953, 2, (H, 128, 512), 0.1)
+    got = np.zeros((T, H, 128), np.float32)
+    assert ref.ns_ds2_mla_decode(g(), q.ctypes.data_as(f32p), kb.view(np.uint16).ctypes.data_as(u16p), vb.view(np.uint16).ctypes.data_as(u16p),
+                                 cache.view(np.uint16).ctypes.data_as(u16p), got.ctypes.data_as(f32p), i64(T), i64(H), i64(pos0), C.c_float(scale)) == 0
+
+    def stated(k_rows, v_rows):      # k_rows [H, 512, 128] (q~[c] = sum_i k[c][i] q[i]), v_rows [H, 128, 512], float64
+        qa = np.einsum("hci,thi->thc", k_rows, q[:, :, :128].astype(np.float64)).astype(np.float32)
+        qfull = np.ascontiguousarray(np.concatenate([qa, q[:, :, 128:]], axis=2))
+        u = O.mla_fused(qfull, cache.view(np.uint16), T, H, 512, 64, pos0, scale)
+        return np.einsum("hvl,thl->thv", v_rows, u.astype(np.float64))
+    close(got, stated(kb.astype(np.float64), vb.astype(np.float64)), 2e-5, "fp16 weights")
+    kvb = _q6k_blocks(W.rng(953, 9), H * 256)
+    vals = O.q6k_rows(kvb, H * 256, 512).reshape(H, 256, 512).astype(np.float64)
+    got6 = np.zeros((T, H, 128), np.float32)
+    assert ref.ns_ds2_mla_decode_q6k(g(), q.ctypes.data_as(f32p), kvb.ctypes.data_as(C.c_void_p), cache.view(np.uint16).ctypes.data_as(u16p),
+                                     got6.ctypes.data_as(f32p), i64(T), i64(H), i64(pos0), C.c_float(scale)) == 0
+    # Q6_K: per head 128 k rows (row i = k_i[0..511]) then 128 v rows
+    close(got6, stated(np.transpose(vals[:, :128], (0, 2, 1)), vals[:, 128:]), 2e-5, "Q6_K weights")
