@@ -76,6 +76,21 @@ def ref_lib():
     return _ref
 
 
+_REF_NH_SO = os.path.join(_HERE, "_ref", "libref_nh.so")
+_ref_nh = None
+
+
+def ref_nh_lib():
+    """nemotronh's attention kernel compiled for the CPU (a unit of its own: it carries the same names as qwen35's)."""
+    global _ref_nh
+    if _ref_nh is None and os.path.exists(_REF_NH_SO):
+        _ref_nh = C.CDLL(_REF_NH_SO)
+        _ref_nh.ref_gpu.restype = C.c_void_p
+        _ref_nh.ref_error.restype = C.c_char_p
+        _ref_nh.ns_nh_attn_scratch.restype = i64
+    return _ref_nh
+
+
 def threads():
     return int(lib().orc_threads())
 

@@ -31,6 +31,7 @@ PIECES = [
     ("kernels/llm/qwen35/q35.cpp", r"^int ns_q35_qk_norm_rope\(", "brace"),
     ("kernels/llm/qwen35/q35.cpp", r"^int ns_q35_rope\(", "brace"),
     ("kernels/llm/qwen35/q35.cpp", r"^int ns_q35_qk_norm_rope_pos\(", "brace"),
+    ("kernels/llm/qwen35/q35.cpp", r"^int ns_q35_attn_probs\(", "brace"),
     ("kernels/llm/qwen35/q35.cpp", r"^int ns_q35_kv_store_q\(", "brace"),
     ("kernels/llm/qwen35/q35.cpp", r"^int ns_q35_fwht32\(", "brace"),
     ("kernels/llm/qwen35/q35.cpp", r"^int ns_q35_kv_store\(", "brace"),
@@ -46,19 +47,59 @@ PIECES = [
     ("kernels/llm/deepseek2/ds2.cpp", r"^int ns_ds2_mla_decode\(", "brace"),
     ("kernels/llm/deepseek2/ds2.cpp", r"^int ns_ds2_mla_decode_q6k\(", "brace"),
     ("kernels/llm/glm5next/glm.cpp", r"^template <int L>$", "brace2"),               # q8_row_bytes: two lines
+    ("kernels/llm/glm5next/glm.cpp", r"^int ns_mla_attend\(", "brace"),
+    ("kernels/llm/glm5next/glm.cpp", r"^int ns_gather_h\(", "brace"),
+    ("kernels/llm/glm5next/glm.cpp", r"^int ns_idx_pool\(", "brace"),
+    ("kernels/llm/glm5next/glm.cpp", r"^int ns_idx_score\(", "brace"),
+    ("kernels/llm/glm5next/glm.cpp", r"^int ns_topk\(", "brace"),
+    ("kernels/llm/glm5next/glm.cpp", r"^int ns_mla_cells\(", "brace"),
+    ("kernels/llm/glm5next/glm.cpp", r"^int ns_softmax_masked\(", "brace"),
+    ("kernels/llm/glm5next/glm.cpp", (r"^template <int L, bool Q8 = false>$", r"^static void mla_dec\("), "brace"),   # the selected-cell decode kernel
+    ("kernels/llm/glm5next/glm.cpp", (r"^template <int HG>$", r"^static void mla_sel\("), "brace"),
+    ("kernels/llm/glm5next/glm.cpp", r"^int ns_mla_attend_sel\(", "brace"),
+    ("kernels/llm/glm5next/glm.cpp", r"^int ns_mla_attend_sel_q8\(", "brace"),
     ("kernels/llm/glm5next/glm.cpp", r"^int ns_to_f16\(", "brace"),
     ("kernels/llm/glm5next/glm.cpp", r"^int ns_to_q8row\(", "brace"),
     ("kernels/llm/glm5next/glm.cpp", r"^int ns_gather_q8_h\(", "brace"),
     ("kernels/llm/deepseek41/silo/ds41.cpp", r"^int ns_ds41_rows_f16\(", "brace"),
+    ("kernels/llm/deepseek41/silo/ds41.cpp", r"^int ns_ds41_ring_put\(", "brace"),
+    ("kernels/llm/deepseek41/silo/ds41.cpp", (r"^template <int HG>$", r"^void attend\("), "brace"),   # the vector form of the MQA-512 attention with sinks
+    ("kernels/llm/deepseek41/silo/ds41.cpp", r"^int ns_ds41_attend\(", "brace"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^inline float pow2_ceil\(", "brace"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^inline float e4m3_round\(", "brace"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^inline float kv_yarn_ramp\(", "brace"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^inline void kv_yarn_cs\(", "brace"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^int ns_ds41_kv_post\(", "brace"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^int ns_ds41_att_post\(", "brace"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^int ns_ds41_block_max\(", "brace"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^int ns_ds41_cand_mask\(", "brace"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^int ns_ds41_cand_pos\(", "brace"),
+]
+
+# a second translation unit: nemotronh's attention carries the same names as qwen35's
+PIECES_NH = [
+    ("kernels/llm/nemotronh/nh.cpp", r"^constexpr int SG = 16;", "line"),
+    ("kernels/llm/nemotronh/nh.cpp", r"^constexpr int NSG_A = 4;", "line"),
+    ("kernels/llm/nemotronh/nh.cpp", r"^int64_t split_keys\(", "brace"),
+    ("kernels/llm/nemotronh/nh.cpp", r"^int64_t splits\(", "brace"),
+    ("kernels/llm/nemotronh/nh.cpp", (r"^template <int DL, int G>$", r"^void attn\("), "brace"),
+    ("kernels/llm/nemotronh/nh.cpp", r"^constexpr int GA = 8;", "line"),
+    ("kernels/llm/nemotronh/nh.cpp", r"^int64_t ns_nh_attn_scratch\(", "brace"),
+    ("kernels/llm/nemotronh/nh.cpp", r"^int ns_nh_attn\(", "brace"),
 ]
 
 HEAD = r'''// GENERATED by oracle/ref_build.py from a nextsycl checkout: the reference's own lines between the markers. Not committed.
 #include <sycl/sycl.hpp>
 #include <cstdint>
+#include <cstdlib>
+#include <string>
 using half = sycl::half;
 struct ns_gpu { sycl::queue q; };
-static const char* ref_last_error = "";
-static int ns_fail(const char* what) { ref_last_error = what; return -1; }
+static std::string ref_last_error;
+static int ns_fail(const std::string& what) { ref_last_error = what; return -1; }
+// the matrix-unit form of deepseek41's attention does not exist on the host: the entry point takes its vector form
+static int ns_ds41_attend_xmx_supported(int64_t, int64_t) { return 0; }
+template <class... A> static int ns_ds41_attend_xmx(A...) { return -1; }
 #define NS_TRY
 #define NS_CATCH
 '''
@@ -66,8 +107,10 @@ static int ns_fail(const char* what) { ref_last_error = what; return -1; }
 TAIL = r'''
 // ---- entry points for what the reference keeps internal (this file's own lines) ----
 extern "C" {
-const char* ref_error() { return ref_last_error; }
-void* ref_gpu() { static ns_gpu g; return &g; }
+const char* ref_error() { return ref_last_error.c_str(); }
+// the sub-group size of the launches that follow (the kernels' [[sycl::reqd_sub_group_size]] means nothing to g++)
+int ref_sub_group_size = 16;
+void* ref_gpu() { static ns_gpu g; sycl::detail::sub_group_size_setting() = &ref_sub_group_size; return &g; }
 // features 8c .. 8c + 7 of a cache row of form kt (1 q8_0, 2 q4_0) as the reference's reader returns them: 8 halves
 void ref_kv_load8(int kt, const uint8_t* row, int c, uint16_t* out8) {
     const sycl::uint4 w = kt == 1 ? kv_load8<1>(row, c) : kv_load8<2>(row, c);
@@ -103,25 +146,38 @@ def take(lines, start_re, how, path):
     raise SystemExit(f"ref_build: the piece {start_re!r} was not found in {path} (the checkout differs from the one this was written against)")
 
 
-def build(checkout):
+def build_unit(checkout, pieces, tail, name):
     os.makedirs(OUT, exist_ok=True)
     parts = [HEAD, 'extern "C++" {\n']
-    for rel, start_re, how in PIECES:
+    for rel, start_re, how in pieces:
         path = os.path.join(checkout, rel)
         with open(path, encoding="utf-8") as f:
             lines = f.read().split("\n")
         piece = take(lines, start_re, how, rel)
         linkage = 'extern "C" ' if re.match(r"^int(64_t)? ns_", piece[0]) else ""
         parts.append(f"// ---- {rel}\n{linkage}" + "\n".join(piece) + "\n")
-    parts.append("}\n" + TAIL)
-    src = os.path.join(OUT, "ref_extracted.cpp")
+    parts.append("}\n" + tail)
+    src = os.path.join(OUT, name + ".cpp")
     with open(src, "w", encoding="utf-8") as f:
         f.write("".join(parts))
-    so = os.path.join(OUT, "libref.so")
+    so = os.path.join(OUT, "lib" + name + ".so")
     cmd = ["g++", "-O2", "-march=x86-64-v3", "-ffp-contract=off", "-std=c++17", "-fPIC", "-shared", "-Wno-attributes", "-Wno-unknown-pragmas",
            "-I", os.path.join(HERE, "ref_shim"), "-o", so, src]
     subprocess.check_call(cmd)
     return so
+
+
+TAIL_NH = r'''
+extern "C" {
+const char* ref_error() { return ref_last_error.c_str(); }
+void* ref_gpu() { static ns_gpu g; return &g; }
+}
+'''
+
+
+def build(checkout):
+    build_unit(checkout, PIECES_NH, TAIL_NH, "ref_nh")
+    return build_unit(checkout, PIECES, TAIL, "ref")
 
 
 if __name__ == "__main__":

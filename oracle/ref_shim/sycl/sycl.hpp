@@ -47,6 +47,12 @@ struct vec {
     const T& y() const { return v[1]; }
     const T& z() const { return v[2]; }
     const T& w() const { return v[3]; }
+    template <class U>
+    vec<U, N> convert() const {
+        vec<U, N> r;
+        for (int i = 0; i < N; ++i) r.v[i] = (U) v[i];
+        return r;
+    }
 };
 using float2 = vec<float, 2>;
 using float4 = vec<float, 4>;
@@ -88,11 +94,34 @@ inline float sin(float a) { return std::sin(a); }
 inline float cos(float a) { return std::cos(a); }
 inline float pow(float a, float b) { return std::pow(a, b); }
 inline float tanh(float a) { return std::tanh(a); }
+inline float rint(float a) { return std::nearbyint(a); }      // to nearest, halves to even
+inline float ldexp(float a, int e) { return std::ldexp(a, e); }
+inline float frexp(float a, int* e) { return std::frexp(a, e); }
 inline float clamp(float x, float lo, float hi) { return std::fmin(std::fmax(x, lo), hi); }
 template <class T>
 T min(T a, T b) { return a < b ? a : b; }
 template <class T>
 T max(T a, T b) { return a > b ? a : b; }
+
+enum class memory_order { relaxed, acquire, release, acq_rel, seq_cst };
+enum class memory_scope { work_item, sub_group, work_group, device, system };
+namespace access {
+enum class address_space { global_space, local_space, private_space, generic_space };
+enum class decorated { no, yes };
+}  // namespace access
+// work-items are fibers of one thread: an atomic is the plain operation
+template <class T, memory_order O, memory_scope S, access::address_space A = access::address_space::generic_space>
+struct atomic_ref {
+    T& r;
+    explicit atomic_ref(T& x) : r(x) {}
+    T fetch_add(T v) {
+        const T old = r;
+        r = old + v;
+        return old;
+    }
+    T load() const { return r; }
+    void store(T v) { r = v; }
+};
 
 template <class T = void>
 struct plus {
@@ -138,6 +167,10 @@ namespace detail {
 inline int& sub_group_size() {
     static int s = 16;
     return s;
+}
+inline int*& sub_group_size_setting() {      // when set: where the size of the next launch is read from
+    static int* p = nullptr;
+    return p;
 }
 
 // a set of work-items that meet in collectives: the work-group, or one of its sub-groups
@@ -270,6 +303,16 @@ T reduce_over_group(const G& g, T v, Op op) {
         return a;
     });
 }
+template <class G, class T, class Op>
+T exclusive_scan_over_group(const G& g, T v, Op op) {
+    int me;
+    detail::SyncSet& s = detail::set_of(g, me);
+    return detail::collective(s, me, v, [&](const T* all, int) {
+        T a = T();
+        for (int i = 0; i < me; ++i) a = i == 0 ? all[0] : op(a, all[i]);
+        return a;
+    });
+}
 template <class T>
 T permute_group_by_xor(const sub_group& g, T v, int mask) {
     int me;
@@ -330,7 +373,7 @@ struct queue {
         using Item = nd_item<1>;
         const size_t local = r.local, ngroups = r.global / r.local;
         detail::GroupRun run;
-        run.sg = std::min<int>(detail::sub_group_size(), (int) local);
+        run.sg = std::min<int>(detail::sub_group_size_setting() ? *detail::sub_group_size_setting() : detail::sub_group_size(), (int) local);
         run.fibers.resize(local);
         for (auto& fb : run.fibers) fb.stack.resize(256 * 1024);
         detail::GroupRun* outer = detail::run();
@@ -372,6 +415,8 @@ struct queue {
     template <class F>
     void submit(F f);
     void wait() {}
+    void memset(void* p, int v, size_t n) { std::memset(p, v, n); }
+    void memcpy(void* d, const void* s, size_t n) { std::memcpy(d, s, n); }
 };
 
 struct handler {

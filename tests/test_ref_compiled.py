@@ -279,3 +279,277 @@ def test_ds2_fused_decode_kernel(T, H, n):
                                      got6.ctypes.data_as(f32p), i64(T), i64(H), i64(pos0), C.c_float(scale)) == 0
     # Q6_K: per head 128 k rows (row i = k_i[0..511]) then 128 v rows
     close(got6, stated(np.transpose(vals[:, :128], (0, 2, 1)), vals[:, 128:]), 2e-5, "Q6_K weights")
+
+
+i32p = C.POINTER(C.c_int32)
+GSCALE = np.float32(1.0 / 16.0)
+
+
+def test_glm_exact_attention_kernel():
+    """ns_mla_attend (kernels/llm/glm5next/glm.cpp: fp32 latents, two passes) against orc_mla_attend_f32."""
+    T, H, L, n = 3, 4, 512, 200
+    qa = W.rng(960, 0).standard_normal((T, H, L)).astype(np.float32)
+    c = (0.5 * W.rng(960, 1).standard_normal((n, L))).astype(np.float32)
+    got = np.zeros((T, H, L), np.float32)
+    assert ref.ns_mla_attend(g(), qa.ctypes.data_as(f32p), c.ctypes.data_as(f32p), got.ctypes.data_as(f32p), i64(T), i64(H), i64(L), i64(n - T), C.c_float(GSCALE)) == 0
+    close(got, O.mla_attend_f32(qa, c, T, H, L, n - T, GSCALE), 1e-5, "exact attention over fp32 latents")
+
+
+@pytest.mark.parametrize("T,H,n,q8", [(1, 8, 300, False), (3, 8, 900, False), (2, 8, 500, True), (12, 4, 400, False)])
+def test_glm_selected_cell_kernels(T, H, n, q8):
+    """ns_mla_attend_sel and ns_mla_attend_sel_q8 (glm.cpp: mla_dec for passes of at most 8 rows, mla_sel above) - dense,
+    selected and mixed rows - against orc_mla_dec512."""
+    qa = W.rng(961, 0).standard_normal((T, H, 512)).astype(np.float32)
+    lat = (0.5 * W.rng(961, 1).standard_normal((n, 512))).astype(np.float32)
+    c16 = lat.astype(np.float16)
+    cache = O.to_q8row(lat) if q8 else c16.view(np.uint16)
+    pos0, K = n - T, 24
+    rng = W.rng(961, 2)
+    sel, cnt = np.zeros((T, K), np.int32), np.zeros(T, np.int32)
+    for t in range(T):
+        pools = (pos0 + t + 1) // 4
+        cnt[t] = min(K, pools) - (t % 3)
+        sel[t, :cnt[t]] = np.sort(rng.choice(pools, size=cnt[t], replace=False))
+    fn = ref.ns_mla_attend_sel_q8 if q8 else ref.ns_mla_attend_sel
+
+    def run(selp, cntp, k):
+        got = np.zeros((T, H, 512), np.float32)
+        rc = fn(g(), qa.ctypes.data_as(f32p), cache.ctypes.data_as(C.c_void_p), got.ctypes.data_as(f32p), i64(T), i64(H), i64(512), i64(pos0), C.c_float(GSCALE),
+                None if selp is None else selp.ctypes.data_as(i32p), None if cntp is None else cntp.ctypes.data_as(i32p), i64(k))
+        assert rc == 0, ref.ref_error()
+        return got
+    close(run(sel, cnt, K), O.mla_dec512(qa, cache, T, H, pos0, GSCALE, sel=sel, sel_cnt=cnt, K=K, q8=q8), 2e-5, "selected cells")
+    if not q8:
+        close(run(None, None, 0), O.mla_dec512(qa, cache, T, H, pos0, GSCALE), 2e-5, "every earlier token")
+        cnt2 = cnt.copy()
+        cnt2[0] = -1
+        close(run(sel, cnt2, K), O.mla_dec512(qa, cache, T, H, pos0, GSCALE, sel=sel, sel_cnt=cnt2, K=K), 2e-5, "a dense row among selected ones")
+
+
+def test_glm_indexer_kernels():
+    """ns_idx_pool, ns_idx_score and ns_topk (glm.cpp) against orc_idx_pool, orc_idx_score and orc_topk (the selection bit for bit)."""
+    D = 128
+    for pos0, T in ((0, 11), (7, 1), (13, 5), (1021, 9)):
+        rng = W.rng(1420, pos0)
+        ik, ig = rng.standard_normal((T, D)).astype(np.float32), rng.standard_normal((T, D)).astype(np.float32)
+        ape = rng.standard_normal((4, D)).astype(np.float32)
+        ring = rng.standard_normal((8, 2 * D)).astype(np.float32)
+        pools = (pos0 + T) // 4 + 2
+        gring, gp = ring.copy(), np.full((pools, D), 9.0, np.float32)
+        wring, wp = ring.copy(), gp.copy()
+        assert ref.ns_idx_pool(g(), gring.ctypes.data_as(f32p), ik.ctypes.data_as(f32p), ig.ctypes.data_as(f32p), ape.ctypes.data_as(f32p), gp.ctypes.data_as(f32p),
+                               i64(pos0), i64(T), i64(D)) == 0
+        O.idx_pool(wring, ik, ig, ape, wp, pos0, T, D)
+        close(gp, wp, 2e-6, "pooled keys")
+        assert np.array_equal(gring, wring)
+    T, H, n, j0, pos0 = 5, 32, 300, 100, 1590
+    ld = j0 + n + 7
+    S = W.rng(1410, 0).standard_normal((T * H, n)).astype(np.float32)
+    w = W.rng(1410, 1).standard_normal((T, H)).astype(np.float32)
+    got, want = (np.full((T, ld), 3.0, np.float32) for _ in range(2))
+    assert ref.ns_idx_score(g(), S.ctypes.data_as(f32p), w.ctypes.data_as(f32p), got.ctypes.data_as(f32p), i64(T), i64(H), i64(j0), i64(n), i64(ld), i64(pos0)) == 0
+    O.idx_score(S, w, want, T, H, j0, n, pos0)
+    assert np.array_equal(np.isneginf(got), np.isneginf(want))
+    fin = np.isfinite(want)
+    close(got[fin], want[fin], 2e-6, "pool scores")
+    for (T, n, ld, K, kind) in ((1, 1000, 1000, 64, "normal"), (3, 4097, 4100, 512, "ties"), (4, 700, 800, 700, "ties"), (2, 3000, 3000, 100, "masked"),
+                                (1, 50, 64, 80, "normal"), (2, 2048, 2048, 300, "constant")):
+        rng = W.rng(1400, n + K)
+        score = np.full((T, ld), 7.0, np.float32)
+        x = rng.standard_normal((T, n)).astype(np.float32)
+        if kind == "ties":
+            x = np.round(x * 2) / 2
+        if kind == "constant":
+            x[:] = -1.5
+        if kind == "masked":
+            x[:, n // 3:] = -np.inf
+            x[1, :10] = 0.0
+            x[1, 5] = -0.0
+        score[:, :n] = x
+        sel = np.full((T, K), -1, np.int32)
+        assert ref.ns_topk(g(), score.ctypes.data_as(f32p), sel.ctypes.data_as(i32p), i64(T), i64(n), i64(ld), i64(K)) == 0, ref.ref_error()
+        assert np.array_equal(sel, O.topk(score, n, K)), kind
+
+
+def test_glm_cell_lists_masked_softmax_and_gather():
+    """ns_mla_cells, ns_softmax_masked and ns_gather_h (glm.cpp), the reference's lines, against the statements the CUDA tests
+    hold the library's kernels to (tests/test_glm_mla_gpu.py::test_helper_kernels)."""
+    T, K, pos0, NC = 3, 4, 50, 64
+    sel = np.array([[1, 3, 7, 0], [2, 4, 6, 8], [0, 0, 0, 0]], np.int32)
+    cnt = np.array([3, 4, -1], np.int32)
+    gi, gn = np.full((T, NC), -7, np.int32), np.zeros(T, np.int32)
+    assert ref.ns_mla_cells(g(), sel.ctypes.data_as(i32p), cnt.ctypes.data_as(i32p), i64(T), i64(K), i64(pos0), gi.ctypes.data_as(i32p), gn.ctypes.data_as(i32p),
+                            i64(NC)) == 0
+    for t in range(T):
+        p = pos0 + t
+        tail0 = 4 * ((p + 1) // 4)
+        cells = list(range(p + 1)) if cnt[t] < 0 else [4 * sel[t, i // 4] + i % 4 for i in range(4 * cnt[t])] + list(range(tail0, p + 1))
+        assert gn[t] == min(len(cells), NC)
+        assert list(gi[t, :gn[t]]) == cells[:NC]
+    S = W.rng(962, 5).standard_normal((T * 2, NC)).astype(np.float32)
+    got = S.copy()
+    assert ref.ns_softmax_masked(g(), got.ctypes.data_as(f32p), i64(T), i64(2), i64(NC), gn.ctypes.data_as(i32p), C.c_float(0.3)) == 0
+    got = got.reshape(T, 2, NC)
+    for t in range(T):
+        m = gn[t]
+        z = S.reshape(T, 2, NC)[t, :, :m].astype(np.float64) * 0.3
+        e = np.exp(z - z.max(-1, keepdims=True))
+        assert np.allclose(got[t, :, :m], e / e.sum(-1, keepdims=True), atol=1e-6)
+        assert not got[t, :, m:].any()
+    x = W.normal_f16(962, 0, (37, 512), 0.5)
+    idx = np.array([5, 0, 36, 5, 17], np.int32)
+    out = np.zeros((len(idx), 512), np.uint16)
+    assert ref.ns_gather_h(g(), x.view(np.uint16).ctypes.data_as(u16p), idx.ctypes.data_as(i32p), out.ctypes.data_as(u16p), i64(len(idx)), i64(512)) == 0
+    assert np.array_equal(out, x.view(np.uint16)[idx])
+
+
+DSCALE = np.float32(512 ** -0.5)
+
+
+def _ds41_case(seed, T, H, pos0, window, R, ratio, K, with_comp=True):
+    rng = W.rng(seed, 0)
+    q = rng.standard_normal((T, H, 512)).astype(np.float32)
+    raw = O.to_f16_bits((0.5 * rng.standard_normal((R, 512))).astype(np.float32))
+    ncomp = (pos0 + T) // ratio if with_comp else 0
+    comp = O.to_f16_bits((0.5 * rng.standard_normal((ncomp, 512))).astype(np.float32)) if ncomp else None
+    sel = None
+    if K and comp is not None:
+        sel = np.zeros((T, K), np.int32)
+        for t in range(T):
+            vis = (pos0 + t + 1) // ratio
+            if vis > K:
+                sel[t] = np.sort(rng.choice(vis, size=K, replace=False))
+    return q, raw, comp, sel, rng.standard_normal(H).astype(np.float32)
+
+
+@pytest.mark.parametrize("T,H,pos0,window,R,ratio,K,with_comp", [
+    (1, 8, 5, 128, 128, 4, 0, False),        # fewer tokens than the window, no compressed cells
+    (1, 8, 1000, 128, 128, 4, 0, False),     # a full window, the ring wrapped many times
+    (1, 4, 2047, 128, 128, 4, 0, True),      # window + every compressed cell
+    (1, 4, 4095, 128, 160, 4, 256, True),    # the indexer's picks, a ring longer than the window
+    (4, 4, 1020, 128, 128, 4, 256, True),    # rows either side of the point where picks start
+    (3, 8, 0, 16, 16, 128, 0, True),         # the first tokens; comp given but nothing visible yet
+    (2, 3, 300, 64, 64, 4, 0, True),         # a head count that is no multiple of four: one head a work-group
+])
+def test_ds41_vector_attention_kernel(T, H, pos0, window, R, ratio, K, with_comp):
+    """ns_ds41_attend (kernels/llm/deepseek41/silo/ds41.cpp: `attend`, the vector form - window ring, compressed cells, picks,
+    per-head sinks) against orc_ds41_attend in that form's numerics (mode 0)."""
+    q, raw, comp, sel, sinks = _ds41_case(980 + T, T, H, pos0, window, R, ratio, K, with_comp)
+    if comp is None and with_comp:
+        comp = np.zeros((1, 512), np.uint16)
+    got = np.zeros((T, H, 512), np.float32)
+    rc = ref.ns_ds41_attend(g(), q.ctypes.data_as(f32p), raw.ctypes.data_as(u16p), i64(R), None if comp is None else comp.ctypes.data_as(u16p), i64(ratio),
+                            None if sel is None else sel.ctypes.data_as(i32p), i64(K), sinks.ctypes.data_as(f32p), got.ctypes.data_as(f32p), i64(T), i64(H),
+                            i64(pos0), i64(window), C.c_float(DSCALE))
+    assert rc == 0, ref.ref_error()
+    close(got, O.ds41_attend(q, raw, R, comp, ratio, sel, K, sinks, T, H, pos0, window, DSCALE, mode=0), 1e-5, "MQA-512 with sinks")
+
+
+def test_ds41_steps_around_attention():
+    """ns_ds41_ring_put, ns_ds41_kv_post, ns_ds41_att_post (norm, YaRN rotation, the model's E4M3 simulation), ns_ds41_block_max,
+    ns_ds41_cand_mask and ns_ds41_cand_pos (ds41.cpp, k41.cpp) against the oracle's functions."""
+    f = C.c_float
+    T, R, D, pos0 = 7, 16, 512, 13
+    kv = W.rng(993, 0).standard_normal((T, D)).astype(np.float32)
+    before = W.rng(993, 1).integers(0, 1 << 15, size=(R, D), dtype=np.uint16)
+    ring = before.copy()
+    assert ref.ns_ds41_ring_put(g(), kv.ctypes.data_as(f32p), ring.ctypes.data_as(u16p), i64(T), i64(pos0), i64(R), i64(D)) == 0
+    want = before.copy()
+    for t in range(T):
+        want[(pos0 + t) % R] = kv[t].astype(np.float16).view(np.uint16)
+    assert np.array_equal(ring, want)
+
+    def grid_close(got, want, what):     # values on the E4M3 grid: equal but for inputs next to a rounding boundary
+        same = got == want
+        assert same.mean() > 0.995, f"{what}: {1 - same.mean():.4f} of the values differ"
+        assert np.all(np.abs(got.astype(np.float64) - want) <= 0.13 * np.abs(want) + 2e-6), what
+    yarn = [float(YARN[k]) for k in YK]
+    T, D, rd, pos0, R = 9, 512, 64, 250, 128
+    kv = W.rng(1360, 0).standard_normal((T, D)).astype(np.float32)
+    w = (1.0 + 0.1 * W.rng(1360, 1).standard_normal(D)).astype(np.float32)
+    before = W.rng(1360, 2).integers(0, 1 << 15, size=(R, D), dtype=np.uint16)
+    gkv, gring = kv.copy(), before.copy()
+    sycl_sg = C.c_int.in_dll(ref, "ref_sub_group_size")
+    sycl_sg.value = 32            # these two kernels ask for sub-groups of 32
+    try:
+        assert ref.ns_ds41_kv_post(g(), gkv.ctypes.data_as(f32p), w.ctypes.data_as(f32p), i64(T), i64(D), f(1e-6), i64(rd), i64(pos0), *[f(v) for v in yarn],
+                                   gring.ctypes.data_as(u16p), i64(R)) == 0, ref.ref_error()
+        wkv, wring = kv.copy(), before.copy()
+        O.ds41_kv_post(wkv, w, T, D, 1e-6, rd, pos0, yarn, wring, R)
+        grid_close(gkv, wkv, "kv_post")
+        slots = [(pos0 + t) % R for t in range(T)]
+        others = [s for s in range(R) if s not in slots]
+        assert np.array_equal(gring[others], before[others])
+        assert np.array_equal(gring[slots].view(np.float16), gkv.astype(np.float16))
+        T, H, D, rd, pos0 = 3, 8, 512, 64, 777
+        x = W.rng(1370, 0).standard_normal((T, H, D)).astype(np.float32)
+        gx = x.copy()
+        assert ref.ns_ds41_att_post(g(), gx.ctypes.data_as(f32p), i64(T), i64(H), i64(D), i64(rd), i64(pos0), *[f(v) for v in yarn]) == 0, ref.ref_error()
+        wx = x.copy()
+        O.ds41_att_post(wx, T, H, D, rd, pos0, yarn)
+        grid_close(gx, wx, "att_post")
+    finally:
+        sycl_sg.value = 16
+    T, n, ld, bs, pos0, ratio, K = 3, 1003, 1008, 8, 4100, 4, 20
+    nb = -(-n // bs)
+    rng = W.rng(1441, 0)
+    score = rng.standard_normal((T, ld)).astype(np.float32)
+    vis = [(pos0 + t + 1) // ratio for t in range(T)]
+    for t in range(T):
+        score[t, min(vis[t], n):] = -np.inf
+    bm = np.zeros((T, nb), np.float32)
+    assert ref.ns_ds41_block_max(g(), score.ctypes.data_as(f32p), bm.ctypes.data_as(f32p), i64(T), i64(n), i64(ld), i64(bs), i64(pos0), i64(ratio)) == 0
+    assert np.array_equal(bm.view(np.uint32), O.ds41_block_max(score, n, bs, pos0, ratio).view(np.uint32))
+    cand = np.stack([np.sort(rng.choice(nb, size=K, replace=False)) for _ in range(T)]).astype(np.int32)
+    cand[1, 0] = -1
+    cand[2, -1] = nb - 1
+    gs, mark = score.copy(), np.zeros((T, nb), np.uint8)
+    assert ref.ns_ds41_cand_mask(g(), gs.ctypes.data_as(f32p), cand.ctypes.data_as(i32p), mark.ctypes.data_as(u8p), i64(T), i64(n), i64(ld), i64(K), i64(bs)) == 0
+    assert np.array_equal(gs.view(np.uint32), O.ds41_cand_mask(score.copy(), cand, n, bs).view(np.uint32))
+    kp = 33
+    selc = np.stack([np.sort(rng.choice(K * 8, size=kp, replace=False)) for _ in range(T)]).astype(np.int32)
+    cand_ok = np.where(cand < 0, 0, cand).astype(np.int32)
+    gsel = np.zeros((T, kp), np.int32)
+    assert ref.ns_ds41_cand_pos(g(), selc.ctypes.data_as(i32p), cand_ok.ctypes.data_as(i32p), gsel.ctypes.data_as(i32p), i64(T), i64(K), i64(kp), i64(bs)) == 0
+    assert np.array_equal(gsel, O.ds41_cand_pos(selc, cand_ok, bs))
+
+
+@pytest.mark.parametrize("T,Hq,Hkv,kv", [(1, 16, 2, 900), (1, 64, 8, 3000), (4, 32, 4, 700), (8, 8, 1, 40)])
+def test_nemotronh_attention_kernel(T, Hq, Hkv, kv):
+    """ns_nh_attn (kernels/llm/nemotronh/nh.cpp: attn<8, 8>, heads of 128, eight query heads a work-group) - the only reference
+    kernel there is for the head width of benchmark configurations 2 and 5 - against orc_gqa_plain with its grouping. To the bit."""
+    nh = O.ref_nh_lib()
+    D = 128
+    q, k, v, p0 = W.gqa_case(951, T, Hq, Hkv, D, kv)
+    qf = q.astype(np.float32)
+    n = nh.ns_nh_attn_scratch(i64(T), i64(Hq), i64(Hkv), i64(D), i64(p0))
+    sc = np.zeros(max(1, n), np.float32)
+    got = np.zeros((T, Hq * D), np.float32)
+    rc = nh.ns_nh_attn(C.c_void_p(nh.ref_gpu()), qf.ctypes.data_as(f32p), i64(Hq * D), k.view(np.uint16).ctypes.data_as(u16p),
+                       v.view(np.uint16).ctypes.data_as(u16p), i64(T), i64(Hq), i64(Hkv), i64(D), i64(kv), i64(p0), got.ctypes.data_as(f32p), sc.ctypes.data_as(f32p))
+    assert rc == 0, nh.ref_error()
+    want = O.gqa_plain(qf, k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, kv, p0, groups=Hq // 8)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("kt,mode", [(0, 0), (1, 0), (2, 1), (0, 1)])
+def test_attention_weights_kernel(kt, mode):
+    """ns_q35_attn_probs (q35.cpp: one row's softmax weights per key over a cache of any form) against orc_q35_attn_probs."""
+    Hq, Hkv, cap, n = 12, 2, 300, 270
+    rb = O.q_row_bytes(kt)
+    k = W.rng(1280, kt).standard_normal((cap, Hkv * 256)).astype(np.float32)
+    if kt == 0:
+        kc = np.ascontiguousarray(k.reshape(cap, Hkv, 256).transpose(1, 0, 2)).astype(np.float16).view(np.uint8).reshape(Hkv, cap, 512)
+    else:
+        kc, junk = np.zeros((Hkv, cap, rb), np.uint8), np.zeros((Hkv, cap, rb), np.uint8)
+        O.kv_store_q(kt, k, k, cap, Hkv, cap, 0, kc, junk)
+    q = W.rng(1285, kt).standard_normal(Hq * 256).astype(np.float32)
+    before = W.rng(1286, 0).random(n).astype(np.float32)
+    got, gsc = before.copy(), np.zeros((Hq, 2), np.float32)
+    rc = ref.ns_q35_attn_probs(g(), C.c_int(kt), q.ctypes.data_as(f32p), kc.ctypes.data_as(C.c_void_p), i64(Hq), i64(Hkv), i64(256), i64(cap), i64(n), C.c_int(mode),
+                               gsc.ctypes.data_as(f32p), got.ctypes.data_as(f32p))
+    assert rc == 0, ref.ref_error()
+    want = before.copy()
+    wsc = O.q35_attn_probs(kt, q, kc, Hq, Hkv, cap, n, mode, want)
+    close(got, want, 2e-6, "weights")
+    close(gsc, wsc, 2e-5, "the heads' maxima and sums")
