@@ -114,13 +114,14 @@ void flash_range(const float* qh, const uint16_t* K, const uint16_t* V, int D, i
         }
         const float mn = std::fmax(m, mx);
         const float c = mn == NEG_INF ? 1.0f : std::exp2(m - mn);   // attn.cpp:219-220
-        float sum = 0.f;
+        float part[4] = {0.f, 0.f, 0.f, 0.f};   // 4 lanes a row, 4 keys a lane, then the lanes' sums pairwise (attn.cpp:224-231)
         float p16[16];
         for (int n = 0; n < 16; ++n) {
             const float pv = s[n] == NEG_INF ? 0.f : std::exp2(s[n] - mn);
-            sum += pv;               // the denominator takes the unrounded weight (attn.cpp:225-233)
+            part[n / 4] += pv;       // the denominator takes the unrounded weight (attn.cpp:225-233)
             p16[n] = round_h(pv);    // the numerator the fp16 one (attn.cpp:227)
         }
+        const float sum = (part[0] + part[1]) + (part[2] + part[3]);
         l = l * c + sum;
         for (int d = 0; d < D; ++d) O[d] *= c;   // attn.cpp:244
         for (int n = 0; n < 16; ++n) {

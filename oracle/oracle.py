@@ -91,6 +91,22 @@ def ref_nh_lib():
     return _ref_nh
 
 
+_units = {}
+
+
+def ref_unit(name):
+    """Another unit of the reference's kernels compiled for the CPU (oracle/_ref/lib<name>.so), or None when not built."""
+    if name not in _units:
+        so = os.path.join(_HERE, "_ref", "lib" + name + ".so")
+        if not os.path.exists(so):
+            return None
+        u = C.CDLL(so)
+        u.ref_gpu.restype = C.c_void_p
+        u.ref_error.restype = C.c_char_p
+        _units[name] = u
+    return _units[name]
+
+
 def threads():
     return int(lib().orc_threads())
 

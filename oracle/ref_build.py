@@ -18,7 +18,7 @@ OUT = os.path.join(HERE, "_ref")
 
 # (file within the checkout, first line of the piece as a regular expression, how the piece ends)
 #   "brace": through the first following line that is a lone "}" (a function or template at file level)
-#   "line": that one line
+#   "line": that one line; "brace2": two lines; a number: that many lines; "struct": through the first lone "};"
 PIECES = [
     ("kernels/llm/qwen35/q35.cpp", r"^constexpr int SG = 16;", "line"),
     ("kernels/llm/qwen35/q35.cpp", r"^inline float kv_value\(", "brace"),
@@ -88,8 +88,37 @@ PIECES_NH = [
     ("kernels/llm/nemotronh/nh.cpp", r"^int ns_nh_attn\(", "brace"),
 ]
 
+# the matrix-unit form of qwen35's attention (prompt blocks of 8 rows, and decode rows split over the keys), on the host's
+# joint_matrix stand-in
+PIECES_Q35X = [
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^namespace jm = ", "line"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^#ifndef Q35_ATTN_CH", 3),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^#ifndef Q35_ATTN_KPAD", 3),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^constexpr int D = 256, HALF_D = 128, SG = 16, M = 8,", "line"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^template <int KT> constexpr int64_t kv_row\(\)", "line"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^template <int KT>$", "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", (r"^template <typename T>$", r"^inline auto lp\("), "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", (r"^template <typename T>$", r"^inline auto gp\("), "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", (r"^template <int G>$", r"^struct Slm \{"), "struct"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^int64_t dec_splits\(int64_t kv, int64_t Hkv\);", "line"),
+    ("kernels/llm/qwen35/silo/attn.cpp", (r"^template <int G, bool SPLIT, int KT>$", r"^void attn_flash\("), "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", (r"^template <int G, int KT>$", r"^void attn_prompt\("), "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^constexpr int KEYS_D = 64;", "line"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^int64_t dec_split\(", "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^int64_t dec_splits\(int64_t kv, int64_t Hkv\) \{", "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", (r"^template <int G, int KT>$", r"^void flash_decode\("), "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^int ns_q35_attn_prompt_supported\(", "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^int ns_q35_attn_prompt\(", "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^int ns_q35_attn_prompt_kv\(", "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^int ns_q35_attn_decode_supported\(", "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^int64_t ns_q35_attn_decode_scratch\(", "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^int ns_q35_attn_decode\(", "brace"),
+    ("kernels/llm/qwen35/silo/attn.cpp", r"^int ns_q35_attn_decode_kv\(", "brace"),
+]
+
 HEAD = r'''// GENERATED by oracle/ref_build.py from a nextsycl checkout: the reference's own lines between the markers. Not committed.
 #include <sycl/sycl.hpp>
+#include <sycl/ext/oneapi/matrix/matrix.hpp>
 #include <cstdint>
 #include <cstdlib>
 #include <string>
@@ -139,8 +168,10 @@ def take(lines, start_re, how, path):
                 return lines[i:i + 1]
             if how == "brace2":
                 return lines[i:i + 2]
+            if isinstance(how, int):
+                return lines[i:i + how]
             for j in range(i + 1, len(lines)):
-                if lines[j].rstrip() == "}":
+                if lines[j].rstrip() == ("};" if how == "struct" else "}"):
                     return lines[i:j + 1]
             break
     raise SystemExit(f"ref_build: the piece {start_re!r} was not found in {path} (the checkout differs from the one this was written against)")
@@ -177,6 +208,7 @@ void* ref_gpu() { static ns_gpu g; return &g; }
 
 def build(checkout):
     build_unit(checkout, PIECES_NH, TAIL_NH, "ref_nh")
+    build_unit(checkout, PIECES_Q35X, TAIL_NH, "ref_q35x")
     return build_unit(checkout, PIECES, TAIL, "ref")
 
 

@@ -1,6 +1,6 @@
-// A host stand-in for the SYCL names that the reference's non-matrix kernels use, so that those kernels - the reference's
-// own source lines, taken from its checkout at build time - compile with g++ and run on the CPU as a check on this
-// repository's oracle. Test infrastructure only.
+// A host stand-in for the SYCL names that the reference's kernels use, so that those kernels - the reference's own source
+// lines, taken from its checkout at build time - compile with g++ and run on the CPU as a check on this repository's
+// oracle. Test infrastructure only. (joint_matrix, for the matrix-unit kernels: sycl/ext/oneapi/matrix/matrix.hpp.)
 //
 // What it covers: sycl::half (IEEE binary16, round to nearest even), vec, uint2 / uint4, bit_cast, the math functions the
 // kernels call, queue::submit / parallel_for over range<1..3> (plain loops) and over nd_range<1> with work-groups:
@@ -8,7 +8,7 @@
 // sub-group. A work-group runs as one cooperative fiber (ucontext) a work-item, scheduled round-robin by the calling
 // thread: a work-item runs until it reaches a collective, and the collective completes when every member has arrived, so
 // execution is deterministic. A reduction folds the members' values in the order of their indices.
-// What it does not cover: joint_matrix (the matrix units), ESIMD, images, USM allocation, atomics, events.
+// What it does not cover: ESIMD, images, USM allocation, events, oneMKL.
 // The sub-group size of the next launch is a setting (sycl::detail::sub_group_size()), because g++ ignores the
 // [[sycl::reqd_sub_group_size]] attribute the kernels carry.
 #pragma once
@@ -349,7 +349,16 @@ struct local_accessor {
     local_accessor(range<1> r, handler&) : mem(std::make_shared<std::vector<T>>(r.n[0])) {}
     T& operator[](size_t i) const { return (*mem)[i]; }
     T* get_pointer() const { return mem->data(); }
+    struct raw_ptr {
+        T* p;
+        T* get() const { return p; }
+    };
+    template <access::decorated>
+    raw_ptr get_multi_ptr() const { return raw_ptr{mem->data()}; }
 };
+// one address space on the host: the cast is the pointer itself
+template <access::address_space, access::decorated, class T>
+T* address_space_cast(T* p) { return p; }
 
 struct queue {
     template <class F>

@@ -553,3 +553,83 @@ def test_attention_weights_kernel(kt, mode):
     wsc = O.q35_attn_probs(kt, q, kc, Hq, Hkv, cap, n, mode, want)
     close(got, want, 2e-6, "weights")
     close(gsc, wsc, 2e-5, "the heads' maxima and sums")
+
+
+# ---- the matrix-unit kernels (joint_matrix on the host stand-in: a product row summed over its 16 terms in order) ----
+q35x = O.ref_unit("ref_q35x")
+needs_q35x = pytest.mark.skipif(q35x is None, reason="oracle/_ref/libref_q35x.so not built (no reference checkout)")
+
+
+def _gqa256(seed, T, Hkv, p0, spare=3):
+    Hq, cap = 6 * Hkv, p0 + T + spare
+    r = W.rng(seed, T * 1000 + p0)
+    q = r.standard_normal((T, Hq * 256), dtype=np.float32)
+    k = (r.standard_normal((Hkv, cap, 256)) * 0.5).astype(np.float16)
+    v = (r.standard_normal((Hkv, cap, 256)) * 0.5).astype(np.float16)
+    return q, k, v, Hq, cap
+
+
+@needs_q35x
+@pytest.mark.parametrize("T,Hkv,p0", [(9, 1, 0), (16, 1, 0), (13, 2, 37), (24, 1, 100), (40, 2, 5)])
+def test_matrix_unit_prompt_kernel(T, Hkv, p0):
+    """ns_q35_attn_prompt (kernels/llm/qwen35/silo/attn.cpp: attn_flash<6, false, 0>, blocks of 8 rows over chunks of 16
+    keys) - the reference's lines - against orc_gqa_flash_prefill. Equal to the bit: whole and partial row blocks, rows
+    whose chunks run past their own last key, a prefix already in the cache."""
+    q, k, v, Hq, cap = _gqa256(960, T, Hkv, p0)
+    assert q35x.ns_q35_attn_prompt_supported(i64(T), i64(Hq), i64(Hkv), i64(256)) == 1
+    got = np.full((T, Hq * 256), np.nan, np.float32)
+    rc = q35x.ns_q35_attn_prompt(C.c_void_p(q35x.ref_gpu()), q.ctypes.data_as(f32p), i64(Hq * 256), k.ctypes.data_as(u16p), v.ctypes.data_as(u16p), i64(T),
+                                 i64(Hq), i64(Hkv), i64(256), i64(cap), i64(p0), got.ctypes.data_as(f32p))
+    assert rc == 0, q35x.ref_error()
+    want = O.gqa_flash_prefill(q, k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, 256, cap, p0)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@needs_q35x
+@pytest.mark.parametrize("T,Hkv,p0", [(1, 1, 0), (1, 2, 299), (3, 1, 1000), (8, 2, 60), (2, 1, 63), (4, 1, 126), (1, 4, 2500)])
+def test_matrix_unit_decode_kernel(T, Hkv, p0):
+    """ns_q35_attn_decode (silo/attn.cpp: flash_decode - attn_flash<6, true, 0> a (key head, split), the merge kernel)
+    against orc_gqa_flash_decode, to the bit, scratch size and scratch contents included: one split and many, rows whose
+    split sizes differ (a context crossing a split step: the row-at-a-time form), a verify pass of 8 rows."""
+    q, k, v, Hq, cap = _gqa256(961, T, Hkv, p0)
+    q35x.ns_q35_attn_decode_scratch.restype = i64
+    n = q35x.ns_q35_attn_decode_scratch(i64(T), i64(Hq), i64(Hkv), i64(256), i64(p0))
+    ns = max(O.flash_splits(p0 + r + 1, Hkv) for r in range(T))
+    assert n == (T * Hq * ns * 258 if ns > 1 else 0)
+    sc = np.zeros(max(1, n), np.float32)
+    got = np.full((T, Hq * 256), np.nan, np.float32)
+    rc = q35x.ns_q35_attn_decode(C.c_void_p(q35x.ref_gpu()), q.ctypes.data_as(f32p), i64(Hq * 256), k.ctypes.data_as(u16p), v.ctypes.data_as(u16p), i64(T),
+                                 i64(Hq), i64(Hkv), i64(256), i64(cap), i64(p0), got.ctypes.data_as(f32p), sc.ctypes.data_as(f32p))
+    assert rc == 0, q35x.ref_error()
+    want = O.gqa_flash_decode(q, k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, 256, cap, p0)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@needs_q35x
+@pytest.mark.parametrize("kt", [1, 2])
+def test_matrix_unit_kernels_over_quantised_caches(kt):
+    """ns_q35_attn_prompt_kv and ns_q35_attn_decode_kv with q8_0 and q4_0 caches: the kernel reads a row through kv_load8,
+    so it equals - to the bit - the oracle over orc_kv_dequant's fp16 values of the same cache bytes."""
+    Hkv, Hq = 2, 12
+    for T, p0, fn in [(11, 20, "prompt"), (2, 150, "decode")]:
+        cap = p0 + T
+        r = W.rng(962, kt * 10 + T)
+        q = r.standard_normal((T, Hq * 256), dtype=np.float32)
+        rows = r.standard_normal((cap, Hkv * 256), dtype=np.float32)
+        rb = O.q_row_bytes(kt)
+        kc, vc = (np.zeros((Hkv, cap, rb), np.uint8) for _ in range(2))
+        O.kv_store_q(kt, rows, np.ascontiguousarray(rows[::-1]), cap, Hkv, cap, 0, kc, vc)
+        got = np.full((T, Hq * 256), np.nan, np.float32)
+        gq = C.c_void_p(q35x.ref_gpu())
+        if fn == "prompt":
+            rc = q35x.ns_q35_attn_prompt_kv(gq, C.c_int(kt), q.ctypes.data_as(f32p), i64(Hq * 256), kc.ctypes.data_as(u8p), vc.ctypes.data_as(u8p), i64(T), i64(Hq),
+                                            i64(Hkv), i64(256), i64(cap), i64(p0), got.ctypes.data_as(f32p))
+        else:
+            q35x.ns_q35_attn_decode_scratch.restype = i64
+            sc = np.zeros(max(1, q35x.ns_q35_attn_decode_scratch(i64(T), i64(Hq), i64(Hkv), i64(256), i64(p0))), np.float32)
+            rc = q35x.ns_q35_attn_decode_kv(gq, C.c_int(kt), q.ctypes.data_as(f32p), i64(Hq * 256), kc.ctypes.data_as(u8p), vc.ctypes.data_as(u8p), i64(T), i64(Hq),
+                                            i64(Hkv), i64(256), i64(cap), i64(p0), got.ctypes.data_as(f32p), sc.ctypes.data_as(f32p))
+        assert rc == 0, q35x.ref_error()
+        kd, vd = O.kv_dequant(kt, kc, Hkv, cap, cap), O.kv_dequant(kt, vc, Hkv, cap, cap)
+        want = (O.gqa_flash_prefill if fn == "prompt" else O.gqa_flash_decode)(q, kd, vd, T, Hq, Hkv, 256, cap, p0)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), fn
