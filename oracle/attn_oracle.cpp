@@ -667,8 +667,10 @@ void orc_mla_dec512(const float* qa, const void* cv, float* u, int64_t T, int64_
 //   mode 0, the vector kernel (kernels/llm/deepseek41/silo/ds41.cpp:139-229): fp32 q, scores (q . c) * scale, the
 //     maximum starts from the sink, natural exp, denominator sum + exp(sink - mx).
 //   mode 1, the XMX kernel (silo/attn.cpp:64-259 and the merge :266-285): q scaled by scale*log2(e) and rounded to fp16,
-//     chunks of 16 cells ascending, exp2, weights rounded to fp16 for the numerator, then
-//     out = O 2^(m - mx) / (l 2^(m - mx) + 2^(sink*log2e - mx)), mx = max(m, sink*log2e).
+//     chunks of 16 cells ascending, exp2, weights rounded to fp16 for the numerator; as ns_ds41_attend_xmx runs it
+//     (attn.cpp:307-352): more than 8 rows, a row's cells in one pass and out = O / (l + 2^(sink*log2e - m)); up to 8
+//     rows, the cells in splits and out = sum_k O_k 2^(m_k - mx) / (2^(sink*log2e - mx) + sum_k l_k 2^(m_k - mx)),
+//     mx = max(sink*log2e, m_k).
 void orc_ds41_attend(const float* q, const uint16_t* raw, int64_t R, const uint16_t* comp, int64_t ratio, const int32_t* sel, int64_t K,
                      const float* sinks, float* out, int64_t T, int64_t H, int64_t pos0, int64_t window, float scale, int mode) {
     const int64_t D = 512;
@@ -709,38 +711,79 @@ void orc_ds41_attend(const float* q, const uint16_t* raw, int64_t R, const uint1
                 }
                 for (int64_t r = 0; r < D; ++r) o[r] = acc[r] / sum;
             } else {
-                std::vector<float> qh((size_t) D), O((size_t) D, 0.f);
+                std::vector<float> qh((size_t) D);
                 for (int64_t r = 0; r < D; ++r) qh[r] = round_h(qr[r] * (scale * LOG2E));
-                float m = NEG_INF, l = 0.f;
-                for (int64_t j0 = 0; j0 < n; j0 += 16) {
-                    float s[16], mxc = NEG_INF;
-                    for (int c = 0; c < 16; ++c) {
-                        s[c] = NEG_INF;
-                        if (j0 + c < n) {
-                            const uint16_t* cc = cell(j0 + c);
-                            float d = 0.f;
-                            for (int64_t r = 0; r < D; ++r) d += qh[r] * h2f(cc[r]);
-                            s[c] = d;
+                // cells [jbeg, jend) in chunks of 16 from jbeg: a score the sum of its four quarters' partial dot products
+                // (attn.cpp:182), the chunk's sum 8 lanes of 2 cells each, then pairwise (attn.cpp:197-204)
+                auto range = [&](int64_t jbeg, int64_t jend, float& m, float& l, float* O) {
+                    for (int64_t j0 = jbeg; j0 < jend; j0 += 16) {
+                        float s[16], mxc = NEG_INF;
+                        for (int c = 0; c < 16; ++c) {
+                            s[c] = NEG_INF;
+                            if (j0 + c < jend) {
+                                const uint16_t* cc = cell(j0 + c);
+                                float v = 0.f;
+                                for (int q4 = 0; q4 < 4; ++q4) {
+                                    float d = 0.f;
+                                    for (int64_t r = 128 * q4; r < 128 * (q4 + 1); ++r) d += qh[r] * h2f(cc[r]);
+                                    v += d;
+                                }
+                                s[c] = v;
+                            }
+                            mxc = std::fmax(mxc, s[c]);
                         }
-                        mxc = std::fmax(mxc, s[c]);
+                        const float mn = std::fmax(m, mxc), cf = mn == NEG_INF ? 1.f : std::exp2(m - mn);
+                        for (int64_t r = 0; r < D; ++r) O[r] *= cf;
+                        float lane[8];
+                        for (int c = 0; c < 16; ++c) {
+                            const float pv = s[c] == NEG_INF ? 0.f : std::exp2(s[c] - mn);
+                            lane[c / 2] = c % 2 ? lane[c / 2] + pv : pv;
+                            if (s[c] == NEG_INF) continue;
+                            const float pr = round_h(pv);
+                            const uint16_t* cc = cell(j0 + c);
+                            for (int64_t r = 0; r < D; ++r) O[r] += pr * h2f(cc[r]);
+                        }
+                        const float sum = ((lane[0] + lane[1]) + (lane[2] + lane[3])) + ((lane[4] + lane[5]) + (lane[6] + lane[7]));
+                        l = l * cf + sum;
+                        m = mn;
                     }
-                    const float mn = std::fmax(m, mxc), cf = mn == NEG_INF ? 1.f : std::exp2(m - mn);
-                    for (int64_t r = 0; r < D; ++r) O[r] *= cf;
-                    float sum = 0.f;
-                    for (int c = 0; c < 16; ++c) {
-                        if (s[c] == NEG_INF) continue;
-                        const float pv = std::exp2(s[c] - mn);
-                        sum += pv;
-                        const float pr = round_h(pv);
-                        const uint16_t* cc = cell(j0 + c);
-                        for (int64_t r = 0; r < D; ++r) O[r] += pr * h2f(cc[r]);
+                };
+                const float sk = sinks[h] * LOG2E;
+                if (T > 8) {
+                    // a prompt pass: one work-group a row's head group, all its cells; the sink joins the sum (attn.cpp:247-255)
+                    std::vector<float> O((size_t) D, 0.f);
+                    float m = NEG_INF, l = 0.f;
+                    range(0, n, m, l, O.data());
+                    l += std::exp2(sk - m);
+                    for (int64_t r = 0; r < D; ++r) o[r] = O[r] / l;
+                } else {
+                    // decode rows (at most 8): the row's cells in splits sized from its own count alone - at most 64 of them,
+                    // at least 32 cells, a multiple of 16 (attn.cpp:325-329) -, then the merge with the sink (attn.cpp:266-285)
+                    int64_t kb = std::max<int64_t>(32, (n + 63) / 64);
+                    kb = (kb + 15) / 16 * 16;
+                    const int64_t nsr = (n + kb - 1) / kb;
+                    std::vector<float> P((size_t) nsr * (D + 2), 0.f);
+                    float mx = sk;
+                    for (int64_t k = 0; k < nsr; ++k) {
+                        float* O = P.data() + k * (D + 2);
+                        float m = NEG_INF, l = 0.f;
+                        range(k * kb, std::min(n, (k + 1) * kb), m, l, O);
+                        O[D] = m;
+                        O[D + 1] = l;
+                        mx = std::fmax(mx, m);
                     }
-                    l = l * cf + sum;
-                    m = mn;
+                    float Ls = std::exp2(sk - mx);
+                    std::vector<float> e((size_t) nsr);
+                    for (int64_t k = 0; k < nsr; ++k) {
+                        e[k] = std::exp2(P[k * (D + 2) + D] - mx);
+                        Ls += P[k * (D + 2) + D + 1] * e[k];
+                    }
+                    for (int64_t r = 0; r < D; ++r) {
+                        float A = 0.f;
+                        for (int64_t k = 0; k < nsr; ++k) A += P[k * (D + 2) + r] * e[k];
+                        o[r] = A / Ls;
+                    }
                 }
-                const float sk = sinks[h] * LOG2E, mx = std::fmax(m, sk);
-                const float f = std::exp2(m - mx), den = l * f + std::exp2(sk - mx);
-                for (int64_t r = 0; r < D; ++r) o[r] = O[r] * f / den;
             }
         }
     }

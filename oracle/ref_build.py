@@ -116,21 +116,43 @@ PIECES_Q35X = [
     ("kernels/llm/qwen35/silo/attn.cpp", r"^int ns_q35_attn_decode_kv\(", "brace"),
 ]
 
+# deepseek41's attention on the matrix units: the prompt form and decode's split form with its merge
+PIECES_DS41X = [
+    ("kernels/llm/deepseek41/silo/attn.cpp", r"^namespace jm = ", "line"),
+    ("kernels/llm/deepseek41/silo/attn.cpp", r"^#ifndef DS4_ATTN_CH$", 3),
+    ("kernels/llm/deepseek41/silo/attn.cpp", r"^#ifndef DS4_ATTN_CH_DEC$", 3),
+    ("kernels/llm/deepseek41/silo/attn.cpp", r"^constexpr int D = 512, QD = 128,", "line"),
+    ("kernels/llm/deepseek41/silo/attn.cpp", r"^constexpr float LOG2E = ", "line"),
+    ("kernels/llm/deepseek41/silo/attn.cpp", (r"^template <typename T>$", r"^inline auto lp\("), "brace"),
+    ("kernels/llm/deepseek41/silo/attn.cpp", (r"^template <typename T>$", r"^inline auto gp\("), "brace"),
+    ("kernels/llm/deepseek41/silo/attn.cpp", (r"^template <int G, int C>$", r"^struct Slm \{"), "struct"),
+    ("kernels/llm/deepseek41/silo/attn.cpp", r"^constexpr int PS = D \+ 16;", "line"),
+    ("kernels/llm/deepseek41/silo/attn.cpp", (r"^template <int G, bool SPLIT, int C = CH>$", r"^void attend_xmx\("), "brace"),
+    ("kernels/llm/deepseek41/silo/attn.cpp", r"^void attend_q16\(", "brace"),
+    ("kernels/llm/deepseek41/silo/attn.cpp", r"^void attend_merge\(", "brace"),
+    ("kernels/llm/deepseek41/silo/attn.cpp", r"^float\* part_buf\(", "brace"),
+    ("kernels/llm/deepseek41/silo/attn.cpp", r"^int ns_ds41_attend_xmx_supported\(", "brace"),
+    ("kernels/llm/deepseek41/silo/attn.cpp", r"^int ns_ds41_attend_xmx\(", "brace"),
+]
+
 HEAD = r'''// GENERATED by oracle/ref_build.py from a nextsycl checkout: the reference's own lines between the markers. Not committed.
 #include <sycl/sycl.hpp>
 #include <sycl/ext/oneapi/matrix/matrix.hpp>
 #include <cstdint>
 #include <cstdlib>
+#include <mutex>
 #include <string>
+#include <vector>
 using half = sycl::half;
 struct ns_gpu { sycl::queue q; };
 static std::string ref_last_error;
 static int ns_fail(const std::string& what) { ref_last_error = what; return -1; }
-// the matrix-unit form of deepseek41's attention does not exist on the host: the entry point takes its vector form
-static int ns_ds41_attend_xmx_supported(int64_t, int64_t) { return 0; }
-template <class... A> static int ns_ds41_attend_xmx(A...) { return -1; }
 #define NS_TRY
 #define NS_CATCH
+'''
+# ns_ds41_attend asks whether the matrix-unit form may take the call: in its unit it may not (that form is a unit of its own)
+HEAD_VECTOR_ONLY = r'''static int ns_ds41_attend_xmx_supported(int64_t, int64_t) { return 0; }
+template <class... A> static int ns_ds41_attend_xmx(A...) { return -1; }
 '''
 
 TAIL = r'''
@@ -177,9 +199,9 @@ def take(lines, start_re, how, path):
     raise SystemExit(f"ref_build: the piece {start_re!r} was not found in {path} (the checkout differs from the one this was written against)")
 
 
-def build_unit(checkout, pieces, tail, name):
+def build_unit(checkout, pieces, tail, name, head=""):
     os.makedirs(OUT, exist_ok=True)
-    parts = [HEAD, 'extern "C++" {\n']
+    parts = [HEAD, head, 'extern "C++" {\n']
     for rel, start_re, how in pieces:
         path = os.path.join(checkout, rel)
         with open(path, encoding="utf-8") as f:
@@ -209,7 +231,8 @@ void* ref_gpu() { static ns_gpu g; return &g; }
 def build(checkout):
     build_unit(checkout, PIECES_NH, TAIL_NH, "ref_nh")
     build_unit(checkout, PIECES_Q35X, TAIL_NH, "ref_q35x")
-    return build_unit(checkout, PIECES, TAIL, "ref")
+    build_unit(checkout, PIECES_DS41X, TAIL_NH, "ref_ds41x")
+    return build_unit(checkout, PIECES, TAIL, "ref", HEAD_VECTOR_ONLY)
 
 
 if __name__ == "__main__":

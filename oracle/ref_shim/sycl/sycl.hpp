@@ -19,6 +19,7 @@
 #include <cmath>
 #include <cstddef>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <type_traits>
@@ -438,5 +439,10 @@ void queue::submit(F f) {
     handler h{this};
     f(h);
 }
+
+// device memory is the host's
+template <class T>
+T* malloc_device(size_t n, const queue&) { return static_cast<T*>(std::malloc(n * sizeof(T))); }
+inline void free(void* p, const queue&) { std::free(p); }
 
 }  // namespace sycl

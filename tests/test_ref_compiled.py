@@ -633,3 +633,34 @@ def test_matrix_unit_kernels_over_quantised_caches(kt):
         kd, vd = O.kv_dequant(kt, kc, Hkv, cap, cap), O.kv_dequant(kt, vc, Hkv, cap, cap)
         want = (O.gqa_flash_prefill if fn == "prompt" else O.gqa_flash_decode)(q, kd, vd, T, Hq, Hkv, 256, cap, p0)
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), fn
+
+
+ds41x = O.ref_unit("ref_ds41x")
+
+
+@pytest.mark.skipif(ds41x is None, reason="oracle/_ref/libref_ds41x.so not built (no reference checkout)")
+@pytest.mark.parametrize("T,H,pos0,window,R,ratio,K,with_comp", [
+    (1, 8, 700, 128, 128, 4, 0, False),       # decode, the window alone: splits of 32 cells
+    (1, 16, 2047, 128, 128, 4, 0, True),      # window + every compressed cell: 640 cells in 20 splits
+    (1, 8, 4095, 128, 160, 4, 256, True),     # the indexer's picks, a ring longer than the window
+    (4, 8, 1020, 128, 128, 4, 256, True),     # a verify pass whose rows' split sizes agree, either side of where picks start
+    (3, 8, 0, 16, 16, 128, 0, True),          # the first tokens: 1, 2, 3 cells, one split
+    (8, 8, 8180, 128, 128, 4, 0, True),       # rows whose split sizes differ: a launch a row
+    (9, 8, 300, 64, 64, 4, 0, True),          # more than 8 rows: the prompt form, 2 head groups a work-group -> 1
+    (12, 16, 40, 128, 128, 4, 0, True),       # the prompt form, two head groups a work-group
+    (64, 64, 0, 32, 32, 4, 8, True),          # 64 rows of 64 heads: a work-group all heads; picks from row 35 on
+])
+def test_ds41_matrix_unit_attention(T, H, pos0, window, R, ratio, K, with_comp):
+    """ns_ds41_attend_xmx (kernels/llm/deepseek41/silo/attn.cpp: attend_xmx in its prompt and split forms, attend_q16,
+    attend_merge) - the reference's lines - against orc_ds41_attend in that kernel's numerics (mode 1), to the bit."""
+    q, raw, comp, sel, sinks = _ds41_case(990 + T, T, H, pos0, window, R, ratio, K, with_comp)
+    if comp is None and with_comp:
+        comp = np.zeros((1, 512), np.uint16)
+    assert ds41x.ns_ds41_attend_xmx_supported(i64(H), i64(512)) == 1
+    got = np.full((T, H, 512), np.nan, np.float32)
+    rc = ds41x.ns_ds41_attend_xmx(C.c_void_p(ds41x.ref_gpu()), q.ctypes.data_as(f32p), raw.ctypes.data_as(u16p), i64(R),
+                                  None if comp is None else comp.ctypes.data_as(u16p), i64(ratio), None if sel is None else sel.ctypes.data_as(i32p), i64(K),
+                                  sinks.ctypes.data_as(f32p), got.ctypes.data_as(f32p), i64(T), i64(H), i64(pos0), i64(window), C.c_float(DSCALE))
+    assert rc == 0, ds41x.ref_error()
+    want = O.ds41_attend(q, raw, R, comp, ratio, sel, K, sinks, T, H, pos0, window, DSCALE, mode=1)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"max abs difference {np.abs(got - want).max():.3e}"
