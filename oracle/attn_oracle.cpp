@@ -1176,17 +1176,35 @@ void orc_topk(const float* score, int32_t* sel, int64_t T, int64_t n, int64_t ld
 }
 
 // ---- deepseek41's indexer (kernels/llm/deepseek41/silo/k41.cpp:96-250,352-483) ---------------------------------------
-// score of key j for row t: sum_h w[t][h] relu(q[t][h] . k_j); q fp32 [T][H][D] (half_q: rounded to fp16 first, as the XMX
-// form stages it, k41.cpp:125-128), k fp16 [n][D]
+// score of key j for row t: sum_h w[t][h] relu(q[t][h] . k_j); q fp32 [T][H][D], k fp16 [n][D].
+//   the scalar form (k41.cpp:363-398): fp32 q; a head's dot product the sum of its 16-dim chunks' sums; the heads in order.
+//   half_q, the matrix-unit form (k41.cpp:106-179; 32 heads): q rounded to fp16 as it is staged (k41.cpp:125-128); a head's
+//   dot product one running sum over the dims; lane l takes heads l and l + 16 (k41.cpp:155-162), the 16 lanes' sums added
+//   in lane order.
 static float ds41_key_score(const float* q, const float* w, const uint16_t* k, int64_t t, int64_t j, int64_t H, int64_t D, bool half_q) {
-    float s = 0.f;
+    std::vector<float> term((size_t) H);
     for (int64_t h = 0; h < H; ++h) {
         float acc = 0.f;
-        for (int64_t c = 0; c < D; ++c) {
-            const float qv = q[(t * H + h) * D + c];
-            acc += (half_q ? round_h(qv) : qv) * h2f(k[j * D + c]);
+        if (half_q) {
+            for (int64_t c = 0; c < D; ++c) acc += round_h(q[(t * H + h) * D + c]) * h2f(k[j * D + c]);
+        } else {
+            for (int64_t c0 = 0; c0 < D; c0 += 16) {
+                float part = 0.f;
+                for (int64_t c = c0; c < c0 + 16; ++c) part += q[(t * H + h) * D + c] * h2f(k[j * D + c]);
+                acc += part;
+            }
         }
-        s += std::fmax(acc, 0.f) * w[t * H + h];
+        term[h] = std::fmax(acc, 0.f) * w[t * H + h];
+    }
+    float s = 0.f;
+    if (half_q && H % 16 == 0) {
+        for (int l = 0; l < 16; ++l) {
+            float sv = 0.f;
+            for (int64_t h = l; h < H; h += 16) sv += term[h];
+            s = l == 0 ? sv : s + sv;
+        }
+    } else {
+        for (int64_t h = 0; h < H; ++h) s += term[h];
     }
     return s;
 }

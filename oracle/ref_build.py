@@ -67,6 +67,14 @@ PIECES = [
     ("kernels/llm/deepseek41/silo/ds41.cpp", r"^int ns_ds41_attend\(", "brace"),
     ("kernels/llm/deepseek41/silo/k41.cpp", r"^inline float pow2_ceil\(", "brace"),
     ("kernels/llm/deepseek41/silo/k41.cpp", r"^inline float e4m3_round\(", "brace"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^namespace jmi = ", "line"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^constexpr int IXD = 128, IXH = 32,", "line"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", (r"^template <typename T>$", r"^inline auto ix_lp\("), "brace"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", (r"^template <typename T>$", r"^inline auto ix_gp\("), "brace"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^void idx_score_xmx\(", "brace"),          # the indexer's scores on the matrix units
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^void idx_score_cand_xmx\(", "brace"),
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^int ns_ds41_idx_score\(", "brace"),       # and their scalar form
+    ("kernels/llm/deepseek41/silo/k41.cpp", r"^int ns_ds41_idx_score_cand\(", "brace"),
     ("kernels/llm/deepseek41/silo/k41.cpp", r"^inline float kv_yarn_ramp\(", "brace"),
     ("kernels/llm/deepseek41/silo/k41.cpp", r"^inline void kv_yarn_cs\(", "brace"),
     ("kernels/llm/deepseek41/silo/k41.cpp", r"^int ns_ds41_kv_post\(", "brace"),
@@ -114,6 +122,30 @@ PIECES_Q35X = [
     ("kernels/llm/qwen35/silo/attn.cpp", r"^int64_t ns_q35_attn_decode_scratch\(", "brace"),
     ("kernels/llm/qwen35/silo/attn.cpp", r"^int ns_q35_attn_decode\(", "brace"),
     ("kernels/llm/qwen35/silo/attn.cpp", r"^int ns_q35_attn_decode_kv\(", "brace"),
+]
+
+# nemotronh's attention on the matrix units: heads of 128, 16 query heads a key head
+_NHX = "kernels/llm/nemotronh/silo/attn.cpp"
+PIECES_NHX = [
+    (_NHX, r"^namespace jm = ", "line"),
+    (_NHX, r"^#ifndef NH_ATTN_CH$", 3),
+    (_NHX, r"^#ifndef NH_ATTN_KPAD$", 3),
+    (_NHX, r"^constexpr int D = 128, HALF_D = 64, SG = 16, M = 8,", "line"),
+    (_NHX, (r"^template <typename T>$", r"^inline auto lp\("), "brace"),
+    (_NHX, (r"^template <typename T>$", r"^inline auto gp\("), "brace"),
+    (_NHX, (r"^template <int G>$", r"^struct Slm \{"), "struct"),
+    (_NHX, r"^int64_t dec_splits\(int64_t kv, int64_t Hkv\);", "line"),
+    (_NHX, (r"^template <int G, bool SPLIT>$", r"^void attn_flash\("), "brace"),
+    (_NHX, (r"^template <int G>$", r"^void attn_prompt\("), "brace"),
+    (_NHX, r"^constexpr int KEYS_D = 64;", "line"),
+    (_NHX, r"^int64_t dec_split\(", "brace"),
+    (_NHX, r"^int64_t dec_splits\(int64_t kv, int64_t Hkv\) \{", "brace"),
+    (_NHX, (r"^template <int G>$", r"^void flash_decode\("), "brace"),
+    (_NHX, r"^int ns_nhs_attn_prompt_supported\(", "brace"),
+    (_NHX, r"^int ns_nhs_attn_prompt\(", "brace"),
+    (_NHX, r"^int ns_nhs_attn_decode_supported\(", "brace"),
+    (_NHX, r"^int64_t ns_nhs_attn_decode_scratch\(", "brace"),
+    (_NHX, r"^int ns_nhs_attn_decode\(", "brace"),
 ]
 
 # deepseek41's attention on the matrix units: the prompt form and decode's split form with its merge
@@ -232,6 +264,7 @@ def build(checkout):
     build_unit(checkout, PIECES_NH, TAIL_NH, "ref_nh")
     build_unit(checkout, PIECES_Q35X, TAIL_NH, "ref_q35x")
     build_unit(checkout, PIECES_DS41X, TAIL_NH, "ref_ds41x")
+    build_unit(checkout, PIECES_NHX, TAIL_NH, "ref_nhx")
     return build_unit(checkout, PIECES, TAIL, "ref", HEAD_VECTOR_ONLY)
 
 

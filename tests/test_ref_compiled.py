@@ -664,3 +664,69 @@ def test_ds41_matrix_unit_attention(T, H, pos0, window, R, ratio, K, with_comp):
     assert rc == 0, ds41x.ref_error()
     want = O.ds41_attend(q, raw, R, comp, ratio, sel, K, sinks, T, H, pos0, window, DSCALE, mode=1)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"max abs difference {np.abs(got - want).max():.3e}"
+
+
+nhx = O.ref_unit("ref_nhx")
+
+
+@pytest.mark.skipif(nhx is None, reason="oracle/_ref/libref_nhx.so not built (no reference checkout)")
+@pytest.mark.parametrize("T,Hkv,p0", [(9, 1, 0), (21, 2, 50), (1, 1, 0), (1, 2, 700), (8, 1, 60), (3, 1, 4000)])
+def test_nemotronh_matrix_unit_kernels(T, Hkv, p0):
+    """ns_nhs_attn_prompt and ns_nhs_attn_decode (kernels/llm/nemotronh/silo/attn.cpp: the flash kernel for heads of 128,
+    16 query heads a key head) - the reference's lines - against orc_gqa_flash_prefill / orc_gqa_flash_decode, to the bit."""
+    Hq, D, cap = 16 * Hkv, 128, p0 + T + 2
+    r = W.rng(963, T * 1000 + p0)
+    q = r.standard_normal((T, Hq * D), dtype=np.float32)
+    k = (r.standard_normal((Hkv, cap, D)) * 0.5).astype(np.float16)
+    v = (r.standard_normal((Hkv, cap, D)) * 0.5).astype(np.float16)
+    got = np.full((T, Hq * D), np.nan, np.float32)
+    gq = C.c_void_p(nhx.ref_gpu())
+    if T > 8:
+        rc = nhx.ns_nhs_attn_prompt(gq, q.ctypes.data_as(f32p), i64(Hq * D), k.ctypes.data_as(u16p), v.ctypes.data_as(u16p), i64(T), i64(Hq), i64(Hkv), i64(D),
+                                    i64(cap), i64(p0), got.ctypes.data_as(f32p))
+        want = O.gqa_flash_prefill(q, k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, cap, p0)
+    else:
+        nhx.ns_nhs_attn_decode_scratch.restype = i64
+        sc = np.zeros(max(1, nhx.ns_nhs_attn_decode_scratch(i64(T), i64(Hq), i64(Hkv), i64(D), i64(p0))), np.float32)
+        rc = nhx.ns_nhs_attn_decode(gq, q.ctypes.data_as(f32p), i64(Hq * D), k.ctypes.data_as(u16p), v.ctypes.data_as(u16p), i64(T), i64(Hq), i64(Hkv), i64(D),
+                                    i64(cap), i64(p0), got.ctypes.data_as(f32p), sc.ctypes.data_as(f32p))
+        want = O.gqa_flash_decode(q, k.view(np.uint16), v.view(np.uint16), T, Hq, Hkv, D, cap, p0)
+    assert rc == 0, nhx.ref_error()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"max abs difference {np.abs(got - want).max():.3e}"
+
+
+@pytest.mark.parametrize("T,H,n,ld,pos0,ratio", [
+    (3, 32, 77, 80, 400, 4),       # the matrix-unit form: a last tile read shifted back, keys past the cache's
+    (2, 32, 300, 300, 20, 4),      # rows that see only the first few keys
+    (1, 32, 8, 8, 100, 4),         # one tile
+    (2, 32, 5, 16, 100, 4),        # fewer than 8 keys: the scalar form
+    (2, 16, 90, 96, 1000, 4),      # 16 heads: the scalar form
+])
+def test_ds41_indexer_score_kernels(T, H, n, ld, pos0, ratio):
+    """ns_ds41_idx_score (kernels/llm/deepseek41/silo/k41.cpp: idx_score_xmx for 32 heads of 128 and at least 8 keys, else the
+    scalar kernel) and ns_ds41_idx_score_cand (idx_score_cand_xmx) - the reference's lines - against orc_ds41_idx_score and
+    orc_ds41_idx_score_cand, to the bit."""
+    D = 128
+    r = W.rng(995, n * 10 + T)
+    q = r.standard_normal((T, H, D), dtype=np.float32)
+    w = r.standard_normal((T, H), dtype=np.float32)
+    k = (r.standard_normal((n, D)) * 0.5).astype(np.float16)
+    got = np.full((T, ld), np.nan, np.float32)
+    rc = ref.ns_ds41_idx_score(g(), q.ctypes.data_as(f32p), w.ctypes.data_as(f32p), k.ctypes.data_as(u16p), got.ctypes.data_as(f32p), i64(T), i64(H), i64(D),
+                               i64(n), i64(ld), i64(pos0), i64(ratio))
+    assert rc == 0, ref.ref_error()
+    xmx = H == 32 and n >= 8
+    want = O.ds41_idx_score(q, w, k.view(np.uint16), T, H, D, n, ld, pos0, ratio, half_q=xmx)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"max abs difference {np.nanmax(np.abs(got - want)):.3e}"
+    if not xmx:
+        return
+    nb = (n + 7) // 8
+    K = min(6, nb + 2)
+    cand = np.stack([np.sort(r.choice(nb + 2, size=K, replace=False)).astype(np.int32) - 1 for _ in range(T)])     # -1 and nb among them: no block
+    cand = np.ascontiguousarray(cand)
+    gotc = np.full((T, K * 8), np.nan, np.float32)
+    rc = ref.ns_ds41_idx_score_cand(g(), q.ctypes.data_as(f32p), w.ctypes.data_as(f32p), k.ctypes.data_as(u16p), cand.ctypes.data_as(i32p), i64(K),
+                                    gotc.ctypes.data_as(f32p), i64(T), i64(H), i64(D), i64(n), i64(pos0), i64(ratio))
+    assert rc == 0, ref.ref_error()
+    wantc = O.ds41_idx_score_cand(q, w, k.view(np.uint16), cand, K, T, H, D, n, pos0, ratio)
+    assert np.array_equal(gotc.view(np.uint32), wantc.view(np.uint32))
