@@ -3,23 +3,27 @@
 // TEST INFRASTRUCTURE ONLY. Nothing in the shipped library calls into this file; it is the checker the GPU parity
 // tests, the smoke test and the benchmark's CPU-baseline leg compare against.
 //
-// PARITY: PINNED FOR THE DEEPSEEK-V4.1 FUNCTIONS AND FOR THE CACHE AND ROW FORMATS, UNPINNED FOR THE REST. The reference tree holds no golden vector,
-// known-answer test or fixture for any attention kernel, and its SYCL kernels cannot be compiled without a oneAPI
-// toolchain. It does hold one importable CPU implementation of arithmetic on this path, reference/deepseek41/ds41ref.py;
-// tests/golden/make_ref_fixtures.py runs that code (its fp8_sim, rms, freqs, rope and its Ref.attention, on seeded weights)
-// and tests/test_oracle.py holds to its output: orc_ds41_attend (both numerics), orc_ds41_kv_post and orc_ds41_att_post
-// (bit for bit), the E4M3 simulation (bit for bit), the YaRN rotation, orc_ds41_idx_score, orc_ds41_block_max and
-// orc_topk. A second pin is the reference's own C++: its simplest kernels - loops over independent work-items - compile for
-// the CPU behind a host stand-in for the SYCL names they use (oracle/ref_build.py takes their lines out of a checkout at build
-// time; nothing of them is kept here), and tests/test_ref_compiled.py holds to them bit for bit: orc_kv_store (ns_q35_kv_store),
-// orc_kv_store_q (ns_q35_kv_store_q, q8_0 and q4_0), orc_kv_dequant (the attention kernel's row reader kv_load8),
-// orc_fwht32 (ns_q35_fwht32), orc_q6k_rows (deepseek2's q6k_cols32), orc_to_q8row (ns_to_q8row; and ns_gather_q8_h,
-// ns_to_f16, ns_ds41_rows_f16 against the roundings the tests state). The attention arithmetic of the GQA, deepseek2 and
-// glm5next functions remains UNPINNED (their kernels use work-group barriers, reductions and matrix units, which that
-// stand-in does not provide): each restates the arithmetic of the reference
-// file and lines it cites (where values are rounded, in which order chunks are visited, which exponential is used) and
-// is checked only against an independent numpy statement of softmax attention and its own fp64 mode. The summation
-// order inside one matrix tile is hardware-defined in the reference and is a plain sequential fp32 sum here.
+// PARITY: PINNED TO THE REFERENCE'S OWN KERNELS RUN FROM SOURCE, except where the reference calls oneMKL. The reference tree
+// holds no golden vector, known-answer test or fixture for any attention kernel, and its SYCL tree cannot be built without a
+// oneAPI toolchain. Two pins stand in:
+//   1. its one importable CPU implementation of arithmetic on this path, reference/deepseek41/ds41ref.py:
+//      tests/golden/make_ref_fixtures.py runs that code (its fp8_sim, rms, freqs, rope and its Ref.attention, on seeded weights)
+//      and tests/test_oracle.py holds to its output orc_ds41_attend (both numerics), orc_ds41_kv_post and orc_ds41_att_post (bit
+//      for bit), the E4M3 simulation (bit for bit), the YaRN rotation, orc_ds41_idx_score, orc_ds41_block_max and orc_topk;
+//   2. its own C++ kernels, compiled for the CPU behind a host stand-in for the SYCL names they use - work-groups as
+//      cooperative fibers with barriers, sub-groups, group reductions and shuffles, local memory, and joint_matrix with a
+//      tile's 16 products added in ascending k (oracle/ref_shim/; oracle/ref_build.py takes the kernels' lines out of a
+//      checkout at build time, nothing of them is kept here). tests/test_ref_compiled.py holds to them, bit for bit:
+//      orc_gqa_flash_prefill and orc_gqa_flash_decode (attn_flash / flash_decode of qwen35's and nemotronh's silo/attn.cpp,
+//      fp16, q8_0 and q4_0 caches), orc_gqa_plain (attn of q35.cpp and nh.cpp), orc_ds41_attend mode 1 (attend_xmx,
+//      attend_merge), orc_ds41_idx_score(_cand) (k41.cpp, both forms), orc_kv_store, orc_kv_store_q, orc_kv_dequant,
+//      orc_fwht32, orc_q6k_rows, orc_to_q8row, orc_topk's selections; and within 2e-5 of the largest magnitude:
+//      orc_mla_fused (ds2.cpp's fused decode), orc_mla_attend_f32, orc_mla_dec512 (glm.cpp), orc_ds41_attend mode 0,
+//      orc_qk_norm_rope, orc_ds2_rope, orc_ds2_kv_store, orc_q35_attn_probs, orc_idx_pool, orc_idx_score, the deepseek41
+//      steps around attention.
+// UNPINNED: orc_gemm_batch_h and orc_mla_gemm - the reference computes these with oneMKL (closed source, not in the image) from
+// its Rust engine; they restate fp16 operands with wide accumulation and the engine's sequence of calls. The order in which
+// the matrix unit adds a tile's 16 products is not published either; it is ascending k here and in the stand-in.
 //
 // Storage: fp16 / bf16 values travel as raw uint16_t bit patterns. All functions are pure (no global state) and
 // parallelise over (row, head) with OpenMP only, so a result does not depend on the thread count.

@@ -2,9 +2,10 @@
 
 TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke test and by the benchmark's CPU-baseline leg, never by the
 library. Parity: the deepseek41 functions are pinned to fixtures produced by running the reference's own Python
-(tests/golden/make_ref_fixtures.py), the cache and row formats to the reference's own kernels compiled for the CPU
-(`build_ref`, tests/test_ref_compiled.py); the attention arithmetic of the rest is unpinned - the reference holds no golden
-vectors for it (see attn_oracle.cpp's header).
+(tests/golden/make_ref_fixtures.py), and every function whose reference kernel has its source in the tree to that kernel,
+compiled for the CPU behind a host stand-in for SYCL work-groups, sub-groups and joint_matrix (`build_ref`, `ref_lib`,
+`ref_nh_lib`, `ref_unit`; tests/test_ref_compiled.py); the steps the reference computes with oneMKL are unpinned (see
+attn_oracle.cpp's header).
 
 Arrays are numpy: fp32 as float32, fp16 / bf16 storage as uint16 bit patterns (`np.float16.view(np.uint16)` for fp16;
 `to_bf16_bits` below for bf16).

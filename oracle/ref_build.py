@@ -1,13 +1,15 @@
-"""Builds oracle/_ref/libref.so: a few of the reference's own kernels, compiled for the CPU as a check on the oracle.
+"""Builds oracle/_ref/lib*.so: the reference's own attention kernels, compiled for the CPU as a check on the oracle.
 
     python oracle/ref_build.py <path of a nextsycl checkout>
 
-The reference's kernels are SYCL; its tree cannot be built without a SYCL toolchain. Its simplest kernels, though - the
-cache writers and readers, the 32-point rotation, the Q6_K row reader, the fp16 and q8 latent-row conversions - are plain
-loops over independent work-items. This script takes exactly those functions' source lines out of the checkout (nothing
-of them is kept in this repository: the generated translation unit lives under oracle/_ref/, which is not committed),
-puts them behind a small host stand-in for the SYCL names they use (oracle/ref_shim/), and compiles the result with g++.
-tests/test_ref_compiled.py then holds the oracle to the reference's own code, bit for bit. Test infrastructure only."""
+The reference's kernels are SYCL; its tree cannot be built without a SYCL toolchain and oneMKL. A kernel, though, is C++
+once the SYCL names it uses exist. This script takes the kernels' source lines out of the checkout (nothing of them is kept
+in this repository: the generated translation units live under oracle/_ref/, which is not committed), puts them behind a
+host stand-in for those names (oracle/ref_shim/: work-groups as cooperative fibers, sub-groups, group collectives, local
+memory, joint_matrix), and compiles the result with g++: libref.so (qwen35's q35.cpp, deepseek2, glm5next, deepseek41's
+vector kernels and indexer), libref_nh.so (nemotronh's nh.cpp), and the three matrix-unit attention files, which share
+names, as libref_q35x.so, libref_nhx.so and libref_ds41x.so. tests/test_ref_compiled.py then holds the oracle to the
+reference's own code. Test infrastructure only."""
 import os
 import re
 import subprocess

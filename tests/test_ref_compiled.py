@@ -1,8 +1,9 @@
-"""The oracle against the reference's OWN kernels, compiled for the CPU (oracle/ref_build.py: the cache writers and
-readers, the 32-point rotation, the Q6_K row reader, the fp16 and q8 latent-row conversions - the reference's source lines
-behind a host stand-in for the SYCL names they use). Bit for bit: all of it is byte, integer or single-rounding work.
+"""The oracle against the reference's OWN kernels, compiled for the CPU (oracle/ref_build.py: the reference's source lines
+behind a host stand-in for the SYCL names they use - work-groups as fibers, sub-groups, group collectives, joint_matrix).
+Bit for bit for the byte, integer and single-rounding work and wherever the oracle follows a kernel's summation order (the
+flash, plain and deepseek41 matrix-unit attention, the indexer scores); a stated tolerance elsewhere.
 
-Skipped where oracle/_ref/libref.so was not built (no checkout of the reference beside the repository)."""
+Skipped where oracle/_ref/ was not built (no checkout of the reference beside the repository)."""
 import ctypes as C
 
 import numpy as np
