@@ -58,6 +58,50 @@ struct Smem {
     static constexpr int TOTAL = 1024 /* alignment slack */ + Q_BYTES + NSTAGE * STAGE + BARS;
 };
 
+// P = exp2(S * scale - m_ref) of one thread's HC keys, rounded to the operand type and written to tensor memory at p_addr
+// (16-bit pairs); returns the sum of the unrounded weights. A tile's exponentials are exactly what the special-function
+// unit does in the time the tensor pipe takes for the tile's products (16 a clock against 128 x 128 x 256 flops), so
+// EMU_OF_16 of every 16 pairs take the FMA pipe instead (tc05::ex2_pair_fma), and the scaling and the sum run as packed pairs.
+#ifndef NS_PREFILL_EMU_OF_16
+#define NS_PREFILL_EMU_OF_16 4
+#endif
+template <int HC, int BF16>
+__device__ __forceinline__ float softmax_weights(const float* s, float scale_log2, float neg_m, uint32_t p_addr) {
+    constexpr int EMU = NS_PREFILL_EMU_OF_16;
+    const uint64_t sc2 = pack2(scale_log2, scale_log2), nm2 = pack2(neg_m, neg_m);
+    uint64_t sum2 = pack2(0.f, 0.f);
+#pragma unroll
+    for (int c = 0; c < HC / 32; ++c) {
+        uint32_t w[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const uint64_t x2 = fma2(pack2(s[c * 32 + 2 * e], s[c * 32 + 2 * e + 1]), sc2, nm2);
+            float a, b;
+            // which pairs: spread evenly over the 16, so that both pipes have work all along the unrolled loop
+            if (((e + 1) * EMU) / 16 != (e * EMU) / 16) {
+                ex2_pair_fma(x2, a, b);
+            } else {
+                float xa, xb;
+                unpack2(x2, xa, xb);
+                a = ex2(xa);
+                b = ex2(xb);
+            }
+            sum2 = add2(sum2, pack2(a, b));
+            if (BF16) {
+                __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+                w[e] = *reinterpret_cast<uint32_t*>(&t);
+            } else {
+                __half2 t = __floats2half2_rn(a, b);
+                w[e] = *reinterpret_cast<uint32_t*>(&t);
+            }
+        }
+        tmem_st16(p_addr + c * 16, w);
+    }
+    float sa, sb;
+    unpack2(sum2, sa, sb);
+    return sa + sb;
+}
+
 template <int DQK, int DV, int BN, int NSTAGE, int BF16, int NG>
 __global__ void __launch_bounds__(SOFTMAX_THREADS * (NG + 1), 1)
 flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -261,7 +305,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             float mx = -INFINITY;
 #pragma unroll
-            for (int e = 0; e < HC; ++e) mx = fmaxf(mx, s[e]);
+            for (int e = 0; e < HC; e += 2) mx = max3(mx, s[e], s[e + 1]);
             mx *= p.scale_log2;
             // lazy rescale: move the reference maximum only when it would grow by more than 2^8
             float corr = 1.0f;
@@ -293,27 +337,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             // P = exp2(S * scale - m_ref), the sum from the unrounded weights, P rounded to the operand type
             const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-            float sum = 0.f;
             const uint32_t p_addr = s_addr;   // P overlays the first half of the S columns it came from
-#pragma unroll
-            for (int c = 0; c < HC / 32; ++c) {
-                uint32_t w[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const float a = ex2(fmaf(s[c * 32 + 2 * e], p.scale_log2, neg_m));
-                    const float b = ex2(fmaf(s[c * 32 + 2 * e + 1], p.scale_log2, neg_m));
-                    sum += a + b;
-                    if (BF16) {
-                        __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
-                        w[e] = *reinterpret_cast<uint32_t*>(&t);
-                    } else {
-                        __half2 t = __floats2half2_rn(a, b);
-                        w[e] = *reinterpret_cast<uint32_t*>(&t);
-                    }
-                }
-                tmem_st16(p_addr + c * 16, w);
-            }
-            l += sum;
+            l += softmax_weights<HC, BF16>(s, p.scale_log2, neg_m, p_addr);
             tmem_wait_st();
             fence_before_sync();
             mbar_arrive(smem_u32(p_full + (j & 1)));
@@ -715,7 +740,7 @@ flash_prefill_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
             }
             float mx = -INFINITY;
 #pragma unroll
-            for (int e = 0; e < HC; ++e) mx = fmaxf(mx, s[e]);
+            for (int e = 0; e < HC; e += 2) mx = max3(mx, s[e], s[e + 1]);
             mx *= p.scale_log2;
             // lazy rescale: move the reference maximum only when it would grow by more than 2^8
             float corr = 1.0f;
@@ -747,27 +772,8 @@ flash_prefill_stream_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
             }
             // P = exp2(S * scale - m_ref), the sum from the unrounded weights, P rounded to the operand type
             const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-            float sum = 0.f;
             const uint32_t p_addr = s_addr;   // P overlays the first half of the S columns it came from
-#pragma unroll
-            for (int c = 0; c < HC / 32; ++c) {
-                uint32_t w[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const float a = ex2(fmaf(s[c * 32 + 2 * e], p.scale_log2, neg_m));
-                    const float b = ex2(fmaf(s[c * 32 + 2 * e + 1], p.scale_log2, neg_m));
-                    sum += a + b;
-                    if (BF16) {
-                        __nv_bfloat162 t2 = __floats2bfloat162_rn(a, b);
-                        w[e] = *reinterpret_cast<uint32_t*>(&t2);
-                    } else {
-                        __half2 t2 = __floats2half2_rn(a, b);
-                        w[e] = *reinterpret_cast<uint32_t*>(&t2);
-                    }
-                }
-                tmem_st16(p_addr + c * 16, w);
-            }
-            l += sum;
+            l += softmax_weights<HC, BF16>(s, p.scale_log2, neg_m, p_addr);
             tmem_wait_st();
             fence_before_sync();
             mbar_arrive(smem_u32(p_full + (t & 1)));

@@ -255,4 +255,54 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// ---- two fp32 values a 64-bit register: one instruction of the FMA pipe works on both ----
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// 2^x for a pair, x <= ~0, on the FMA and integer pipes instead of the special-function unit: x = n + r with n = round(x)
+// (the magic-number addition leaves n in the sum's low mantissa bits) and r in [-1/2, 1/2]; 2^r by a cubic fitted to a
+// relative error of 7.5e-5 - well inside a 16-bit weight's rounding, 4.9e-4 for fp16 -; n goes into the exponent by an
+// integer addition. x is held at -125 from below (2^-125: a weight of zero once rounded).
+__device__ __forceinline__ void ex2_pair_fma(uint64_t x2, float& a, float& b) {
+    float xa, xb;
+    unpack2(x2, xa, xb);
+    xa = fmaxf(xa, -125.0f);
+    xb = fmaxf(xb, -125.0f);
+    const uint64_t x = pack2(xa, xb);
+    const uint64_t magic = pack2(12582912.0f, 12582912.0f), neg_magic = pack2(-12582912.0f, -12582912.0f);
+    const uint64_t minus1 = pack2(-1.0f, -1.0f);
+    const uint64_t t = add2(x, magic);                  // round(x) in the low mantissa bits
+    const uint64_t n = add2(t, neg_magic);              // round(x) as a float
+    const uint64_t r = fma2(n, minus1, x);              // x - round(x)
+    uint64_t q = fma2(pack2(0.05517167f, 0.05517167f), r, pack2(0.24261113f, 0.24261113f));
+    q = fma2(q, r, pack2(0.69326097f, 0.69326097f));
+    q = fma2(q, r, pack2(0.99992806f, 0.99992806f));
+    float qa, qb, ta, tb;
+    unpack2(q, qa, qb);
+    unpack2(t, ta, tb);
+    a = __uint_as_float(__float_as_uint(qa) + (__float_as_uint(ta) << 23));
+    b = __uint_as_float(__float_as_uint(qb) + (__float_as_uint(tb) << 23));
+}
+
 }  // namespace tc05
