@@ -936,11 +936,13 @@ int launch(ns_gpu* g, const FlashPrefillArgs& a, const char* where) {
         p.chunk = (int) (kvh * p.G);
     }
     if ((int64_t) p.nblk * a.Hq > 0x7fffffffll) return ns_fail(std::string(where) + ": too many row blocks");
-    // A few rounds of items, all of one chunk: the streaming kernel, a CTA an SM (dealt back and forth the items come out
-    // even). Up to one round there is nothing to stream; with many rounds, or several chunks (whose lengths start over,
-    // which the deal does not even out), a CTA an item, started by the hardware as SMs come free, is as fast or faster.
+    // Short rows, three to eight rounds of items, all of one chunk: the streaming kernel, a CTA an SM (dealt back and forth the
+    // items come out even). Up to one round there is nothing to stream; with many rounds, or several chunks (whose lengths
+    // start over, which the deal does not even out), a CTA an item, started by the hardware as SMs come free, is as fast or
+    // faster; and with long rows an item's fixed part no longer counts while the streaming loop's pass is the longer one
+    // (16,384 rows x 2 heads: 134 us streamed, 119 a CTA an item; 2,048 rows x 32 / 64 heads: 47.0 / 86.2 against 48.8 / 90.5).
     const int64_t nitems = (int64_t) p.nblk * a.Hq;
-    if constexpr (STREAM) if (nitems > g->sms && nitems <= 8ll * g->sms && p.chunk >= a.Hq) {
+    if constexpr (STREAM) if (p.nblk <= 16 && nitems >= 3ll * g->sms && nitems <= 8ll * g->sms && p.chunk >= a.Hq) {
         using LS = StreamSmem<DQK, DV, BN, NSTAGE, NG>;
         static_assert(LS::TOTAL <= 232448, "shared memory of one CTA");
         auto inv = [](int64_t d) { return d <= 1 ? 0xffffffffu : (uint32_t) ((1ull << 32) / (uint64_t) d); };
